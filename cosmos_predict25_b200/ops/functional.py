@@ -1,0 +1,295 @@
+"""Differentiable front-ends of the fused ops.
+
+CUDA tensors run the sm_100a kernels of the in-tree extension (forward and backward are
+both hand-written kernels wrapped in ``torch.autograd.Function``); CPU tensors run the
+PyTorch oracle in ``ref.py`` under ordinary autograd. The two contraction families that
+also exist as vendor library calls (GEMM, attention) have a switch in ``settings`` so the
+library twin can be timed against the hand-written kernel on the same box.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import native, ref
+
+
+@dataclass
+class OpSettings:
+    """Which implementation serves the two contraction families on CUDA tensors.
+
+    attention: "native" (tcgen05 flash attention of this package) or "cudnn"
+               (torch SDPA pinned to the cuDNN backend: what the reference selects on sm_100,
+               cosmos_predict2/_src/predict2/networks/attention.py:132-138).
+    gemm:      "native" (tcgen05/TMA GEMM with fused epilogues) or "cublas" (torch.matmul).
+    """
+
+    attention: str = os.environ.get("COSMOS_B200_ATTENTION", "native")
+    gemm: str = os.environ.get("COSMOS_B200_GEMM", "native")
+
+
+settings = OpSettings()
+
+
+# --------------------------------------------------------------------------------------
+# AdaLN: LayerNorm + modulate
+# --------------------------------------------------------------------------------------
+class _LnModulate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shift, scale, eps):
+        ops = native.load()
+        B, T, L, D = x.shape
+        xc = x.contiguous()
+        shift_c = shift.float().contiguous()
+        scale_c = scale.float().contiguous()
+        y, mean, rstd = ops.ln_modulate_fwd(xc.view(B * T * L, D), shift_c.view(B * T, D), scale_c.view(B * T, D), L, eps)
+        native.count_launch()
+        ctx.save_for_backward(xc, scale_c, mean, rstd)
+        ctx.dims = (B, T, L, D)
+        ctx.in_dtypes = (shift.dtype, scale.dtype)
+        return y.view(B, T, L, D)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ops = native.load()
+        x, scale, mean, rstd = ctx.saved_tensors
+        B, T, L, D = ctx.dims
+        dx, dshift, dscale = ops.ln_modulate_bwd(
+            dy.contiguous().view(B * T * L, D), x.view(B * T * L, D), mean, rstd, scale.view(B * T, D), L
+        )
+        native.count_launch(2)
+        return (dx.view(B, T, L, D), dshift.view(B, T, D).to(ctx.in_dtypes[0]),
+                dscale.view(B, T, D).to(ctx.in_dtypes[1]), None)
+
+
+def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """LayerNorm(x) * (1 + scale) + shift; x [B,T,L,D], shift/scale [B,T,D]."""
+    if native.use_native(x):
+        return _LnModulate.apply(x, shift, scale, eps)
+    return ref.ln_modulate(x, shift, scale, eps)
+
+
+# --------------------------------------------------------------------------------------
+# gated residual
+# --------------------------------------------------------------------------------------
+class _GateResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, y):
+        ops = native.load()
+        B, T, L, D = x.shape
+        gate_c = gate.float().contiguous()
+        yc = y.contiguous()
+        out = ops.gate_residual_fwd(x.contiguous().view(-1, D), gate_c.view(B * T, D), yc.view(-1, D), L)
+        native.count_launch()
+        ctx.save_for_backward(gate_c, yc)
+        ctx.dims = (B, T, L, D)
+        ctx.gate_dtype = gate.dtype
+        return out.view(B, T, L, D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ops = native.load()
+        gate, y = ctx.saved_tensors
+        B, T, L, D = ctx.dims
+        dout = dout.contiguous()
+        dy, dgate = ops.gate_residual_bwd(dout.view(-1, D), gate.view(B * T, D), y.view(-1, D), L)
+        native.count_launch(2)
+        return dout, dgate.view(B, T, D).to(ctx.gate_dtype), dy.view(B, T, L, D)
+
+
+def gate_residual(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x + gate * y; x,y [B,T,L,D], gate [B,T,D]."""
+    if native.use_native(x):
+        return _GateResidual.apply(x, gate, y.view_as(x))
+    return ref.gate_residual(x, gate, y.view_as(x))
+
+
+# --------------------------------------------------------------------------------------
+# per-head RMSNorm (+ RoPE)
+# --------------------------------------------------------------------------------------
+class _RmsNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, angles, eps):
+        ops = native.load()
+        xc = x.contiguous()
+        ang = angles.float().contiguous() if angles is not None else None
+        y, rstd = ops.rmsnorm_rope_fwd(xc, weight.contiguous(), ang, eps)
+        native.count_launch()
+        ctx.save_for_backward(xc, weight, rstd, ang if ang is not None else torch.empty(0, device=x.device))
+        ctx.has_rope = ang is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ops = native.load()
+        x, weight, rstd, ang = ctx.saved_tensors
+        dx, dw = ops.rmsnorm_rope_bwd(dy.contiguous(), x, weight.contiguous(), rstd, ang if ctx.has_rope else None)
+        native.count_launch(2)
+        return dx, dw.to(weight.dtype), None, None
+
+
+def rmsnorm_rope(x: torch.Tensor, weight: torch.Tensor, angles: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
+    """Per-head RMSNorm then rotate-half RoPE (if angles [S,D] given); x [B,S,H,D]."""
+    if native.use_native(x):
+        return _RmsNormRope.apply(x, weight, angles, eps)
+    return ref.rmsnorm_rope(x, weight, angles, eps)
+
+
+# --------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        ops = native.load()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = ops.fa_fwd(q, k, v, scale)
+        native.count_launch()
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        ops = native.load()
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ops.fa_bwd(do.contiguous(), q, k, v, o, lse, ctx.scale)
+        native.count_launch(3)
+        return dq, dk, dv, None
+
+
+def native_attention_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
+    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and native.available() and \
+        hasattr(native.load(), "fa_fwd")
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    """Non-causal softmax attention, layout [B, S, H, D] in and out."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if not q.is_cuda:
+        return ref.attention(q, k, v, scale)[0]
+    if settings.attention == "native" and native_attention_supported(q, k):
+        return _FlashAttention.apply(q, k, v, scale)
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    backends = [SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION]
+    if q.dtype == torch.float32:
+        backends = [SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]
+    with sdpa_kernel(backends):
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale)
+    return o.transpose(1, 2)
+
+
+def attention_jvp(q, k, v, tq, tk, tv, scale: Optional[float] = None):
+    """Primal and tangent output of attention in one pass: returns (o, to)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and native.available() and hasattr(native.load(), "fa_jvp") and q.dtype == torch.bfloat16 \
+            and q.shape[-1] == 128:
+        o, to, _ = native.load().fa_jvp(q.contiguous(), k.contiguous(), v.contiguous(), tq.contiguous(),
+                                        tk.contiguous(), tv.contiguous(), scale)
+        native.count_launch()
+        return o, to
+    o, to, _ = ref.attention_jvp(q, k, v, tq, tk, tv, scale)
+    return o, to
+
+
+# --------------------------------------------------------------------------------------
+# GEMM with fused epilogue
+# --------------------------------------------------------------------------------------
+_ACT_CODE = {"none": 0, "gelu": 1}
+
+
+def _native_gemm_ok(x2d: torch.Tensor, w: torch.Tensor) -> bool:
+    if settings.gemm != "native" or not x2d.is_cuda or x2d.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    if not native.available() or not hasattr(native.load(), "gemm_bf16"):
+        return False
+    M, K = x2d.shape
+    N = w.shape[0]
+    return K % 64 == 0 and N % 8 == 0 and M >= 1
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none",
+            trans_a: bool = False, trans_b: bool = False) -> torch.Tensor:
+    """C[M,N] = op(A) @ op(B)^T-style contraction on the tcgen05 GEMM.
+
+    With both flags False: A is [M,K] and B is [N,K] (both K-major, the nn.Linear form).
+    trans_a: A is stored [K,M]; trans_b: B is stored [K,N].
+    """
+    ops = native.load()
+    out = ops.gemm_bf16(a, b, bias, _ACT_CODE[act], trans_a, trans_b)
+    native.count_launch()
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, act):
+        x2d = x.reshape(-1, x.shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        if act == "gelu":
+            pre = gemm_nt(x2d, w, bias, "none")
+            ops = native.load()
+            y = ops.gelu_fwd(pre)
+            native.count_launch()
+            ctx.save_for_backward(x2d, w, pre)
+        else:
+            y = gemm_nt(x2d, w, bias, "none")
+            ctx.save_for_backward(x2d, w)
+        ctx.act = act
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy2d = dy.reshape(-1, dy.shape[-1])
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        if ctx.act == "gelu":
+            x2d, w, pre = ctx.saved_tensors
+            ops = native.load()
+            dy2d = ops.gelu_bwd(dy2d, pre)
+            native.count_launch()
+        else:
+            x2d, w = ctx.saved_tensors
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # dX[M,K] = dY[M,N] @ W[N,K]: B operand stored [contract, out] -> trans_b
+            dx = gemm_nt(dy2d, w, None, "none", False, True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            # dW[N,K] = dY^T[N,M] @ X[M,K]: both operands stored [contract, out]
+            dw = gemm_nt(dy2d, x2d, None, "none", True, True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2d.float().sum(0).to(dy.dtype)
+        return dx, dw, db, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none") -> torch.Tensor:
+    """act(x @ w.T + bias); act in {none, gelu(erf)}."""
+    x2d_shape_ok = x.shape[-1] == w.shape[1]
+    assert x2d_shape_ok, (x.shape, w.shape)
+    if x.is_cuda and _native_gemm_ok(x.reshape(-1, x.shape[-1]), w) and x.shape[-1] % 64 == 0 \
+            and x.numel() // x.shape[-1] % 8 == 0:
+        return _Linear.apply(x, w, bias, act)
+    y = F.linear(x, w, bias)
+    if act == "gelu":
+        y = F.gelu(y)
+    return y
+
+
+# --------------------------------------------------------------------------------------
+# small fused elementwise ops used by sampling
+# --------------------------------------------------------------------------------------
+def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, guidance: float) -> torch.Tensor:
+    if cond.is_cuda and native.available() and hasattr(native.load(), "cfg_combine"):
+        native.count_launch()
+        return native.load().cfg_combine(cond.contiguous(), uncond.contiguous(), float(guidance))
+    return ref.cfg_combine(cond, uncond, guidance)

@@ -1,0 +1,66 @@
+"""Loader for the in-tree sm_100a extension (``_C.so`` beside this file).
+
+The library registers its operators under ``torch.ops.cosmos_b200``. It is built by
+``cosmos_predict25_b200.ops.build.build_extension`` (also reachable as
+``python -m cosmos_predict25_b200.ops.build``). On a machine with a GPU a missing library
+is an error: nothing silently falls back to eager PyTorch for CUDA tensors.
+"""
+
+from __future__ import annotations
+
+import os
+import threading
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_C.so")
+_lock = threading.Lock()
+_loaded = False
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    """True when the compiled extension exists on disk."""
+    return os.path.exists(_LIB_PATH)
+
+
+def load():
+    """Load the extension once and return the ``torch.ops.cosmos_b200`` namespace."""
+    global _loaded
+    if not _loaded:
+        with _lock:
+            if not _loaded:
+                if not os.path.exists(_LIB_PATH):
+                    raise RuntimeError(
+                        f"native extension {_LIB_PATH} is missing; run `python -m cosmos_predict25_b200.ops.build` "
+                        "(CUDA tensors are never served by a PyTorch fallback)"
+                    )
+                torch.ops.load_library(_LIB_PATH)
+                _loaded = True
+    return torch.ops.cosmos_b200
+
+
+def use_native(t: torch.Tensor) -> bool:
+    """CUDA tensors go to the extension; CPU tensors go to the PyTorch oracle."""
+    return t.is_cuda
+
+
+_launch_count = 0
+
+
+def count_launch(n: int = 1) -> None:
+    """Host-side tally of kernels launched by this package (bench.py reports it)."""
+    global _launch_count
+    _launch_count += n
+
+
+def launches() -> int:
+    return _launch_count
+
+
+def reset_launches() -> None:
+    global _launch_count
+    _launch_count = 0

@@ -1,0 +1,121 @@
+"""Ulysses (all-to-all) context parallelism for self-attention.
+
+Activations stay sharded along the sequence (whole latent frames per rank) everywhere except
+inside self-attention, where q, k, v are exchanged so that each rank holds the *full* sequence
+for ``H / cp`` heads, and the attention output is exchanged back. The backward of each exchange
+is the reverse exchange. Semantics follow the reference
+(cosmos_predict2/_src/predict2/networks/a2a_cp.py:45-226).
+
+Two transports implement the exchange:
+  * ``torch.distributed.all_to_all_single`` (NCCL on GPUs, gloo on CPU test worlds): the twin
+    kept as baseline and as oracle;
+  * the peer-memory transport in ``symm.py``: a kernel of this package writes each head slice
+    straight into the destination rank's buffer over NVLink (selected when the group has a
+    symmetric workspace attached through ``attach_peer_transport``).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as ops
+
+_peer_transports = {}
+
+
+def group_size_rank(group) -> Tuple[int, int]:
+    if group is None or not dist.is_available() or not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+def attach_peer_transport(group, transport) -> None:
+    """Route the exchanges of ``group`` through a peer-memory transport (see symm.PeerAllToAll)."""
+    _peer_transports[id(group)] = transport
+
+
+def detach_peer_transport(group) -> None:
+    _peer_transports.pop(id(group), None)
+
+
+def _a2a(inp: torch.Tensor, group) -> torch.Tensor:
+    out = torch.empty_like(inp)
+    try:
+        dist.all_to_all_single(out, inp, group=group)
+    except RuntimeError:
+        # gloo builds without alltoall: emulate with P point-to-point rounds (CPU test worlds only)
+        P, r = group_size_rank(group)
+        chunks_in = list(inp.chunk(P, dim=0))
+        chunks_out = list(out.chunk(P, dim=0))
+        chunks_out[r].copy_(chunks_in[r])
+        reqs = []
+        for p in range(P):
+            if p != r:
+                reqs.append(dist.isend(chunks_in[p].contiguous(), dist.get_global_rank(group, p), group=group))
+                reqs.append(dist.irecv(chunks_out[p], dist.get_global_rank(group, p), group=group))
+        for q in reqs:
+            q.wait()
+    return out
+
+
+def seq_to_head(x: torch.Tensor, group) -> torch.Tensor:
+    """[B, S_loc, H, D] (all heads, local tokens) -> [B, S_loc*P, H/P, D] (all tokens, local heads)."""
+    P, _ = group_size_rank(group)
+    B, S, H, D = x.shape
+    assert H % P == 0, f"heads {H} not divisible by context-parallel size {P}"
+    t = _peer_transports.get(id(group))
+    if t is not None and x.is_cuda:
+        return t.seq_to_head(x)
+    send = x.view(B, S, P, H // P, D).permute(2, 0, 1, 3, 4).contiguous()  # [P, B, S, H/P, D]
+    recv = _a2a(send, group)  # slot p = tokens of rank p for my heads
+    return recv.permute(1, 0, 2, 3, 4).reshape(B, P * S, H // P, D)
+
+
+def head_to_seq(x: torch.Tensor, group) -> torch.Tensor:
+    """[B, S_loc*P, H/P, D] -> [B, S_loc, H, D]; the inverse of ``seq_to_head``."""
+    P, _ = group_size_rank(group)
+    B, SP, Hl, D = x.shape
+    S = SP // P
+    t = _peer_transports.get(id(group))
+    if t is not None and x.is_cuda:
+        return t.head_to_seq(x)
+    send = x.view(B, P, S, Hl, D).permute(1, 0, 2, 3, 4).contiguous()  # [P, B, S, Hl, D]
+    recv = _a2a(send, group)  # slot p = my tokens for heads of rank p
+    return recv.permute(1, 2, 0, 3, 4).reshape(B, S, P * Hl, D)
+
+
+class _SeqToHead(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return seq_to_head(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return head_to_seq(g.contiguous(), ctx.group), None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return head_to_seq(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return seq_to_head(g.contiguous(), ctx.group), None
+
+
+def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: Optional[float] = None):
+    """Self-attention over a sequence sharded on dim 1 across ``group``."""
+    P, _ = group_size_rank(group)
+    if P == 1:
+        return ops.attention(q, k, v, scale)
+    qh = _SeqToHead.apply(q, group)
+    kh = _SeqToHead.apply(k, group)
+    vh = _SeqToHead.apply(v, group)
+    oh = ops.attention(qh, kh, vh, scale)
+    return _HeadToSeq.apply(oh, group)
