@@ -266,8 +266,8 @@ class Attention(nn.Module):
         k = ops.rmsnorm_rope(k, self.k_norm.weight, None, self.k_norm.eps)
         return k, v
 
-    def forward(self, x: torch.Tensor, context: Optional[torch.Tensor] = None,
-                rope: Optional[torch.Tensor] = None, kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+    def forward(self, x: torch.Tensor, context: Optional[torch.Tensor] = None, rope=None,
+                kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, return_pre_proj: bool = False):
         B, S, _ = x.shape
         q = self.q_proj(x).view(B, S, self.n_heads, self.head_dim)
         if self.is_selfattn:
@@ -283,7 +283,8 @@ class Attention(nn.Module):
             q = ops.rmsnorm_rope(q, self.q_norm.weight, None, self.q_norm.eps)
             k, v = kv if kv is not None else self.project_kv(context)
             o = ops.attention(q, k, v)
-        return self.output_proj(o.reshape(B, S, self.n_heads * self.head_dim))
+        o = o.reshape(B, S, self.n_heads * self.head_dim)
+        return o if return_pre_proj else self.output_proj(o)
 
 
 class GPT2FeedForward(nn.Module):
@@ -357,16 +358,16 @@ class Block(nn.Module):
         sh3, sc3, g3 = _run_adaln(self.adaln_modulation_mlp, emb, lora, fp32).chunk(3, dim=-1)
 
         h = ops.ln_modulate(x, sh1, sc1)
-        y = self.self_attn(h.view(B, T * L, D), None, rope)
-        x = ops.gate_residual(x, g1, y.view(B, T, L, D))
+        o = self.self_attn(h.view(B, T * L, D), None, rope, return_pre_proj=True)
+        x = ops.linear_gate_residual(o, self.self_attn.output_proj.weight, x, g1)
 
         h = ops.ln_modulate(x, sh2, sc2)
-        y = self.cross_attn(h.view(B, T * L, D), context, None, cross_kv)
-        x = ops.gate_residual(x, g2, y.view(B, T, L, D))
+        o = self.cross_attn(h.view(B, T * L, D), context, None, cross_kv, return_pre_proj=True)
+        x = ops.linear_gate_residual(o, self.cross_attn.output_proj.weight, x, g2)
 
         h = ops.ln_modulate(x, sh3, sc3)
-        y = self.mlp(h.view(B, T * L, D))
-        x = ops.gate_residual(x, g3, y.view(B, T, L, D))
+        a = self.mlp.layer1(h.view(B, T * L, D))
+        x = ops.linear_gate_residual(a, self.mlp.layer2.weight, x, g3)
         return x
 
 
@@ -509,7 +510,8 @@ class CosmosDiT(nn.Module):
         x = self._embed(x_B_C_T_H_W, condition_video_input_mask_B_C_T_H_W, padding_mask)  # [B,T,H,W,D]
         B, T, H, W, D = x.shape
         cp_size, cp_rank = ulysses.group_size_rank(self.cp_group)
-        rope = self.pos_embedder.generate(T, H, W, fps, t_offset=cp_rank * T) if "rope" in cfg.pos_emb_cls else None
+        rope = ops.RopeTable(self.pos_embedder.generate(T, H, W, fps, t_offset=cp_rank * T)) \
+            if "rope" in cfg.pos_emb_cls else None
         extra = None
         if cfg.extra_per_block_abs_pos_emb:
             extra = self.extra_pos_embedder.generate(T, H, W, t_offset=cp_rank * T).to(x.dtype).reshape(1, T, H * W, D)

@@ -1,0 +1,337 @@
+// torch.ops.cosmos_b200.* : registration of the sm_100a kernels with the PyTorch dispatcher.
+// Only this file sees torch headers; kernels are reached through the C launchers in launchers.h.
+
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <tuple>
+
+#include "launchers.h"
+
+namespace {
+
+using at::Tensor;
+
+inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+inline void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+inline void check_f32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+constexpr int kRowsPerCta = 32;
+constexpr int kRowsPerWarp = 64;
+
+}  // namespace
+
+// per-device error word written by kernels whose bounded waits gave up
+int* cb200_error_word(int device) {
+  static int* words[64] = {nullptr};
+  if (words[device] == nullptr) {
+    C10_CUDA_CHECK(cudaMalloc(&words[device], sizeof(int)));
+    C10_CUDA_CHECK(cudaMemset(words[device], 0, sizeof(int)));
+  }
+  return words[device];
+}
+
+namespace {
+inline int* error_word(int device) { return cb200_error_word(device); }
+
+std::tuple<Tensor, Tensor, Tensor> ln_modulate_fwd(const Tensor& x, const Tensor& shift, const Tensor& scale, int64_t L,
+                                                   double eps) {
+  check_bf16(x, "x");
+  check_f32(shift, "shift");
+  check_f32(scale, "scale");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t rows = x.size(0), D = x.size(1);
+  TORCH_CHECK(D % 8 == 0 && D <= 8192, "channel dim must be a multiple of 8 and <= 8192");
+  TORCH_CHECK(rows % L == 0 && shift.size(0) == rows / L && shift.size(1) == D, "shift/scale must be [rows/L, D]");
+  Tensor y = at::empty_like(x);
+  Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat));
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  cb200_ln_modulate_fwd(x.data_ptr(), shift.data_ptr<float>(), scale.data_ptr<float>(), y.data_ptr(), mean.data_ptr<float>(),
+                        rstd.data_ptr<float>(), rows, (int)D, (int)L, (float)eps, stream());
+  return {y, mean, rstd};
+}
+
+std::tuple<Tensor, Tensor, Tensor> ln_modulate_bwd(const Tensor& dy, const Tensor& x, const Tensor& mean, const Tensor& rstd,
+                                                   const Tensor& scale, int64_t L) {
+  check_bf16(dy, "dy");
+  check_bf16(x, "x");
+  check_f32(scale, "scale");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t rows = x.size(0), D = x.size(1), frames = rows / L;
+  Tensor dx = at::empty_like(x);
+  Tensor dshift = at::empty({frames, D}, scale.options());
+  Tensor dscale = at::empty({frames, D}, scale.options());
+  const int G = cb200_ln_groups_per_frame((int)L, kRowsPerCta);
+  Tensor partials = at::empty({frames * G, 2, D}, scale.options());
+  cb200_ln_modulate_bwd(dy.data_ptr(), x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), scale.data_ptr<float>(),
+                        dx.data_ptr(), dshift.data_ptr<float>(), dscale.data_ptr<float>(), partials.data_ptr<float>(), frames,
+                        (int)D, (int)L, kRowsPerCta, stream());
+  return {dx, dshift, dscale};
+}
+
+Tensor gate_residual_fwd(const Tensor& x, const Tensor& gate, const Tensor& y, int64_t L) {
+  check_bf16(x, "x");
+  check_bf16(y, "y");
+  check_f32(gate, "gate");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t rows = x.size(0), D = x.size(1);
+  TORCH_CHECK(D % 8 == 0 && gate.size(0) == rows / L && gate.size(1) == D, "gate must be [rows/L, D]");
+  Tensor out = at::empty_like(x);
+  cb200_gate_residual_fwd(x.data_ptr(), gate.data_ptr<float>(), y.data_ptr(), out.data_ptr(), rows, (int)D, (int)L, stream());
+  return out;
+}
+
+std::tuple<Tensor, Tensor> gate_residual_bwd(const Tensor& dout, const Tensor& gate, const Tensor& y, int64_t L) {
+  check_bf16(dout, "dout");
+  check_bf16(y, "y");
+  check_f32(gate, "gate");
+  c10::cuda::CUDAGuard g(y.device());
+  const int64_t rows = y.size(0), D = y.size(1), frames = rows / L;
+  TORCH_CHECK(D <= 8192, "channel dim must be <= 8192");
+  Tensor dy = at::empty_like(y);
+  Tensor dgate = at::empty({frames, D}, gate.options());
+  const int G = cb200_ln_groups_per_frame((int)L, kRowsPerCta);
+  Tensor partials = at::empty({frames * G, D}, gate.options());
+  cb200_gate_residual_bwd(dout.data_ptr(), gate.data_ptr<float>(), y.data_ptr(), dy.data_ptr(), dgate.data_ptr<float>(),
+                          partials.data_ptr<float>(), frames, (int)D, (int)L, kRowsPerCta, stream());
+  return {dy, dgate};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_rope_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& cosv,
+                                            const c10::optional<Tensor>& sinv, double eps) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 4, "x must be [B, S, H, D]");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t B = x.size(0), S = x.size(1), H = x.size(2), HD = x.size(3);
+  TORCH_CHECK(HD == 128 || HD == 64, "head_dim must be 64 or 128");
+  Tensor wf = w.to(at::kFloat).contiguous();
+  const float* cp = nullptr;
+  const float* sp = nullptr;
+  if (cosv.has_value()) {
+    check_f32(*cosv, "cos");
+    check_f32(*sinv, "sin");
+    TORCH_CHECK(cosv->size(0) == S && cosv->size(1) == HD / 2, "cos/sin must be [S, D/2]");
+    cp = cosv->data_ptr<float>();
+    sp = sinv->data_ptr<float>();
+  }
+  Tensor y = at::empty_like(x);
+  Tensor rstd = at::empty({B, S, H}, x.options().dtype(at::kFloat));
+  cb200_rmsnorm_rope_fwd(x.data_ptr(), wf.data_ptr<float>(), cp, sp, y.data_ptr(), rstd.data_ptr<float>(), B * S * H, (int)S,
+                         (int)H, (int)HD, (float)eps, stream());
+  return {y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_rope_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                            const c10::optional<Tensor>& cosv, const c10::optional<Tensor>& sinv) {
+  check_bf16(dy, "dy");
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t B = x.size(0), S = x.size(1), H = x.size(2), HD = x.size(3);
+  Tensor wf = w.to(at::kFloat).contiguous();
+  const float* cp = cosv.has_value() ? cosv->data_ptr<float>() : nullptr;
+  const float* sp = sinv.has_value() ? sinv->data_ptr<float>() : nullptr;
+  Tensor dx = at::empty_like(x);
+  Tensor dw = at::empty({HD}, x.options().dtype(at::kFloat));
+  const int64_t blocks = cb200_rmsnorm_bwd_blocks(B * S * H, kRowsPerWarp);
+  Tensor partials = at::empty({blocks, HD}, dw.options());
+  cb200_rmsnorm_rope_bwd(dy.data_ptr(), x.data_ptr(), wf.data_ptr<float>(), rstd.data_ptr<float>(), cp, sp, dx.data_ptr(),
+                         dw.data_ptr<float>(), partials.data_ptr<float>(), B * S * H, (int)S, (int)H, (int)HD, kRowsPerWarp,
+                         stream());
+  return {dx, dw};
+}
+
+Tensor gelu_fwd(const Tensor& x) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.numel() % 8 == 0, "numel must be a multiple of 8");
+  c10::cuda::CUDAGuard g(x.device());
+  Tensor y = at::empty_like(x);
+  cb200_gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), stream());
+  return y;
+}
+
+Tensor gelu_bwd(const Tensor& dy, const Tensor& x) {
+  check_bf16(x, "x");
+  check_bf16(dy, "dy");
+  c10::cuda::CUDAGuard g(x.device());
+  Tensor dx = at::empty_like(x);
+  cb200_gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), stream());
+  return dx;
+}
+
+Tensor cfg_combine(const Tensor& c, const Tensor& u, double gval) {
+  check_f32(c, "cond");
+  check_f32(u, "uncond");
+  c10::cuda::CUDAGuard g(c.device());
+  Tensor o = at::empty_like(c);
+  cb200_cfg_combine(c.data_ptr<float>(), u.data_ptr<float>(), o.data_ptr<float>(), (float)gval, c.numel(), stream());
+  return o;
+}
+
+void grad_cast_norm(const Tensor& g16, Tensor g32, Tensor sumsq, double scale) {
+  check_bf16(g16, "grad");
+  check_f32(g32, "grad_shard");
+  check_f32(sumsq, "sumsq");
+  TORCH_CHECK(g16.numel() == g32.numel(), "size mismatch");
+  c10::cuda::CUDAGuard g(g16.device());
+  Tensor partials = at::empty({cb200_grad_cast_norm_blocks(g16.numel())}, g32.options());
+  cb200_grad_cast_norm(g16.data_ptr(), g32.data_ptr<float>(), sumsq.data_ptr<float>(), partials.data_ptr<float>(), (float)scale,
+                       g16.numel(), stream());
+}
+
+void adamw_ema_shard(Tensor master, const Tensor& grad, Tensor m, Tensor v, const c10::optional<Tensor>& ema,
+                     const c10::optional<Tensor>& out16, const Tensor& clip, double lr, double beta1, double beta2, double eps,
+                     double wd, int64_t step, double ema_beta) {
+  check_f32(master, "master");
+  check_f32(grad, "grad");
+  check_f32(m, "exp_avg");
+  check_f32(v, "exp_avg_sq");
+  check_f32(clip, "clip");
+  c10::cuda::CUDAGuard g(master.device());
+  float* ema_p = nullptr;
+  void* out_p = nullptr;
+  if (ema.has_value()) {
+    check_f32(*ema, "ema");
+    ema_p = ema->data_ptr<float>();
+  }
+  if (out16.has_value()) {
+    check_bf16(*out16, "out16");
+    TORCH_CHECK(out16->numel() >= master.numel(), "bf16 output too small");
+    out_p = out16->data_ptr();
+  }
+  cb200_adamw_ema_shard(master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), ema_p, out_p,
+                        clip.data_ptr<float>(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, step,
+                        (float)ema_beta, master.numel(), stream());
+}
+
+void cast_f32_bf16(const Tensor& src, Tensor dst) {
+  check_f32(src, "src");
+  check_bf16(dst, "dst");
+  TORCH_CHECK(dst.numel() >= src.numel(), "dst too small");
+  c10::cuda::CUDAGuard g(src.device());
+  cb200_cast_f32_bf16(src.data_ptr<float>(), dst.data_ptr(), src.numel(), stream());
+}
+
+// ---- GEMM ------------------------------------------------------------------------------------
+struct GemmDims {
+  int M, N, K;
+};
+
+GemmDims gemm_dims(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b) {
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "GEMM operands must be 2-D");
+  GemmDims d;
+  d.M = (int)(trans_a ? a.size(1) : a.size(0));
+  d.K = (int)(trans_a ? a.size(0) : a.size(1));
+  d.N = (int)(trans_b ? b.size(1) : b.size(0));
+  const int64_t kb = trans_b ? b.size(0) : b.size(1);
+  TORCH_CHECK(kb == d.K, "contraction dims differ: ", d.K, " vs ", kb);
+  TORCH_CHECK(a.size(1) % 8 == 0 && b.size(1) % 8 == 0, "row strides must be multiples of 16 bytes");
+  return d;
+}
+
+int sm_count(int device) {
+  static int cache[64] = {0};
+  if (cache[device] == 0) cache[device] = at::cuda::getDeviceProperties(device)->multiProcessorCount;
+  return cache[device];
+}
+
+Tensor gemm_impl(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, int64_t act, bool trans_a, bool trans_b,
+                 Tensor* pre, const Tensor* resid, const Tensor* gate, int64_t L) {
+  check_bf16(a, "a");
+  check_bf16(b, "b");
+  c10::cuda::CUDAGuard g(a.device());
+  const GemmDims d = gemm_dims(a, b, trans_a, trans_b);
+  Tensor c = at::empty({d.M, d.N}, a.options());
+  const void* bias_p = nullptr;
+  Tensor bias_c;
+  if (bias.has_value()) {
+    bias_c = bias->to(at::kBFloat16).contiguous();
+    TORCH_CHECK(bias_c.numel() == d.N, "bias must be [N]");
+    bias_p = bias_c.data_ptr();
+  }
+  void* pre_p = nullptr;
+  if (pre != nullptr) {
+    *pre = at::empty({d.M, d.N}, a.options());
+    pre_p = pre->data_ptr();
+  }
+  const void* resid_p = nullptr;
+  const float* gate_p = nullptr;
+  if (resid != nullptr) {
+    check_bf16(*resid, "resid");
+    check_f32(*gate, "gate");
+    TORCH_CHECK(resid->numel() == (int64_t)d.M * d.N && gate->size(-1) == d.N && gate->numel() == (d.M / L) * (int64_t)d.N,
+                "gated-residual epilogue shapes");
+    resid_p = resid->data_ptr();
+    gate_p = gate->data_ptr<float>();
+  }
+  const int dev = a.get_device();
+  const int rc = cb200_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), d.M, d.N, d.K, trans_a ? 1 : 0, trans_b ? 1 : 0, bias_p,
+                                 (int)act, pre_p, resid_p, gate_p, (int)L, error_word(dev), sm_count(dev), stream());
+  TORCH_CHECK(rc == 0, "tcgen05 GEMM launch failed with code ", rc);
+  return c;
+}
+
+Tensor gemm_bf16(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, int64_t act, bool trans_a, bool trans_b) {
+  return gemm_impl(a, b, bias, act, trans_a, trans_b, nullptr, nullptr, nullptr, 1);
+}
+
+std::tuple<Tensor, Tensor> gemm_bf16_gelu_pre(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias) {
+  Tensor pre;
+  Tensor c = gemm_impl(a, b, bias, 1, false, false, &pre, nullptr, nullptr, 1);
+  return {c, pre};
+}
+
+Tensor gemm_bf16_gate_residual(const Tensor& a, const Tensor& b, const Tensor& resid, const Tensor& gate, int64_t L) {
+  return gemm_impl(a, b, c10::nullopt, 0, false, false, nullptr, &resid, &gate, L);
+}
+
+int64_t kernel_error(int64_t device, bool clear) {
+  int v = 0;
+  int* w = error_word((int)device);
+  C10_CUDA_CHECK(cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost));
+  if (clear && v != 0) C10_CUDA_CHECK(cudaMemset(w, 0, sizeof(int)));
+  return v;
+}
+
+}  // namespace
+
+// defined in bindings_attn.cpp / bindings_peer.cpp
+void register_attention_ops(torch::Library& m);
+void register_peer_ops(torch::Library& m);
+void register_conv_ops(torch::Library& m);
+
+TORCH_LIBRARY(cosmos_b200, m) {
+  m.def("ln_modulate_fwd(Tensor x, Tensor shift, Tensor scale, int L, float eps) -> (Tensor, Tensor, Tensor)", &ln_modulate_fwd);
+  m.def("ln_modulate_bwd(Tensor dy, Tensor x, Tensor mean, Tensor rstd, Tensor scale, int L) -> (Tensor, Tensor, Tensor)",
+        &ln_modulate_bwd);
+  m.def("gate_residual_fwd(Tensor x, Tensor gate, Tensor y, int L) -> Tensor", &gate_residual_fwd);
+  m.def("gate_residual_bwd(Tensor dout, Tensor gate, Tensor y, int L) -> (Tensor, Tensor)", &gate_residual_bwd);
+  m.def("rmsnorm_rope_fwd(Tensor x, Tensor w, Tensor? cos, Tensor? sin, float eps) -> (Tensor, Tensor)", &rmsnorm_rope_fwd);
+  m.def("rmsnorm_rope_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, Tensor? cos, Tensor? sin) -> (Tensor, Tensor)",
+        &rmsnorm_rope_bwd);
+  m.def("gelu_fwd(Tensor x) -> Tensor", &gelu_fwd);
+  m.def("gelu_bwd(Tensor dy, Tensor x) -> Tensor", &gelu_bwd);
+  m.def("cfg_combine(Tensor cond, Tensor uncond, float guidance) -> Tensor", &cfg_combine);
+  m.def("grad_cast_norm(Tensor g16, Tensor(a!) g32, Tensor(b!) sumsq, float scale) -> ()", &grad_cast_norm);
+  m.def("adamw_ema_shard(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? ema, Tensor(e!)? out16, "
+        "Tensor clip, float lr, float beta1, float beta2, float eps, float wd, int step, float ema_beta) -> ()",
+        &adamw_ema_shard);
+  m.def("cast_f32_bf16(Tensor src, Tensor(a!) dst) -> ()", &cast_f32_bf16);
+  m.def("gemm_bf16(Tensor a, Tensor b, Tensor? bias, int act, bool trans_a, bool trans_b) -> Tensor", &gemm_bf16);
+  m.def("gemm_bf16_gelu_pre(Tensor a, Tensor b, Tensor? bias) -> (Tensor, Tensor)", &gemm_bf16_gelu_pre);
+  m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor", &gemm_bf16_gate_residual);
+  m.def("kernel_error(int device, bool clear) -> int", &kernel_error);
+  register_attention_ops(m);
+  register_peer_ops(m);
+  register_conv_ops(m);
+}

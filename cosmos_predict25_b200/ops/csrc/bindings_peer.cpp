@@ -1,0 +1,101 @@
+// Peer-memory (NVLink) operators of torch.ops.cosmos_b200; the kernels are in peer.cu.
+// Peer pointers arrive as Python int lists (virtual addresses of the same symmetric buffer on each rank).
+
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <vector>
+
+#include "launchers.h"
+
+int* cb200_error_word(int device);
+
+namespace {
+using at::Tensor;
+
+inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+std::vector<int64_t> ptr_vec(c10::ArrayRef<int64_t> v) {
+  TORCH_CHECK(v.size() >= 1 && v.size() <= 8, "1..8 peers supported");
+  return std::vector<int64_t>(v.begin(), v.end());
+}
+
+void peer_barrier(c10::ArrayRef<int64_t> flag_ptrs, int64_t rank, int64_t epoch, int64_t device) {
+  c10::cuda::CUDAGuard g((c10::DeviceIndex)device);
+  auto p = ptr_vec(flag_ptrs);
+  cb200_peer_barrier(p.data(), (int)rank, (int)p.size(), (unsigned)epoch, cb200_error_word((int)device), stream());
+}
+
+// segs: int64 CUDA tensor [nseg, 4] = (full_offset, stride, shard_offset, numel)
+void rs_cast_norm_peer(c10::ArrayRef<int64_t> grad_ptrs, const Tensor& segs, Tensor g32, Tensor unit_sumsq,
+                       const c10::optional<Tensor>& total_sumsq, int64_t rank, double scale) {
+  TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kLong && segs.is_contiguous() && segs.size(1) == 4, "bad segment table");
+  c10::cuda::CUDAGuard g(g32.device());
+  auto p = ptr_vec(grad_ptrs);
+  const int nseg = (int)segs.size(0);
+  Tensor partials = at::empty({(int64_t)cb200_rs_blocks_x() * nseg}, g32.options());
+  cb200_rs_cast_norm_peer(p.data(), segs.data_ptr(), nseg, g32.data_ptr<float>(), partials.data_ptr<float>(),
+                          unit_sumsq.data_ptr<float>(), total_sumsq.has_value() ? total_sumsq->data_ptr<float>() : nullptr,
+                          (int)rank, (int)p.size(), (float)scale, stream());
+}
+
+void adamw_push_peer(c10::ArrayRef<int64_t> full_ptrs, c10::ArrayRef<int64_t> sumsq_ptrs, const Tensor& segs, Tensor master,
+                     const Tensor& grad, Tensor m, Tensor v, const c10::optional<Tensor>& ema, int64_t rank, double max_norm,
+                     double lr, double beta1, double beta2, double eps, double wd, int64_t step, double ema_beta,
+                     const c10::optional<Tensor>& norm_out) {
+  c10::cuda::CUDAGuard g(master.device());
+  auto fp = ptr_vec(full_ptrs);
+  auto sp = ptr_vec(sumsq_ptrs);
+  TORCH_CHECK(fp.size() == sp.size(), "pointer lists differ in length");
+  cb200_adamw_push_peer(fp.data(), sp.data(), segs.data_ptr(), (int)segs.size(0), master.data_ptr<float>(), grad.data_ptr<float>(),
+                        m.data_ptr<float>(), v.data_ptr<float>(), ema.has_value() ? ema->data_ptr<float>() : nullptr, (int)rank,
+                        (int)fp.size(), (float)max_norm, (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, step,
+                        (float)ema_beta, norm_out.has_value() ? norm_out->data_ptr<float>() : nullptr, stream());
+}
+
+// x [B,S,H,HD] -> peers' buffers laid out [B, P*S, H/P, HD]; returns rstd [B,S,H] when norm is applied
+Tensor a2a_scatter_heads_peer(const Tensor& x, c10::ArrayRef<int64_t> out_ptrs, const c10::optional<Tensor>& w,
+                              const c10::optional<Tensor>& cosv, const c10::optional<Tensor>& sinv, int64_t rank, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 4, "x must be bf16 [B,S,H,HD]");
+  c10::cuda::CUDAGuard g(x.device());
+  auto p = ptr_vec(out_ptrs);
+  const int64_t B = x.size(0), S = x.size(1), H = x.size(2), HD = x.size(3);
+  TORCH_CHECK((HD == 128 || HD == 64) && H % (int64_t)p.size() == 0, "head_dim 64/128 and heads divisible by peers");
+  Tensor rstd = at::empty({w.has_value() ? B * S * H : 0}, x.options().dtype(at::kFloat));
+  Tensor wf;
+  const float* wp = nullptr;
+  if (w.has_value()) {
+    wf = w->to(at::kFloat).contiguous();
+    wp = wf.data_ptr<float>();
+  }
+  cb200_a2a_scatter_heads_peer(x.data_ptr(), p.data(), wp, cosv.has_value() ? cosv->data_ptr<float>() : nullptr,
+                               sinv.has_value() ? sinv->data_ptr<float>() : nullptr,
+                               w.has_value() ? rstd.data_ptr<float>() : nullptr, B * S * H, (int)S, (int)H, (int)HD, (int)rank,
+                               (int)p.size(), w.has_value() ? 1 : 0, (float)eps, stream());
+  return rstd;
+}
+
+Tensor a2a_gather_seq_peer(c10::ArrayRef<int64_t> src_ptrs, int64_t B, int64_t S, int64_t H, int64_t HD, int64_t rank,
+                           const Tensor& like) {
+  c10::cuda::CUDAGuard g(like.device());
+  auto p = ptr_vec(src_ptrs);
+  Tensor out = at::empty({B, S, H, HD}, like.options().dtype(at::kBFloat16));
+  cb200_a2a_gather_seq_peer(p.data(), out.data_ptr(), B, (int)S, (int)H, (int)HD, (int)rank, (int)p.size(), stream());
+  return out;
+}
+
+}  // namespace
+
+void register_peer_ops(torch::Library& m) {
+  m.def("peer_barrier(int[] flag_ptrs, int rank, int epoch, int device) -> ()", &peer_barrier);
+  m.def("rs_cast_norm_peer(int[] grad_ptrs, Tensor segs, Tensor(a!) g32, Tensor(b!) unit_sumsq, Tensor(c!)? total_sumsq, int rank, "
+        "float scale) -> ()", &rs_cast_norm_peer);
+  m.def("adamw_push_peer(int[] full_ptrs, int[] sumsq_ptrs, Tensor segs, Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, "
+        "Tensor(d!)? ema, int rank, float max_norm, float lr, float beta1, float beta2, float eps, float wd, int step, "
+        "float ema_beta, Tensor(e!)? norm_out) -> ()", &adamw_push_peer);
+  m.def("a2a_scatter_heads_peer(Tensor x, int[] out_ptrs, Tensor? w, Tensor? cos, Tensor? sin, int rank, float eps) -> Tensor",
+        &a2a_scatter_heads_peer);
+  m.def("a2a_gather_seq_peer(int[] src_ptrs, int B, int S, int H, int HD, int rank, Tensor like) -> Tensor", &a2a_gather_seq_peer);
+}

@@ -1,0 +1,309 @@
+// bf16 GEMM on the 5th-generation tensor cores (sm_100a): C[M,N] = epilogue(A x B), fp32 accumulation.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0   TMA producer: streams 128x64 A tiles and 256x64 B tiles (128-byte swizzle) through a
+//            4-stage shared-memory ring; completion by mbarrier transaction bytes.
+//   warp 1   MMA issuer: one thread issues tcgen05.mma (UMMA 128x256x16, cta_group::1) from
+//            shared-memory descriptors into one of two 128x256 fp32 accumulators in TMEM
+//            (2 x 256 = all 512 columns), and releases ring slots with tcgen05.commit.
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (each warp owns one 32-lane quarter of
+//            TMEM), apply the fused epilogue in registers and store bf16 straight to global memory,
+//            while warp 1 already accumulates the next tile into the other TMEM buffer.
+//
+// Operand majors are template parameters so the same kernel serves forward (x @ W^T: both K-major),
+// dgrad (dy @ W: B is N-major) and wgrad (dy^T @ x: both MN-major) without transposing in memory.
+// Fused epilogues: + bias, exact GELU (optionally also writing the pre-activation for backward),
+// and the AdaLN gated residual  out = resid + gate[row / L, col] * acc.
+//
+// All mbarrier waits are bounded; on timeout the CTA records an error code in `err`, lets in-flight
+// copies land, frees its TMEM and returns.
+
+#include <math.h>
+
+#include "launchers.h"
+#include "common.cuh"
+#include "sm100.cuh"
+#include "tmap.h"
+
+namespace cb200 {
+using namespace sm100;
+
+constexpr int BM = 128, BN = 256, BK = 64, UK = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;  // 16 KB
+constexpr int kBBytes = BN * BK * 2;  // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kGemmThreads = 192;
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmEpilogue {
+  bf16* C;
+  bf16* pre;          // optional pre-activation output (only with act == 1)
+  const bf16* bias;   // optional [N]
+  const bf16* resid;  // optional [M, N] (gated residual)
+  const float* gate;  // optional [M / L, N]
+  int act;            // 0 none, 1 gelu(erf)
+  int L;              // rows per gate vector
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, int M, int N, int K,
+                 GemmEpilogue ep, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full = bars;                    // [kStages]
+  uint64_t* empty = bars + kStages;         // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;  // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tma_a);
+      prefetch_tmap(&tma_b);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          mbar_arrive_expect_tx(&full[s], kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d(sa, &tma_a, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, &full[s], m0 + j * 64, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sb, &tma_b, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, &full[s], n0 + j * 64, k0);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) { atomicCAS(err, 0, 1); *abort_flag = 1; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t da = A_MN ? umma_desc_sw128(sa + k * (UK * 128), 8192, 1024)
+                                     : umma_desc_sw128(sa + k * (UK * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UK * 128), 8192, 1024)
+                                     : umma_desc_sw128(sb + k * (UK * 2), 16, 1024);
+            umma_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // slot reusable once these MMAs have read it
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+      if (!ok) { atomicCAS(err, 0, 2); *abort_flag = 1; }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    const bool vec_ok = (N % 8) == 0;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+      if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      const float* gate_row = (ep.gate != nullptr && row < M) ? ep.gate + (size_t)(row / ep.L) * N : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          const bool full_chunk = vec_ok && (col0 + 32 <= N);
+          const size_t off = (size_t)row * N + col0;
+          if (ep.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full_chunk || col0 + j < N) v[j] += __bfloat162float(ep.bias[col0 + j]);
+          }
+          if (ep.act == 1) {
+            if (ep.pre != nullptr) {
+              if (full_chunk) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 o;
+                  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+                  *reinterpret_cast<uint4*>(ep.pre + off + q * 8) = o;
+                }
+              } else {
+                for (int j = 0; j < 32 && col0 + j < N; ++j) ep.pre[off + j] = __float2bfloat16(v[j]);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+          }
+          if (gate_row != nullptr) {
+            if (full_chunk) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(ep.resid + off + q * 8);
+                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+                const float4 g0 = *reinterpret_cast<const float4*>(gate_row + col0 + q * 8);
+                const float4 g1 = *reinterpret_cast<const float4*>(gate_row + col0 + q * 8 + 4);
+                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 rf = __bfloat1622float2(r2[j]);
+                  v[q * 8 + 2 * j] = rf.x + g[2 * j] * v[q * 8 + 2 * j];
+                  v[q * 8 + 2 * j + 1] = rf.y + g[2 * j + 1] * v[q * 8 + 2 * j + 1];
+                }
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j)
+                v[j] = __bfloat162float(ep.resid[off + j]) + gate_row[col0 + j] * v[j];
+            }
+          }
+          if (full_chunk) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+              *reinterpret_cast<uint4*>(ep.C + off + q * 8) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < N; ++j) ep.C[off + j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+    if (!ok && lane == 0) { atomicCAS(err, 0, 3); *abort_flag = 1; }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (*abort_flag) {
+    // let outstanding bulk copies / MMAs drain before shared memory and TMEM go away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace cb200
+
+using namespace cb200;
+
+template <int A_MN, int B_MN>
+static int launch_gemm(const void* A, const void* B, int M, int N, int K, const GemmEpilogue& ep, int* err, int sms,
+                       cudaStream_t st) {
+  CUtensorMap ta, tb;
+  int rc;
+  // A: K-major [M,K] -> dims {K, M}, box {64, 128};  MN-major stored [K,M] -> dims {M, K}, box {64, 64}
+  if (A_MN == 0) rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM);
+  else rc = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)M * 2, 64, BK);
+  if (rc) return rc;
+  if (B_MN == 0) rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BN);
+  else rc = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, BK);
+  if (rc) return rc;
+  static bool attr_set[4] = {false, false, false, false};
+  auto kern = gemm_bf16_kernel<A_MN, B_MN>;
+  if (!attr_set[A_MN * 2 + B_MN]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return 100 + (int)e;
+    attr_set[A_MN * 2 + B_MN] = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, kGemmThreads, kSmemBytes, st>>>(ta, tb, M, N, K, ep, err);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn,
+                               const void* bias, int act, void* pre, const void* resid, const float* gate, int L, int* err,
+                               int sms, cudaStream_t st) {
+  GemmEpilogue ep;
+  ep.C = (bf16*)C;
+  ep.pre = (bf16*)pre;
+  ep.bias = (const bf16*)bias;
+  ep.resid = (const bf16*)resid;
+  ep.gate = gate;
+  ep.act = act;
+  ep.L = L > 0 ? L : 1;
+  if (a_mn == 0 && b_mn == 0) return launch_gemm<0, 0>(A, B, M, N, K, ep, err, sms, st);
+  if (a_mn == 0 && b_mn == 1) return launch_gemm<0, 1>(A, B, M, N, K, ep, err, sms, st);
+  if (a_mn == 1 && b_mn == 0) return launch_gemm<1, 0>(A, B, M, N, K, ep, err, sms, st);
+  return launch_gemm<1, 1>(A, B, M, N, K, ep, err, sms, st);
+}

@@ -1,0 +1,59 @@
+// C launch interface of the kernels (no torch headers here: the .cu files compile in seconds).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+extern "C" {
+// elementwise.cu
+int cb200_ln_groups_per_frame(int L, int rows_per_cta);
+void cb200_ln_modulate_fwd(const void* x, const float* shift, const float* scale, void* y, float* mean, float* rstd,
+                           long rows, int D, int L, float eps, cudaStream_t st);
+void cb200_ln_modulate_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const float* scale,
+                           void* dx, float* dshift, float* dscale, float* partials, long frames, int D, int L,
+                           int rows_per_cta, cudaStream_t st);
+void cb200_gate_residual_fwd(const void* x, const float* gate, const void* y, void* out, long rows, int D, int L,
+                             cudaStream_t st);
+void cb200_gate_residual_bwd(const void* dout, const float* gate, const void* y, void* dy, float* dgate, float* partials,
+                             long frames, int D, int L, int rows_per_cta, cudaStream_t st);
+void cb200_rmsnorm_rope_fwd(const void* x, const float* w, const float* cosv, const float* sinv, void* y, float* rstd,
+                            long n_rows, int S, int H, int HD, float eps, cudaStream_t st);
+long cb200_rmsnorm_bwd_blocks(long n_rows, int rows_per_warp);
+void cb200_rmsnorm_rope_bwd(const void* dy, const void* x, const float* w, const float* rstd, const float* cosv,
+                            const float* sinv, void* dx, float* dw, float* partials, long n_rows, int S, int H, int HD,
+                            int rows_per_warp, cudaStream_t st);
+void cb200_gelu_fwd(const void* x, void* y, long n, cudaStream_t st);
+void cb200_gelu_bwd(const void* dy, const void* x, void* dx, long n, cudaStream_t st);
+void cb200_cfg_combine(const float* c, const float* u, float* o, float g, long n, cudaStream_t st);
+int cb200_grad_cast_norm_blocks(long n);
+void cb200_grad_cast_norm(const void* g16, float* g32, float* sumsq, float* partials, float scale, long n, cudaStream_t st);
+void cb200_adamw_ema_shard(float* master, const float* grad, float* m, float* v, float* ema, void* out16,
+                           const float* clip_coef, float lr, float beta1, float beta2, float eps, float wd, long step,
+                           float ema_beta, long n, cudaStream_t st);
+void cb200_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t st);
+
+// gemm_tcgen05.cu
+int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn, const void* bias,
+                    int act, void* pre, const void* resid, const float* gate, int L, int* err, int sms, cudaStream_t st);
+}
+
+extern "C" {
+// fa_fwd.cu
+int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
+                 int* err, cudaStream_t st);
+}
+
+extern "C" {
+// peer.cu
+void cb200_peer_barrier(const int64_t* flag_ptrs, int rank, int P, unsigned epoch, int* err, cudaStream_t st);
+int cb200_rs_blocks_x(void);
+void cb200_rs_cast_norm_peer(const int64_t* grad_ptrs, const void* segs, int nseg, float* g32, float* partials, float* unit_sumsq,
+                             float* total_sumsq, int rank, int P, float scale, cudaStream_t st);
+void cb200_adamw_push_peer(const int64_t* full_ptrs, const int64_t* sumsq_ptrs, const void* segs, int nseg, float* master,
+                           const float* grad, float* m, float* v, float* ema, int rank, int P, float max_norm, float lr,
+                           float beta1, float beta2, float eps, float wd, long step, float ema_beta, float* norm_out,
+                           cudaStream_t st);
+void cb200_a2a_scatter_heads_peer(const void* x, const int64_t* out_ptrs, const float* w, const float* cosv, const float* sinv,
+                                  float* rstd, long n_rows, int S, int H, int HD, int rank, int P, int norm, float eps,
+                                  cudaStream_t st);
+void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S, int H, int HD, int rank, int P, cudaStream_t st);
+}

