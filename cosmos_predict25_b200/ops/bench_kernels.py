@@ -1,0 +1,170 @@
+"""Per-kernel device timing at the headline shapes, with roofline fractions.
+
+``python -m cosmos_predict25_b200.ops.bench_kernels [--quick] [--only NAME] [--json PATH]``
+
+Each row: kernel, shape, CUDA-event time (median of timed iterations after warm-up, L2 flushed between
+iterations by writing a 256 MB buffer), achieved TFLOP/s or GB/s, and the fraction of the measured
+peak (``MEASURED_PEAKS.json`` at the repository root when present, otherwise 6.65 TB/s and
+1.59 PFLOP/s). The library twin (cuBLAS / cuDNN via torch) is timed next to each contraction.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+
+import torch
+
+from . import functional as F_ops
+from . import native
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "src": "fallback"}
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_ms(fn, iters=5, warmup=3):
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true", help="1/8 of the tokens (fast sanity pass)")
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    ops = native.load()
+    pk = peaks()
+    N = 84480 // (8 if args.quick else 1)
+    D, H, HD, Fm, L, T = 2048, 16, 128, 8192, 3520 // (8 if args.quick else 1), 24
+    rows = []
+
+    def add(name, shape, ms, flops=None, bytes_=None, note=""):
+        r = {"kernel": name, "shape": shape, "ms": round(ms, 4), "note": note}
+        if flops is not None:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["frac_of_" + pk["src"] + "_bf16_peak"] = round(flops / ms / 1e9 / pk["tflops"], 3)
+        if bytes_ is not None:
+            r["gbs"] = round(bytes_ / ms / 1e6, 1)
+            r["frac_of_" + pk["src"] + "_hbm"] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+        rows.append(r)
+        print(json.dumps(r), flush=True)
+
+    def want(name):
+        return args.only is None or args.only in name
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    if want("gemm"):
+        for (M, Nn, K, tag) in [(N, D, D, "qkv/out proj"), (N, Fm, D, "mlp.layer1"), (N, D, Fm, "mlp.layer2")]:
+            a = torch.randn(M, K, device=dev).bfloat16()
+            b = torch.randn(Nn, K, device=dev).bfloat16()
+            fl = 2.0 * M * Nn * K
+            add("gemm_tcgen05 nt", f"{M}x{Nn}x{K} {tag}", time_ms(lambda: ops.gemm_bf16(a, b, None, 0, False, False)), fl)
+            add("cublas nt (twin)", f"{M}x{Nn}x{K}", time_ms(lambda: torch.matmul(a, b.T)), fl)
+        a = torch.randn(N, D, device=dev).bfloat16()
+        b = torch.randn(Fm, D, device=dev).bfloat16()
+        add("gemm_tcgen05 nt +gelu(+pre)", f"{N}x{Fm}x{D}", time_ms(lambda: ops.gemm_bf16_gelu_pre(a, b, None)), 2.0 * N * Fm * D)
+        dy = torch.randn(N, Fm, device=dev).bfloat16()
+        add("gemm_tcgen05 dgrad (B n-major)", f"{N}x{D}x{Fm}", time_ms(lambda: ops.gemm_bf16(dy, b, None, 0, False, True)), 2.0 * N * Fm * D)
+        add("cublas dgrad (twin)", f"{N}x{D}x{Fm}", time_ms(lambda: torch.matmul(dy, b)), 2.0 * N * Fm * D)
+        add("gemm_tcgen05 wgrad (both mn-major)", f"{Fm}x{D}x{N}", time_ms(lambda: ops.gemm_bf16(dy, a, None, 0, True, True)), 2.0 * N * Fm * D)
+        add("cublas wgrad (twin)", f"{Fm}x{D}x{N}", time_ms(lambda: torch.matmul(dy.T, a)), 2.0 * N * Fm * D)
+        del a, b, dy
+    if want("attention"):
+        heads = 2 if args.quick else H
+        q, k, v = (torch.randn(1, N, heads, HD, device=dev).bfloat16() for _ in range(3))
+        fl = 4.0 * N * N * HD * heads
+        scale = 1 / math.sqrt(HD)
+        add("fa_fwd tcgen05", f"S={N} H={heads} hd=128", time_ms(lambda: ops.fa_fwd(q, k, v, scale), iters=3, warmup=1), fl)
+        add("cudnn sdpa fwd (twin)", f"S={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, k, v, scale), iters=3, warmup=1), fl)
+        if hasattr(ops, "fa_bwd"):
+            o, lse = ops.fa_fwd(q, k, v, scale)
+            do = torch.randn_like(o)
+            add("fa_bwd tcgen05", f"S={N} H={heads}", time_ms(lambda: ops.fa_bwd(do, q, k, v, o, lse, scale), iters=3, warmup=1), 2.5 * fl)
+        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+        og = F_ops._sdpa(qg, kg, vg, scale)
+        dog = torch.randn_like(og)
+        add("cudnn sdpa bwd (twin)", f"S={N} H={heads}",
+            time_ms(lambda: torch.autograd.grad(og, (qg, kg, vg), dog, retain_graph=True), iters=3, warmup=1), 2.5 * fl)
+        kc, vc = (torch.randn(1, 512, heads, HD, device=dev).bfloat16() for _ in range(2))
+        add("fa_fwd tcgen05 cross (Skv=512)", f"Sq={N} H={heads}", time_ms(lambda: ops.fa_fwd(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
+        add("cudnn sdpa cross (twin)", f"Sq={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
+        del q, k, v
+    if want("elementwise"):
+        x = torch.randn(1, T, L, D, device=dev).bfloat16()
+        y = torch.randn_like(x)
+        sh, sc, g = (torch.randn(1, T, D, device=dev) for _ in range(3))
+        nb = x.numel() * 2
+        xf = x.view(-1, D)
+        add("ln_modulate_fwd", f"{T * L}x{D}", time_ms(lambda: ops.ln_modulate_fwd(xf, sh.view(-1, D), sc.view(-1, D), L, 1e-6)), bytes_=2 * nb)
+        yy, mean, rstd = ops.ln_modulate_fwd(xf, sh.view(-1, D), sc.view(-1, D), L, 1e-6)
+        add("ln_modulate_bwd", f"{T * L}x{D}", time_ms(lambda: ops.ln_modulate_bwd(y.view(-1, D), xf, mean, rstd, sc.view(-1, D), L)), bytes_=3 * nb)
+        add("torch LN+mod fwd (twin)", f"{T * L}x{D}",
+            time_ms(lambda: torch.nn.functional.layer_norm(x, (D,), eps=1e-6) * (1 + sc.bfloat16().unsqueeze(2)) + sh.bfloat16().unsqueeze(2)), bytes_=2 * nb)
+        add("gate_residual_fwd", f"{T * L}x{D}", time_ms(lambda: ops.gate_residual_fwd(xf, g.view(-1, D), y.view(-1, D), L)), bytes_=3 * nb)
+        add("gate_residual_bwd", f"{T * L}x{D}", time_ms(lambda: ops.gate_residual_bwd(xf, g.view(-1, D), y.view(-1, D), L)), bytes_=3 * nb)
+        add("torch x+g*y (twin)", f"{T * L}x{D}", time_ms(lambda: x + g.bfloat16().unsqueeze(2) * y), bytes_=3 * nb)
+        q = torch.randn(1, T * L, H, HD, device=dev).bfloat16()
+        w = torch.ones(HD, device=dev)
+        ang = torch.rand(T * L, HD, device=dev)
+        rope = F_ops.RopeTable(ang)
+        cos, sin = rope.cos_sin()
+        add("rmsnorm_rope_fwd", f"{T * L}x{H}x{HD}", time_ms(lambda: ops.rmsnorm_rope_fwd(q, w, cos, sin, 1e-6)), bytes_=2 * q.numel() * 2 + 2 * cos.numel() * 4)
+        yq, rs = ops.rmsnorm_rope_fwd(q, w, cos, sin, 1e-6)
+        add("rmsnorm_rope_bwd", f"{T * L}x{H}x{HD}", time_ms(lambda: ops.rmsnorm_rope_bwd(q, q, w, rs, cos, sin)), bytes_=3 * q.numel() * 2)
+        h = torch.randn(T * L, Fm, device=dev).bfloat16()
+        add("gelu_bwd", f"{T * L}x{Fm}", time_ms(lambda: ops.gelu_bwd(h, h)), bytes_=3 * h.numel() * 2)
+        del x, y, q, h
+    if want("optimizer"):
+        n = 69_000_000 if not args.quick else 8_000_000
+        g16 = torch.randn(n, device=dev).bfloat16()
+        g32 = torch.empty(n, device=dev)
+        ss = torch.zeros(1, device=dev)
+        add("grad_cast_norm", f"{n}", time_ms(lambda: ops.grad_cast_norm(g16, g32, ss, 1.0)), bytes_=6 * n)
+        ms_, m_, v_, e_ = (torch.zeros(n, device=dev) for _ in range(4))
+        o16 = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        clip = torch.ones(1, device=dev)
+        add("adamw_ema_shard", f"{n}", time_ms(lambda: ops.adamw_ema_shard(ms_, g32, m_, v_, e_, o16, clip, 1e-4, 0.9, 0.999, 1e-8, 1e-3, 1, 0.99)),
+            bytes_=(4 * 5 + 4 * 4 + 2) * n)
+    err = ops.kernel_error(torch.cuda.current_device(), True)
+    print(json.dumps({"kernel_error": int(err), "peaks": pk}))
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump({"rows": rows, "peaks": pk, "kernel_error": int(err)}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -188,7 +188,15 @@ class _FlashAttention(torch.autograd.Function):
 
 
 def _sdpa(q, k, v, scale):
-    return _sdpa(q, k, v, scale)
+    """torch SDPA pinned to the cuDNN backend (flash / efficient as fall-backs), [B,S,H,D] layout."""
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    backends = [SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION]
+    if q.dtype == torch.float32:
+        backends = [SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]
+    with sdpa_kernel(backends):
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=scale)
+    return o.transpose(1, 2)
 
 
 def native_attention_supported(q: torch.Tensor, k: torch.Tensor) -> bool:

@@ -67,26 +67,37 @@ _DTYPES = [torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.in
            torch.int8, torch.uint8, torch.bool]
 
 
-def robust_broadcast(x: Optional[torch.Tensor], src: int, group, device=None) -> torch.Tensor:
-    """Broadcast a tensor whose shape/dtype only the source knows: header (ndim, dtype id, dims)
-    first, then the payload. ``src`` is a global rank."""
+def robust_broadcast(x: Optional[torch.Tensor], src: int, group, device=None):
+    """Broadcast from global rank ``src`` something whose kind, shape and dtype only the source knows.
+    A 10-word header goes first: (kind, ndim, dtype id, dims...), kind 0 = tensor, 1 = picklable object;
+    then the payload. Receivers may pass anything (it is ignored)."""
     rank = dist.get_rank()
-    dev = device if device is not None else (x.device if x is not None else torch.device("cpu"))
-    header = torch.zeros(10, dtype=torch.int64, device=dev)
-    if rank == src:
-        assert x is not None and x.ndim <= 8
-        header[0] = x.ndim
-        header[1] = _DTYPES.index(x.dtype)
-        header[2:2 + x.ndim] = torch.tensor(list(x.shape), dtype=torch.int64)
+    is_src = rank == src
+    if device is None:
+        device = x.device if isinstance(x, torch.Tensor) else torch.device("cpu")
+        if dist.get_backend(group) == "nccl" and device.type != "cuda":
+            device = torch.device("cuda", torch.cuda.current_device())
+    header = torch.zeros(10, dtype=torch.int64, device=device)
+    if is_src:
+        if isinstance(x, torch.Tensor):
+            assert x.ndim <= 7
+            header[0] = 0
+            header[1] = x.ndim
+            header[2] = _DTYPES.index(x.dtype)
+            if x.ndim:
+                header[3:3 + x.ndim] = torch.tensor(list(x.shape), dtype=torch.int64)
+        else:
+            header[0] = 1
     dist.broadcast(header, src, group=group)
     h = header.tolist()
-    shape, dtype = h[2:2 + h[0]], _DTYPES[h[1]]
-    if rank != src:
-        x = torch.empty(shape, dtype=dtype, device=dev)
-    else:
-        x = x.to(dev).contiguous()
-    dist.broadcast(x, src, group=group)
-    return x
+    if h[0] == 1:
+        box = [x if is_src else None]
+        dist.broadcast_object_list(box, src, group=group)
+        return box[0]
+    shape, dtype = h[3:3 + h[1]], _DTYPES[h[2]]
+    buf = x.to(device).contiguous() if is_src else torch.empty(shape, dtype=dtype, device=device)
+    dist.broadcast(buf, src, group=group)
+    return buf
 
 
 def broadcast(item, cp_group):
@@ -94,12 +105,8 @@ def broadcast(item, cp_group):
     P, _ = _size_rank(cp_group)
     if P == 1:
         return item
-    src = dist.get_global_rank(cp_group, 0) if cp_group is not dist.group.WORLD and cp_group is not None else 0
-    if isinstance(item, torch.Tensor):
-        return robust_broadcast(item, src, cp_group)
-    box = [item]
-    dist.broadcast_object_list(box, src, group=cp_group)
-    return box[0]
+    src = dist.get_global_rank(cp_group, 0) if cp_group is not None else 0
+    return robust_broadcast(item, src, cp_group)
 
 
 def broadcast_split_tensor(x: torch.Tensor, seq_dim: int, cp_group) -> torch.Tensor:

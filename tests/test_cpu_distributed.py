@@ -1,0 +1,228 @@
+"""world_size = 2 tests on CPU with the gloo backend: context-parallel plumbing, Ulysses attention
+equivalence, the sharded engine against a single-rank run, and host-side failure detection."""
+
+import os
+import socket
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn_name, tmp, kwargs):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(2)
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        globals()[fn_name](rank, world, tmp, **kwargs)
+        dist.barrier()
+        with open(os.path.join(tmp, f"ok{rank}"), "w") as f:
+            f.write("ok")
+    except Exception:
+        with open(os.path.join(tmp, f"err{rank}"), "w") as f:
+            f.write(traceback.format_exc())
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_distributed(fn_name: str, world: int = 2, **kwargs):
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(world, _free_port(), fn_name, tmp, kwargs), nprocs=world, join=True)
+        errs = [open(os.path.join(tmp, f)).read() for f in sorted(os.listdir(tmp)) if f.startswith("err")]
+        assert not errs, "\n".join(errs)
+        assert all(os.path.exists(os.path.join(tmp, f"ok{r}")) for r in range(world))
+
+
+# ------------------------------------------------------------------------------------------------
+def _cp_utils(rank, world, tmp):
+    from cosmos_predict25_b200.parallel import context_parallel as cp
+    g = dist.group.WORLD
+    x = torch.arange(24, dtype=torch.float32).view(2, 6, 2) if rank == 0 else torch.zeros(1)
+    y = cp.broadcast(x if rank == 0 else None, g)
+    assert y.shape == (2, 6, 2) and y[1, 5, 1] == 23
+    loc = cp.split_inputs_cp(y, 1, g)
+    assert loc.shape == (2, 3, 2) and loc[0, 0, 0] == rank * 6
+    full = cp.cat_outputs_cp(loc, 1, g)
+    assert torch.equal(full, y)
+    z = loc.clone().requires_grad_(True)
+    out = cp.cat_outputs_cp_with_grad(z, 1, g)
+    (out * torch.arange(24, dtype=torch.float32).view(2, 6, 2)).sum().backward()
+    assert torch.equal(z.grad, cp.split_inputs_cp(torch.arange(24, dtype=torch.float32).view(2, 6, 2), 1, g))
+    obj = cp.broadcast({"a": 1} if rank == 0 else None, g)
+    assert obj == {"a": 1}
+
+
+def test_context_parallel_tensor_utils():
+    run_distributed("_cp_utils")
+
+
+def _ulysses(rank, world, tmp):
+    from cosmos_predict25_b200.ops import ref
+    from cosmos_predict25_b200.parallel import context_parallel as cp
+    from cosmos_predict25_b200.parallel import ulysses
+    torch.manual_seed(0)
+    g = dist.group.WORLD
+    B, S, H, D = 2, 12, 4, 16
+    q, k, v = (torch.randn(B, S, H, D) for _ in range(3))
+    full, _ = ref.attention(q, k, v)
+    ql, kl, vl = (cp.split_inputs_cp(t, 1, g).clone().requires_grad_(True) for t in (q, k, v))
+    out = ulysses.ulysses_attention(ql, kl, vl, g)
+    assert torch.allclose(out, cp.split_inputs_cp(full, 1, g), atol=1e-5)
+    # round trip of the exchange and gradient = reverse exchange
+    h = ulysses.seq_to_head(ql.detach(), g)
+    assert h.shape == (B, S, H // world, D)
+    assert torch.equal(ulysses.head_to_seq(h, g), ql.detach())
+    w = torch.randn(B, S, H, D)
+    (out * cp.split_inputs_cp(w, 1, g)).sum().backward()
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    (ref.attention(qf, kf, vf)[0] * w).sum().backward()
+    assert torch.allclose(ql.grad, cp.split_inputs_cp(qf.grad, 1, g), atol=1e-5)
+    assert torch.allclose(kl.grad, cp.split_inputs_cp(kf.grad, 1, g), atol=1e-5)
+    assert torch.allclose(vl.grad, cp.split_inputs_cp(vf.grad, 1, g), atol=1e-5)
+
+
+def test_ulysses_attention_matches_full_attention():
+    run_distributed("_ulysses")
+
+
+def _dit_cp(rank, world, tmp):
+    """Tiny DiT: context-parallel forward/backward over T equals the single-rank result."""
+    from cosmos_predict25_b200.models.dit import CosmosDiT, dit_tiny
+    from cosmos_predict25_b200.parallel import context_parallel as cp
+    torch.manual_seed(0)
+    g = dist.group.WORLD
+    net = CosmosDiT(dit_tiny())
+    net.init_weights()
+    for p in net.parameters():
+        if p.abs().sum() == 0:
+            torch.nn.init.normal_(p, std=0.05)
+    x = torch.randn(1, 16, 4, 16, 16)
+    mask = torch.zeros(1, 1, 4, 16, 16)
+    mask[:, :, :1] = 1
+    t = torch.tensor([[300.0, 700.0, 700.0, 700.0]])
+    ctx = torch.randn(1, 32, 256)
+    want = net(x, t, ctx, condition_video_input_mask_B_C_T_H_W=mask)
+    want.pow(2).mean().backward()
+    ref_grads = {n: p.grad.clone() for n, p in net.named_parameters() if p.grad is not None}
+    net.zero_grad()
+    net.enable_context_parallel(g)
+    xl, ml = cp.split_inputs_cp(x, 2, g), cp.split_inputs_cp(mask, 2, g)
+    tl = cp.split_inputs_cp(t, 1, g)
+    out = net(xl, tl, ctx, condition_video_input_mask_B_C_T_H_W=ml)
+    assert torch.allclose(out, cp.split_inputs_cp(want, 2, g), atol=2e-4), (out - cp.split_inputs_cp(want, 2, g)).abs().max()
+    (out.pow(2).sum() / want.numel()).backward()
+    for n, p in net.named_parameters():
+        if p.grad is None:
+            continue
+        gsum = p.grad.clone()
+        dist.all_reduce(gsum)
+        assert torch.allclose(gsum, ref_grads[n], atol=2e-4, rtol=1e-3), n
+
+
+def test_dit_context_parallel_equals_single_rank():
+    run_distributed("_dit_cp")
+
+
+def _engine(rank, world, tmp):
+    """Two-rank sharded engine == single-process engine on the summed batch gradient."""
+    from cosmos_predict25_b200.parallel.fsdp import ShardedEngine
+    torch.manual_seed(0)
+
+    def make():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.GELU(), torch.nn.Linear(40, 7, bias=False))
+
+    data = torch.randn(2, 5, 24)
+    net1 = make()
+    eng1 = ShardedEngine(net1, group=None, compute_dtype=torch.float32, use_ema=True, units=[net1[0]])
+    netP = make()
+    engP = ShardedEngine(netP, group=dist.group.WORLD, compute_dtype=torch.float32, use_ema=True, units=[netP[0]])
+    assert engP.units[0].shard_numel < eng1.units[0].shard_numel
+    for step in range(3):
+        sum(net1(data[r]).pow(2).mean() for r in range(world)).div(world).backward()
+        n1 = eng1.step(lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01, max_grad_norm=0.5, ema_beta=0.9)
+        netP(data[rank]).pow(2).mean().backward()
+        nP = engP.step(lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01, max_grad_norm=0.5, ema_beta=0.9)
+        assert torch.allclose(n1, nP, atol=1e-5), (n1, nP)
+        for p1, pP in zip(net1.parameters(), netP.parameters()):
+            assert torch.allclose(p1, pP, atol=1e-6), step
+    sd1, sdP = eng1.full_state_dict("ema"), engP.full_state_dict("ema")
+    for k in sd1:
+        assert torch.allclose(sd1[k], sdP[k], atol=1e-6)
+    # consolidated load restores both shards and the full parameters
+    engP.load_full_state_dict({k: torch.zeros_like(v) for k, v in sdP.items()}, "master")
+    assert all(p.abs().sum() == 0 for p in netP.parameters())
+
+
+def test_sharded_engine_two_ranks_equals_one():
+    run_distributed("_engine")
+
+
+def _model_fsdp_cp(rank, world, tmp):
+    """Full model with parameter sharding + context parallelism over the same two ranks: both ranks see the
+    same loss (one sample, sequence-sharded) and the step keeps parameters identical across ranks."""
+    from cosmos_predict25_b200.models.dit import dit_tiny
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig, SchedulerConfig
+    torch.manual_seed(0)
+    g = dist.group.WORLD
+    cfg = Video2WorldRFConfig(net=dit_tiny(), precision="float32", state_t=4)
+    m = Video2WorldModelRectifiedFlow(cfg, device=torch.device("cpu"), fsdp_group=g, cp_group=g)
+    opt, sch = m.init_optimizer_scheduler(OptimizerConfig(lr=1e-3), SchedulerConfig(kind="constant"))
+    torch.manual_seed(10 + rank)  # different local data: rank 0's sample must win
+    batch = {"latents": torch.randn(1, 16, 4, 16, 16), "t5_text_embeddings": torch.randn(1, 32, 256),
+             "fps": torch.tensor([16.0]), "padding_mask": torch.zeros(1, 1, 16, 16), "num_conditional_frames": 1}
+    out, loss = m.training_step(batch, 0)
+    assert out["x0"].shape[2] == 2  # T-sharded
+    loss.backward()
+    opt.step()
+    flat = torch.cat([p.detach().reshape(-1) for p in m.net.parameters()])
+    other = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(other, flat)
+    assert torch.equal(other[0], other[1])
+    s = m.generate_samples_from_batch(dict(batch), guidance=2.0, seed=3, num_steps=2, solver="euler")
+    assert s.shape == (1, 16, 4, 16, 16)
+
+
+def test_model_with_fsdp_and_context_parallel():
+    run_distributed("_model_fsdp_cp")
+
+
+def _missing_rank(rank, world, tmp):
+    """Failure detection on the host: a rank that never joins a collective ends it with an error on
+    the others after a short process-group timeout (no GPU involved)."""
+    import datetime
+    g = dist.new_group([0, 1], timeout=datetime.timedelta(seconds=2), backend="gloo")
+    if rank == 0:
+        with pytest.raises(Exception):
+            dist.all_reduce(torch.ones(1), group=g)
+    else:
+        import time
+        time.sleep(4)  # never joins
+
+
+def test_short_timeout_surfaces_a_missing_rank():
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker_nobarrier, args=(2, _free_port(), "_missing_rank", tmp), nprocs=2, join=True)
+        errs = [open(os.path.join(tmp, f)).read() for f in sorted(os.listdir(tmp)) if f.startswith("err")]
+        assert not errs, "\n".join(errs)
+
+
+def _worker_nobarrier(rank, world, port, fn_name, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        globals()[fn_name](rank, world, tmp)
+    except Exception:
+        with open(os.path.join(tmp, f"err{rank}"), "w") as f:
+            f.write(traceback.format_exc())
