@@ -64,6 +64,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="1/8 of the tokens (fast sanity pass)")
     ap.add_argument("--only", default=None)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--variants", action="store_true", help="also time the tuning variants of kernels that have them")
     args = ap.parse_args()
     ops = native.load()
     pk = peaks()
@@ -110,6 +111,10 @@ def main():
         scale = 1 / math.sqrt(HD)
         add("fa_fwd tcgen05", f"S={N} H={heads} hd=128", time_ms(lambda: ops.fa_fwd(q, k, v, scale), iters=3, warmup=1), fl)
         add("cudnn sdpa fwd (twin)", f"S={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, k, v, scale), iters=3, warmup=1), fl)
+        if args.variants and hasattr(ops, "fa_fwd_variant"):
+            for var in range(1, 6):
+                add(f"fa_fwd tcgen05 variant {var}", f"S={N} H={heads}",
+                    time_ms(lambda: ops.fa_fwd_variant(q, k, v, scale, var), iters=3, warmup=1), fl)
         if hasattr(ops, "fa_bwd"):
             o, lse = ops.fa_fwd(q, k, v, scale)
             do = torch.randn_like(o)

@@ -20,7 +20,7 @@ inline void check_qkv(const Tensor& t, const char* name) {
 }
 
 // q [B,Sq,H,128], k/v [B,Skv,H,128] -> (o [B,Sq,H,128], lse [B,H,Sq] fp32, natural log)
-std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale) {
+std::tuple<Tensor, Tensor> fa_fwd_variant(const Tensor& q, const Tensor& k, const Tensor& v, double scale, int64_t variant) {
   check_qkv(q, "q");
   check_qkv(k, "k");
   check_qkv(v, "v");
@@ -30,12 +30,16 @@ std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor
   Tensor o = at::empty_like(q);
   Tensor lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
   const int rc = cb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
-                              (float)scale, cb200_error_word(q.get_device()), at::cuda::getCurrentCUDAStream().stream());
+                              (float)scale, (int)variant, cb200_error_word(q.get_device()), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "fa_fwd launch failed with code ", rc);
   return {o, lse};
+}
+std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale) {
+  return fa_fwd_variant(q, k, v, scale, 0);
 }
 }  // namespace
 
 void register_attention_ops(torch::Library& m) {
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)", &fa_fwd);
+  m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)", &fa_fwd_variant);
 }

@@ -4,15 +4,20 @@
 //
 //   warps 0-3   softmax of query tile 0   (thread i <-> query row i <-> TMEM lane i)
 //   warps 4-7   softmax of query tile 1
-//   warp  8     TMA producer: Q once, then K_j and V_j through two 2-slot rings (128-byte swizzle)
+//   warp  8     TMA producer: Q once, then K_0 V_0 K_1 V_1 ... through one 5-slot ring (128-byte swizzle)
 //   warp  9     MMA issuer (one thread): S_t = Q_t K_j^T  (SS form, both operands K-major in smem)
 //                                        O_t += P_t V_j   (TS form: P read from TMEM, V N-major in smem)
 //
 // TMEM (512 columns): S_0 [0,128) S_1 [128,256) fp32 scores, O_0 [256,384) O_1 [384,512) fp32 outputs.
-// The softmax thread reads its score row with tcgen05.ld, and writes the bf16 probabilities back over
-// the first 64 columns of the same S buffer with tcgen05.st; the P·V MMA takes them from there, so
-// probabilities never visit shared memory. While one tile is in softmax the tensor core runs the
-// other tile's P·V and next Q·K^T (ping-pong).
+// The softmax thread pulls its whole score row into registers with four tcgen05.ld, and writes the bf16
+// probabilities back over the first 64 columns of the same S buffer with tcgen05.st; the P.V MMA takes
+// them from there, so probabilities never visit shared memory. While one tile is in softmax the tensor
+// core runs the other tile's P.V and next Q.K^T (ping-pong).
+//
+// Register budget decides the shape of this kernel: 10 warps leave 168 registers per thread, enough to hold a
+// full 128-column score row; a layout with two threads per row (18 warps, 96 registers) spilled and measured
+// 1.7x slower. Template switches keep two measured alternatives for the exponentials (a degree-4 polynomial
+// on the FMA pipe for one element in POLY_MOD, packed fp32x2 scale/subtract); the plain MUFU path is fastest.
 //
 // Online softmax keeps a reference maximum per row that is only moved when the running maximum grows
 // by more than 2^8; the output accumulator is rescaled in TMEM only then (rare after the first tiles).
@@ -34,8 +39,10 @@ constexpr int BQ = 128;          // query rows per tile (two tiles per CTA)
 constexpr int BKV = 128;         // keys per tile
 constexpr int kTileBytes = 128 * HD * 2;  // 32 KB
 constexpr int kHalfBytes = kTileBytes / 2;
+constexpr int kRing = 5;         // K/V ring slots
 constexpr int kThreads = 320;
-constexpr size_t kSmem = 6 * (size_t)kTileBytes + 1024 + 256;
+constexpr int kMmaWarp = 9, kTmaWarp = 8;
+constexpr size_t kSmem = (2 + kRing) * (size_t)kTileBytes + 1024 + 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 }  // namespace fa
 
@@ -45,6 +52,20 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 2^x for x <= ~8 on the FMA/ALU pipes: round to nearest integer with the 1.5*2^23 trick, degree-4
+// polynomial for 2^f on [-0.5, 0.5] (relative error < 5e-5, far below bf16 resolution), exponent add.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.00961813f, 0.0555041f);
+  p = fmaf(p, f, 0.240227f);
+  p = fmaf(p, f, 0.693147f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + ((__float_as_int(t) - 0x4B400000) << 23));
+}
+
+template <int POLY_MOD, bool PACKED>
 __global__ void __launch_bounds__(fa::kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, int Sq, int Skv, int H,
@@ -52,18 +73,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   using namespace fa;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;                    // 2 tiles
-  uint8_t* sK = smem + 2 * kTileBytes;   // 2 slots
-  uint8_t* sV = smem + 4 * kTileBytes;   // 2 slots
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
-  uint64_t* q_full = bars;        // [1]
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
-  uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;    // [2]  scores of tile t ready (also: all earlier MMAs of the CTA complete)
-  uint64_t* p_ready = bars + 11;  // [2]  probabilities of tile t written to TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint8_t* sQ = smem;                     // 2 tiles
+  uint8_t* sR = smem + 2 * kTileBytes;    // ring of kRing tiles: K_0 V_0 K_1 V_1 ...
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + kRing) * kTileBytes);
+  uint64_t* q_full = bars;                 // [1]
+  uint64_t* r_full = bars + 1;             // [kRing]
+  uint64_t* r_empty = bars + 1 + kRing;    // [kRing]
+  uint64_t* s_full = bars + 1 + 2 * kRing; // [2]  scores of tile t ready (also: all earlier MMAs complete)
+  uint64_t* p_ready = s_full + 2;          // [2]  probabilities of tile t written to TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_ready + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -73,18 +91,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(&r_full[i], 1);
+      mbar_init(&r_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -93,7 +111,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // -------------------------------------------------------------------- TMA producer
     if (lane == 0) {
       prefetch_tmap(&tm_q);
@@ -104,26 +122,25 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int c = 0; c < 2; ++c)
           tma_load_4d(sQ + t * kTileBytes + c * kHalfBytes, &tm_q, q_full, c * 64, h, q_base + t * BQ, b);
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int slot = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[slot], ph ^ 1, abort_flag)) { ok = false; break; }
-        mbar_arrive_expect_tx(&k_full[slot], kTileBytes);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sK + slot * kTileBytes + c * kHalfBytes, &tm_k, &k_full[slot], c * 64, h, j * BKV, b);
-        if (!mbar_wait(&v_empty[slot], ph ^ 1, abort_flag)) { ok = false; break; }
-        mbar_arrive_expect_tx(&v_full[slot], kTileBytes);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sV + slot * kTileBytes + c * kHalfBytes, &tm_v, &v_full[slot], c * 64, h, j * BKV, b);
+      int slot = 0;
+      uint32_t ph = 0;
+      for (int n = 0; n < 2 * n_kv; ++n) {  // even n: K_{n/2}, odd n: V_{n/2}
+        if (!mbar_wait(&r_empty[slot], ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(&r_full[slot], kTileBytes);
+        const CUtensorMap* tm = (n & 1) ? &tm_v : &tm_k;
+        for (int c = 0; c < 2; ++c) tma_load_4d(sR + slot * kTileBytes + c * kHalfBytes, tm, &r_full[slot], c * 64, h, (n >> 1) * BKV, b);
+        if (++slot == kRing) { slot = 0; ph ^= 1; }
       }
       if (!ok) { atomicCAS(err, 0, 11); *abort_flag = 1; }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto issue_qk = [&](int t, int slot) {
-        const uint32_t qa = smem_u32(sQ + t * kTileBytes), ka = smem_u32(sK + slot * kTileBytes);
+        const uint32_t qa = smem_u32(sQ + t * kTileBytes), ka = smem_u32(sR + slot * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
@@ -132,36 +149,44 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       };
       auto issue_pv = [&](int t, int slot, bool accumulate) {
-        const uint32_t va = smem_u32(sV + slot * kTileBytes);
+        const uint32_t va = smem_u32(sR + slot * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, umma_desc_sw128(va + kk * 2048, kHalfBytes, 1024),
                   idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
         }
       };
-      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+      // ring cursor of the item to consume next (K_0 first)
+      int slot = 0;
+      uint32_t ph = 0;
+      auto advance = [&]() { if (++slot == kRing) { slot = 0; ph ^= 1; } };
+      if (ok) ok = mbar_wait(&r_full[slot], ph, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_qk(0, 0);
+        issue_qk(0, slot);
         umma_commit(&s_full[0]);
-        issue_qk(1, 0);
+        issue_qk(1, slot);
         umma_commit(&s_full[1]);
-        umma_commit(&k_empty[0]);
+        umma_commit(&r_empty[slot]);
+        advance();
       }
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int slot = j & 1, nslot = (j + 1) & 1;
-        const uint32_t ph = (j >> 1) & 1, nph = ((j + 1) >> 1) & 1;
         const bool has_next = (j + 1) < n_kv;
-        if (!mbar_wait(&v_full[slot], ph, abort_flag)) { ok = false; break; }
-        if (has_next && !mbar_wait(&k_full[nslot], nph, abort_flag)) { ok = false; break; }
+        const int v_slot = slot;
+        if (!mbar_wait(&r_full[v_slot], ph, abort_flag)) { ok = false; break; }
+        advance();
+        const int k_slot = slot;
+        if (has_next) {
+          if (!mbar_wait(&r_full[k_slot], ph, abort_flag)) { ok = false; break; }
+          advance();
+        }
         for (int t = 0; t < 2; ++t) {
           if (!mbar_wait(&p_ready[t], j & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          issue_pv(t, slot, j > 0);
-          if (t == 1) umma_commit(&v_empty[slot]);
-          if (has_next) issue_qk(t, nslot);
-          // K_{j+1} is free again once tile 1's Q.K^T on it has completed
-          if (t == 1 && has_next) umma_commit(&k_empty[nslot]);
+          issue_pv(t, v_slot, j > 0);
+          if (t == 1) umma_commit(&r_empty[v_slot]);
+          if (has_next) issue_qk(t, k_slot);
+          if (t == 1 && has_next) umma_commit(&r_empty[k_slot]);
           umma_commit(&s_full[t]);
         }
       }
@@ -181,21 +206,26 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(&s_full[t], j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int n_valid = min(BKV, Skv - j * BKV);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + c * 32, r);
-        tmem_ld_wait();
+      uint32_t r[4][32];
+      tmem_ld32(tS, r[0]);
+      tmem_ld32(tS + 32, r[1]);
+      tmem_ld32(tS + 64, r[2]);
+      tmem_ld32(tS + 96, r[3]);
+      tmem_ld_wait();
+      const int n_valid = Skv - j * BKV;
+      if (n_valid < BKV) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(r[i]);
-          mx = fmaxf(mx, (c * 32 + i < n_valid) ? s : -INFINITY);
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i >= n_valid) r[c][i] = 0xff800000u;  // -inf
       }
-      mx *= scale_log2;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const bool need = mx > m_ref + kRescaleThreshold;
       float alpha = 1.f;
       if (need) {
@@ -207,40 +237,43 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // rescale the output accumulator of this warp's 32 rows in TMEM
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + c * 32, r);
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tO + c * 32, r);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tO + c * 32, o);
         }
         tmem_st_wait();
       }
-      // pass 2: probabilities -> bf16 pairs over the first 64 columns of the score buffer
-      float lsum = 0.f;
-#pragma unroll 1
+      // probabilities -> bf16 pairs over the first 64 columns of the score buffer
+      const float neg_m = -m_ref;
+      float2 lsum2 = make_float2(0.f, 0.f);
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(__uint_as_float(r[2 * i]) * scale_log2 - m_ref);
-          float p1 = ex2(__uint_as_float(r[2 * i + 1]) * scale_log2 - m_ref);
-          if (c * 32 + 2 * i >= n_valid) p0 = 0.f;
-          if (c * 32 + 2 * i + 1 >= n_valid) p1 = 0.f;
-          lsum += p0 + p1;
-          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          float2 x;
+          if (PACKED) {
+            x = fma2(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
+                     make_float2(scale_log2, scale_log2), make_float2(neg_m, neg_m));
+          } else {
+            x.x = fmaf(__uint_as_float(r[c][2 * i]), scale_log2, neg_m);
+            x.y = fmaf(__uint_as_float(r[c][2 * i + 1]), scale_log2, neg_m);
+          }
+          float2 p;
+          const bool poly = (POLY_MOD > 0) && ((i % (POLY_MOD > 0 ? POLY_MOD : 1)) == 0);
+          p.x = poly ? exp2_poly(x.x) : ex2(x.x);
+          p.y = poly ? exp2_poly(x.y) : ex2(x.y);
+          lsum2.x += p.x;
+          lsum2.y += p.y;
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p.x, p.y);
           pk[i] = *reinterpret_cast<uint32_t*>(&pb);
         }
-        asm volatile(
-            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-            ::"r"(tS + c * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]),
-              "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]), "r"(pk[15])
-            : "memory");
+        tmem_st16(tS + c * 16, pk);
       }
-      l += lsum;
+      l += lsum2.x + lsum2.y;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -253,18 +286,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       bf16* orow = O + (((size_t)b * Sq + q_row) * H + h) * HD;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tO + c * 32, r);
+        uint32_t o[32];
+        tmem_ld32(tO + c * 32, o);
         tmem_ld_wait();
         if (q_row < Sq) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+            uint4 ov;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              o2[i] = __floats2bfloat162_rn(__uint_as_float(r[q * 8 + 2 * i]) * inv_l, __uint_as_float(r[q * 8 + 2 * i + 1]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
+              o2[i] = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = ov;
           }
         }
       }
@@ -281,7 +314,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -291,9 +324,26 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 using namespace cb200;
 
-// q [B, Sq, H, 128]; k, v [B, Skv, H, 128]; o like q; lse [B, H, Sq] fp32
+template <int POLY_MOD, bool PACKED>
+static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, float* lse, int B, int Sq,
+                         int Skv, int H, float scale, int* err, cudaStream_t st) {
+  using namespace fa;
+  auto kern = fa_fwd_kernel<POLY_MOD, PACKED>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    if (e != cudaSuccess) return 100 + (int)e;
+    attr = true;
+  }
+  dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
+  kern<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, err);
+  return (int)cudaGetLastError();
+}
+
+// q [B, Sq, H, 128]; k, v [B, Skv, H, 128]; o like q; lse [B, H, Sq] fp32.
+// variant: 0 = default; 1..: tuning variants (all produce the same result within rounding)
 extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,
-                            float scale, int* err, cudaStream_t st) {
+                            float scale, int variant, int* err, cudaStream_t st) {
   using namespace fa;
   CUtensorMap tq, tk, tv;
   auto make = [&](CUtensorMap* m, const void* p, int S) {
@@ -308,13 +358,12 @@ extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o
   if (rc) return rc;
   rc = make(&tv, v, Skv);
   if (rc) return rc;
-  static bool attr = false;
-  if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
-    if (e != cudaSuccess) return 100 + (int)e;
-    attr = true;
+  switch (variant) {
+    case 1: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
+    case 2: return launch_fa_fwd<0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
+    case 3: return launch_fa_fwd<2, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
+    case 4: return launch_fa_fwd<3, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
+    case 5: return launch_fa_fwd<4, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
+    default: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
   }
-  dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
-  fa_fwd_kernel<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, err);
-  return (int)cudaGetLastError();
 }

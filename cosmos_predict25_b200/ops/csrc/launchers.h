@@ -39,7 +39,7 @@ int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
 extern "C" {
 // fa_fwd.cu
 int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
-                 int* err, cudaStream_t st);
+                 int variant, int* err, cudaStream_t st);
 }
 
 extern "C" {
