@@ -65,10 +65,13 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--json", default=None)
     ap.add_argument("--variants", action="store_true", help="also time the tuning variants of kernels that have them")
+    ap.add_argument("--seq", type=int, default=None, help="override the token count (small cases for profiler captures)")
+    ap.add_argument("--heads", type=int, default=None, help="override the head count of the attention rows")
+    ap.add_argument("--no-twin", action="store_true", help="skip the library twins")
     args = ap.parse_args()
     ops = native.load()
     pk = peaks()
-    N = 84480 // (8 if args.quick else 1)
+    N = args.seq or (84480 // (8 if args.quick else 1))
     D, H, HD, Fm, L, T = 2048, 16, 128, 8192, 3520 // (8 if args.quick else 1), 24
     rows = []
 
@@ -105,7 +108,7 @@ def main():
         add("cublas wgrad (twin)", f"{Fm}x{D}x{N}", time_ms(lambda: torch.matmul(dy.T, a)), 2.0 * N * Fm * D)
         del a, b, dy
     if want("attention"):
-        heads = 2 if args.quick else H
+        heads = args.heads or (2 if args.quick else H)
         q, k, v = (torch.randn(1, N, heads, HD, device=dev).bfloat16() for _ in range(3))
         fl = 4.0 * N * N * HD * heads
         scale = 1 / math.sqrt(HD)

@@ -37,9 +37,30 @@ std::tuple<Tensor, Tensor> fa_fwd_variant(const Tensor& q, const Tensor& k, cons
 std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale) {
   return fa_fwd_variant(q, k, v, scale, 0);
 }
+
+// gradients of softmax(q k^T scale) v given the forward's output and log-sum-exp
+std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                          const Tensor& lse, double scale) {
+  check_qkv(d_o, "do");
+  check_qkv(q, "q");
+  check_qkv(k, "k");
+  check_qkv(v, "v");
+  check_qkv(o, "o");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse must be contiguous fp32 [B,H,Sq]");
+  c10::cuda::CUDAGuard g(q.device());
+  const int B = (int)q.size(0), Sq = (int)q.size(1), H = (int)q.size(2), Skv = (int)k.size(1);
+  Tensor dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
+  Tensor scratch = at::empty({(int64_t)cb200_fa_bwd_scratch_floats(B, Sq, H)}, q.options().dtype(at::kFloat));
+  const int rc = cb200_fa_bwd(d_o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr<float>(), B, Sq, Skv, H, (float)scale,
+                              cb200_error_word(q.get_device()), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "fa_bwd launch failed with code ", rc);
+  return {dq, dk, dv};
+}
 }  // namespace
 
 void register_attention_ops(torch::Library& m) {
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)", &fa_fwd);
+  m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)", &fa_bwd);
   m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)", &fa_fwd_variant);
 }

@@ -57,3 +57,10 @@ void cb200_a2a_scatter_heads_peer(const void* x, const int64_t* out_ptrs, const 
                                   cudaStream_t st);
 void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S, int H, int HD, int rank, int P, cudaStream_t st);
 }
+
+extern "C" {
+// fa_bwd.cu
+int cb200_fa_bwd_scratch_floats(int B, int Sq, int H);
+int cb200_fa_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq, void* dk,
+                 void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st);
+}

@@ -199,6 +199,25 @@ def test_flash_attention_large_scores_rescale():
     _close(o, orf, 3e-2, 3e-2, "o")
 
 
+@pytest.mark.parametrize("B,Sq,Skv,H", [(1, 256, 128, 2), (2, 512, 384, 3), (1, 1000, 999, 2), (1, 300, 15, 2), (1, 2048, 2048, 2)])
+def test_flash_attention_bwd(B, Sq, Skv, H):
+    torch.manual_seed(12)
+    q = torch.randn(B, Sq, H, 128, device=DEV).bfloat16()
+    k = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
+    v = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
+    do = torch.randn(B, Sq, H, 128, device=DEV).bfloat16()
+    scale = 1.0 / math.sqrt(128)
+    o, lse = _ops().fa_fwd(q, k, v, scale)
+    dq, dk, dv = _ops().fa_bwd(do, q, k, v, o, lse, scale)
+    _no_kernel_error()
+    qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
+    orf, _ = ref.attention(qr, kr, vr, scale)
+    orf.backward(do.float())
+    _close(dv, vr.grad, 3e-2, 3e-2, "dv")
+    _close(dk, kr.grad, 3e-2, 3e-2, "dk")
+    _close(dq, qr.grad, 3e-2, 3e-2, "dq")
+
+
 def test_attention_autograd():
     torch.manual_seed(10)
     B, S, H = 1, 384, 2
