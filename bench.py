@@ -143,6 +143,12 @@ def main():
     torch.manual_seed(1234 + rank)
     model = Video2WorldModelRectifiedFlow(cfg, device=dev, fsdp_group=groups.fsdp, cp_group=groups.cp)
     model.train()
+    if args.cp > 1 and args.transport == "peer":
+        from cosmos_predict25_b200.parallel import ulysses
+        from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext
+        per_rank = (args.frames // args.cp) * (args.height // 2) * (args.width // 2) * net_cfg.model_channels
+        ctx = PeerContext(groups.cp, dev, arena_bytes=8 * (per_rank * 2 + 4096) + (1 << 20))
+        ulysses.attach_peer_transport(groups.cp, PeerAllToAll(ctx, max_elems=per_rank))
     out_dir = os.path.join("/tmp", f"cosmos_b200_bench_{os.getpid()}")
     trainer = Trainer(TrainerConfig(max_iter=10 ** 9, output_dir=out_dir), model,
                       OptimizerConfig(lr=2 ** -14.5, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-3, max_grad_norm=1.0),

@@ -273,11 +273,12 @@ class Attention(nn.Module):
         if self.is_selfattn:
             k = self.k_proj(x).view(B, S, self.n_heads, self.head_dim)
             v = self.v_proj(x).view(B, S, self.n_heads, self.head_dim)
-            q = ops.rmsnorm_rope(q, self.q_norm.weight, rope, self.q_norm.eps)
-            k = ops.rmsnorm_rope(k, self.k_norm.weight, rope, self.k_norm.eps)
             if self.cp_group is not None:
-                o = ulysses.ulysses_attention(q, k, v, self.cp_group)
+                o = ulysses.ulysses_attention_fused(q, k, v, self.q_norm.weight, self.k_norm.weight, rope, self.cp_group,
+                                                    self.q_norm.eps)
             else:
+                q = ops.rmsnorm_rope(q, self.q_norm.weight, rope, self.q_norm.eps)
+                k = ops.rmsnorm_rope(k, self.k_norm.weight, rope, self.k_norm.eps)
                 o = ops.attention(q, k, v)
         else:
             q = ops.rmsnorm_rope(q, self.q_norm.weight, None, self.q_norm.eps)

@@ -22,10 +22,10 @@ std::vector<int64_t> ptr_vec(c10::ArrayRef<int64_t> v) {
   return std::vector<int64_t>(v.begin(), v.end());
 }
 
-void peer_barrier(c10::ArrayRef<int64_t> flag_ptrs, int64_t rank, int64_t epoch, int64_t device) {
+void peer_barrier(c10::ArrayRef<int64_t> flag_ptrs, int64_t rank, int64_t epoch, int64_t device, int64_t max_spins) {
   c10::cuda::CUDAGuard g((c10::DeviceIndex)device);
   auto p = ptr_vec(flag_ptrs);
-  cb200_peer_barrier(p.data(), (int)rank, (int)p.size(), (unsigned)epoch, cb200_error_word((int)device), stream());
+  cb200_peer_barrier(p.data(), (int)rank, (int)p.size(), (unsigned)epoch, (unsigned)max_spins, cb200_error_word((int)device), stream());
 }
 
 // segs: int64 CUDA tensor [nseg, 4] = (full_offset, stride, shard_offset, numel)
@@ -89,7 +89,7 @@ Tensor a2a_gather_seq_peer(c10::ArrayRef<int64_t> src_ptrs, int64_t B, int64_t S
 }  // namespace
 
 void register_peer_ops(torch::Library& m) {
-  m.def("peer_barrier(int[] flag_ptrs, int rank, int epoch, int device) -> ()", &peer_barrier);
+  m.def("peer_barrier(int[] flag_ptrs, int rank, int epoch, int device, int max_spins) -> ()", &peer_barrier);
   m.def("rs_cast_norm_peer(int[] grad_ptrs, Tensor segs, Tensor(a!) g32, Tensor(b!) unit_sumsq, Tensor(c!)? total_sumsq, int rank, "
         "float scale) -> ()", &rs_cast_norm_peer);
   m.def("adamw_push_peer(int[] full_ptrs, int[] sumsq_ptrs, Tensor segs, Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, "

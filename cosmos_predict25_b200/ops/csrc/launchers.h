@@ -44,7 +44,7 @@ int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* ls
 
 extern "C" {
 // peer.cu
-void cb200_peer_barrier(const int64_t* flag_ptrs, int rank, int P, unsigned epoch, int* err, cudaStream_t st);
+void cb200_peer_barrier(const int64_t* flag_ptrs, int rank, int P, unsigned epoch, unsigned max_spins, int* err, cudaStream_t st);
 int cb200_rs_blocks_x(void);
 void cb200_rs_cast_norm_peer(const int64_t* grad_ptrs, const void* segs, int nseg, float* g32, float* partials, float* unit_sumsq,
                              float* total_sumsq, int rank, int P, float scale, cudaStream_t st);

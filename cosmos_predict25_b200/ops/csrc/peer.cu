@@ -22,7 +22,7 @@
 namespace cb200 {
 
 constexpr int kMaxPeers = 8;
-constexpr unsigned kPeerSpinLimit = 1u << 22;  // x ~100 ns back-off each => bounded at a few hundred ms
+constexpr unsigned kPeerSpinLimit = 1u << 24;  // default bound when the caller passes 0: ~1 us per probe => tens of seconds
 
 struct PeerPtrs {
   void* p[kMaxPeers];
@@ -39,7 +39,7 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* addr) {
 
 // flags: per rank a symmetric array of kMaxPeers words; flags[r] on rank q is written by rank r.
 // Thread p < P: publish `epoch` into peer p's slot [rank], then wait for our slot [p] to reach it.
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int P, unsigned epoch, int* err) {
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int P, unsigned epoch, unsigned max_spins, int* err) {
   const int p = threadIdx.x;
   if (p < P) {
     __threadfence_system();
@@ -49,7 +49,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int P, unsigned ep
     // epochs grow monotonically; signed distance tolerates wrap-around
     while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
       __nanosleep(100);
-      if (++i >= kPeerSpinLimit) {
+      if (++i >= max_spins) {
         atomicCAS(err, 0, 100 + p);
         break;
       }
@@ -243,8 +243,8 @@ static PeerPtrs make_ptrs(const int64_t* ptrs, int P) {
 
 extern "C" {
 
-void cb200_peer_barrier(const int64_t* flag_ptrs, int rank, int P, unsigned epoch, int* err, cudaStream_t st) {
-  peer_barrier_kernel<<<1, 32, 0, st>>>(make_ptrs(flag_ptrs, P), rank, P, epoch, err);
+void cb200_peer_barrier(const int64_t* flag_ptrs, int rank, int P, unsigned epoch, unsigned max_spins, int* err, cudaStream_t st) {
+  peer_barrier_kernel<<<1, 32, 0, st>>>(make_ptrs(flag_ptrs, P), rank, P, epoch, max_spins ? max_spins : kPeerSpinLimit, err);
 }
 
 int cb200_rs_blocks_x(void) { return 148 * 2; }

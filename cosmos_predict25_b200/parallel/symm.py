@@ -1,0 +1,157 @@
+"""Symmetric (peer-mapped) device memory and the device-side barrier used by the fused collectives.
+
+Every rank of a group allocates the same-sized arena; after a rendezvous each rank knows the virtual
+address of every peer's arena in its own address space, so kernels can load from / store to a peer's
+buffer over NVLink with ordinary ld/st. The handle exchange is done by torch's symmetric-memory
+allocator (plumbing); everything that moves data is a kernel of this package
+(``ops/csrc/peer.cu``). NVSwitch multicast objects are not created: the kernels use plain peer
+accesses only, and a rank that exits never leaves a multicast binding behind.
+
+``PeerContext.barrier()`` enqueues a 1-block kernel on the current stream: it publishes an epoch into
+every peer's flag word, then waits - with a bound - until every peer has published the same epoch. If
+the bound is hit the kernel records an error code (readable with ``check()``) and returns; the host
+raises, the GPU context stays usable.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+
+@dataclass
+class SymmetricTensor:
+    """A local tensor carved from a symmetric arena plus the address of the same bytes on every peer."""
+
+    tensor: torch.Tensor
+    ptrs: List[int]
+
+
+class SymmetricArena:
+    """One symmetric allocation per rank, bump-allocated into tensors (256-byte aligned)."""
+
+    def __init__(self, nbytes: int, group, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group
+        self.device = device
+        self.nbytes = (nbytes + 255) // 256 * 256
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert self.base_ptrs[self.rank] == self.buf.data_ptr(), "symmetric arena: local pointer mismatch"
+        self.offset = 0
+
+    def alloc(self, numel: int, dtype: torch.dtype, zero: bool = True) -> SymmetricTensor:
+        esize = torch.empty((), dtype=dtype).element_size()
+        nbytes = (numel * esize + 255) // 256 * 256
+        if self.offset + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric arena exhausted: need {nbytes} more bytes, {self.nbytes - self.offset} left")
+        t = self.buf[self.offset: self.offset + numel * esize].view(dtype)
+        if zero:
+            t.zero_()
+        st = SymmetricTensor(t, [p + self.offset for p in self.base_ptrs])
+        self.offset += nbytes
+        return st
+
+
+class PeerContext:
+    """Rank/size of a group, a flag word array in symmetric memory and the epoch counter of its barrier."""
+
+    def __init__(self, group, device: torch.device, arena: Optional[SymmetricArena] = None, arena_bytes: int = 1 << 20):
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = device
+        self.arena = arena or SymmetricArena(arena_bytes, self.group, device)
+        self.rank, self.world = self.arena.rank, self.arena.world
+        assert self.world <= 8, "peer kernels support up to 8 ranks (one NVSwitch domain)"
+        self.flags = self.arena.alloc(64, torch.int32)
+        self.epoch = 0
+        self.timeout_s = float(os.environ.get("COSMOS_B200_PEER_TIMEOUT_S", "30"))  # bound of device-side waits
+        self.ops = native.load()
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)  # flag words are zeroed everywhere before the first device barrier
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        self.ops.peer_barrier(self.flags.ptrs, self.rank, self.epoch, self.device.index, int(self.timeout_s * 1e6))
+        native.count_launch()
+
+    def check(self) -> None:
+        """Host-side check of the device error word (synchronises the device)."""
+        code = int(self.ops.kernel_error(self.device.index, True))
+        if code != 0:
+            raise RuntimeError(f"a peer-memory kernel gave up waiting (error code {code}): rank {code - 100} did not arrive"
+                               if code >= 100 else f"kernel error code {code}")
+
+
+class PeerAllToAll:
+    """Ulysses exchanges over peer memory for one context-parallel group.
+
+    seq_to_head: every 16-byte vector of x [B, S_loc, H, D] is stored straight into the staging buffer of
+    the rank that owns its head (optionally after per-head RMSNorm + RoPE: the q/k epilogue chain and the
+    exchange are one kernel). head_to_seq: each rank reads its token rows of every peer's staged
+    attention output. Staging buffers rotate so that a buffer is rewritten only two exchanges later,
+    after a barrier every rank has passed."""
+
+    def __init__(self, ctx: PeerContext, max_elems: int, n_slots: int = 8):
+        self.ctx = ctx
+        self.ops = ctx.ops
+        self.slots = [ctx.arena.alloc(max_elems, torch.bfloat16, zero=False) for _ in range(n_slots)]
+        self.max_elems = max_elems
+        self.cursor = 0
+
+    def _next(self, numel: int) -> SymmetricTensor:
+        assert numel <= self.max_elems, f"exchange of {numel} elements exceeds the staging size {self.max_elems}"
+        s = self.slots[self.cursor]
+        self.cursor = (self.cursor + 1) % len(self.slots)
+        return s
+
+    def scatter_heads(self, xs, norm_weights=None, rope=None, eps: float = 1e-6, copy_out: bool = True):
+        """Exchange a list of [B, S_loc, H, D] tensors with one barrier. ``norm_weights[i]`` (or None)
+        applies per-head RMSNorm (+RoPE when ``rope`` is given) to tensor i on the way out.
+        Returns (list of [B, S_loc*P, H/P, D] tensors, list of rstd or None). With ``copy_out`` the results
+        are copied out of the rotating staging buffers (needed whenever they are kept for a backward pass);
+        without it they alias the staging memory and must be consumed before eight more exchanges."""
+        P, r = self.ctx.world, self.ctx.rank
+        outs, rstds = [], []
+        cos, sin = rope.cos_sin() if rope is not None else (None, None)
+        for i, x in enumerate(xs):
+            B, S, H, D = x.shape
+            slot = self._next(x.numel())
+            w = norm_weights[i] if norm_weights is not None else None
+            rstd = self.ops.a2a_scatter_heads_peer(x.contiguous(), slot.ptrs, w, cos if w is not None else None,
+                                                   sin if w is not None else None, r, eps)
+            native.count_launch()
+            outs.append(slot.tensor[: x.numel()].view(B, S * P, H // P, D))
+            rstds.append(rstd.view(B, S, H) if w is not None else None)
+        self.ctx.barrier()
+        if copy_out:
+            outs = [o.clone() for o in outs]
+        return outs, rstds
+
+    def seq_to_head(self, x: torch.Tensor, copy_out: bool = True) -> torch.Tensor:
+        return self.scatter_heads([x], copy_out=copy_out)[0][0]
+
+    def head_to_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """[B, S_loc*P, H/P, D] (all tokens, local heads) -> [B, S_loc, H, D]."""
+        P, r = self.ctx.world, self.ctx.rank
+        B, SP, Hl, D = x.shape
+        slot = self._next(x.numel())
+        stage = slot.tensor[: x.numel()].view_as(x)
+        if stage.data_ptr() != x.data_ptr():
+            stage.copy_(x)
+        self.ctx.barrier()
+        out = self.ops.a2a_gather_seq_peer(slot.ptrs, B, SP // P, Hl * P, D, r, x)
+        native.count_launch()
+        self.ctx.barrier()  # peers have finished reading this rank's stage before it is reused
+        return out

@@ -109,6 +109,51 @@ class _HeadToSeq(torch.autograd.Function):
         return seq_to_head(g.contiguous(), ctx.group), None
 
 
+class _ScatterHeadsFused(torch.autograd.Function):
+    """q, k: per-head RMSNorm (+RoPE) fused with the seq->head exchange; v: plain exchange; one barrier for
+    the three. Backward: head->seq exchange of the gradients, then the RMSNorm/RoPE backward kernel."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, wq, wk, rope, eps, transport):
+        (qh, kh, vh), (rq, rk, _) = transport.scatter_heads([q, k, v], [wq, wk, None], rope, eps)
+        ctx.save_for_backward(q, k, wq, wk, rq, rk)
+        ctx.rope, ctx.transport = rope, transport
+        return qh, kh, vh
+
+    @staticmethod
+    def backward(ctx, dqh, dkh, dvh):
+        from ..ops import native
+        ops_n = native.load()
+        q, k, wq, wk, rq, rk = ctx.saved_tensors
+        t = ctx.transport
+        dqn, dkn, dv = (t.head_to_seq(g.contiguous()) for g in (dqh, dkh, dvh))
+        cos, sin = ctx.rope.cos_sin() if ctx.rope is not None else (None, None)
+        dq, dwq = ops_n.rmsnorm_rope_bwd(dqn, q, wq, rq, cos, sin)
+        dk, dwk = ops_n.rmsnorm_rope_bwd(dkn, k, wk, rk, cos, sin)
+        native.count_launch(4)
+        return dq, dk, dv, dwq.to(wq.dtype), dwk.to(wk.dtype), None, None, None
+
+
+def ulysses_attention_fused(q_raw, k_raw, v, q_norm_weight, k_norm_weight, rope, group, eps: float = 1e-6,
+                            scale: Optional[float] = None):
+    """Self-attention on un-normalised q/k projections with the q/k epilogue chain (RMSNorm, RoPE) fused into
+    the peer-memory all-to-all. Falls back to the unfused composition when no peer transport is attached."""
+    t = _peer_transports.get(id(group))
+    if t is None or not q_raw.is_cuda:
+        q = ops.rmsnorm_rope(q_raw, q_norm_weight, rope, eps)
+        k = ops.rmsnorm_rope(k_raw, k_norm_weight, rope, eps)
+        return ulysses_attention(q, k, v, group, scale)
+    if not (torch.is_grad_enabled() and any(x.requires_grad for x in (q_raw, k_raw, v, q_norm_weight, k_norm_weight))):
+        # inference: consume the staged tensors in place, nothing is kept for a backward pass
+        (qh, kh, vh), _ = t.scatter_heads([q_raw.contiguous(), k_raw.contiguous(), v.contiguous()],
+                                          [q_norm_weight, k_norm_weight, None], rope, eps, copy_out=False)
+        return t.head_to_seq(ops.attention(qh, kh, vh, scale))
+    qh, kh, vh = _ScatterHeadsFused.apply(q_raw.contiguous(), k_raw.contiguous(), v.contiguous(), q_norm_weight, k_norm_weight,
+                                          rope, eps, t)
+    oh = ops.attention(qh, kh, vh, scale)
+    return _HeadToSeq.apply(oh, group)
+
+
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: Optional[float] = None):
     """Self-attention over a sequence sharded on dim 1 across ``group``."""
     P, _ = group_size_rank(group)

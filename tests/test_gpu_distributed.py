@@ -1,0 +1,187 @@
+"""Multi-GPU tests (2 ranks, one process per GPU, NCCL for plumbing): the peer-memory kernels against their
+NCCL twins, and the bounded-wait error path (which needs one GPU only and faults nothing)."""
+
+import os
+import socket
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn_name, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        globals()[fn_name](rank, world)
+        torch.cuda.synchronize()
+        dist.barrier()
+        with open(os.path.join(tmp, f"ok{rank}"), "w") as f:
+            f.write("ok")
+    except Exception:
+        with open(os.path.join(tmp, f"err{rank}"), "w") as f:
+            f.write(traceback.format_exc())
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _run(fn_name, world=2):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(world, _free_port(), fn_name, tmp), nprocs=world, join=True)
+        errs = [open(os.path.join(tmp, f)).read() for f in sorted(os.listdir(tmp)) if f.startswith("err")]
+        assert not errs, "\n".join(errs)
+        assert all(os.path.exists(os.path.join(tmp, f"ok{r}")) for r in range(world))
+
+
+def _a2a_peer_vs_nccl(rank, world):
+    from cosmos_predict25_b200.ops import functional as F_ops
+    from cosmos_predict25_b200.parallel import ulysses
+    from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+    torch.manual_seed(7 + rank)
+    B, S, H, D = 1, 96, 4, 128
+    ctx = PeerContext(g, dev, arena_bytes=64 << 20)
+    t = PeerAllToAll(ctx, max_elems=B * S * H * D)
+    x = torch.randn(B, S, H, D, device=dev).bfloat16()
+    want = ulysses.seq_to_head(x, g)            # NCCL all_to_all_single
+    got = t.seq_to_head(x).clone()
+    assert torch.equal(got, want)
+    back = t.head_to_seq(got)
+    assert torch.equal(back, x)
+    # fused per-head RMSNorm + RoPE + exchange == separate kernels + NCCL exchange
+    w = (1 + 0.1 * torch.randn(D, device=dev))
+    half = torch.rand(S, D // 2, device=dev) * 30
+    rope = F_ops.RopeTable(torch.cat([half, half], -1))
+    (fq, fv), (rstd, _) = t.scatter_heads([x, x], [w, None], rope)
+    nq = ulysses.seq_to_head(F_ops.rmsnorm_rope(x, w, rope), g)
+    assert torch.equal(fv, want)
+    assert (fq.float() - nq.float()).abs().max() < 2e-2
+    ctx.check()
+    # end-to-end through autograd: fused path == NCCL path
+    q, k, v = (torch.randn(B, S, H, D, device=dev).bfloat16().requires_grad_(True) for _ in range(3))
+    o_ref = ulysses.ulysses_attention(F_ops.rmsnorm_rope(q, w, rope), F_ops.rmsnorm_rope(k, w, rope), v, g)
+    go = torch.randn_like(o_ref)
+    gr = torch.autograd.grad(o_ref, (q, k, v), go)
+    ulysses.attach_peer_transport(g, t)
+    o = ulysses.ulysses_attention_fused(q, k, v, w, w, rope, g)
+    gp = torch.autograd.grad(o, (q, k, v), go)
+    ulysses.detach_peer_transport(g)
+    assert (o.float() - o_ref.float()).abs().max() < 3e-2
+    for a, b in zip(gp, gr):
+        assert (a.float() - b.float()).abs().max() < 5e-2
+    ctx.check()
+
+
+def test_peer_all_to_all_matches_nccl():
+    _run("_a2a_peer_vs_nccl")
+
+
+def _engine_peer_vs_nccl(rank, world):
+    from cosmos_predict25_b200.parallel.fsdp import ShardedEngine
+    from cosmos_predict25_b200.parallel.peer_fsdp import PeerShardedEngine
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+
+    def make():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 64, bias=False)).to(dev)
+
+    na, nb = make(), make()
+    ea = ShardedEngine(na, group=g, compute_dtype=torch.bfloat16, use_ema=True, transport="nccl", units=[na[0]])
+    eb = PeerShardedEngine(nb, group=g, compute_dtype=torch.bfloat16, use_ema=True, units=[nb[0]])
+    torch.manual_seed(100 + rank)
+    for step in range(3):
+        x = torch.randn(32, 256, device=dev).bfloat16()
+        na(x).float().pow(2).mean().backward()
+        nb(x).float().pow(2).mean().backward()
+        n1 = ea.step(lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01, max_grad_norm=0.5, ema_beta=0.9)
+        n2 = eb.step(lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01, max_grad_norm=0.5, ema_beta=0.9)
+        eb.ctx.check()
+        # the peer path sums gradients in fp32, NCCL in bf16: norms agree to bf16 accuracy
+        assert abs(n1.item() - n2.item()) <= 2e-2 * max(n1.item(), 1e-6), (n1.item(), n2.item())
+        for pa, pb in zip(na.parameters(), nb.parameters()):
+            assert (pa.float() - pb.float()).abs().max() <= 2e-2 * pa.float().abs().max() + 1e-3, step
+    # all ranks hold identical full parameters after the peer all-gather
+    flat = torch.cat([p.detach().float().reshape(-1) for p in nb.parameters()])
+    other = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(other, flat)
+    assert torch.equal(other[0], other[1])
+
+
+def test_peer_sharded_engine_matches_nccl_engine():
+    _run("_engine_peer_vs_nccl")
+
+
+def _model_step_peer(rank, world):
+    """Mini Video2World model: parameter sharding over 2 GPUs with the peer engine, plus context parallelism
+    over the same 2 GPUs with the fused exchange; loss is identical on both ranks and finite."""
+    from cosmos_predict25_b200.models.dit import dit_mini
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.parallel import ulysses
+    from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig
+    from cosmos_predict25_b200.trainer.trainer import Trainer, TrainerConfig
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+    torch.manual_seed(0)
+    cfg = Video2WorldRFConfig(net=dit_mini(crossattn_proj_in_channels=2048, checkpoint_mode="save_attention"), state_t=4,
+                              sharding_transport="peer")
+    model = Video2WorldModelRectifiedFlow(cfg, device=dev, fsdp_group=g, cp_group=g).train()
+    ctx = PeerContext(g, dev, arena_bytes=256 << 20)
+    ulysses.attach_peer_transport(g, PeerAllToAll(ctx, max_elems=1 * 2 * 256 * 8 * 128))
+    trainer = Trainer(TrainerConfig(output_dir=f"/tmp/cosmos_b200_t{rank}"), model, OptimizerConfig(lr=1e-4))
+    torch.manual_seed(5)
+    batch = {"latents": torch.randn(1, 16, 4, 32, 32), "t5_text_embeddings": torch.randn(1, 64, 2048).bfloat16(),
+             "fps": torch.tensor([16.0]), "padding_mask": torch.zeros(1, 1, 32, 32), "num_conditional_frames": 1}
+    losses = [trainer.train_step(dict(batch)) for _ in range(2)]
+    ctx.check()
+    model.engine.ctx.check()
+    # each rank's loss is the mean over its own sequence shard (rank 0 holds the clean conditioning frame),
+    # so the values differ; what must agree is the model after the sharded update
+    assert all(l == l and abs(l) < 1e4 for l in losses), losses
+    flat = torch.cat([p.detach().float().reshape(-1) for p in model.net.parameters()])
+    gathered = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(gathered, flat)
+    assert torch.equal(gathered[0], gathered[1])
+    assert torch.isfinite(flat).all()
+
+
+def test_model_step_with_peer_engine_and_fused_context_parallel():
+    _run("_model_step_peer")
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A flag that nothing ever sets: the barrier kernel gives up after its bound (well under a second),
+    records which peer was missing and returns; the context stays usable."""
+    from cosmos_predict25_b200.ops import native
+    ops = native.load()
+    dev = torch.device("cuda", 0)
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    lonely = torch.zeros(64, dtype=torch.int32, device=dev)  # stands in for a peer that never signals back
+    ops.kernel_error(0, True)
+    # rank 0 of a 2-rank group: slot [1] of our own flag array is never written
+    ops.peer_barrier([flags.data_ptr(), lonely.data_ptr()], 0, 1, 0, 300_000)  # ~0.3 s bound
+    torch.cuda.synchronize()
+    code = ops.kernel_error(0, True)
+    assert code == 101, code
+    assert lonely[0].item() == 1            # our signal did reach the "peer"
+    y = torch.ones(4, device=dev) * 2        # the context is alive
+    assert y.sum().item() == 8
+    assert ops.kernel_error(0, True) == 0
