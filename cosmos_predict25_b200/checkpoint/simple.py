@@ -1,0 +1,106 @@
+"""Non-distributed checkpointers: ``DummyCheckpointer`` (no I/O; tests, smoke runs) and ``PtCheckpointer``, the legacy
+layout ``iter_%09d_{model,optim,scheduler}.pt`` + ``iter_%09d.pt`` (trainer state) + ``latest_checkpoint.txt`` written
+by the first data-parallel rank from host copies on a background thread.
+
+Parity targets: cosmos_predict2/_src/imaginaire/checkpointer/dummy.py:25, .../ddp.py:35-446 (layout, resume priority,
+``strict_resume``, ``scheduler.last_epoch = iteration``, background thread save).
+"""
+
+from __future__ import annotations
+
+import os
+import threading
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils import log
+
+
+def _rank():
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+class DummyCheckpointer:
+    def __init__(self, *a, **k):
+        pass
+
+    def save(self, model, optimizer, scheduler, iteration, grad_scaler=None, trainer=None):
+        pass
+
+    def load(self, model, optimizer=None, scheduler=None, grad_scaler=None, trainer=None) -> int:
+        return 0
+
+    def finalize(self):
+        pass
+
+
+class PtCheckpointer:
+    def __init__(self, config_checkpoint, job_dir: str, callbacks=None):
+        self.cfg = config_checkpoint
+        self.dir = os.path.join(job_dir, "checkpoints")
+        self.load_path = config_checkpoint.get("load_path") or None
+        self.load_training_state = config_checkpoint.get("load_training_state", False)
+        self.only_load_scheduler_state = config_checkpoint.get("only_load_scheduler_state", False)
+        self.strict_resume = config_checkpoint.get("strict_resume", True)
+        self.callbacks = callbacks
+        self._thread: Optional[threading.Thread] = None
+
+    def _latest(self):
+        f = os.path.join(self.dir, "latest_checkpoint.txt")
+        return open(f).read().strip() if os.path.exists(f) else None
+
+    def save(self, model, optimizer, scheduler, iteration, grad_scaler=None, trainer=None):
+        self.finalize()
+        name = f"iter_{iteration:09d}"
+        cpu = lambda sd: {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in sd.items()}
+        parts = {"model": cpu(model.state_dict()), "optim": cpu(optimizer.state_dict()) if optimizer is not None else {},
+                 "scheduler": scheduler.state_dict() if scheduler is not None else {}}
+        trainer_state = {"iteration": iteration, "grad_scaler": {}}
+
+        def work():
+            if _rank() == 0:
+                os.makedirs(self.dir, exist_ok=True)
+                for k, v in parts.items():
+                    torch.save(v, os.path.join(self.dir, f"{name}_{k}.pt"))
+                torch.save(trainer_state, os.path.join(self.dir, f"{name}.pt"))
+                with open(os.path.join(self.dir, "latest_checkpoint.txt"), "w") as f:
+                    f.write(name + "\n")
+                log.info(f"saved checkpoint {name}")
+
+        self._thread = threading.Thread(target=work, daemon=True)
+        self._thread.start()
+
+    def load(self, model, optimizer=None, scheduler=None, grad_scaler=None, trainer=None) -> int:
+        latest = self._latest()
+        if latest is not None:
+            base, resume = os.path.join(self.dir, latest), {"model", "optim", "scheduler", "trainer"}
+        elif self.load_path:
+            base = self.load_path[:-3] if self.load_path.endswith(".pt") else self.load_path
+            if base.endswith("_model"):
+                base = base[:-6]
+            resume = {"model", "optim", "scheduler", "trainer"} if self.load_training_state else \
+                ({"model", "scheduler"} if self.only_load_scheduler_state else {"model"})
+        else:
+            return 0
+        iteration = 0
+        mp = base + "_model.pt" if os.path.exists(base + "_model.pt") else base + ".pt"
+        if "model" in resume:
+            sd = torch.load(mp, map_location="cpu", weights_only=False)
+            model.load_state_dict(sd, strict=self.strict_resume)
+        if "optim" in resume and optimizer is not None and os.path.exists(base + "_optim.pt"):
+            optimizer.load_state_dict(torch.load(base + "_optim.pt", map_location="cpu", weights_only=False))
+        if "trainer" in resume and os.path.exists(base + ".pt") and os.path.exists(base + "_model.pt"):
+            iteration = int(torch.load(base + ".pt", map_location="cpu", weights_only=False)["iteration"])
+        if "scheduler" in resume and scheduler is not None and os.path.exists(base + "_scheduler.pt"):
+            scheduler.load_state_dict(torch.load(base + "_scheduler.pt", map_location="cpu", weights_only=False))
+            if iteration:
+                scheduler.load_state_dict({"last_epoch": iteration})
+        log.info(f"loaded checkpoint {base} at iteration {iteration}")
+        return iteration
+
+    def finalize(self):
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None

@@ -144,7 +144,8 @@ class Trainer:
         if cfg.timeout_period > 0:
             signal.alarm(0)
         if self.checkpointer is not None and cfg.save_iter:
-            self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
+            if self.iteration % cfg.save_iter != 0:  # otherwise the loop has just written this iteration
+                self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
             self.checkpointer.finalize()
         self.callbacks.on_train_end(self.model, iteration=self.iteration)
         if dist.is_available() and dist.is_initialized():

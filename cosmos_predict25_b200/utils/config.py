@@ -328,6 +328,13 @@ def load_config_module(path: str):
     import importlib
     import importlib.util
     if path.endswith(".py") and os.path.exists(path):
+        # a file inside an importable package is imported under its package name (relative imports work)
+        rel = os.path.relpath(os.path.abspath(path), os.getcwd())
+        if not rel.startswith(".."):
+            try:
+                return importlib.import_module(rel[:-3].replace(os.sep, "."))
+            except ImportError:
+                pass
         spec = importlib.util.spec_from_file_location("_cosmos_b200_config_" + str(abs(hash(path))), path)
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
