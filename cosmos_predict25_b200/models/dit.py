@@ -82,6 +82,15 @@ class FusedLinear(nn.Linear):
         return ops.linear(x, self.weight, self.bias, self.act)
 
 
+def _proj_gate_residual(proj: nn.Module, a: torch.Tensor, x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``x + gate * proj(a)``. A plain projection runs as one GEMM with the gated residual in its epilogue; a
+    projection wrapped by a LoRA adapter adds the low-rank term to the GEMM input of the residual instead."""
+    if isinstance(proj, FusedLinear) and proj.bias is None:
+        return ops.linear_gate_residual(a, proj.weight, x, gate)
+    B, T, L, D = x.shape
+    return ops.gate_residual(x, gate, proj(a).view(B, T, L, D))
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-6):
         super().__init__()
@@ -360,15 +369,15 @@ class Block(nn.Module):
 
         h = ops.ln_modulate(x, sh1, sc1)
         o = self.self_attn(h.view(B, T * L, D), None, rope, return_pre_proj=True)
-        x = ops.linear_gate_residual(o, self.self_attn.output_proj.weight, x, g1)
+        x = _proj_gate_residual(self.self_attn.output_proj, o, x, g1)
 
         h = ops.ln_modulate(x, sh2, sc2)
         o = self.cross_attn(h.view(B, T * L, D), context, None, cross_kv, return_pre_proj=True)
-        x = ops.linear_gate_residual(o, self.cross_attn.output_proj.weight, x, g2)
+        x = _proj_gate_residual(self.cross_attn.output_proj, o, x, g2)
 
         h = ops.ln_modulate(x, sh3, sc3)
         a = self.mlp.layer1(h.view(B, T * L, D))
-        x = ops.linear_gate_residual(a, self.mlp.layer2.weight, x, g3)
+        x = _proj_gate_residual(self.mlp.layer2, a, x, g3)
         return x
 
 

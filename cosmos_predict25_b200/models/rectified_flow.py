@@ -134,6 +134,10 @@ class Text2WorldModelRectifiedFlow(nn.Module):
     def on_train_start(self):
         """Move parameters into the flat sharded buffers (bf16 compute copies + fp32 masters + EMA)."""
         if self.engine is None:
+            if self.config.use_lora:  # frozen base weights take the compute dtype; adapters get fp32 masters in the engine
+                for p in self.net.parameters():
+                    if not p.requires_grad and p.is_floating_point():
+                        p.data = p.data.to(self.precision)
             make = ShardedEngine
             if self.config.sharding_transport == "peer" and self.device_.type == "cuda":
                 from ..parallel.peer_fsdp import PeerShardedEngine as make
