@@ -52,10 +52,11 @@ def _attention_ops():
 def _mm_ops():
     aten = torch.ops.aten
     s = {aten.mm.default, aten.addmm.default, aten.bmm.default}
-    try:
-        s.add(torch.ops.cosmos_b200.gemm_bf16.default)
-    except (AttributeError, RuntimeError):
-        pass
+    for name in ("gemm_bf16", "gemm_bf16_gelu_pre", "gemm_bf16_gate_residual"):
+        try:
+            s.add(getattr(torch.ops.cosmos_b200, name).default)
+        except (AttributeError, RuntimeError):
+            pass
     return s
 
 

@@ -121,7 +121,10 @@ def main():
         if hasattr(ops, "fa_bwd"):
             o, lse = ops.fa_fwd(q, k, v, scale)
             do = torch.randn_like(o)
-            add("fa_bwd tcgen05", f"S={N} H={heads}", time_ms(lambda: ops.fa_bwd(do, q, k, v, o, lse, scale), iters=3, warmup=1), 2.5 * fl)
+            add("fa_bwd tcgen05 two-kernel (7 GEMM)", f"S={N} H={heads}",
+                time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 1), iters=3, warmup=1), 2.5 * fl)
+            add("fa_bwd tcgen05 single-pass (5 GEMM)", f"S={N} H={heads}",
+                time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 2), iters=3, warmup=1), 2.5 * fl)
         qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
         og = F_ops._sdpa(qg, kg, vg, scale)
         dog = torch.randn_like(og)

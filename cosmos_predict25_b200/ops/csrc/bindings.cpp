@@ -327,11 +327,18 @@ TORCH_LIBRARY(cosmos_b200, m) {
         "Tensor clip, float lr, float beta1, float beta2, float eps, float wd, int step, float ema_beta) -> ()",
         &adamw_ema_shard);
   m.def("cast_f32_bf16(Tensor src, Tensor(a!) dst) -> ()", &cast_f32_bf16);
-  m.def("gemm_bf16(Tensor a, Tensor b, Tensor? bias, int act, bool trans_a, bool trans_b) -> Tensor", &gemm_bf16);
-  m.def("gemm_bf16_gelu_pre(Tensor a, Tensor b, Tensor? bias) -> (Tensor, Tensor)", &gemm_bf16_gelu_pre);
-  m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor", &gemm_bf16_gate_residual);
+  // schema only; kernels sit under the CUDA key (end of file) so dispatch modes can intercept them
+  m.def("gemm_bf16(Tensor a, Tensor b, Tensor? bias, int act, bool trans_a, bool trans_b) -> Tensor");
+  m.def("gemm_bf16_gelu_pre(Tensor a, Tensor b, Tensor? bias) -> (Tensor, Tensor)");
+  m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor");
   m.def("kernel_error(int device, bool clear) -> int", &kernel_error);
   register_attention_ops(m);
   register_peer_ops(m);
   register_conv_ops(m);
+}
+
+TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
+  m.impl("gemm_bf16", &gemm_bf16);
+  m.impl("gemm_bf16_gelu_pre", &gemm_bf16_gelu_pre);
+  m.impl("gemm_bf16_gate_residual", &gemm_bf16_gate_residual);
 }

@@ -39,8 +39,9 @@ std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor
 }
 
 // gradients of softmax(q k^T scale) v given the forward's output and log-sum-exp
-std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
-                                          const Tensor& lse, double scale) {
+// variant 0: by problem size; 1: two deterministic kernels; 2: single pass with fp32 dQ accumulation
+std::tuple<Tensor, Tensor, Tensor> fa_bwd_variant(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                                  const Tensor& lse, double scale, int64_t variant) {
   check_qkv(d_o, "do");
   check_qkv(q, "q");
   check_qkv(k, "k");
@@ -50,17 +51,32 @@ std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, co
   c10::cuda::CUDAGuard g(q.device());
   const int B = (int)q.size(0), Sq = (int)q.size(1), H = (int)q.size(2), Skv = (int)k.size(1);
   Tensor dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
-  Tensor scratch = at::empty({(int64_t)cb200_fa_bwd_scratch_floats(B, Sq, H)}, q.options().dtype(at::kFloat));
-  const int rc = cb200_fa_bwd(d_o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
-                              dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr<float>(), B, Sq, Skv, H, (float)scale,
-                              cb200_error_word(q.get_device()), at::cuda::getCurrentCUDAStream().stream());
+  Tensor scratch = at::empty({(int64_t)cb200_fa_bwd_scratch_floats_v(B, Sq, Skv, H, (int)variant)}, q.options().dtype(at::kFloat));
+  const int rc = cb200_fa_bwd_v(d_o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr<float>(), B, Sq, Skv, H, (float)scale,
+                                (int)variant, cb200_error_word(q.get_device()), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "fa_bwd launch failed with code ", rc);
   return {dq, dk, dv};
+}
+
+std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                          const Tensor& lse, double scale) {
+  return fa_bwd_variant(d_o, q, k, v, o, lse, scale, 0);
 }
 }  // namespace
 
 void register_attention_ops(torch::Library& m) {
-  m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)", &fa_fwd);
-  m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)", &fa_bwd);
-  m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)", &fa_fwd_variant);
+  // Schemas only: the kernels are registered under the CUDA dispatch key below so that dispatch modes (selective
+  // activation checkpointing keeps the attention output by intercepting this op) see the call.
+  m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)");
+  m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");
+  m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)");
+  m.def("fa_bwd_variant(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, int variant) -> (Tensor, Tensor, Tensor)");
+}
+
+TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
+  m.impl("fa_fwd", &fa_fwd);
+  m.impl("fa_bwd", &fa_bwd);
+  m.impl("fa_fwd_variant", &fa_fwd_variant);
+  m.impl("fa_bwd_variant", &fa_bwd_variant);
 }

@@ -547,15 +547,40 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
 using namespace cb200;
 
+extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const void* k, const void* v, const float* lse2,
+                                       const float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Skv, int H,
+                                       int S_pad, float scale, int* err, cudaStream_t st);
+
+// variant 0: choose by problem size; 1: two deterministic kernels (7 GEMMs); 2: single pass with fp32 dQ accumulation (5 GEMMs)
+static bool fa_bwd_use_fused(int Skv, int variant) { return variant == 2 || (variant == 0 && Skv >= 2048); }
+
+extern "C" long cb200_fa_bwd_scratch_floats_v(int B, int Sq, int Skv, int H, int variant) {
+  const long S_pad = (Sq + 63) / 64 * 64;
+  long n = 2L * B * H * S_pad;
+  if (fa_bwd_use_fused(Skv, variant)) n += (long)B * Sq * H * 128;
+  return n;
+}
+
 extern "C" int cb200_fa_bwd_scratch_floats(int B, int Sq, int H) {
   const int S_pad = (Sq + 63) / 64 * 64;
   return 2 * B * H * S_pad;
 }
 
 // q, o, do, dq [B,Sq,H,128]; k, v, dk, dv [B,Skv,H,128]; lse [B,H,Sq]; scratch: cb200_fa_bwd_scratch_floats floats
+extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
+                              void* dk, void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int variant, int* err,
+                              cudaStream_t st);
+
 extern "C" int cb200_fa_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
                             void* dk, void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int* err,
                             cudaStream_t st) {
+  return cb200_fa_bwd_v(d_o, q, k, v, o, lse, dq, dk, dv, scratch, B, Sq, Skv, H, scale, 1, err, st);
+}
+
+// scratch: cb200_fa_bwd_scratch_floats_v(B, Sq, Skv, H, variant) floats
+extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
+                              void* dk, void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int variant, int* err,
+                              cudaStream_t st) {
   using namespace fab;
   const int S_pad = (Sq + 63) / 64 * 64;
   float* delta = scratch;
@@ -564,6 +589,9 @@ extern "C" int cb200_fa_bwd(const void* d_o, const void* q, const void* k, const
     const long rows = (long)B * H * S_pad;
     fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, lse, delta, lse2, B, Sq, H, S_pad);
   }
+  if (fa_bwd_use_fused(Skv, variant))
+    return cb200_fa_bwd_fused_main(d_o, q, k, v, lse2, delta, scratch + 2 * (size_t)B * H * S_pad, dq, dk, dv, B, Sq, Skv, H, S_pad, scale,
+                                   err, st);
   auto make = [&](CUtensorMap* m, const void* p, int S, int box_rows) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)HD * 2, (uint64_t)H * HD * 2, (uint64_t)S * H * HD * 2};

@@ -61,6 +61,9 @@ void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S
 extern "C" {
 // fa_bwd.cu
 int cb200_fa_bwd_scratch_floats(int B, int Sq, int H);
+long cb200_fa_bwd_scratch_floats_v(int B, int Sq, int Skv, int H, int variant);
+int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq, void* dk,
+                   void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int variant, int* err, cudaStream_t st);
 int cb200_fa_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq, void* dk,
                  void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st);
 }

@@ -199,8 +199,9 @@ def test_flash_attention_large_scores_rescale():
     _close(o, orf, 3e-2, 3e-2, "o")
 
 
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("B,Sq,Skv,H", [(1, 256, 128, 2), (2, 512, 384, 3), (1, 1000, 999, 2), (1, 300, 15, 2), (1, 2048, 2048, 2)])
-def test_flash_attention_bwd(B, Sq, Skv, H):
+def test_flash_attention_bwd(B, Sq, Skv, H, variant):
     torch.manual_seed(12)
     q = torch.randn(B, Sq, H, 128, device=DEV).bfloat16()
     k = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
@@ -208,7 +209,7 @@ def test_flash_attention_bwd(B, Sq, Skv, H):
     do = torch.randn(B, Sq, H, 128, device=DEV).bfloat16()
     scale = 1.0 / math.sqrt(128)
     o, lse = _ops().fa_fwd(q, k, v, scale)
-    dq, dk, dv = _ops().fa_bwd(do, q, k, v, o, lse, scale)
+    dq, dk, dv = _ops().fa_bwd_variant(do, q, k, v, o, lse, scale, variant)
     _no_kernel_error()
     qr, kr, vr = (t.float().requires_grad_(True) for t in (q, k, v))
     orf, _ = ref.attention(qr, kr, vr, scale)
