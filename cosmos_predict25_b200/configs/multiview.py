@@ -117,7 +117,7 @@ cs.store(group="experiment", package="_global_", name="tiny_multiview_cpu", node
     defaults=["_self_"],
     job=dict(group="tests", name="tiny_multiview_cpu"),
     model=_mv_model("tiny_multiview", tokenizer="dummy_tokenizer", precision="float32", state_t=2, tokens_per_view=8,
-                    sharding_transport="nccl"),
+                    resolution="tiny", sharding_transport="nccl"),
     dataloader_train=L(build_dataloader)(dataset=L(MockMultiviewLatentDataset)(n_views=3, state_t=2, height=8, width=8, text_dim=256,
                                                                                text_len=8, length=16), batch_size=1, num_workers=0),
     optimizer=dict(lr=1e-3),

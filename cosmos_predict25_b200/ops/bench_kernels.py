@@ -125,6 +125,10 @@ def main():
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 1), iters=3, warmup=1), 2.5 * fl)
             add("fa_bwd tcgen05 single-pass (5 GEMM)", f"S={N} H={heads}",
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 2), iters=3, warmup=1), 2.5 * fl)
+            if args.variants:
+                for var, what in ((11, "no red"), (13, "no dQ read-back"), (17, "no dQ MMA / read-back")):
+                    add(f"fa_bwd single-pass experiment: {what} (results invalid)", f"S={N} H={heads}",
+                        time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, var), iters=3, warmup=1), 2.5 * fl)
         qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
         og = F_ops._sdpa(qg, kg, vg, scale)
         dog = torch.randn_like(og)

@@ -549,10 +549,11 @@ using namespace cb200;
 
 extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const void* k, const void* v, const float* lse2,
                                        const float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Skv, int H,
-                                       int S_pad, float scale, int* err, cudaStream_t st);
+                                       int S_pad, float scale, int dbg, int* err, cudaStream_t st);
 
+// variant 10 + bits: timing experiments on the single-pass kernel with parts of the dQ path switched off (results wrong)
 // variant 0: choose by problem size; 1: two deterministic kernels (7 GEMMs); 2: single pass with fp32 dQ accumulation (5 GEMMs)
-static bool fa_bwd_use_fused(int Skv, int variant) { return variant == 2 || (variant == 0 && Skv >= 2048); }
+static bool fa_bwd_use_fused(int Skv, int variant) { return variant == 2 || variant >= 10 || (variant == 0 && Skv >= 2048); }
 
 extern "C" long cb200_fa_bwd_scratch_floats_v(int B, int Sq, int Skv, int H, int variant) {
   const long S_pad = (Sq + 63) / 64 * 64;
@@ -591,7 +592,7 @@ extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, con
   }
   if (fa_bwd_use_fused(Skv, variant))
     return cb200_fa_bwd_fused_main(d_o, q, k, v, lse2, delta, scratch + 2 * (size_t)B * H * S_pad, dq, dk, dv, B, Sq, Skv, H, S_pad, scale,
-                                   err, st);
+                                   variant >= 10 ? variant - 10 : 0, err, st);
   auto make = [&](CUtensorMap* m, const void* p, int S, int box_rows) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)HD * 2, (uint64_t)H * HD * 2, (uint64_t)S * H * HD * 2};

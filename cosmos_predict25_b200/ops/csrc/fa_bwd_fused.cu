@@ -55,7 +55,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dQacc,
                     bf16* __restrict__ dK, bf16* __restrict__ dV, int Sq, int Skv, int H, int Sq_pad, float scale,
-                    int* __restrict__ err) {
+                    int dbg, int* __restrict__ err) {
   using namespace faf;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -200,7 +200,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t par = (i >> 1) & 1;
         if (!mbar_wait(&p_ready[u], par, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        issue_dq(u);
+        if (!(dbg & 4)) issue_dq(u);
         umma_commit(&dq_full[u]);
         issue_dv_dk(u, qs[u], ds[u], i > 0);
         umma_commit(&r_empty[qs[u]]);
@@ -286,14 +286,16 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!mbar_wait(&dq_full[u], par, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t a[32], c2[32];
-      tmem_ld32(tST + 32, a);
-      tmem_ld32(tST + 64, c2);
-      tmem_ld_wait();
+      if (!(dbg & 2)) {
+        tmem_ld32(tST + 32, a);
+        tmem_ld32(tST + 64, c2);
+        tmem_ld_wait();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_free[u]);
       float* qrow = dQacc + (((size_t)b * Sq + (size_t)i * 64) * H + h) * HD + row;
-      const int n_valid = min(64, Sq - i * 64);
+      const int n_valid = (dbg & 3) ? 0 : min(64, Sq - i * 64);
       const size_t qstride = (size_t)H * HD;
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -367,7 +369,7 @@ using namespace cb200;
 // dq_acc: B*Sq*H*128 floats of scratch, zeroed here.
 extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const void* k, const void* v, const float* lse2,
                                        const float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Skv, int H,
-                                       int S_pad, float scale, int* err, cudaStream_t st) {
+                                       int S_pad, float scale, int dbg, int* err, cudaStream_t st) {
   using namespace faf;
   auto make = [&](CUtensorMap* m, const void* p, int S, int box_rows) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
@@ -389,7 +391,7 @@ extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const voi
   if (e != cudaSuccess) return 400 + (int)e;
   dim3 grid((Skv + 127) / 128, H, B);
   fa_bwd_fused_kernel<<<grid, kThreads, kSmem, st>>>(q64, do64, k128, v128, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, Sq, Skv, H, S_pad,
-                                                     scale, err);
+                                                     scale, dbg, err);
   const long n8 = (long)(n / 8);
   fa_bwd_dq_convert_kernel<<<(unsigned)std::min<long>((n8 + 255) / 256, 148 * 16), 256, 0, st>>>(dq_acc, (bf16*)dq, n8, scale);
   return (int)cudaGetLastError();

@@ -100,3 +100,46 @@ def test_view_subsampling():
     out = m.with_latent_view_indices(b)
     assert out["latents"].shape[2] == 4 and out["t5_text_embeddings"].shape[1] == 16
     assert out["ai_caption"] == ["a -- b"] and out["latent_view_indices_B_T"].tolist() == [[0, 0, 1, 1]]
+
+
+def test_multiview_public_api_end_to_end(tmp_path):
+    """experiment name -> model -> local per-camera files -> sample -> mp4, with a stand-in decoder (no codec needed)."""
+    import numpy as np
+
+    from cosmos_predict25_b200.multiview import MultiviewInference
+    from cosmos_predict25_b200.multiview_config import MultiviewInferenceArguments, MultiviewSetupArguments
+    from cosmos_predict25_b200.pipeline.multiview import Vid2VidInference
+
+    pipe = Vid2VidInference("tiny_multiview_cpu", None, device=torch.device("cpu"))
+    assert type(pipe.model).__name__ == "MultiviewVid2VidModelRectifiedFlow"
+    files = {}
+    for cam in ("front_wide", "cross_right", "rear_right"):
+        p = tmp_path / f"{cam}.mp4"
+        p.write_bytes(cam.encode())
+        files[cam] = {"video_path": str(p)}
+    setup = MultiviewSetupArguments(output_dir=tmp_path / "out", experiment="tiny_multiview_cpu", checkpoint_path="none",
+                                    context_parallel_size=1)
+    args = MultiviewInferenceArguments(prompt="a drive through town", n_views=3, num_input_frames=1, num_steps=2, guidance=3, **files)
+
+    def fake_decode(raw: bytes):
+        rng = np.random.default_rng(len(raw))
+        return rng.integers(0, 255, size=(12, 36, 64, 3), dtype=np.uint8), 30.0
+
+    torch.manual_seed(0)
+    grad_was = torch.is_grad_enabled()
+    try:
+        outs = MultiviewInference(setup, pipe=pipe).generate(args, decode_fn=fake_decode)
+    finally:
+        torch.set_grad_enabled(grad_was)
+    assert len(outs) == 1 and (tmp_path / "out" / "config.yaml").exists()
+
+
+def test_multiview_experiments_registered():
+    from cosmos_predict25_b200.configs import multiview as cfgmod
+    from cosmos_predict25_b200.utils.checkpoint_db import get_checkpoint_by_uuid
+    from cosmos_predict25_b200.utils.config import override
+    ck = get_checkpoint_by_uuid("6b9d7548-33bb-4517-b5e8-60caf47edba7")
+    cfg = override(cfgmod.make_config(), ["--", f"experiment={ck.experiment}"])
+    assert cfg["model"]["config"]["state_t"] == 8
+    assert cfg["model"]["config"]["net"]["rope_enable_fps_modulation"] is False
+    assert cfg["model_parallel"]["context_parallel_size"] == 8
