@@ -59,3 +59,38 @@ def test_wan_rf_model_training_and_sampling():
     loss.backward()
     x = m.generate_samples_from_batch(dict(batch), guidance=2.0, num_steps=2)
     assert x.shape == (1, 16, 2, 8, 8) and torch.isfinite(x).all()
+
+
+def test_clip_vision_tower_and_i2v_embedder():
+    from cosmos_predict25_b200.models import wan_encoders as we
+    torch.manual_seed(0)
+    clip = we.XLMRobertaCLIP(embed_dim=32, image_size=28, patch_size=14, vision_dim=1280, vision_heads=4, vision_layers=2,
+                             text_dim=32, text_heads=4, text_layers=1, vocab_size=100, max_text_len=20)
+    assert "visual.transformer.0.attn.to_qkv.weight" in clip.state_dict() and "textual.blocks.0.attn.q.weight" in clip.state_dict()
+    cm = we.CLIPModel(dtype=torch.float32, model=clip)
+    tok = cm.visual(torch.rand(2, 3, 40, 56) * 2 - 1)
+    assert tok.shape == (2, 5, 1280)
+    img, txt = clip(torch.randn(1, 3, 28, 28), torch.tensor([[0, 5, 6, 2, 1, 1]]))
+    assert img.shape == (1, 32) and txt.shape == (1, 32)
+    emb = we.Wan2pt1CLIPEmb(num_token=5, dtype="float32", clip_model=cm)
+    out = emb(None, torch.rand(1, 3, 5, 28, 28), torch.randn(1, 16, 2, 4, 4))
+    assert out["y_B_C_T_H_W"].shape == (1, 20, 2, 4, 4) and out["y_B_C_T_H_W"][0, :4, 0].min() == 1 and out["y_B_C_T_H_W"][0, :4, 1].max() == 0
+    assert out["frame_cond_crossattn_emb_B_L_D"].shape == (1, 5, 1280)
+    out_img = emb(torch.rand(1, 3, 1, 28, 28), None, torch.randn(1, 16, 1, 4, 4))
+    assert out_img["frame_cond_crossattn_emb_B_L_D"].abs().sum() == 0
+
+
+def test_umt5_encoder_masks_padding():
+    from cosmos_predict25_b200.models import wan_encoders as we
+    torch.manual_seed(0)
+    enc = we.UMT5Encoder(vocab=50, dim=32, dim_attn=32, dim_ffn=64, num_heads=4, num_layers=2, num_buckets=8)
+    ids = torch.tensor([[3, 4, 5, 0, 0, 0]])
+    mask = torch.tensor([[1, 1, 1, 0, 0, 0]])
+    a = enc(ids, mask)
+    ids2 = ids.clone()
+    ids2[0, 4] = 7                       # a padded position must not influence valid positions
+    b = enc(ids2, mask)
+    assert torch.allclose(a[:, :3], b[:, :3], atol=1e-6)
+    rel = we.T5RelativeEmbedding(8, 4)
+    assert rel(5, 5).shape == (1, 4, 5, 5)
+    assert "blocks.0.pos_embedding.embedding.weight" in enc.state_dict() and "blocks.1.ffn.gate.0.weight" in enc.state_dict()
