@@ -92,16 +92,17 @@ class QwenAttention(nn.Module):
 
     def forward(self, x, cos, sin, mask):
         B, S, _ = x.shape
-        q = self.q_proj(x).view(B, S, self.h, self.hd).transpose(1, 2)
-        k = self.k_proj(x).view(B, S, self.kv, self.hd).transpose(1, 2)
-        v = self.v_proj(x).view(B, S, self.kv, self.hd).transpose(1, 2)
+        # head counts are inferred from the projection width so that column-sharded (tensor-parallel) projections work
+        q = self.q_proj(x).view(B, S, -1, self.hd).transpose(1, 2)
+        k = self.k_proj(x).view(B, S, -1, self.hd).transpose(1, 2)
+        v = self.v_proj(x).view(B, S, -1, self.hd).transpose(1, 2)
         q = q * cos + _rotate_half(q) * sin
         k = k * cos + _rotate_half(k) * sin
         rep = self.h // self.kv
         k = k.repeat_interleave(rep, dim=1)
         v = v.repeat_interleave(rep, dim=1)
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, is_causal=mask is None)
-        return self.o_proj(o.transpose(1, 2).reshape(B, S, self.h * self.hd))
+        return self.o_proj(o.transpose(1, 2).reshape(B, S, -1))
 
 
 class QwenMLP(nn.Module):

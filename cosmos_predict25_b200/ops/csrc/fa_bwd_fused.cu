@@ -15,7 +15,8 @@
 // one 128-byte line). A small kernel converts that buffer to bf16 at the end.
 //
 // TMEM (512 columns): buffer u in {0,1} at u*128: S^T fp32 [0,64), dP^T fp32 [64,128); after the element-wise
-// pass P^T bf16 sits in [0,32), dS^T bf16 in [96,128) and the freed middle [32,96) receives dQ^T;
+// pass P^T bf16 sits in [0,32), dS^T bf16 in [32,64) and the freed half [64,128) receives dQ^T, so the next S^T can be
+// issued without waiting for the dQ^T read-back (only the next dP^T waits for it);
 // dV = [256,384), dK = [384,512). Two buffers ping-pong between the MMA thread and two 4-warp groups.
 //
 // All waits are bounded and report through `err`.
@@ -143,14 +144,17 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, 128, 0, 1);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 64, 1, 1);
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      auto issue_st_dpt = [&](int u, int q_slot, int do_slot) {
-        const uint32_t qa = smem_u32(sR + q_slot * kSmall), da = smem_u32(sR + do_slot * kSmall);
+      auto issue_st = [&](int u, int q_slot) {
+        const uint32_t qa = smem_u32(sR + q_slot * kSmall);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offa = (kk >> 2) * (kBig / 2) + (kk & 3) * 32, offb = (kk >> 2) * (kSmall / 2) + (kk & 3) * 32;
           umma_ss(tmem_base + u * 128, umma_desc_sw128(ka + offa, 16, 1024), umma_desc_sw128(qa + offb, 16, 1024), idesc_s,
                   kk > 0 ? 1u : 0u);
         }
+      };
+      auto issue_dpt = [&](int u, int do_slot) {
+        const uint32_t da = smem_u32(sR + do_slot * kSmall);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offa = (kk >> 2) * (kBig / 2) + (kk & 3) * 32, offb = (kk >> 2) * (kSmall / 2) + (kk & 3) * 32;
@@ -164,7 +168,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t dsa = smem_u32(sDS + u * kSmall);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tmem_base + u * 128 + 32, umma_desc_sw128(ka + kk * 2048, kBig / 2, 1024),
+          umma_ss(tmem_base + u * 128 + 64, umma_desc_sw128(ka + kk * 2048, kBig / 2, 1024),
                   umma_desc_sw128(dsa + kk * 2048, kSmall / 2, 1024), idesc_dq, kk > 0 ? 1u : 0u);
       };
       auto issue_dv_dk = [&](int u, int q_slot, int do_slot, bool accumulate) {
@@ -175,7 +179,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                   (accumulate || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem_base + 384, tmem_base + u * 128 + 96 + kk * 8, umma_desc_sw128(qa + kk * 2048, kSmall / 2, 1024), idesc_acc,
+          umma_ts(tmem_base + 384, tmem_base + u * 128 + 32 + kk * 8, umma_desc_sw128(qa + kk * 2048, kSmall / 2, 1024), idesc_acc,
                   (accumulate || kk > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag);
@@ -192,7 +196,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         ok = take(qs[u]) && take(ds[u]);
         if (!ok) break;
         tc_fence_after();
-        issue_st_dpt(u, qs[u], ds[u]);
+        issue_st(u, qs[u]);
+        issue_dpt(u, ds[u]);
         umma_commit(&s_full[u]);
       }
       for (int i = 0; i < n_q && ok; ++i) {
@@ -208,10 +213,13 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (i + 2 < n_q) {
           ok = take(qs[u]) && take(ds[u]);
           if (!ok) break;
-          // the next scores overwrite the columns that hold dQ^T of this sub-tile
+          // S^T only overwrites P^T / dS^T, which the MMAs just issued consume in order: no wait. dP^T overwrites the
+          // columns that hold dQ^T of this sub-tile, so it waits for the read-back (hidden behind dV / dK / S^T).
+          tc_fence_after();
+          issue_st(u, qs[u]);
           if (!mbar_wait(&dq_free[u], par, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          issue_st_dpt(u, qs[u], ds[u]);
+          issue_dpt(u, ds[u]);
           umma_commit(&s_full[u]);
         }
       }
@@ -265,11 +273,11 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           pd[c][g * 2 + 1] = *reinterpret_cast<uint32_t*>(&b1);
         }
       }
-      // every fp32 column of this row has been read: P^T -> [0,32), dS^T -> [96,128) and the shared-memory tile
+      // every fp32 column of this row has been read: P^T -> [0,32), dS^T -> [32,64) and the shared-memory tile
       tmem_st16(tST, pp[0]);
       tmem_st16(tST + 16, pp[1]);
-      tmem_st16(tST + 96, pd[0]);
-      tmem_st16(tST + 112, pd[1]);
+      tmem_st16(tST + 32, pd[0]);
+      tmem_st16(tST + 48, pd[1]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {  // 16-byte chunk j = queries 8j..8j+7, 128-byte swizzle
         const uint4 v = make_uint4(pd[j >> 2][(j & 3) * 4], pd[j >> 2][(j & 3) * 4 + 1], pd[j >> 2][(j & 3) * 4 + 2],
@@ -287,8 +295,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_after();
       uint32_t a[32], c2[32];
       if (!(dbg & 2)) {
-        tmem_ld32(tST + 32, a);
-        tmem_ld32(tST + 64, c2);
+        tmem_ld32(tST + 64, a);
+        tmem_ld32(tST + 96, c2);
         tmem_ld_wait();
       }
       tc_fence_before();

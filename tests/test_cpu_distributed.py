@@ -226,3 +226,52 @@ def _worker_nobarrier(rank, world, port, fn_name, tmp):
     except Exception:
         with open(os.path.join(tmp, f"err{rank}"), "w") as f:
             f.write(traceback.format_exc())
+
+
+# ------------------------------------------------------------------------------------------------
+def _tp_qwen(rank, world, tmp, sequence_parallel):
+    from cosmos_predict25_b200.models.text_encoder import QwenConfig, QwenLanguageModel
+    from cosmos_predict25_b200.parallel.parallel_dims import ParallelDims
+    from cosmos_predict25_b200.parallel.parallelize_qwen import parallelize_qwen
+    torch.manual_seed(0)
+    cfg = QwenConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2)
+    ref = QwenLanguageModel(cfg)
+    tp_model = QwenLanguageModel(cfg)
+    tp_model.load_state_dict(ref.state_dict())
+    dims = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, world_size=world)
+    mesh = dims.build_mesh("cpu")
+    parallelize_qwen(tp_model, mesh, dims, sequence_parallel=sequence_parallel)
+    from torch.distributed.tensor import DTensor
+    assert isinstance(tp_model.layers[0].self_attn.q_proj.weight, DTensor)
+    assert tp_model.layers[0].self_attn.q_proj.weight.to_local().shape[0] == 32 // world
+    ids = torch.randint(0, 64, (2, 8), generator=torch.Generator().manual_seed(1))
+    want = ref(ids)[-1]
+    got = tp_model(ids)[-1]
+    if isinstance(got, DTensor):
+        got = got.full_tensor()
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("sequence_parallel", [False])
+def test_tensor_parallel_qwen_matches_single_rank(sequence_parallel):
+    run_distributed("_tp_qwen", 2, sequence_parallel=sequence_parallel)
+
+
+def test_parallel_dims_layout():
+    from cosmos_predict25_b200.parallel.parallel_dims import ParallelDims
+    d = ParallelDims(dp_replicate=2, dp_shard=-1, cp=2, tp=2, pp=1, world_size=32)
+    assert d.dp_shard == 4 and d.mesh_shape() == ([2, 4, 2, 2], ["dp_replicate", "dp_shard", "cp", "tp"])
+    assert d.flattened_views() == {"dp": ["dp_replicate", "dp_shard"], "dp_shard_cp": ["dp_shard", "cp"], "dp_cp": ["dp_replicate", "dp_shard", "cp"]}
+    assert d.coordinates(0) == {"tp": 0, "cp": 0, "dp_shard": 0, "dp_replicate": 0, "pp": 0}
+    assert d.coordinates(7) == {"tp": 1, "cp": 1, "dp_shard": 1, "dp_replicate": 0, "pp": 0}
+    assert d.non_data_parallel_size == 4 and d.dp_enabled and d.tp_enabled and not d.pp_enabled
+    fixed = ParallelDims(dp_replicate=3, dp_shard=2, cp=1, tp=2, pp=1, world_size=8)     # 3*2*2 != 8 -> dp_replicate recomputed
+    assert fixed.dp_replicate == 2
+    with pytest.raises(AssertionError):
+        ParallelDims(dp_replicate=1, dp_shard=3, cp=1, tp=1, pp=1, world_size=8)
+    from cosmos_predict25_b200.utils.train_metrics import dit_flop_per_sample, get_num_flop_per_token, get_peak_flops, mfu
+    assert get_peak_flops("NVIDIA B200") == 2.25e15 and get_peak_flops("NVIDIA H100 80GB HBM3") == 989e12
+    f = dit_flop_per_sample(2048, 28, 84480, training=False)
+    assert 1.7e15 < f < 2.2e15                                    # ~1.9 PFLOP per 2B forward at 84,480 tokens
+    assert abs(mfu(f * 3, 8.0, 1, 2.25e15) - f * 3 / 8.0 / 2.25e15) < 1e-12
+    assert get_num_flop_per_token(7_000_000_000, 28, 28, 128, 4096) == 6 * 7_000_000_000 + 12 * 28 * 28 * 128 * 4096
