@@ -125,10 +125,14 @@ def main():
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 1), iters=3, warmup=1), 2.5 * fl)
             add("fa_bwd tcgen05 single-pass (5 GEMM)", f"S={N} H={heads}",
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 2), iters=3, warmup=1), 2.5 * fl)
-            if args.variants:
-                for var, what in ((11, "no red"), (13, "no dQ read-back"), (17, "no dQ MMA / read-back")):
-                    add(f"fa_bwd single-pass experiment: {what} (results invalid)", f"S={N} H={heads}",
-                        time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, var), iters=3, warmup=1), 2.5 * fl)
+        if hasattr(ops, "red_f32_bench"):
+            # L2 reduction rate that bounds the dQ accumulation of the single-pass backward: one head's dQ matrix [S, 128] fp32,
+            # 660 key tiles adding into it = the traffic of one head of the S=84480 problem
+            acc = torch.zeros(N, 128, device=dev)
+            n_ctas = (N + 127) // 128
+            ms = time_ms(lambda: ops.red_f32_bench(acc, n_ctas), iters=3, warmup=1)
+            gb = n_ctas * N * 512 / 1e9
+            add("red.global.add.f32 rate (one head of dQ accumulation)", f"rows={N} ctas={n_ctas}", ms, bytes_=gb * 1e9)
         qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
         og = F_ops._sdpa(qg, kg, vg, scale)
         dog = torch.randn_like(og)

@@ -63,6 +63,13 @@ std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, co
                                           const Tensor& lse, double scale) {
   return fa_bwd_variant(d_o, q, k, v, o, lse, scale, 0);
 }
+// hardware-rate probe: n_ctas CTAs each add 1.0 into every element of acc [rows, 128]
+void red_f32_bench(Tensor acc, int64_t n_ctas) {
+  TORCH_CHECK(acc.is_cuda() && acc.scalar_type() == at::kFloat && acc.is_contiguous() && acc.dim() == 2 && acc.size(1) == 128);
+  c10::cuda::CUDAGuard g(acc.device());
+  const int rc = cb200_red_f32_bench(acc.data_ptr<float>(), (int)acc.size(0), (int)n_ctas, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "red_f32_bench launch failed with code ", rc);
+}
 }  // namespace
 
 void register_attention_ops(torch::Library& m) {
@@ -71,6 +78,7 @@ void register_attention_ops(torch::Library& m) {
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)");
   m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");
   m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)");
+  m.def("red_f32_bench(Tensor(a!) acc, int n_ctas) -> ()");
   m.def("fa_bwd_variant(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, int variant) -> (Tensor, Tensor, Tensor)");
 }
 
@@ -79,4 +87,5 @@ TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
   m.impl("fa_bwd", &fa_bwd);
   m.impl("fa_fwd_variant", &fa_fwd_variant);
   m.impl("fa_bwd_variant", &fa_bwd_variant);
+  m.impl("red_f32_bench", &red_f32_bench);
 }

@@ -48,11 +48,12 @@ __device__ __forceinline__ float ex2b(float x) {
 
 // ------------------------------------------------------------------------------------------------
 // preprocessing: delta[b,h,s] = sum_d dO*O ; lse2 = lse * log2(e); both padded to a multiple of 64 rows
-// (padding: lse2 = +inf so that recomputed probabilities of out-of-range queries are exactly 0)
+// (padding: lse2 = +inf so that recomputed probabilities of out-of-range queries are exactly 0); `sign` = -1 stores both
+// negated, which lets the single-pass kernel use packed fused multiply-adds without negations
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) fa_bwd_prep_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o,
                                                            const float* __restrict__ lse, float* __restrict__ delta,
-                                                           float* __restrict__ lse2, int B, int S, int H, int S_pad) {
+                                                           float* __restrict__ lse2, int B, int S, int H, int S_pad, float sign) {
   const int lane = threadIdx.x & 31;
   const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5);  // over B * H * S_pad
   if (row >= (long)B * H * S_pad) return;
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(256) fa_bwd_prep_kernel(const bf16* __restrict
   if (s >= S) {
     if (lane == 0) {
       delta[row] = 0.f;
-      lse2[row] = INFINITY;
+      lse2[row] = sign * INFINITY;
     }
     return;
   }
@@ -77,8 +78,8 @@ __global__ void __launch_bounds__(256) fa_bwd_prep_kernel(const bf16* __restrict
   float acc = o0.x * d0.x + o0.y * d0.y + o1.x * d1.x + o1.y * d1.y;
   acc = warp_sum(acc);
   if (lane == 0) {
-    delta[row] = acc;
-    lse2[row] = lse[bh * S + s] * 1.4426950408889634f;
+    delta[row] = sign * acc;
+    lse2[row] = sign * lse[bh * S + s] * 1.4426950408889634f;
   }
 }
 
@@ -588,7 +589,8 @@ extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, con
   float* lse2 = scratch + (size_t)B * H * S_pad;
   {
     const long rows = (long)B * H * S_pad;
-    fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, lse, delta, lse2, B, Sq, H, S_pad);
+    fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, lse, delta, lse2, B, Sq, H, S_pad,
+                                                                   fa_bwd_use_fused(Skv, variant) ? -1.f : 1.f);
   }
   if (fa_bwd_use_fused(Skv, variant))
     return cb200_fa_bwd_fused_main(d_o, q, k, v, lse2, delta, scratch + 2 * (size_t)B * H * S_pad, dq, dk, dv, B, Sq, Skv, H, S_pad, scale,

@@ -17,7 +17,8 @@
 // TMEM (512 columns): buffer u in {0,1} at u*128: S^T fp32 [0,64), dP^T fp32 [64,128); after the element-wise
 // pass P^T bf16 sits in [0,32), dS^T bf16 in [32,64) and the freed half [64,128) receives dQ^T, so the next S^T can be
 // issued without waiting for the dQ^T read-back (only the next dP^T waits for it);
-// dV = [256,384), dK = [384,512). Two buffers ping-pong between the MMA thread and two 4-warp groups.
+// dV = [256,384), dK = [384,512). Two buffers ping-pong between the MMA thread and two 8-warp groups (two warps per
+// TMEM lane quarter, 32 query columns each: the element-wise pass is latency-bound, so it is spread over 16 warps).
 //
 // All waits are bounded and report through `err`.
 
@@ -35,8 +36,8 @@ namespace faf {
 constexpr int HD = 128;
 constexpr int kBig = 128 * HD * 2;    // 32 KB
 constexpr int kSmall = 64 * HD * 2;   // 16 KB
-constexpr int kThreads = 320;
-constexpr int kMmaWarp = 9, kTmaWarp = 8;
+constexpr int kThreads = 576;          // 16 element-wise warps + TMA warp + MMA warp
+constexpr int kMmaWarp = 17, kTmaWarp = 16;
 constexpr int kRing = 7;
 constexpr int kStat = 512;            // per ring slot: 64 lse2 + 64 delta floats
 constexpr size_t kSmem = 2 * (size_t)kBig + kRing * (size_t)kSmall + 2 * (size_t)kSmall + kRing * (size_t)kStat + 1024 + 512;
@@ -70,9 +71,9 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* r_full = bars + 1;
   uint64_t* r_empty = r_full + kRing;
   uint64_t* s_full = r_empty + kRing;   // [2] S^T / dP^T written
-  uint64_t* p_ready = s_full + 2;       // [2] P^T / dS^T written (4 warps)
+  uint64_t* p_ready = s_full + 2;       // [2] P^T / dS^T written (8 warps)
   uint64_t* dq_full = p_ready + 2;      // [2] dQ^T written
-  uint64_t* dq_free = dq_full + 2;      // [2] dQ^T read back (4 warps)
+  uint64_t* dq_free = dq_full + 2;      // [2] dQ^T read back (8 warps)
   uint64_t* done = dq_free + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -91,9 +92,9 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 4);
+      mbar_init(&p_ready[i], 8);
       mbar_init(&dq_full[i], 1);
-      mbar_init(&dq_free[i], 4);
+      mbar_init(&dq_free[i], 8);
     }
     mbar_init(done, 1);
     *abort_flag = 0;
@@ -139,7 +140,9 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!ok) { atomicCAS(err, 0, 41); *abort_flag = 1; }
     }
   } else if (warp == kMmaWarp) {
-    if (lane == 0) {
+    {
+      // the whole warp runs this code with identical values; only `leader` issues (see umma_ss_w)
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, 128, 0, 1);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 64, 1, 1);
@@ -149,8 +152,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offa = (kk >> 2) * (kBig / 2) + (kk & 3) * 32, offb = (kk >> 2) * (kSmall / 2) + (kk & 3) * 32;
-          umma_ss(tmem_base + u * 128, umma_desc_sw128(ka + offa, 16, 1024), umma_desc_sw128(qa + offb, 16, 1024), idesc_s,
-                  kk > 0 ? 1u : 0u);
+          umma_ss_w(tmem_base + u * 128, umma_desc_sw128(ka + offa, 16, 1024), umma_desc_sw128(qa + offb, 16, 1024), idesc_s,
+                  kk > 0 ? 1u : 0u, leader);
         }
       };
       auto issue_dpt = [&](int u, int do_slot) {
@@ -158,8 +161,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offa = (kk >> 2) * (kBig / 2) + (kk & 3) * 32, offb = (kk >> 2) * (kSmall / 2) + (kk & 3) * 32;
-          umma_ss(tmem_base + u * 128 + 64, umma_desc_sw128(va + offa, 16, 1024), umma_desc_sw128(da + offb, 16, 1024), idesc_s,
-                  kk > 0 ? 1u : 0u);
+          umma_ss_w(tmem_base + u * 128 + 64, umma_desc_sw128(va + offa, 16, 1024), umma_desc_sw128(da + offb, 16, 1024), idesc_s,
+                  kk > 0 ? 1u : 0u, leader);
         }
       };
       // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: A = K tile read M-major (two 64-wide d chunks, 16 keys per step),
@@ -168,19 +171,19 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t dsa = smem_u32(sDS + u * kSmall);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tmem_base + u * 128 + 64, umma_desc_sw128(ka + kk * 2048, kBig / 2, 1024),
-                  umma_desc_sw128(dsa + kk * 2048, kSmall / 2, 1024), idesc_dq, kk > 0 ? 1u : 0u);
+          umma_ss_w(tmem_base + u * 128 + 64, umma_desc_sw128(ka + kk * 2048, kBig / 2, 1024),
+                  umma_desc_sw128(dsa + kk * 2048, kSmall / 2, 1024), idesc_dq, kk > 0 ? 1u : 0u, leader);
       };
       auto issue_dv_dk = [&](int u, int q_slot, int do_slot, bool accumulate) {
         const uint32_t qa = smem_u32(sR + q_slot * kSmall), da = smem_u32(sR + do_slot * kSmall);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem_base + 256, tmem_base + u * 128 + kk * 8, umma_desc_sw128(da + kk * 2048, kSmall / 2, 1024), idesc_acc,
-                  (accumulate || kk > 0) ? 1u : 0u);
+          umma_ts_w(tmem_base + 256, tmem_base + u * 128 + kk * 8, umma_desc_sw128(da + kk * 2048, kSmall / 2, 1024), idesc_acc,
+                  (accumulate || kk > 0) ? 1u : 0u, leader);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts(tmem_base + 384, tmem_base + u * 128 + 32 + kk * 8, umma_desc_sw128(qa + kk * 2048, kSmall / 2, 1024), idesc_acc,
-                  (accumulate || kk > 0) ? 1u : 0u);
+          umma_ts_w(tmem_base + 384, tmem_base + u * 128 + 32 + kk * 8, umma_desc_sw128(qa + kk * 2048, kSmall / 2, 1024), idesc_acc,
+                  (accumulate || kk > 0) ? 1u : 0u, leader);
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       int slot = 0;
@@ -198,18 +201,18 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tc_fence_after();
         issue_st(u, qs[u]);
         issue_dpt(u, ds[u]);
-        umma_commit(&s_full[u]);
+        umma_commit_w(&s_full[u], leader);
       }
       for (int i = 0; i < n_q && ok; ++i) {
         const int u = i & 1;
         const uint32_t par = (i >> 1) & 1;
         if (!mbar_wait(&p_ready[u], par, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        if (!(dbg & 4)) issue_dq(u);
-        umma_commit(&dq_full[u]);
+        issue_dq(u);
+        umma_commit_w(&dq_full[u], leader);
         issue_dv_dk(u, qs[u], ds[u], i > 0);
-        umma_commit(&r_empty[qs[u]]);
-        umma_commit(&r_empty[ds[u]]);
+        umma_commit_w(&r_empty[qs[u]], leader);
+        umma_commit_w(&r_empty[ds[u]], leader);
         if (i + 2 < n_q) {
           ok = take(qs[u]) && take(ds[u]);
           if (!ok) break;
@@ -220,15 +223,17 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (!mbar_wait(&dq_free[u], par, abort_flag)) { ok = false; break; }
           tc_fence_after();
           issue_dpt(u, ds[u]);
-          umma_commit(&s_full[u]);
+          umma_commit_w(&s_full[u], leader);
         }
       }
-      if (ok) umma_commit(done);
-      if (!ok) { atomicCAS(err, 0, 42); *abort_flag = 1; }
+      if (ok) umma_commit_w(done, leader);
+      if (!ok && lane == 0) { atomicCAS(err, 0, 42); *abort_flag = 1; }
     }
   } else {
     // ------------------------------------------------------------------ element-wise groups
-    const int u = warp >> 2, quarter = warp & 3;
+    // 8 warps per buffer: warp pair (half = 0 / 1) shares a lane quarter and splits the 64 query columns, so a thread
+    // handles one key row x 32 queries (two chunks of 16).
+    const int u = warp >> 3, quarter = warp & 3, half = (warp >> 2) & 1;
     const int row = quarter * 32 + lane;            // key row inside the tile == TMEM lane == d index when draining dQ^T
     const int kv_row = kv_base + row;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
@@ -236,6 +241,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t tDPT = tST + 64;
     uint8_t* ds_row = sDS + u * kSmall + row * 128;
     const int sw = row & 7;
+    const int pair_bar = 1 + u * 4 + quarter;       // named barrier of the two warps that share these TMEM lanes
     bool ok = true;
     for (int i = u; i < n_q; i += 2) {
       const uint32_t par = (i >> 1) & 1;
@@ -244,45 +250,43 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (!mbar_wait(&s_full[u], par, abort_flag)) { ok = false; break; }
       if (!mbar_wait(&r_full[qslot], (n / kRing) & 1, abort_flag)) { ok = false; break; }  // row statistics landed
       tc_fence_after();
-      const float4* l4 = reinterpret_cast<const float4*>(sStat + qslot * (kStat / 4));
+      const float4* l4 = reinterpret_cast<const float4*>(sStat + qslot * (kStat / 4)) + half * 8;
       const float4* d4 = l4 + 16;
-      uint32_t pp[2][16], pd[2][16];
+      uint32_t pp[16], pd[16];
+      const float2 sc2 = make_float2(scale_log2, scale_log2);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tST + c * 32, s);
-        tmem_ld32(tDPT + c * 32, dp);
+        uint32_t s[16], dp[16];
+        tmem_ld16(tST + half * 32 + c * 16, s);
+        tmem_ld16(tDPT + half * 32 + c * 16, dp);
         tmem_ld_wait();
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 lv = l4[c * 8 + g];
-          const float4 dv = d4[c * 8 + g];
-          const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
-          const float de[4] = {dv.x, dv.y, dv.z, dv.w};
-          float p[4], d[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            p[e] = ex2f(fmaf(__uint_as_float(s[g * 4 + e]), scale_log2, -ls[e]));
-            d[e] = p[e] * (__uint_as_float(dp[g * 4 + e]) - de[e]);
-          }
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(p[0], p[1]), a1 = __floats2bfloat162_rn(p[2], p[3]);
-          __nv_bfloat162 b0 = __floats2bfloat162_rn(d[0], d[1]), b1 = __floats2bfloat162_rn(d[2], d[3]);
-          pp[c][g * 2] = *reinterpret_cast<uint32_t*>(&a0);
-          pp[c][g * 2 + 1] = *reinterpret_cast<uint32_t*>(&a1);
-          pd[c][g * 2] = *reinterpret_cast<uint32_t*>(&b0);
-          pd[c][g * 2 + 1] = *reinterpret_cast<uint32_t*>(&b1);
+        for (int g = 0; g < 4; ++g) {
+          const float4 nl = l4[c * 4 + g];   // -lse * log2(e)
+          const float4 nd = d4[c * 4 + g];   // -delta
+          // packed f32x2 arithmetic: the element-wise pass is bound by instruction issue
+          const float2 x0 = fma2(make_float2(__uint_as_float(s[g * 4]), __uint_as_float(s[g * 4 + 1])), sc2, make_float2(nl.x, nl.y));
+          const float2 x1 = fma2(make_float2(__uint_as_float(s[g * 4 + 2]), __uint_as_float(s[g * 4 + 3])), sc2, make_float2(nl.z, nl.w));
+          const float2 p0 = make_float2(ex2f(x0.x), ex2f(x0.y)), p1 = make_float2(ex2f(x1.x), ex2f(x1.y));
+          const float2 t0 = add2(make_float2(__uint_as_float(dp[g * 4]), __uint_as_float(dp[g * 4 + 1])), make_float2(nd.x, nd.y));
+          const float2 t1 = add2(make_float2(__uint_as_float(dp[g * 4 + 2]), __uint_as_float(dp[g * 4 + 3])), make_float2(nd.z, nd.w));
+          const float2 d0 = mul2(p0, t0), d1 = mul2(p1, t1);
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(p0.x, p0.y), a1 = __floats2bfloat162_rn(p1.x, p1.y);
+          __nv_bfloat162 b0 = __floats2bfloat162_rn(d0.x, d0.y), b1 = __floats2bfloat162_rn(d1.x, d1.y);
+          pp[c * 8 + g * 2] = *reinterpret_cast<uint32_t*>(&a0);
+          pp[c * 8 + g * 2 + 1] = *reinterpret_cast<uint32_t*>(&a1);
+          pd[c * 8 + g * 2] = *reinterpret_cast<uint32_t*>(&b0);
+          pd[c * 8 + g * 2 + 1] = *reinterpret_cast<uint32_t*>(&b1);
         }
       }
-      // every fp32 column of this row has been read: P^T -> [0,32), dS^T -> [32,64) and the shared-memory tile
-      tmem_st16(tST, pp[0]);
-      tmem_st16(tST + 16, pp[1]);
-      tmem_st16(tST + 32, pd[0]);
-      tmem_st16(tST + 48, pd[1]);
+      // P^T -> [0,32) and dS^T -> [32,64) overwrite fp32 scores that the partner warp reads: both must have loaded first
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      tmem_st16(tST + half * 16, pp);
+      tmem_st16(tST + 32 + half * 16, pd);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {  // 16-byte chunk j = queries 8j..8j+7, 128-byte swizzle
-        const uint4 v = make_uint4(pd[j >> 2][(j & 3) * 4], pd[j >> 2][(j & 3) * 4 + 1], pd[j >> 2][(j & 3) * 4 + 2],
-                                   pd[j >> 2][(j & 3) * 4 + 3]);
-        *reinterpret_cast<uint4*>(ds_row + ((j ^ sw) << 4)) = v;
+      for (int j = 0; j < 4; ++j) {  // 16-byte chunk (half*4 + j) = queries half*32 + 8j .. +7, 128-byte swizzle
+        const uint4 v = make_uint4(pd[j * 4], pd[j * 4 + 1], pd[j * 4 + 2], pd[j * 4 + 3]);
+        *reinterpret_cast<uint4*>(ds_row + (((half * 4 + j) ^ sw) << 4)) = v;
       }
       fence_proxy_async();
       tmem_st_wait();
@@ -290,38 +294,34 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[u]);
 
-      // ---- read dQ^T of this sub-tile back (lane = d) and add it into the fp32 dQ buffer
+      // ---- read this warp's half of dQ^T back (lane = d) and add it into the fp32 dQ buffer
       if (!mbar_wait(&dq_full[u], par, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      uint32_t a[32], c2[32];
-      if (!(dbg & 2)) {
-        tmem_ld32(tST + 64, a);
-        tmem_ld32(tST + 96, c2);
-        tmem_ld_wait();
-      }
+      uint32_t a[32];
+      tmem_ld32(tST + 64 + half * 32, a);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_free[u]);
-      float* qrow = dQacc + (((size_t)b * Sq + (size_t)i * 64) * H + h) * HD + row;
-      const int n_valid = (dbg & 3) ? 0 : min(64, Sq - i * 64);
-      const size_t qstride = (size_t)H * HD;
+      const int q0 = i * 64 + half * 32;
+      // head-major accumulator [B, H, Sq, 128]: consecutive queries are 512 bytes apart, so every reduction below is one
+      // instruction with an immediate offset from a single base pointer
+      float* qrow = dQacc + (bh * Sq + (size_t)q0) * HD + row;
+      const int n_valid = min(32, Sq - q0);
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (j < n_valid) red_add_f32(qrow + j * qstride, __uint_as_float(a[j]));
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j + 32 < n_valid) red_add_f32(qrow + (j + 32) * qstride, __uint_as_float(c2[j]));
+        if (j < n_valid) red_add_f32(qrow + j * HD, __uint_as_float(a[j]));
     }
     if (ok) ok = mbar_wait(done, 0, abort_flag);
     if (ok) {
       tc_fence_after();
-      // warps 0-3 write dV, warps 4-7 write dK (scaled)
+      // warps 0-7 write dV, warps 8-15 write dK (scaled); the two warps of a lane quarter take 64 columns each
       const uint32_t tAcc = tmem_base + 256 + u * 128 + lane_off;
       const float mul = (u == 0) ? 1.f : scale;
       bf16* base = (u == 0) ? dV : dK;
       bf16* orow = base + (((size_t)b * Skv + kv_row) * H + h) * HD;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t o[32];
         tmem_ld32(tAcc + c * 32, o);
         tmem_ld_wait();
@@ -355,16 +355,25 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
 }
 
-// dq = bf16(acc * scale)
-__global__ void __launch_bounds__(256) fa_bwd_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, long n8, float scale) {
+// dq[b, s, h, :] = bf16(acc[b, h, s, :] * scale)
+__global__ void __launch_bounds__(256) fa_bwd_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int B, int S, int H,
+                                                                 float scale) {
+  const long n8 = (long)B * S * H * 16;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
-    const float4 a = reinterpret_cast<const float4*>(acc)[2 * i], c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+    const int c = (int)(i & 15);
+    const long row = i >> 4;             // over (b, s, h)
+    const int h = (int)(row % H);
+    const long bs = row / H;
+    const int s_ = (int)(bs % S);
+    const long b = bs / S;
+    const float4* src = reinterpret_cast<const float4*>(acc + (((size_t)b * H + h) * S + s_) * 128 + c * 8);
+    const float4 a = src[0], e = src[1];
     uint4 o;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
     o2[0] = __floats2bfloat162_rn(a.x * scale, a.y * scale);
     o2[1] = __floats2bfloat162_rn(a.z * scale, a.w * scale);
-    o2[2] = __floats2bfloat162_rn(c.x * scale, c.y * scale);
-    o2[3] = __floats2bfloat162_rn(c.z * scale, c.w * scale);
+    o2[2] = __floats2bfloat162_rn(e.x * scale, e.y * scale);
+    o2[3] = __floats2bfloat162_rn(e.z * scale, e.w * scale);
     reinterpret_cast<uint4*>(dq)[i] = o;
   }
 }
@@ -401,6 +410,6 @@ extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const voi
   fa_bwd_fused_kernel<<<grid, kThreads, kSmem, st>>>(q64, do64, k128, v128, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, Sq, Skv, H, S_pad,
                                                      scale, dbg, err);
   const long n8 = (long)(n / 8);
-  fa_bwd_dq_convert_kernel<<<(unsigned)std::min<long>((n8 + 255) / 256, 148 * 16), 256, 0, st>>>(dq_acc, (bf16*)dq, n8, scale);
+  fa_bwd_dq_convert_kernel<<<(unsigned)std::min<long>((n8 + 255) / 256, 148 * 16), 256, 0, st>>>(dq_acc, (bf16*)dq, B, Sq, H, scale);
   return (int)cudaGetLastError();
 }

@@ -59,6 +59,9 @@ void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S
 }
 
 extern "C" {
+// microbench.cu
+int cb200_red_f32_bench(float* acc, int rows, int n_ctas, cudaStream_t st);
+
 // fa_bwd.cu
 int cb200_fa_bwd_scratch_floats(int B, int Sq, int H);
 long cb200_fa_bwd_scratch_floats_v(int B, int Sq, int Skv, int H, int variant);
