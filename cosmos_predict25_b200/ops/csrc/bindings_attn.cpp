@@ -63,6 +63,14 @@ std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, co
                                           const Tensor& lse, double scale) {
   return fa_bwd_variant(d_o, q, k, v, o, lse, scale, 0);
 }
+// event trace (SM clocks, [256 sub-tiles, 8 events]) of CTA 0 of the single-pass backward; for performance analysis
+Tensor fa_bwd_fused_trace(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse, double scale) {
+  Tensor tr = at::zeros({256, 8}, q.options().dtype(at::kLong));
+  cb200_fa_bwd_fused_set_trace(reinterpret_cast<long long*>(tr.data_ptr<int64_t>()));
+  fa_bwd_variant(d_o, q, k, v, o, lse, scale, 2);
+  cb200_fa_bwd_fused_set_trace(nullptr);
+  return tr;
+}
 // hardware-rate probe: n_ctas CTAs each add 1.0 into every element of acc [rows, 128]
 void red_f32_bench(Tensor acc, int64_t n_ctas) {
   TORCH_CHECK(acc.is_cuda() && acc.scalar_type() == at::kFloat && acc.is_contiguous() && acc.dim() == 2 && acc.size(1) == 128);
@@ -78,6 +86,7 @@ void register_attention_ops(torch::Library& m) {
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)");
   m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");
   m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)");
+  m.def("fa_bwd_fused_trace(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> Tensor");
   m.def("red_f32_bench(Tensor(a!) acc, int n_ctas) -> ()");
   m.def("fa_bwd_variant(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, int variant) -> (Tensor, Tensor, Tensor)");
 }
@@ -88,4 +97,5 @@ TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
   m.impl("fa_fwd_variant", &fa_fwd_variant);
   m.impl("fa_bwd_variant", &fa_bwd_variant);
   m.impl("red_f32_bench", &red_f32_bench);
+  m.impl("fa_bwd_fused_trace", &fa_bwd_fused_trace);
 }

@@ -57,8 +57,11 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dQacc,
                     bf16* __restrict__ dK, bf16* __restrict__ dV, int Sq, int Skv, int H, int Sq_pad, float scale,
-                    int dbg, int* __restrict__ err) {
+                    long long* __restrict__ trace, int* __restrict__ err) {
   using namespace faf;
+  // optional event trace of CTA (0,0,0): trace[i*8 + k] = SM clock at event k of sub-tile i (i < 256); see the call sites
+  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#define FAF_TRACE(i_, k_) do { if (tracing && (i_) < 256) trace[(i_) * 8 + (k_)] = clock64(); } while (0)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -78,7 +81,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the shuffle makes the warp index (and every role branch below) provably warp-uniform for the compiler
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int h = blockIdx.y, b = blockIdx.z;
   const int kv_base = blockIdx.x * 128;
   const int n_q = (Sq + 63) / 64;
@@ -142,54 +146,61 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp == kMmaWarp) {
     {
       // the whole warp runs this code with identical values; only `leader` issues (see umma_ss_w)
-      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      // votes keep the loop conditions warp-uniform
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)); };
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, 128, 0, 1);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 64, 1, 1);
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      // Base descriptors are built once; an operand slice is the base plus a constant added to the address field (16-byte
+      // units, no carry out of the field because shared memory is smaller than 256 KB).
+      const uint64_t dK_km = umma_desc_sw128(smem_u32(sK), 16, 1024);            // K  as K-major A   (S^T)
+      const uint64_t dV_km = umma_desc_sw128(smem_u32(sV), 16, 1024);            // V  as K-major A   (dP^T)
+      const uint64_t dK_mn = umma_desc_sw128(smem_u32(sK), kBig / 2, 1024);      // K^T as M-major A  (dQ^T)
+      const uint64_t dR_km = umma_desc_sw128(smem_u32(sR), 16, 1024);            // ring slot as K-major B  (Q in S^T, dO in dP^T)
+      const uint64_t dR_mn = umma_desc_sw128(smem_u32(sR), kSmall / 2, 1024);    // ring slot as N-major B  (dO in dV, Q in dK)
+      const uint64_t dDS_mn = umma_desc_sw128(smem_u32(sDS), kSmall / 2, 1024);  // dS^T tile as N-major B  (dQ^T)
       auto issue_st = [&](int u, int q_slot) {
-        const uint32_t qa = smem_u32(sR + q_slot * kSmall);
+        const uint64_t bq = dR_km + (uint64_t)(q_slot * (kSmall >> 4));
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offa = (kk >> 2) * (kBig / 2) + (kk & 3) * 32, offb = (kk >> 2) * (kSmall / 2) + (kk & 3) * 32;
-          umma_ss_w(tmem_base + u * 128, umma_desc_sw128(ka + offa, 16, 1024), umma_desc_sw128(qa + offb, 16, 1024), idesc_s,
-                  kk > 0 ? 1u : 0u, leader);
+          const uint32_t offa = ((kk >> 2) * (kBig / 2) + (kk & 3) * 32) >> 4, offb = ((kk >> 2) * (kSmall / 2) + (kk & 3) * 32) >> 4;
+          umma_ss_w(tmem_base + u * 128, dK_km + offa, bq + offb, idesc_s, kk > 0 ? 1u : 0u, leader);
         }
       };
       auto issue_dpt = [&](int u, int do_slot) {
-        const uint32_t da = smem_u32(sR + do_slot * kSmall);
+        const uint64_t bd = dR_km + (uint64_t)(do_slot * (kSmall >> 4));
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offa = (kk >> 2) * (kBig / 2) + (kk & 3) * 32, offb = (kk >> 2) * (kSmall / 2) + (kk & 3) * 32;
-          umma_ss_w(tmem_base + u * 128 + 64, umma_desc_sw128(va + offa, 16, 1024), umma_desc_sw128(da + offb, 16, 1024), idesc_s,
-                  kk > 0 ? 1u : 0u, leader);
+          const uint32_t offa = ((kk >> 2) * (kBig / 2) + (kk & 3) * 32) >> 4, offb = ((kk >> 2) * (kSmall / 2) + (kk & 3) * 32) >> 4;
+          umma_ss_w(tmem_base + u * 128 + 64, dV_km + offa, bd + offb, idesc_s, kk > 0 ? 1u : 0u, leader);
         }
       };
       // dQ^T[d, q] = sum_kv K[kv, d] dS^T[kv, q]: A = K tile read M-major (two 64-wide d chunks, 16 keys per step),
       // B = dS^T tile read N-major (one 64-wide q chunk)
       auto issue_dq = [&](int u) {
-        const uint32_t dsa = smem_u32(sDS + u * kSmall);
+        const uint64_t bs = dDS_mn + (uint64_t)(u * (kSmall >> 4));
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss_w(tmem_base + u * 128 + 64, umma_desc_sw128(ka + kk * 2048, kBig / 2, 1024),
-                  umma_desc_sw128(dsa + kk * 2048, kSmall / 2, 1024), idesc_dq, kk > 0 ? 1u : 0u, leader);
+          umma_ss_w(tmem_base + u * 128 + 64, dK_mn + (uint32_t)(kk * (2048 >> 4)), bs + (uint32_t)(kk * (2048 >> 4)), idesc_dq,
+                    kk > 0 ? 1u : 0u, leader);
       };
       auto issue_dv_dk = [&](int u, int q_slot, int do_slot, bool accumulate) {
-        const uint32_t qa = smem_u32(sR + q_slot * kSmall), da = smem_u32(sR + do_slot * kSmall);
+        const uint64_t bq = dR_mn + (uint64_t)(q_slot * (kSmall >> 4)), bd = dR_mn + (uint64_t)(do_slot * (kSmall >> 4));
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts_w(tmem_base + 256, tmem_base + u * 128 + kk * 8, umma_desc_sw128(da + kk * 2048, kSmall / 2, 1024), idesc_acc,
-                  (accumulate || kk > 0) ? 1u : 0u, leader);
+          umma_ts_w(tmem_base + 256, tmem_base + u * 128 + kk * 8, bd + (uint32_t)(kk * (2048 >> 4)), idesc_acc,
+                    (accumulate || kk > 0) ? 1u : 0u, leader);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_ts_w(tmem_base + 384, tmem_base + u * 128 + 32 + kk * 8, umma_desc_sw128(qa + kk * 2048, kSmall / 2, 1024), idesc_acc,
-                  (accumulate || kk > 0) ? 1u : 0u, leader);
+          umma_ts_w(tmem_base + 384, tmem_base + u * 128 + 32 + kk * 8, bq + (uint32_t)(kk * (2048 >> 4)), idesc_acc,
+                    (accumulate || kk > 0) ? 1u : 0u, leader);
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      bool ok = wait_all(kv_full, 0);
       int slot = 0;
       uint32_t ph = 0;
       auto take = [&](int& out_slot) -> bool {
-        if (!mbar_wait(&r_full[slot], ph, abort_flag)) return false;
+        if (!wait_all(&r_full[slot], ph)) return false;
         out_slot = slot;
         if (++slot == kRing) { slot = 0; ph ^= 1; }
         return true;
@@ -206,7 +217,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       for (int i = 0; i < n_q && ok; ++i) {
         const int u = i & 1;
         const uint32_t par = (i >> 1) & 1;
-        if (!mbar_wait(&p_ready[u], par, abort_flag)) { ok = false; break; }
+        if (!wait_all(&p_ready[u], par)) { ok = false; break; }
+        if (lane == 0) FAF_TRACE(i, 4);
         tc_fence_after();
         issue_dq(u);
         umma_commit_w(&dq_full[u], leader);
@@ -220,10 +232,13 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           // columns that hold dQ^T of this sub-tile, so it waits for the read-back (hidden behind dV / dK / S^T).
           tc_fence_after();
           issue_st(u, qs[u]);
-          if (!mbar_wait(&dq_free[u], par, abort_flag)) { ok = false; break; }
+          if (lane == 0) FAF_TRACE(i, 5);
+          if (!wait_all(&dq_free[u], par)) { ok = false; break; }
+          if (lane == 0) FAF_TRACE(i, 6);
           tc_fence_after();
           issue_dpt(u, ds[u]);
           umma_commit_w(&s_full[u], leader);
+          if (lane == 0) FAF_TRACE(i, 7);
         }
       }
       if (ok) umma_commit_w(done, leader);
@@ -249,6 +264,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int qslot = n % kRing;
       if (!mbar_wait(&s_full[u], par, abort_flag)) { ok = false; break; }
       if (!mbar_wait(&r_full[qslot], (n / kRing) & 1, abort_flag)) { ok = false; break; }  // row statistics landed
+      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 0);
       tc_fence_after();
       const float4* l4 = reinterpret_cast<const float4*>(sStat + qslot * (kStat / 4)) + half * 8;
       const float4* d4 = l4 + 16;
@@ -293,9 +309,11 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[u]);
+      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 1);
 
       // ---- read this warp's half of dQ^T back (lane = d) and add it into the fp32 dQ buffer
       if (!mbar_wait(&dq_full[u], par, abort_flag)) { ok = false; break; }
+      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 2);
       tc_fence_after();
       uint32_t a[32];
       tmem_ld32(tST + 64 + half * 32, a);
@@ -303,6 +321,7 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_free[u]);
+      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 3);
       const int q0 = i * 64 + half * 32;
       // head-major accumulator [B, H, Sq, 128]: consecutive queries are 512 bytes apart, so every reduction below is one
       // instruction with an immediate offset from a single base pointer
@@ -382,12 +401,17 @@ __global__ void __launch_bounds__(256) fa_bwd_dq_convert_kernel(const float* __r
 
 using namespace cb200;
 
+static long long* g_faf_trace = nullptr;
+// device buffer of 256*8 int64 that receives the event trace of the next launches (nullptr switches tracing off)
+extern "C" void cb200_fa_bwd_fused_set_trace(long long* buf) { g_faf_trace = buf; }
+
 // Runs after the preprocessing kernel has produced lse2 / delta (padded to S_pad rows per (b, h)).
 // dq_acc: B*Sq*H*128 floats of scratch, zeroed here.
 extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const void* k, const void* v, const float* lse2,
                                        const float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Skv, int H,
                                        int S_pad, float scale, int dbg, int* err, cudaStream_t st) {
   using namespace faf;
+  (void)dbg;
   auto make = [&](CUtensorMap* m, const void* p, int S, int box_rows) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)HD * 2, (uint64_t)H * HD * 2, (uint64_t)S * H * HD * 2};
@@ -408,7 +432,7 @@ extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const voi
   if (e != cudaSuccess) return 400 + (int)e;
   dim3 grid((Skv + 127) / 128, H, B);
   fa_bwd_fused_kernel<<<grid, kThreads, kSmem, st>>>(q64, do64, k128, v128, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, Sq, Skv, H, S_pad,
-                                                     scale, dbg, err);
+                                                     scale, g_faf_trace, err);
   const long n8 = (long)(n / 8);
   fa_bwd_dq_convert_kernel<<<(unsigned)std::min<long>((n8 + 255) / 256, 148 * 16), 256, 0, st>>>(dq_acc, (bf16*)dq, B, Sq, H, scale);
   return (int)cudaGetLastError();

@@ -59,6 +59,7 @@ void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S
 }
 
 extern "C" {
+void cb200_fa_bwd_fused_set_trace(long long* buf);
 // microbench.cu
 int cb200_red_f32_bench(float* acc, int rows, int n_ctas, cudaStream_t st);
 
