@@ -84,7 +84,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_ready + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the shuffle makes the warp index (and every role branch below) provably warp-uniform for the compiler
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int h = blockIdx.y, b = blockIdx.z;
   const int q_base = blockIdx.x * 2 * BQ;
   const int n_kv = (Skv + BKV - 1) / BKV;
@@ -135,62 +136,68 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    {
+      // The whole warp runs this code with identical values and only the elected lane issues: warp-uniform control flow
+      // and descriptor arithmetic stay on the uniform datapath, which roughly halves the issue cost per MMA.
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)); };
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
+      bool ok = wait_all(q_full, 0);
+      const uint64_t dQ_km = umma_desc_sw128(smem_u32(sQ), 16, 1024);          // Q tiles as K-major A
+      const uint64_t dR_km = umma_desc_sw128(smem_u32(sR), 16, 1024);          // ring slot as K-major B (K)
+      const uint64_t dR_mn = umma_desc_sw128(smem_u32(sR), kHalfBytes, 1024);  // ring slot as N-major B (V)
       auto issue_qk = [&](int t, int slot) {
-        const uint32_t qa = smem_u32(sQ + t * kTileBytes), ka = smem_u32(sR + slot * kTileBytes);
+        const uint64_t bq = dQ_km + (uint64_t)(t * (kTileBytes >> 4)), bk = dR_km + (uint64_t)(slot * (kTileBytes >> 4));
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          umma_ss(tmem_base + t * 128, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_qk,
-                  kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+          umma_ss_w(tmem_base + t * 128, bq + off, bk + off, idesc_qk, kk > 0 ? 1u : 0u, leader);
         }
       };
       auto issue_pv = [&](int t, int slot, bool accumulate) {
-        const uint32_t va = smem_u32(sR + slot * kTileBytes);
+        const uint64_t bv = dR_mn + (uint64_t)(slot * (kTileBytes >> 4));
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, umma_desc_sw128(va + kk * 2048, kHalfBytes, 1024),
-                  idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          umma_ts_w(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, bv + (uint32_t)(kk * (2048 >> 4)), idesc_pv,
+                    (accumulate || kk > 0) ? 1u : 0u, leader);
         }
       };
       // ring cursor of the item to consume next (K_0 first)
       int slot = 0;
       uint32_t ph = 0;
       auto advance = [&]() { if (++slot == kRing) { slot = 0; ph ^= 1; } };
-      if (ok) ok = mbar_wait(&r_full[slot], ph, abort_flag);
+      if (ok) ok = wait_all(&r_full[slot], ph);
       if (ok) {
         tc_fence_after();
         issue_qk(0, slot);
-        umma_commit(&s_full[0]);
+        umma_commit_w(&s_full[0], leader);
         issue_qk(1, slot);
-        umma_commit(&s_full[1]);
-        umma_commit(&r_empty[slot]);
+        umma_commit_w(&s_full[1], leader);
+        umma_commit_w(&r_empty[slot], leader);
         advance();
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         const bool has_next = (j + 1) < n_kv;
         const int v_slot = slot;
-        if (!mbar_wait(&r_full[v_slot], ph, abort_flag)) { ok = false; break; }
+        if (!wait_all(&r_full[v_slot], ph)) { ok = false; break; }
         advance();
         const int k_slot = slot;
         if (has_next) {
-          if (!mbar_wait(&r_full[k_slot], ph, abort_flag)) { ok = false; break; }
+          if (!wait_all(&r_full[k_slot], ph)) { ok = false; break; }
           advance();
         }
         for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(&p_ready[t], j & 1, abort_flag)) { ok = false; break; }
+          if (!wait_all(&p_ready[t], j & 1)) { ok = false; break; }
           tc_fence_after();
           issue_pv(t, v_slot, j > 0);
-          if (t == 1) umma_commit(&r_empty[v_slot]);
+          if (t == 1) umma_commit_w(&r_empty[v_slot], leader);
           if (has_next) issue_qk(t, k_slot);
-          if (t == 1 && has_next) umma_commit(&r_empty[k_slot]);
-          umma_commit(&s_full[t]);
+          if (t == 1 && has_next) umma_commit_w(&r_empty[k_slot], leader);
+          umma_commit_w(&s_full[t], leader);
         }
       }
-      if (!ok) { atomicCAS(err, 0, 12); *abort_flag = 1; }
+      if (!ok && lane == 0) { atomicCAS(err, 0, 12); *abort_flag = 1; }
     }
   } else {
     // -------------------------------------------------------------------- softmax warpgroups

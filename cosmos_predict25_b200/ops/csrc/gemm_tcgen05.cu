@@ -62,7 +62,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the shuffle makes the warp index (and every role branch below) provably warp-uniform for the compiler
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + BK - 1) / BK;
@@ -123,38 +124,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this loop with identical values and only the elected lane issues: warp-uniform control flow and
+    // descriptor arithmetic stay on the uniform datapath, which lowers the issue cost per MMA.
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)); };
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      // stage-0 descriptors; a stage / k-slice is a constant added to the address field (16-byte units)
+      const uint64_t da0 = A_MN ? umma_desc_sw128(smem_u32(smem), 8192, 1024) : umma_desc_sw128(smem_u32(smem), 16, 1024);
+      const uint64_t db0 = B_MN ? umma_desc_sw128(smem_u32(smem) + kABytes, 8192, 1024) : umma_desc_sw128(smem_u32(smem) + kABytes, 16, 1024);
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
+        if (!wait_all(&acc_empty[acc], acc_ph ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+          if (!wait_all(&full[s], ph)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
-          const uint32_t sb = sa + kABytes;
+          const uint64_t da_s = da0 + (uint64_t)(s * (kStageBytes >> 4)), db_s = db0 + (uint64_t)(s * (kStageBytes >> 4));
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
-            const uint64_t da = A_MN ? umma_desc_sw128(sa + k * (UK * 128), 8192, 1024)
-                                     : umma_desc_sw128(sa + k * (UK * 2), 16, 1024);
-            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UK * 128), 8192, 1024)
-                                     : umma_desc_sw128(sb + k * (UK * 2), 16, 1024);
-            umma_ss(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            const uint64_t da = da_s + (uint32_t)((A_MN ? k * (UK * 128) : k * (UK * 2)) >> 4);
+            const uint64_t db = db_s + (uint32_t)((B_MN ? k * (UK * 128) : k * (UK * 2)) >> 4);
+            umma_ss_w(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u, leader);
           }
-          umma_commit(&empty[s]);  // slot reusable once these MMAs have read it
+          umma_commit_w(&empty[s], leader);  // slot reusable once these MMAs have read it
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit(&acc_full[acc]);
+        umma_commit_w(&acc_full[acc], leader);
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
       }
-      if (!ok) { atomicCAS(err, 0, 2); *abort_flag = 1; }
+      if (!ok && lane == 0) { atomicCAS(err, 0, 2); *abort_flag = 1; }
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
