@@ -327,9 +327,14 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // instruction with an immediate offset from a single base pointer
       float* qrow = dQacc + (bh * Sq + (size_t)q0) * HD + row;
       const int n_valid = min(32, Sq - q0);
+      if (n_valid == 32) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < n_valid) red_add_f32(qrow + j * HD, __uint_as_float(a[j]));
+        for (int j = 0; j < 32; ++j) red_add_f32(qrow + j * HD, __uint_as_float(a[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < n_valid) red_add_f32(qrow + j * HD, __uint_as_float(a[j]));
+      }
     }
     if (ok) ok = mbar_wait(done, 0, abort_flag);
     if (ok) {
