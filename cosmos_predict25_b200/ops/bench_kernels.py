@@ -125,6 +125,11 @@ def main():
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 1), iters=3, warmup=1), 2.5 * fl)
             add("fa_bwd tcgen05 single-pass (5 GEMM)", f"S={N} H={heads}",
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 2), iters=3, warmup=1), 2.5 * fl)
+        if hasattr(ops, "fa_jvp"):
+            tq, tk, tv = (torch.randn_like(t) for t in (q, k, v))
+            # useful work: S, tS (2 GEMMs), P V (forward), A V, P tV = 6 GEMM units of 2 S^2 D H each
+            add("fa_jvp tcgen05 (forward + tangent pass)", f"S={N} H={heads}",
+                time_ms(lambda: ops.fa_jvp(q, k, v, tq, tk, tv, scale), iters=3, warmup=1), 3.0 * fl)
         if hasattr(ops, "red_f32_bench"):
             # L2 reduction rate that bounds the dQ accumulation of the single-pass backward: one head's dQ matrix [S, 128] fp32,
             # 660 key tiles adding into it = the traffic of one head of the S=84480 problem

@@ -60,6 +60,9 @@ void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S
 
 extern "C" {
 void cb200_fa_bwd_fused_set_trace(long long* buf);
+// fa_jvp.cu
+int cb200_fa_jvp(const void* q, const void* k, const void* v, const void* tq, const void* tk, const void* tv, const void* o,
+                 const float* lse, void* to, int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st);
 // microbench.cu
 int cb200_red_f32_bench(float* acc, int rows, int n_ctas, cudaStream_t st);
 

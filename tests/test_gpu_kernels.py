@@ -219,6 +219,27 @@ def test_flash_attention_bwd(B, Sq, Skv, H, variant):
     _close(dq, qr.grad, 3e-2, 3e-2, "dq")
 
 
+@pytest.mark.parametrize("B,Sq,Skv,H", [(1, 256, 128, 2), (2, 384, 512, 3), (1, 1000, 999, 2), (1, 300, 15, 2), (1, 2048, 2048, 2)])
+def test_flash_attention_jvp(B, Sq, Skv, H):
+    torch.manual_seed(14)
+    q, tq = (torch.randn(B, Sq, H, 128, device=DEV).bfloat16() for _ in range(2))
+    k, v, tk, tv = (torch.randn(B, Skv, H, 128, device=DEV).bfloat16() for _ in range(4))
+    scale = 1.0 / math.sqrt(128)
+    o, to, lse = _ops().fa_jvp(q, k, v, tq, tk, tv, scale)
+    _no_kernel_error()
+    orf, tor, lser = ref.attention_jvp(q.float(), k.float(), v.float(), tq.float(), tk.float(), tv.float(), scale)
+    _close(o, orf, 3e-2, 3e-2, "o")
+    _close(lse, lser, 3e-2, 2e-3, "lse")
+    _close(to, tor, 4e-2, 4e-2, "to")
+    # cross-check against autograd's forward-mode on the fp32 reference
+    import torch.autograd.forward_ad as fwAD
+    with fwAD.dual_level():
+        qd, kd, vd = (fwAD.make_dual(a.float(), t.float()) for a, t in ((q, tq), (k, tk), (v, tv)))
+        od, _ = ref.attention(qd, kd, vd, scale)
+        to_ad = fwAD.unpack_dual(od).tangent
+    _close(to, to_ad, 4e-2, 4e-2, "to vs forward-mode autograd")
+
+
 def test_attention_autograd():
     torch.manual_seed(10)
     B, S, H = 1, 384, 2
