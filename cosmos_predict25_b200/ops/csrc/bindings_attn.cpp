@@ -63,16 +63,18 @@ std::tuple<Tensor, Tensor, Tensor> fa_bwd(const Tensor& d_o, const Tensor& q, co
                                           const Tensor& lse, double scale) {
   return fa_bwd_variant(d_o, q, k, v, o, lse, scale, 0);
 }
-// primal output, tangent output and log-sum-exp of attention for tangents (tq, tk, tv): forward kernel, then one JVP pass
-std::tuple<Tensor, Tensor, Tensor> fa_jvp(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tq, const Tensor& tk,
-                                          const Tensor& tv, double scale) {
+// tangent of the attention output given the primal output and log-sum-exp of the forward kernel
+Tensor fa_jvp_tangent(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tq, const Tensor& tk, const Tensor& tv,
+                      const Tensor& o, const Tensor& lse, double scale) {
+  check_qkv(q, "q");
+  check_qkv(k, "k");
+  check_qkv(v, "v");
   check_qkv(tq, "tq");
   check_qkv(tk, "tk");
   check_qkv(tv, "tv");
+  check_qkv(o, "o");
   TORCH_CHECK(tq.sizes() == q.sizes() && tk.sizes() == k.sizes() && tv.sizes() == v.sizes(), "tangent shapes must match the primals");
-  auto ol = fa_fwd(q, k, v, scale);
-  const Tensor& o = std::get<0>(ol);
-  const Tensor& lse = std::get<1>(ol);
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse must be contiguous fp32 [B,H,Sq]");
   c10::cuda::CUDAGuard g(q.device());
   Tensor to = at::empty_like(q);
   const int B = (int)q.size(0), Sq = (int)q.size(1), H = (int)q.size(2), Skv = (int)k.size(1);
@@ -80,7 +82,16 @@ std::tuple<Tensor, Tensor, Tensor> fa_jvp(const Tensor& q, const Tensor& k, cons
                               lse.data_ptr<float>(), to.data_ptr(), B, Sq, Skv, H, (float)scale, cb200_error_word(q.get_device()),
                               at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "fa_jvp launch failed with code ", rc);
-  return {o, to, lse};
+  return to;
+}
+
+// primal output, tangent output and log-sum-exp of attention for tangents (tq, tk, tv): forward kernel, then one JVP pass
+std::tuple<Tensor, Tensor, Tensor> fa_jvp(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tq, const Tensor& tk,
+                                          const Tensor& tv, double scale) {
+  auto ol = fa_fwd(q, k, v, scale);
+  const Tensor& o = std::get<0>(ol);
+  const Tensor& lse = std::get<1>(ol);
+  return {o, fa_jvp_tangent(q, k, v, tq, tk, tv, o, lse, scale), lse};
 }
 
 // event trace (SM clocks, [256 sub-tiles, 8 events]) of CTA 0 of the single-pass backward; for performance analysis
@@ -107,6 +118,7 @@ void register_attention_ops(torch::Library& m) {
   m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");
   m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)");
   m.def("fa_jvp(Tensor q, Tensor k, Tensor v, Tensor tq, Tensor tk, Tensor tv, float scale) -> (Tensor, Tensor, Tensor)");
+  m.def("fa_jvp_tangent(Tensor q, Tensor k, Tensor v, Tensor tq, Tensor tk, Tensor tv, Tensor o, Tensor lse, float scale) -> Tensor");
   m.def("fa_bwd_fused_trace(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> Tensor");
   m.def("red_f32_bench(Tensor(a!) acc, int n_ctas) -> ()");
   m.def("fa_bwd_variant(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, int variant) -> (Tensor, Tensor, Tensor)");
@@ -120,4 +132,5 @@ TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
   m.impl("red_f32_bench", &red_f32_bench);
   m.impl("fa_bwd_fused_trace", &fa_bwd_fused_trace);
   m.impl("fa_jvp", &fa_jvp);
+  m.impl("fa_jvp_tangent", &fa_jvp_tangent);
 }

@@ -187,6 +187,45 @@ class _FlashAttention(torch.autograd.Function):
         return dq, dk, dv, None
 
 
+class _FlashAttentionJVP(torch.autograd.Function):
+    """Attention with a forward-mode rule: ``jvp`` runs the tangent pass of the JVP kernel on the saved forward
+    statistics; ``backward`` differentiates the primal only (the tangent is used under stop-gradient by consistency
+    training), like the reference's Triton function (flash_attention_jvp_triton.py:436-520)."""
+
+    @staticmethod
+    def forward(q, k, v, scale):
+        ops = native.load()
+        o, lse = ops.fa_fwd(q.contiguous(), k.contiguous(), v.contiguous(), scale)
+        native.count_launch()
+        return o, lse
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        q, k, v, scale = inputs
+        o, lse = output
+        ctx.scale = scale
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.save_for_forward(q, k, v, o, lse)
+        ctx.mark_non_differentiable(lse)
+
+    @staticmethod
+    def jvp(ctx, tq, tk, tv, _tscale):
+        ops = native.load()
+        q, k, v, o, lse = ctx.saved_tensors
+        z = lambda t, like: torch.zeros_like(like) if t is None else t.to(like.dtype).contiguous()
+        to = ops.fa_jvp_tangent(q.contiguous(), k.contiguous(), v.contiguous(), z(tq, q), z(tk, k), z(tv, v), o, lse, ctx.scale)
+        native.count_launch()
+        return to, torch.zeros_like(lse)
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        ops = native.load()
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ops.fa_bwd(do.contiguous(), q.contiguous(), k.contiguous(), v.contiguous(), o, lse, ctx.scale)
+        native.count_launch(3)
+        return dq, dk, dv, None
+
+
 def _sdpa(q, k, v, scale):
     """torch SDPA pinned to the cuDNN backend (flash / efficient as fall-backs), [B,S,H,D] layout."""
     from torch.nn.attention import SDPBackend, sdpa_kernel
@@ -209,6 +248,10 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not q.is_cuda:
         return ref.attention(q, k, v, scale)[0]
+    if native.forward_mode():
+        if native_attention_supported(q, k):
+            return _FlashAttentionJVP.apply(q, k, v, scale)[0]
+        return ref.attention(q, k, v, scale)[0]      # explicit softmax: carries forward-mode tangents
     if settings.attention == "native" and native_attention_supported(q, k):
         return _FlashAttention.apply(q, k, v, scale)
     return _sdpa(q, k, v, scale)
@@ -234,6 +277,8 @@ _ACT_CODE = {"none": 0, "gelu": 1}
 
 
 def _native_gemm_ok(x2d: torch.Tensor, w: torch.Tensor) -> bool:
+    if native.forward_mode():
+        return False
     if settings.gemm != "native" or not x2d.is_cuda or x2d.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
     if not native.available() or not hasattr(native.load(), "gemm_bf16"):

@@ -8,6 +8,7 @@ is an error: nothing silently falls back to eager PyTorch for CUDA tensors.
 
 from __future__ import annotations
 
+import contextlib
 import os
 import threading
 
@@ -43,9 +44,28 @@ def load():
     return torch.ops.cosmos_b200
 
 
+_forward_mode = False
+
+
+def forward_mode() -> bool:
+    """True inside ``forward_mode_ad()``: element-wise and GEMM operators then run as plain torch ops (which carry
+    forward-mode tangents) and only attention uses its kernel, through a function with a JVP rule."""
+    return _forward_mode
+
+
+@contextlib.contextmanager
+def forward_mode_ad():
+    global _forward_mode
+    prev, _forward_mode = _forward_mode, True
+    try:
+        yield
+    finally:
+        _forward_mode = prev
+
+
 def use_native(t: torch.Tensor) -> bool:
-    """CUDA tensors go to the extension; CPU tensors go to the PyTorch oracle."""
-    return t.is_cuda
+    """CUDA tensors go to the extension; CPU tensors (and everything in forward-mode AD) go to the PyTorch oracle."""
+    return t.is_cuda and not _forward_mode
 
 
 _launch_count = 0

@@ -281,3 +281,33 @@ def test_optimizer_kernels():
         ref.adamw_step(mr, g32 * 0.7, mm, vv, lr=1e-2, beta1=0.9, beta2=0.99, eps=1e-8, weight_decay=0.1, step=step)
     _close(master, mr, 1e-5, 1e-4, "master")
     _close(out16, mr, 1e-2, 1e-2, "bf16 params")
+
+
+def test_network_jvp_uses_attention_jvp_kernel(monkeypatch):
+    """Forward-mode through the DiT on the GPU: attention goes through the JVP kernel; everything else through torch ops.
+    Compared with the same forward-mode pass that uses the explicit-softmax reference attention."""
+    from cosmos_predict25_b200.models.distill import network_jvp
+    from cosmos_predict25_b200.models.dit import CosmosDiT, dit_mini
+    from cosmos_predict25_b200.ops import functional as F_ops
+    torch.manual_seed(0)
+    net = CosmosDiT(dit_mini(crossattn_proj_in_channels=256)).to(DEV)
+    net.init_weights()
+    for blk in net.blocks:
+        for m in (blk.adaln_modulation_self_attn, blk.adaln_modulation_cross_attn, blk.adaln_modulation_mlp):
+            torch.nn.init.normal_(m[-1].weight, std=0.05)
+    torch.nn.init.normal_(net.final_layer.linear.weight, std=0.05)
+    net = net.bfloat16()
+    x = torch.randn(1, 16, 2, 16, 16, device=DEV).bfloat16()
+    t = torch.full((1, 1), 400.0, device=DEV)
+    tx, tt = torch.randn_like(x), torch.full_like(t, 1000.0)
+    kw = dict(crossattn_emb=torch.randn(1, 16, 256, device=DEV).bfloat16(), fps=torch.tensor([16.0], device=DEV),
+              padding_mask=torch.zeros(1, 1, 16, 16, device=DEV))
+    before = native.launches()
+    F1, dF1 = network_jvp(net, x, t, tx, tt, **kw)
+    assert native.launches() - before >= 2 * len(net.blocks) * 2        # forward + tangent kernels for self- and cross-attention
+    _no_kernel_error()
+    monkeypatch.setattr(F_ops, "native_attention_supported", lambda q, k: False)
+    F2, dF2 = network_jvp(net, x, t, tx, tt, **kw)
+    _close(F1, F2, 5e-2, 5e-2, "F")
+    _close(dF1, dF2, 8e-2, 8e-2, "dF")
+    assert dF2.float().abs().max() > 1e-2
