@@ -143,3 +143,24 @@ def test_guardrails():
     frames = (np.random.rand(3, 32, 32, 3) * 255).astype(np.uint8)
     out = presets.run_video_guardrail(frames, vr)
     assert out is not None and out.shape == frames.shape
+
+
+def test_folder_monitor_and_text2image(tmp_path):
+    from cosmos_predict25_b200.pipeline.online import FolderMonitor, Text2ImageInference
+    from cosmos_predict25_b200.pipeline.video2world import Video2WorldInference
+    pipe = Video2WorldInference("tiny_video2world_cpu", None, device=torch.device("cpu"))
+    prompts, results = tmp_path / "prompts", tmp_path / "results"
+    mon = FolderMonitor(pipe, str(prompts), str(results), guidance=3.0, num_video_frames=13, resolution="32,32", seed=5, num_steps=2)
+    (prompts / "a_cat.txt").write_text("a cat walking")
+    (prompts / "empty.txt").write_text("   ")
+    assert mon.run_once() == 2
+    out = results / "a_cat"
+    assert (out / "prompt.txt").read_text() == "a cat walking" and "Seed: 5" in (out / "generation_info.txt").read_text()
+    assert mon.existing_video("a_cat") is not None and not (results / "empty").exists()
+    assert mon.run_once() == 0                                     # nothing new
+    mon.processed_files.clear()
+    assert mon.process_prompt_file(prompts / "a_cat.txt") is None    # output exists -> skipped
+    (prompts / "STOP").write_text("")
+    mon.run()                                                        # returns at once
+    img = Text2ImageInference("tiny_video2world_cpu", None, pipe=pipe).generate_image("a dog", resolution="32,32", num_steps=2, guidance=2.0)
+    assert img.shape[0] == 1 and img.shape[2] == 1 and torch.isfinite(img).all()
