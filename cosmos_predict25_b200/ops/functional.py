@@ -215,7 +215,7 @@ class _FlashAttentionJVP(torch.autograd.Function):
         z = lambda t, like: torch.zeros_like(like) if t is None else t.to(like.dtype).contiguous()
         to = ops.fa_jvp_tangent(q.contiguous(), k.contiguous(), v.contiguous(), z(tq, q), z(tk, k), z(tv, v), o, lse, ctx.scale)
         native.count_launch()
-        return to, torch.zeros_like(lse)
+        return to, None      # lse is marked non-differentiable
 
     @staticmethod
     def backward(ctx, do, _dlse):
