@@ -267,6 +267,10 @@ class Attention(nn.Module):
         self.q_norm.reset_parameters()
         self.k_norm.reset_parameters()
 
+    def _plain_projections(self) -> bool:
+        return all(type(p) is FusedLinear and p.bias is None and p.weight.dtype == torch.bfloat16
+                   for p in (self.q_proj, self.k_proj, self.v_proj))
+
     def project_kv(self, context: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """K (normalised) and V of a context; constant across sampling steps for cross-attention."""
         B, S, _ = context.shape
@@ -278,6 +282,13 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, context: Optional[torch.Tensor] = None, rope=None,
                 kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, return_pre_proj: bool = False):
         B, S, _ = x.shape
+        if (self.is_selfattn and self.cp_group is not None and self._plain_projections()
+                and ulysses.projected_attention_available(x, self.cp_group, self.head_dim)):
+            # inference under context parallelism: the sequence->head exchange is the epilogue of the q/k/v GEMMs
+            o = ulysses.ulysses_projected_attention(x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight,
+                                                    self.q_norm.weight, self.k_norm.weight, rope, self.cp_group, self.q_norm.eps)
+            o = o.reshape(B, S, self.n_heads * self.head_dim)
+            return o if return_pre_proj else self.output_proj(o)
         q = self.q_proj(x).view(B, S, self.n_heads, self.head_dim)
         if self.is_selfattn:
             k = self.k_proj(x).view(B, S, self.n_heads, self.head_dim)

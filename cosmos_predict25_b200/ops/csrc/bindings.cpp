@@ -295,6 +295,41 @@ Tensor gemm_bf16_gate_residual(const Tensor& a, const Tensor& b, const Tensor& r
   return gemm_impl(a, b, c10::nullopt, 0, false, false, nullptr, &resid, &gate, L);
 }
 
+// x [B*S, K] @ w [H*128, K]^T with the Ulysses sequence->head exchange as the epilogue: nothing is returned, head h of token
+// (b, s) lands in out_ptrs[h / (H/P)] (a staging buffer of that rank, [B, P*S, H/P, 128]) after optional RMSNorm and RoPE.
+void gemm_scatter_heads_peer(const Tensor& x, const Tensor& w, c10::ArrayRef<int64_t> out_ptrs, const c10::optional<Tensor>& norm_w,
+                             const c10::optional<Tensor>& cosv, const c10::optional<Tensor>& sinv, int64_t S, int64_t rank,
+                             double eps) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "operands must be contiguous");
+  c10::cuda::CUDAGuard g(x.device());
+  const GemmDims d = gemm_dims(x, w, false, false);
+  TORCH_CHECK(d.N % 128 == 0 && out_ptrs.size() >= 1 && out_ptrs.size() <= 8 && (d.N / 128) % (int64_t)out_ptrs.size() == 0,
+              "heads of 128 channels, divisible by the peer count");
+  TORCH_CHECK(S > 0 && d.M % S == 0, "rows must be B * S");
+  Tensor wf;
+  const float *wp = nullptr, *cp = nullptr, *sp = nullptr;
+  if (norm_w.has_value()) {
+    wf = norm_w->to(at::kFloat).contiguous();
+    TORCH_CHECK(wf.numel() == 128, "norm weight must be [128]");
+    wp = wf.data_ptr<float>();
+    if (cosv.has_value()) {
+      check_f32(*cosv, "cos");
+      check_f32(*sinv, "sin");
+      TORCH_CHECK(cosv->numel() >= S * 64 && sinv->numel() >= S * 64 && cosv->is_contiguous() && sinv->is_contiguous(),
+                  "cos/sin must be [S, 64]");
+      cp = cosv->data_ptr<float>();
+      sp = sinv->data_ptr<float>();
+    }
+  }
+  std::vector<int64_t> p(out_ptrs.begin(), out_ptrs.end());
+  const int dev = x.get_device();
+  const int rc = cb200_gemm_bf16_scatter_heads(x.data_ptr(), w.data_ptr(), d.M, d.N, d.K, p.data(), (int)p.size(), (int)rank, (int)S,
+                                               wp, cp, sp, (float)eps, error_word(dev), sm_count(dev), stream());
+  TORCH_CHECK(rc == 0, "tcgen05 GEMM (head-scatter epilogue) launch failed with code ", rc);
+}
+
 int64_t kernel_error(int64_t device, bool clear) {
   int v = 0;
   int* w = error_word((int)device);
@@ -331,6 +366,8 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor? bias, int act, bool trans_a, bool trans_b) -> Tensor");
   m.def("gemm_bf16_gelu_pre(Tensor a, Tensor b, Tensor? bias) -> (Tensor, Tensor)");
   m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor");
+  m.def("gemm_scatter_heads_peer(Tensor x, Tensor w, int[] out_ptrs, Tensor? norm_w, Tensor? cos, Tensor? sin, int S, int rank, "
+        "float eps) -> ()", &gemm_scatter_heads_peer);
   m.def("kernel_error(int device, bool clear) -> int", &kernel_error);
   register_attention_ops(m);
   register_peer_ops(m);

@@ -6,6 +6,7 @@
 #include <torch/library.h>
 
 #include <tuple>
+#include <vector>
 
 #include "launchers.h"
 
@@ -34,6 +35,27 @@ std::tuple<Tensor, Tensor> fa_fwd_variant(const Tensor& q, const Tensor& k, cons
   TORCH_CHECK(rc == 0, "fa_fwd launch failed with code ", rc);
   return {o, lse};
 }
+// Attention on local heads of the whole sequence with the head->sequence exchange as its epilogue: output row s goes to
+// out_ptrs[s / (Sq/P)], a buffer [B, Sq/P, P*H, 128] on that rank, at heads [rank*H, rank*H + H).  Returns lse.
+Tensor fa_fwd_scatter_seq_peer(const Tensor& q, const Tensor& k, const Tensor& v, double scale, c10::ArrayRef<int64_t> out_ptrs,
+                               int64_t rank) {
+  check_qkv(q, "q");
+  check_qkv(k, "k");
+  check_qkv(v, "v");
+  TORCH_CHECK(k.sizes() == v.sizes() && q.size(0) == k.size(0) && q.size(2) == k.size(2), "q/k/v shape mismatch");
+  const int P = (int)out_ptrs.size();
+  TORCH_CHECK(P >= 1 && P <= 8 && q.size(1) % P == 0, "sequence must divide over 1..8 peers");
+  c10::cuda::CUDAGuard g(q.device());
+  const int B = (int)q.size(0), Sq = (int)q.size(1), H = (int)q.size(2), Skv = (int)k.size(1);
+  Tensor lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
+  std::vector<int64_t> p(out_ptrs.begin(), out_ptrs.end());
+  const int rc = cb200_fa_fwd_scatter_seq(q.data_ptr(), k.data_ptr(), v.data_ptr(), p.data(), P, (int)rank, lse.data_ptr<float>(), B,
+                                          Sq, Skv, H, (float)scale, cb200_error_word(q.get_device()),
+                                          at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "fa_fwd (sequence-scatter epilogue) launch failed with code ", rc);
+  return lse;
+}
+
 std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale) {
   return fa_fwd_variant(q, k, v, scale, 0);
 }
@@ -115,6 +137,8 @@ void register_attention_ops(torch::Library& m) {
   // Schemas only: the kernels are registered under the CUDA dispatch key below so that dispatch modes (selective
   // activation checkpointing keeps the attention output by intercepting this op) see the call.
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)");
+  m.def("fa_fwd_scatter_seq_peer(Tensor q, Tensor k, Tensor v, float scale, int[] out_ptrs, int rank) -> Tensor",
+        &fa_fwd_scatter_seq_peer);
   m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");
   m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)");
   m.def("fa_jvp(Tensor q, Tensor k, Tensor v, Tensor tq, Tensor tk, Tensor tv, float scale) -> (Tensor, Tensor, Tensor)");

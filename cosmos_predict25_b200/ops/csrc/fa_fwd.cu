@@ -65,11 +65,19 @@ __device__ __forceinline__ float exp2_poly(float x) {
   return __int_as_float(__float_as_int(p) + ((__float_as_int(t) - 0x4B400000) << 23));
 }
 
+// Ulysses head->sequence exchange fused into the output store: this rank holds heads [rank*H, rank*H + H) of the whole
+// sequence (Sq = P * S_loc rows); row s of the output belongs to rank s / S_loc and is stored straight into that rank's buffer
+// [B, S_loc, P*H, 128] (plain 16-byte stores, local or over NVLink).  P == 0: the output goes to O as usual.
+struct SeqScatter {
+  int64_t ptrs[8];
+  int P, rank, S_loc;
+};
+
 template <int POLY_MOD, bool PACKED>
 __global__ void __launch_bounds__(fa::kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, int Sq, int Skv, int H,
-              float scale_log2, int* __restrict__ err) {
+              float scale_log2, SeqScatter sc, int* __restrict__ err) {
   using namespace fa;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -291,6 +299,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tc_fence_after();
       const float inv_l = 1.f / l;
       bf16* orow = O + (((size_t)b * Sq + q_row) * H + h) * HD;
+      if (sc.P > 0 && q_row < Sq) {
+        const int dst = q_row / sc.S_loc, s_loc = q_row - dst * sc.S_loc;
+        orow = reinterpret_cast<bf16*>(sc.ptrs[dst]) + (((size_t)b * sc.S_loc + s_loc) * (sc.P * H) + sc.rank * H + h) * HD;
+      }
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -333,7 +345,7 @@ using namespace cb200;
 
 template <int POLY_MOD, bool PACKED>
 static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, float* lse, int B, int Sq,
-                         int Skv, int H, float scale, int* err, cudaStream_t st) {
+                         int Skv, int H, float scale, const SeqScatter& sc, int* err, cudaStream_t st) {
   using namespace fa;
   auto kern = fa_fwd_kernel<POLY_MOD, PACKED>;
   static bool attr = false;
@@ -343,14 +355,14 @@ static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
     attr = true;
   }
   dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
-  kern<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, err);
+  kern<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, sc, err);
   return (int)cudaGetLastError();
 }
 
 // q [B, Sq, H, 128]; k, v [B, Skv, H, 128]; o like q; lse [B, H, Sq] fp32.
 // variant: 0 = default; 1..: tuning variants (all produce the same result within rounding)
-extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,
-                            float scale, int variant, int* err, cudaStream_t st) {
+static int fa_fwd_dispatch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,
+                           float scale, int variant, const SeqScatter& sc, int* err, cudaStream_t st) {
   using namespace fa;
   CUtensorMap tq, tk, tv;
   auto make = [&](CUtensorMap* m, const void* p, int S) {
@@ -366,11 +378,29 @@ extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o
   rc = make(&tv, v, Skv);
   if (rc) return rc;
   switch (variant) {
-    case 1: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
-    case 2: return launch_fa_fwd<0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
-    case 3: return launch_fa_fwd<2, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
-    case 4: return launch_fa_fwd<3, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
-    case 5: return launch_fa_fwd<4, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
-    default: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, err, st);
+    case 1: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 2: return launch_fa_fwd<0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 3: return launch_fa_fwd<2, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 4: return launch_fa_fwd<3, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 5: return launch_fa_fwd<4, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    default: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
   }
+}
+
+extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,
+                            float scale, int variant, int* err, cudaStream_t st) {
+  SeqScatter sc{};
+  return fa_fwd_dispatch(q, k, v, o, lse, B, Sq, Skv, H, scale, variant, sc, err, st);
+}
+
+// Attention whose output rows are scattered to the P ranks' sequence shards (out_ptrs[r]: [B, Sq / P, P*H, 128] bf16 on rank r).
+extern "C" int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void* v, const int64_t* out_ptrs, int P, int rank,
+                                        float* lse, int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st) {
+  if (P < 1 || P > 8 || Sq % P != 0 || rank < 0 || rank >= P) return -21;
+  SeqScatter sc{};
+  for (int i = 0; i < P; ++i) sc.ptrs[i] = out_ptrs[i];
+  sc.P = P;
+  sc.rank = rank;
+  sc.S_loc = Sq / P;
+  return fa_fwd_dispatch(q, k, v, nullptr, lse, B, Sq, Skv, H, scale, 0, sc, err, st);
 }

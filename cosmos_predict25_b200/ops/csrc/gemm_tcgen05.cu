@@ -36,7 +36,20 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kGemmThreads = 192;
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
+// Ulysses exchange fused into the epilogue: the output [M, N] is a projection to H = N / 128 heads of a local sequence of S
+// tokens per batch item; head h of token (b, s) is normalised (optional per-head RMSNorm), rotated (optional rotate-half
+// RoPE) and stored straight into the staging buffer of the rank that owns the head, at its place in the gathered sequence.
+struct HeadScatter {
+  int64_t ptrs[8];    // staging buffers of the P ranks, each [B, P * S, Hl, 128] bf16
+  const float* w;     // [128] RMSNorm weight or nullptr
+  const float* cosv;  // [S, 64] or nullptr
+  const float* sinv;
+  int S, Hl, P, rank;
+  float eps;
+};
+
 struct GemmEpilogue {
+  HeadScatter hs;     // hs.P == 0: disabled
   bf16* C;
   bf16* pre;          // optional pre-activation output (only with act == 1)
   const bf16* bias;   // optional [N]
@@ -174,6 +187,87 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      if (ep.hs.P > 0) {
+        // ---- fused head scatter: this thread owns one token row; a 256-wide tile holds two complete heads
+        // tcgen05.ld is warp-collective: every lane runs every load, rows past M only skip their stores
+        const bool valid = row < M;
+        {
+          const int row_c = valid ? row : M - 1;
+          const int b_idx = row_c / ep.hs.S, s_idx = row_c % ep.hs.S;
+#pragma unroll 1
+          for (int hh = 0; hh < BN / 128; ++hh) {
+            const int head = (n0 + hh * 128) >> 7;
+            if ((head + 1) * 128 > N) break;
+            const uint32_t t_head = t_row + hh * 128;
+            float rstd = 1.f;
+            if (ep.hs.w != nullptr) {          // pass 1: sum of squares over the head (TMEM re-reads are cheap)
+              float ss = 0.f;
+#pragma unroll 1
+              for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(t_head + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ss = fmaf(__uint_as_float(r[j]), __uint_as_float(r[j]), ss);
+              }
+              rstd = rsqrtf(ss * (1.f / 128.f) + ep.hs.eps);
+            }
+            const int dst_rank = head / ep.hs.Hl, hl = head - dst_rank * ep.hs.Hl;
+            bf16* dst = reinterpret_cast<bf16*>(ep.hs.ptrs[dst_rank]) +
+                        ((((size_t)b_idx * ep.hs.P + ep.hs.rank) * ep.hs.S + s_idx) * ep.hs.Hl + hl) * 128;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {      // pass 2: columns [32c, 32c+32) and their rotation partners [64+32c, 64+32c+32)
+              uint32_t lo[32], hi[32];
+              tmem_ld32(t_head + c * 32, lo);
+              tmem_ld32(t_head + 64 + c * 32, hi);
+              tmem_ld_wait();
+              float a[32], bb[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                a[j] = __uint_as_float(lo[j]);
+                bb[j] = __uint_as_float(hi[j]);
+              }
+              if (ep.hs.w != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  a[j] *= rstd * ep.hs.w[c * 32 + j];
+                  bb[j] *= rstd * ep.hs.w[64 + c * 32 + j];
+                }
+                if (ep.hs.cosv != nullptr) {
+                  const float* cs = ep.hs.cosv + (size_t)s_idx * 64 + c * 32;
+                  const float* sn = ep.hs.sinv + (size_t)s_idx * 64 + c * 32;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) {
+                    const float x0 = a[j], x1 = bb[j], cc = cs[j], s1 = sn[j];
+                    a[j] = x0 * cc - x1 * s1;
+                    bb[j] = x1 * cc + x0 * s1;
+                  }
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o0, o1;
+                __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+                __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  p0[j] = __floats2bfloat162_rn(a[q * 8 + 2 * j], a[q * 8 + 2 * j + 1]);
+                  p1[j] = __floats2bfloat162_rn(bb[q * 8 + 2 * j], bb[q * 8 + 2 * j + 1]);
+                }
+                if (valid) {                                                   // plain stores: local or peer memory over NVLink
+                  *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o0;
+                  *reinterpret_cast<uint4*>(dst + 64 + c * 32 + q * 8) = o1;
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        continue;
+      }
       const float* gate_row = (ep.gate != nullptr && row < M) ? ep.gate + (size_t)(row / ep.L) * N : nullptr;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -299,7 +393,7 @@ static int launch_gemm(const void* A, const void* B, int M, int N, int K, const 
 extern "C" int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn,
                                const void* bias, int act, void* pre, const void* resid, const float* gate, int L, int* err,
                                int sms, cudaStream_t st) {
-  GemmEpilogue ep;
+  GemmEpilogue ep{};
   ep.C = (bf16*)C;
   ep.pre = (bf16*)pre;
   ep.bias = (const bf16*)bias;
@@ -311,4 +405,26 @@ extern "C" int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int
   if (a_mn == 0 && b_mn == 1) return launch_gemm<0, 1>(A, B, M, N, K, ep, err, sms, st);
   if (a_mn == 1 && b_mn == 0) return launch_gemm<1, 0>(A, B, M, N, K, ep, err, sms, st);
   return launch_gemm<1, 1>(A, B, M, N, K, ep, err, sms, st);
+}
+
+// C is not written: row (b, s) of A[M = B*S, K] @ W[N = H*128, K]^T is split into heads, each head is RMS-normalised with
+// `norm_w` (optional), rotated by cos/sin [S, 64] (optional, needs norm_w) and stored into staging buffer ptrs[head / Hl] at
+// [b, rank * S + s, head % Hl, :].  The buffers may live on peer GPUs (plain stores over NVLink).
+extern "C" int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M, int N, int K, const int64_t* ptrs, int P,
+                                             int rank, int S, const float* norm_w, const float* cosv, const float* sinv,
+                                             float eps, int* err, int sms, cudaStream_t st) {
+  if (P < 1 || P > 8 || N % 128 != 0 || (N / 128) % P != 0 || S <= 0 || M % S != 0) return -21;
+  if (cosv != nullptr && norm_w == nullptr) return -22;
+  GemmEpilogue ep{};
+  for (int i = 0; i < P; ++i) ep.hs.ptrs[i] = ptrs[i];
+  ep.hs.w = norm_w;
+  ep.hs.cosv = cosv;
+  ep.hs.sinv = sinv;
+  ep.hs.S = S;
+  ep.hs.Hl = (N / 128) / P;
+  ep.hs.P = P;
+  ep.hs.rank = rank;
+  ep.hs.eps = eps;
+  ep.L = 1;
+  return launch_gemm<0, 0>(A, W, M, N, K, ep, err, sms, st);
 }

@@ -34,10 +34,15 @@ void cb200_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t st);
 // gemm_tcgen05.cu
 int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn, const void* bias,
                     int act, void* pre, const void* resid, const float* gate, int L, int* err, int sms, cudaStream_t st);
+int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M, int N, int K, const int64_t* ptrs, int P, int rank, int S,
+                                  const float* norm_w, const float* cosv, const float* sinv, float eps, int* err, int sms,
+                                  cudaStream_t st);
 }
 
 extern "C" {
 // fa_fwd.cu
+int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void* v, const int64_t* out_ptrs, int P, int rank, float* lse,
+                             int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st);
 int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
                  int variant, int* err, cudaStream_t st);
 }

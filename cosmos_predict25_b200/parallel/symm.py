@@ -139,6 +139,40 @@ class PeerAllToAll:
             outs = [o.clone() for o in outs]
         return outs, rstds
 
+    def project_scatter_heads(self, x2d: torch.Tensor, weights, norm_weights, rope, B: int, S: int, eps: float = 1e-6):
+        """``x2d [B*S, K] @ w_i^T`` for every projection weight ``w_i [H*128, K]`` with the sequence->head exchange
+        as the GEMM epilogue: accumulator rows leave TMEM normalised (``norm_weights[i]``) and rotated (``rope``)
+        and are stored straight into the owning rank's staging buffer, so the projected activations never exist
+        in sequence layout. One barrier for all projections. The results alias the rotating staging buffers
+        (inference only: consume them before eight more exchanges)."""
+        P, r = self.ctx.world, self.ctx.rank
+        cos, sin = rope.cos_sin() if rope is not None else (None, None)
+        outs = []
+        for w, nw in zip(weights, norm_weights):
+            H = w.shape[0] // 128
+            numel = B * S * w.shape[0]
+            slot = self._next(numel)
+            self.ops.gemm_scatter_heads_peer(x2d, w, slot.ptrs, nw, cos if nw is not None else None,
+                                             sin if nw is not None else None, S, r, eps)
+            native.count_launch()
+            outs.append(slot.tensor[:numel].view(B, S * P, H // P, 128))
+        self.ctx.barrier()
+        return outs
+
+    def attention_scatter_seq(self, qh: torch.Tensor, kh: torch.Tensor, vh: torch.Tensor, scale: float) -> torch.Tensor:
+        """Attention on this rank's heads of the gathered sequence ([B, S_loc*P, H/P, 128]) with the head->sequence
+        exchange as the kernel's output store: each finished query tile is written straight into the sequence shard
+        of the rank that owns its rows. Returns this rank's [B, S_loc, H, 128] (aliases a rotating staging buffer).
+        The trailing barrier publishes the peers' stores; the buffer is rewritten two attention calls later, behind
+        at least one more barrier, so no barrier is needed after the consumer."""
+        P, r = self.ctx.world, self.ctx.rank
+        B, SP, Hl, D = qh.shape
+        slot = self._next(qh.numel())
+        self.ops.fa_fwd_scatter_seq_peer(qh, kh, vh, scale, slot.ptrs, r)
+        native.count_launch()
+        self.ctx.barrier()
+        return slot.tensor[: qh.numel()].view(B, SP // P, Hl * P, D)
+
     def seq_to_head(self, x: torch.Tensor, copy_out: bool = True) -> torch.Tensor:
         return self.scatter_heads([x], copy_out=copy_out)[0][0]
 

@@ -18,6 +18,8 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
+import math
+
 import torch
 import torch.distributed as dist
 
@@ -152,6 +154,33 @@ def ulysses_attention_fused(q_raw, k_raw, v, q_norm_weight, k_norm_weight, rope,
                                           rope, eps, t)
     oh = ops.attention(qh, kh, vh, scale)
     return _HeadToSeq.apply(oh, group)
+
+
+def projected_attention_available(x: torch.Tensor, group, head_dim: int) -> bool:
+    """True when ``ulysses_projected_attention`` can run: a peer transport is attached to ``group``, nothing needs a
+    backward pass, and the activations are bf16 on the GPU with 128-wide heads."""
+    from ..ops import native
+    from ..ops.functional import settings
+    return (id(group) in _peer_transports and x.is_cuda and x.dtype == torch.bfloat16 and head_dim == 128
+            and not torch.is_grad_enabled() and native.use_native(x) and settings.attention == "native"
+            and settings.gemm == "native")
+
+
+def ulysses_projected_attention(x, wq, wk, wv, q_norm_weight, k_norm_weight, rope, group, eps: float = 1e-6,
+                                scale: Optional[float] = None):
+    """Inference self-attention on a sequence shard ``x [B, S_loc, D]``: the three projection GEMMs write their
+    heads, normalised and rotated, directly into the peers' staging buffers (exchange in the GEMM epilogue),
+    attention runs on the staged tensors and stores its output rows directly into the sequence shards of their
+    owners (exchange in the attention epilogue). No stand-alone exchange kernel runs; two device barriers per call.
+    Returns [B, S_loc, H, 128], aliasing a staging buffer: consume it before the next four calls."""
+    t = _peer_transports[id(group)]
+    B, S, D = x.shape
+    x2d = x.reshape(B * S, D)
+    if not x2d.is_contiguous():
+        x2d = x2d.contiguous()
+    qh, kh, vh = t.project_scatter_heads(x2d, [wq, wk, wv], [q_norm_weight, k_norm_weight, None], rope, B, S, eps)
+    scale = scale if scale is not None else 1.0 / math.sqrt(qh.shape[-1])
+    return t.attention_scatter_seq(qh, kh, vh, scale)
 
 
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: Optional[float] = None):

@@ -20,32 +20,53 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+_HANG_S = 240  # a rank still inside its test body after this many seconds dumps its stack and exits
+
+
 def _worker(rank, world, port, fn_name, tmp):
+    import datetime
+    import faulthandler
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    hang = open(os.path.join(tmp, f"hang{rank}"), "w")
+    faulthandler.dump_traceback_later(_HANG_S, exit=True, file=hang)
+    failed = False
     try:
         torch.cuda.set_device(rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=90))
         globals()[fn_name](rank, world)
         torch.cuda.synchronize()
         dist.barrier()
         with open(os.path.join(tmp, f"ok{rank}"), "w") as f:
             f.write("ok")
     except Exception:
+        failed = True
         with open(os.path.join(tmp, f"err{rank}"), "w") as f:
             f.write(traceback.format_exc())
-    finally:
-        if dist.is_initialized():
-            dist.destroy_process_group()
+    faulthandler.cancel_dump_traceback_later()
+    if failed:
+        # leave at once: the peers learn of it from the launcher instead of waiting inside a collective
+        os._exit(1)
+    dist.destroy_process_group()
 
 
 def _run(fn_name, world=2):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     with tempfile.TemporaryDirectory() as tmp:
-        mp.spawn(_worker, args=(world, _free_port(), fn_name, tmp), nprocs=world, join=True)
-        errs = [open(os.path.join(tmp, f)).read() for f in sorted(os.listdir(tmp)) if f.startswith("err")]
-        assert not errs, "\n".join(errs)
+        spawn_error = None
+        try:
+            mp.spawn(_worker, args=(world, _free_port(), fn_name, tmp), nprocs=world, join=True)
+        except Exception as e:  # a rank exited non-zero; its report is in the scratch folder
+            spawn_error = e
+        notes = []
+        for f in sorted(os.listdir(tmp)):
+            if f.startswith("err") or f.startswith("hang"):
+                text = open(os.path.join(tmp, f)).read()
+                if text.strip():
+                    notes.append(f"--- {f}\n{text}")
+        assert not notes and spawn_error is None, "\n".join(notes) + f"\n{spawn_error}"
         assert all(os.path.exists(os.path.join(tmp, f"ok{r}")) for r in range(world))
 
 
@@ -87,6 +108,55 @@ def _a2a_peer_vs_nccl(rank, world):
     for a, b in zip(gp, gr):
         assert (a.float() - b.float()).abs().max() < 5e-2
     ctx.check()
+
+
+def _projected_scatter_vs_unfused(rank, world):
+    from cosmos_predict25_b200.models.dit import Attention
+    from cosmos_predict25_b200.ops import functional as F_ops
+    from cosmos_predict25_b200.parallel import ulysses
+    from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+    torch.manual_seed(11 + rank)
+    B, S, H, D, K = 2, 200, 4, 128, 512          # 400 rows: the last 128-row tile is ragged
+    ctx = PeerContext(g, dev, arena_bytes=64 << 20)
+    t = PeerAllToAll(ctx, max_elems=B * S * H * D)
+    x = torch.randn(B, S, K, device=dev).bfloat16()
+    torch.manual_seed(3)                          # same weights on every rank
+    wq, wv = (torch.randn(H * D, K, device=dev) * K ** -0.5).bfloat16(), (torch.randn(H * D, K, device=dev) * K ** -0.5).bfloat16()
+    nw = 1 + 0.1 * torch.randn(D, device=dev)
+    half = torch.rand(S, D // 2, device=dev) * 30
+    rope = F_ops.RopeTable(torch.cat([half, half], -1))
+    # fp32 oracle: projection, per-head RMSNorm, rotate-half RoPE, then the NCCL exchange
+    qf = (x.float() @ wq.float().t()).view(B, S, H, D)
+    qn = qf * torch.rsqrt(qf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw
+    cos, sin = half.cos()[None, :, None, :], half.sin()[None, :, None, :]
+    q0, q1 = qn[..., :64], qn[..., 64:]
+    qr = torch.cat([q0 * cos - q1 * sin, q1 * cos + q0 * sin], -1)
+    want_q = ulysses.seq_to_head(qr.bfloat16(), g)
+    want_v = ulysses.seq_to_head((x.float() @ wv.float().t()).view(B, S, H, D).bfloat16(), g)
+    got_q, got_v = t.project_scatter_heads(x.view(B * S, K), [wq, wv], [nw, None], rope, B, S)
+    ctx.check()
+    assert (got_q.float() - want_q.float()).abs().max() < 3e-2
+    assert (got_v.float() - want_v.float()).abs().max() < 3e-2
+    # the attention module takes the fused route under no_grad and agrees with its autograd route
+    torch.manual_seed(5)
+    attn = Attention(K, None, H, D).to(dev).bfloat16()
+    attn.init_weights()
+    attn.cp_group = g
+    ulysses.attach_peer_transport(g, t)
+    with torch.enable_grad():
+        o_ref = attn(x.clone().requires_grad_(True), rope=rope).detach()
+    with torch.no_grad():
+        assert ulysses.projected_attention_available(x, g, D)
+        o = attn(x, rope=rope)
+    ulysses.detach_peer_transport(g)
+    ctx.check()
+    assert (o.float() - o_ref.float()).abs().max() < 3e-2 * max(1.0, o_ref.float().abs().max().item())
+
+
+def test_projection_gemm_with_exchange_epilogue():
+    _run("_projected_scatter_vs_unfused")
 
 
 def test_peer_all_to_all_matches_nccl():
