@@ -92,11 +92,11 @@ def main() -> int:
                                                                          is_negative_prompt=True, num_steps=args.steps))
         launches = native.launches()
         ms_decode, frames = 0.0, None
-        if tok is not None and rank == 0:
-            tok.decode(lat[:, :, :2])                                                                                      # warm-up
         if tok is not None:
-            ms_decode, video = timed(lambda: tok.decode(lat) if rank == 0 else None)
-            frames = int(video.shape[2]) if rank == 0 else None
+            model.tokenizer = tok
+            model.decode(lat[:, :, :2])                                                                                    # warm-up
+            ms_decode, video = timed(lambda: model.decode(lat))   # row bands over the CP group; every rank gets the video
+            frames = int(video.shape[2])
     err = native.load().kernel_error(local_rank, True)
     if rank == 0:
         total = (ms_sample + ms_decode) / 1e3
@@ -108,7 +108,8 @@ def main() -> int:
             "config": {"model": f"cosmos-predict2.5-{args.model}-video2world", "steps": args.steps, "guidance": args.guidance,
                        "cfg": "batched cond/uncond (one batch-2 forward per step)", "latent_shape": [1, 16, args.frames, args.height, args.width],
                        "parallelism": f"cp{world}", "transport": args.transport if world > 1 else "single",
-                       "vae": "Wan2.1 causal Conv3d decode on torch/cuDNN convolutions, rank 0" if tok is not None else "skipped"}}))
+                       "vae": ("Wan2.1 causal Conv3d decode (cuDNN convolutions)" + (f", {world} row bands with halo exchange" if world > 1 else ""))
+                       if tok is not None else "skipped"}}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -208,6 +208,11 @@ class Text2WorldModelRectifiedFlow(nn.Module):
 
     @torch.no_grad()
     def decode(self, latent: torch.Tensor) -> torch.Tensor:
+        """Latent -> pixels. Under context parallelism every rank holds the gathered latent after sampling; the ranks
+        of the group then decode one horizontal band of the frame each (exact, neighbours exchange boundary rows)
+        and all of them return the whole video."""
+        if self.cp_group is not None and cp._size_rank(self.cp_group)[0] > 1 and hasattr(self.tokenizer, "decode_parallel"):
+            return self.tokenizer.decode_parallel(latent, self.cp_group)
         return self.tokenizer.decode(latent)
 
     def get_data_and_condition(self, batch: Dict) -> Tuple[Optional[torch.Tensor], torch.Tensor, Text2WorldCondition]:

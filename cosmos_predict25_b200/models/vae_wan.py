@@ -14,8 +14,9 @@ temporal up-sampler is skipped on the first chunk); encode is deterministic (mu 
 (mu - mean) / std scaling.
 
 The streaming state is an explicit ``StreamState`` object keyed by module instead of a positional list that
-is threaded through every forward call. Convolutions run through ``ops.conv`` so the sm_100a implicit-GEMM
-kernel can take the decoder's hot layers.
+is threaded through every forward call. Convolutions run on cuDNN through torch. Under
+``vae_parallel.row_sharded`` the decoder works on a horizontal band of the frame per rank and swaps boundary
+rows with its neighbours (``Wan2pt1VAEInterface.decode_parallel``).
 """
 
 from __future__ import annotations
@@ -25,6 +26,8 @@ from typing import Dict, List, Optional, Sequence
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
+
+from . import vae_parallel
 
 CACHE_T = 2
 
@@ -71,6 +74,10 @@ class CausalConv3d(nn.Conv3d):
         if cache_x is not None and pad[4] > 0:
             x = torch.cat([cache_x.to(x.device, x.dtype), x], dim=2)
             pad[4] -= cache_x.shape[2]
+        if pad[2] > 0 and vae_parallel.active() is not None:
+            # row-sharded decode: the neighbours' boundary rows stand in for the padding along H
+            x = vae_parallel.exchange_rows(x, 3, pad[2])
+            pad[2] = pad[3] = 0
         x = F.pad(x, pad)
         return super().forward(x)
 
@@ -139,7 +146,13 @@ class Resample(nn.Module):
                 x = torch.stack((x[:, 0], x[:, 1]), 3).reshape(b, c, t * 2, h, w)
         t = x.shape[2]
         x = x.permute(0, 2, 1, 3, 4).reshape(b * t, x.shape[1], h, w)
-        x = self.resample(x)
+        if vae_parallel.active() is not None and self.mode in ("upsample2d", "upsample3d"):
+            conv = self.resample[1]
+            x = vae_parallel.exchange_rows(self.resample[0](x), 2, 1)
+            x = F.conv2d(x, conv.weight, conv.bias, padding=(0, 1))
+        else:
+            assert vae_parallel.active() is None or self.mode == "none", "row sharding covers the decoder only"
+            x = self.resample(x)
         x = x.reshape(b, t, *x.shape[1:]).permute(0, 2, 1, 3, 4)
         if self.mode == "downsample3d" and state is not None:
             prev = state.get(self)
@@ -185,6 +198,8 @@ class AttentionBlock(nn.Module):
         y = x.permute(0, 2, 1, 3, 4).reshape(b * t, c, h, w)
         y = self.norm(y)
         q, k, v = self.to_qkv(y).reshape(b * t, 1, c * 3, -1).permute(0, 1, 3, 2).contiguous().chunk(3, dim=-1)
+        if vae_parallel.active() is not None:  # local rows attend to the whole frame
+            k, v = vae_parallel.gather_tokens(k, 2), vae_parallel.gather_tokens(v, 2)
         y = F.scaled_dot_product_attention(q, k, v)
         y = y.squeeze(1).permute(0, 2, 1).reshape(b * t, c, h, w)
         y = self.proj(y)
@@ -407,6 +422,15 @@ class Wan2pt1VAEInterface(VideoTokenizerInterface):
         elif n <= self.video_mean.shape[2]:
             latent = latent * self.video_std[:, :, :n].type_as(latent) + self.video_mean[:, :, :n].type_as(latent)
         return self.model.decode(latent, self.scale, clear_decoder_cache=not self.keep_decoder_cache)
+
+    @torch.no_grad()
+    def decode_parallel(self, latent: torch.Tensor, group, dst: Optional[int] = None) -> Optional[torch.Tensor]:
+        """``decode`` with the frame split into horizontal bands over ``group`` (every rank passes the same latent).
+        Exact: neighbours exchange boundary rows before every spatial convolution. Falls back to ``decode`` when
+        the latent rows do not divide over the group. With ``dst`` only that rank of the group gets the video."""
+        if not vae_parallel.can_shard(latent.shape[3], group):
+            return self.decode(latent)
+        return vae_parallel.decode_row_sharded(self.decode, latent, group, dst)
 
     def get_latent_num_frames(self, num_pixel_frames: int) -> int:
         return 1 + (num_pixel_frames - 1) // 4

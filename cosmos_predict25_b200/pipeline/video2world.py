@@ -6,8 +6,8 @@ pre-process the conditioning image / video into a uint8 clip, compute prompt and
 sample 35 UniPC steps with classifier-free guidance, decode to pixels in [-1, 1].
 
 Differences by design: cond / uncond run as one batch-2 forward with the text context and cross-attention K/V
-cached across the 35 steps; the VAE decode runs on one rank per context-parallel group (rank 0) instead of on all
-of them redundantly.
+cached across the 35 steps; the VAE decode is split into horizontal bands over the context-parallel group
+(exact: boundary rows are exchanged) instead of being repeated on every rank.
 """
 
 from __future__ import annotations

@@ -275,3 +275,35 @@ def test_parallel_dims_layout():
     assert 1.7e15 < f < 2.2e15                                    # ~1.9 PFLOP per 2B forward at 84,480 tokens
     assert abs(mfu(f * 3, 8.0, 1, 2.25e15) - f * 3 / 8.0 / 2.25e15) < 1e-12
     assert get_num_flop_per_token(7_000_000_000, 28, 28, 128, 4096) == 6 * 7_000_000_000 + 12 * 28 * 28 * 128 * 4096
+
+
+# ------------------------------------------------------------------------------------------------
+def _vae_row_sharded(rank, world, tmp):
+    """Row-sharded VAE decode with halo exchange equals the single-rank decode (attention block included)."""
+    from cosmos_predict25_b200.models.vae_wan import Wan2pt1VAEInterface
+    torch.manual_seed(0)
+    tok = Wan2pt1VAEInterface(device="cpu", dtype=torch.float32, dim=8)
+    for p in tok.model.parameters():            # the attention projection starts at zero: make it count
+        if p.abs().sum() == 0:
+            torch.nn.init.normal_(p, std=0.05)
+    torch.manual_seed(1)
+    lat = torch.randn(1, 16, 3, 2 * world, 6)
+    full = tok.decode(lat)
+    got = tok.decode_parallel(lat, dist.group.WORLD)
+    assert got.shape == full.shape == (1, 3, 9, 16 * world, 48)
+    assert (got - full).abs().max() < 1e-4 * max(1.0, full.abs().max().item())
+    only0 = tok.decode_parallel(lat, dist.group.WORLD, dst=0)
+    assert (only0 is None) == (rank != 0)
+    if rank == 0:
+        assert torch.equal(only0, got)
+    # rows that do not divide over the group: plain decode on every rank
+    odd = tok.decode_parallel(torch.randn(1, 16, 1, 3, 4), dist.group.WORLD)
+    assert odd.shape == (1, 3, 1, 24, 32)
+
+
+def test_vae_decode_row_sharded_matches_single_rank():
+    run_distributed("_vae_row_sharded", world=2)
+
+
+def test_vae_decode_row_sharded_three_ranks():
+    run_distributed("_vae_row_sharded", world=3)
