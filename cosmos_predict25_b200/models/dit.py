@@ -258,6 +258,8 @@ class Attention(nn.Module):
         self.v_proj = FusedLinear(context_dim, inner)
         self.output_proj = FusedLinear(inner, query_dim)
         self.cp_group = None
+        self.sparse_op = None      # NeighborhoodAttention in blocks switched to sparse self-attention
+        self.video_size = None     # (T, H, W) of the whole token grid, set by the network before the blocks run
 
     def init_weights(self):
         _trunc_normal_(self.q_proj.weight, 1.0 / math.sqrt(self.query_dim))
@@ -266,6 +268,22 @@ class Attention(nn.Module):
         _trunc_normal_(self.output_proj.weight, 1.0 / math.sqrt(self.n_heads * self.head_dim))
         self.q_norm.reset_parameters()
         self.k_norm.reset_parameters()
+
+    def _sparse_forward(self, x, rope, return_pre_proj):
+        """Self-attention through the neighbourhood operator. Under context parallelism q/k/v are exchanged to
+        (whole sequence, local heads) first, like the reference's a2a wrapper around NATTEN
+        (minimal_v4_dit.py:1176-1192), and the output is exchanged back."""
+        B, S, _ = x.shape
+        q = ops.rmsnorm_rope(self.q_proj(x).view(B, S, self.n_heads, self.head_dim), self.q_norm.weight, rope, self.q_norm.eps)
+        k = ops.rmsnorm_rope(self.k_proj(x).view(B, S, self.n_heads, self.head_dim), self.k_norm.weight, rope, self.k_norm.eps)
+        v = self.v_proj(x).view(B, S, self.n_heads, self.head_dim)
+        if self.cp_group is not None and ulysses.group_size_rank(self.cp_group)[0] > 1:
+            q, k, v = (ulysses._SeqToHead.apply(t, self.cp_group) for t in (q, k, v))
+            o = ulysses._HeadToSeq.apply(self.sparse_op(q, k, v, self.video_size), self.cp_group)
+        else:
+            o = self.sparse_op(q, k, v, self.video_size)
+        o = o.reshape(B, S, self.n_heads * self.head_dim)
+        return o if return_pre_proj else self.output_proj(o)
 
     def _plain_projections(self) -> bool:
         return all(type(p) is FusedLinear and p.bias is None and p.weight.dtype == torch.bfloat16
@@ -282,6 +300,8 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, context: Optional[torch.Tensor] = None, rope=None,
                 kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, return_pre_proj: bool = False):
         B, S, _ = x.shape
+        if self.is_selfattn and self.sparse_op is not None and self.video_size is not None:
+            return self._sparse_forward(x, rope, return_pre_proj)
         if (self.is_selfattn and self.cp_group is not None and self._plain_projections()
                 and ulysses.projected_attention_available(x, self.cp_group, self.head_dim)):
             # inference under context parallelism: the sequence->head exchange is the epilogue of the q/k/v GEMMs
@@ -556,12 +576,17 @@ class CosmosDiT(nn.Module):
 
         x = x.view(B, T, H * W, D)
         from .checkpointing import run_block
+        for block in self.blocks:
+            block.self_attn.video_size = (T * cp_size, H, W)
 
         for i, block in enumerate(self.blocks):
             kv = cross_kv[i] if cross_kv else None
             x = run_block(block, cfg.checkpoint_mode if self.training else "none", x, emb, context, rope, lora, extra, kv)
         out = self.final_layer(x, emb, lora).view(B, T, H, W, -1)
         return self.unpatchify(out)
+
+    def use_sparse_attention(self, n_dense_blocks: int = 0, natten_parameters=None) -> "CosmosDiT":
+        return replace_selfattn_op_with_sparse_attn_op(self, n_dense_blocks, natten_parameters)
 
     def unpatchify(self, x_B_T_H_W_M):
         """``B T H W (p1 p2 t C) -> B C (T t) (H p1) (W p2)``."""
@@ -607,3 +632,37 @@ def dit_tiny(**kw) -> DiTConfig:
 
 
 NET_PRESETS = {"2B": dit_2b, "14B": dit_14b, "7B": dit_7b, "mini": dit_mini, "tiny": dit_tiny}
+
+
+def replace_selfattn_op_with_sparse_attn_op(model, n_dense_blocks: int = 0, natten_parameters=None):
+    """Switch the self-attention of DiT blocks to neighbourhood attention
+    (minimal_v4_dit.py:1739-1812 of the reference). ``natten_parameters`` is one dict for all sparse blocks or a list
+    with one entry per block (None keeps a block dense). ``n_dense_blocks``: -1 leaves the model alone; 0 makes every
+    block sparse; 1 keeps the middle block dense; n > 1 keeps n blocks dense, spread evenly from first to last."""
+    from ..modules.neighborhood_attn import NeighborhoodAttention
+    if n_dense_blocks == -1:
+        return model
+    if natten_parameters is None:
+        raise ValueError("natten_parameters is required when n_dense_blocks > -1")
+    n = len(model.blocks)
+    if isinstance(natten_parameters, (list, tuple)):
+        if len(natten_parameters) != n:
+            raise ValueError(f"got {len(natten_parameters)} parameter sets for {n} blocks")
+        if n_dense_blocks > 0:
+            raise ValueError("a per-block list already says which blocks stay dense: n_dense_blocks must be 0")
+        per_block = list(natten_parameters)
+    else:
+        if n_dense_blocks >= n:
+            raise ValueError(f"n_dense_blocks ({n_dense_blocks}) must be less than the number of blocks ({n})")
+        dense = set()
+        if n_dense_blocks == 1:
+            dense.add(n // 2)
+        elif n_dense_blocks > 1:
+            dense.update(int(i) for i in torch.linspace(0, n - 1, n_dense_blocks).long().tolist())
+        per_block = [None if i in dense else natten_parameters for i in range(n)]
+    for i, (block, params) in enumerate(zip(model.blocks, per_block)):
+        if params is not None:
+            layer = dict(params)
+            layer["layer_id"] = i
+            block.self_attn.sparse_op = NeighborhoodAttention(layer, base_attn_op=ops.attention)
+    return model

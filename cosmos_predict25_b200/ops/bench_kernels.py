@@ -130,6 +130,17 @@ def main():
             # useful work: S, tS (2 GEMMs), P V (forward), A V, P tV = 6 GEMM units of 2 S^2 D H each
             add("fa_jvp tcgen05 (forward + tangent pass)", f"S={N} H={heads}",
                 time_ms(lambda: ops.fa_jvp(q, k, v, tq, tk, tv, scale), iters=3, warmup=1), 3.0 * fl)
+        if hasattr(ops, "fa_fwd_na") and N == 84480:
+            # neighbourhood attention at the reference's tuned 720p configuration: grid 24 x 44 x 80 tokens, window (24, 12, 24),
+            # stride (1, 4, 8); "useful" FLOPs count visible keys only (window volume per query)
+            from ..modules import neighborhood_attn as na
+            vs, win, st = (24, 44, 80), (24, 12, 24), (1, 4, 8)
+            plan = na.tile_plan(vs, win, st, (False, False, False), q.device)
+            qt, kt, vt = (plan.to_tiles(t) for t in (q, k, v))
+            fl_na = 4.0 * N * (win[0] * win[1] * win[2]) * HD * heads
+            add("fa_fwd_na tcgen05 (tile-sparse neighbourhood attention)", f"grid={vs} window={win} stride={st} H={heads}",
+                time_ms(lambda: ops.fa_fwd_na(qt, kt, vt, scale, plan.kv_idx, plan.kv_cnt, plan.bt, plan.bh, plan.bw), iters=3, warmup=1),
+                fl_na, note=f"visited key tiles: {plan.visited_fraction:.3f} of dense; dense fa_fwd above is the baseline")
         if hasattr(ops, "red_f32_bench"):
             # L2 reduction rate that bounds the dQ accumulation of the single-pass backward: one head's dQ matrix [S, 128] fp32,
             # 660 key tiles adding into it = the traffic of one head of the S=84480 problem

@@ -56,6 +56,37 @@ Tensor fa_fwd_scatter_seq_peer(const Tensor& q, const Tensor& k, const Tensor& v
   return lse;
 }
 
+// Neighbourhood attention on tile-ordered tokens (128 consecutive rows = one 4x4x8 tile of the T x H x W grid).
+// kv_idx [n_blocks, max_n] int32, kv_cnt [n_blocks] int32 (n_blocks = ceil(n_tiles / 2)); bt/bh/bw: uint8 visibility tables
+// [T, nT], [H, nH], [W, nW].  Returns (o, lse).
+std::tuple<Tensor, Tensor> fa_fwd_na(const Tensor& q, const Tensor& k, const Tensor& v, double scale, const Tensor& kv_idx,
+                                     const Tensor& kv_cnt, const Tensor& bt, const Tensor& bh, const Tensor& bw) {
+  check_qkv(q, "q");
+  check_qkv(k, "k");
+  check_qkv(v, "v");
+  TORCH_CHECK(q.sizes() == k.sizes() && k.sizes() == v.sizes(), "neighbourhood attention is self-attention: equal shapes");
+  const int B = (int)q.size(0), S = (int)q.size(1), H = (int)q.size(2);
+  TORCH_CHECK(S % 128 == 0, "sequence must be whole 128-token tiles");
+  const int n_tiles = S / 128, n_blocks = (n_tiles + 1) / 2;
+  for (const Tensor* t : {&kv_idx, &kv_cnt})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "tile lists must be contiguous CUDA int32");
+  for (const Tensor* t : {&bt, &bh, &bw})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kByte && t->is_contiguous() && t->dim() == 2, "visibility tables: CUDA uint8 2-D");
+  TORCH_CHECK(kv_idx.dim() == 2 && kv_idx.size(0) == n_blocks && kv_cnt.numel() == n_blocks, "one tile list per query block");
+  const int nT = (int)bt.size(1), nH = (int)bh.size(1), nW = (int)bw.size(1);
+  TORCH_CHECK((int64_t)nT * nH * nW == n_tiles && bt.size(0) == 4 * nT && bh.size(0) == 4 * nH && bw.size(0) == 8 * nW,
+              "tables do not match the tile grid");
+  c10::cuda::CUDAGuard g(q.device());
+  Tensor o = at::empty_like(q);
+  Tensor lse = at::empty({B, H, S}, q.options().dtype(at::kFloat));
+  const int rc = cb200_fa_fwd_na(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, S, H, (float)scale,
+                                 kv_idx.data_ptr<int>(), kv_cnt.data_ptr<int>(), (int)kv_idx.size(1), bt.data_ptr<uint8_t>(),
+                                 bh.data_ptr<uint8_t>(), bw.data_ptr<uint8_t>(), nT, nH, nW, cb200_error_word(q.get_device()),
+                                 at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "fa_fwd_na launch failed with code ", rc);
+  return {o, lse};
+}
+
 std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale) {
   return fa_fwd_variant(q, k, v, scale, 0);
 }
@@ -137,6 +168,8 @@ void register_attention_ops(torch::Library& m) {
   // Schemas only: the kernels are registered under the CUDA dispatch key below so that dispatch modes (selective
   // activation checkpointing keeps the attention output by intercepting this op) see the call.
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)");
+  m.def("fa_fwd_na(Tensor q, Tensor k, Tensor v, float scale, Tensor kv_idx, Tensor kv_cnt, Tensor bt, Tensor bh, Tensor bw) -> "
+        "(Tensor, Tensor)", &fa_fwd_na);
   m.def("fa_fwd_scatter_seq_peer(Tensor q, Tensor k, Tensor v, float scale, int[] out_ptrs, int rank) -> Tensor",
         &fa_fwd_scatter_seq_peer);
   m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");

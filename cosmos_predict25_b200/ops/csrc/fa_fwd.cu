@@ -73,11 +73,24 @@ struct SeqScatter {
   int P, rank, S_loc;
 };
 
-template <int POLY_MOD, bool PACKED>
+// Neighbourhood (tile-sparse) attention.  The sequence is a T x H x W token grid stored tile by tile: 128 consecutive rows
+// are one 4 x 4 x 8 (t, h, w) tile, tiles in (tile_t, tile_h, tile_w) row-major order.  A CTA (two query tiles) visits only
+// the key tiles of its list; inside a visited tile a key is visible to a query iff it is visible along each axis, which
+// three byte tables give: bit i of bt[t_query * nT + tile_t_key] says whether key plane i of that tile is visible, etc.
+struct NaParams {
+  const int* kv_idx;        // [n_blocks, max_n] key-tile indices per query block (ascending), nullptr: dense attention
+  const int* kv_cnt;        // [n_blocks] >= 1
+  const uint8_t* bt;        // [T, nT]
+  const uint8_t* bh;        // [H, nH]
+  const uint8_t* bw;        // [W, nW]
+  int max_n, nT, nH, nW;
+};
+
+template <int POLY_MOD, bool PACKED, bool NA>
 __global__ void __launch_bounds__(fa::kThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, int Sq, int Skv, int H,
-              float scale_log2, SeqScatter sc, int* __restrict__ err) {
+              float scale_log2, SeqScatter sc, NaParams na, int* __restrict__ err) {
   using namespace fa;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -96,7 +109,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int h = blockIdx.y, b = blockIdx.z;
   const int q_base = blockIdx.x * 2 * BQ;
-  const int n_kv = (Skv + BKV - 1) / BKV;
+  const int n_kv = NA ? na.kv_cnt[blockIdx.x] : (Skv + BKV - 1) / BKV;
+  const int* kv_list = NA ? na.kv_idx + (size_t)blockIdx.x * na.max_n : nullptr;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -137,7 +151,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!mbar_wait(&r_empty[slot], ph ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&r_full[slot], kTileBytes);
         const CUtensorMap* tm = (n & 1) ? &tm_v : &tm_k;
-        for (int c = 0; c < 2; ++c) tma_load_4d(sR + slot * kTileBytes + c * kHalfBytes, tm, &r_full[slot], c * 64, h, (n >> 1) * BKV, b);
+        const int kv_tile = NA ? kv_list[n >> 1] : (n >> 1);
+        for (int c = 0; c < 2; ++c) tma_load_4d(sR + slot * kTileBytes + c * kHalfBytes, tm, &r_full[slot], c * 64, h, kv_tile * BKV, b);
         if (++slot == kRing) { slot = 0; ph ^= 1; }
       }
       if (!ok) { atomicCAS(err, 0, 11); *abort_flag = 1; }
@@ -218,7 +233,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     float m_ref = -INFINITY;  // reference maximum used in the exponent (log2 domain)
     float l = 0.f;
     bool ok = true;
+    // neighbourhood mode: rows of the byte tables that belong to this query (clamped for rows past the sequence end)
+    const uint8_t *row_bt = nullptr, *row_bh = nullptr, *row_bw = nullptr;
+    if (NA) {
+      const int qr = q_row < Sq ? q_row : Sq - 1;
+      const int qt = qr >> 7, loc = qr & 127;
+      const int qT = qt / (na.nH * na.nW), qH = (qt / na.nW) % na.nH, qW = qt % na.nW;
+      row_bt = na.bt + (size_t)(qT * 4 + (loc >> 5)) * na.nT;
+      row_bh = na.bh + (size_t)(qH * 4 + ((loc >> 3) & 3)) * na.nH;
+      row_bw = na.bw + (size_t)(qW * 8 + (loc & 7)) * na.nW;
+    }
     for (int j = 0; j < n_kv; ++j) {
+      uint32_t vis[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};  // visibility of the 128 keys of this tile
+      if (NA) {
+        const int kt = kv_list[j];
+        const uint32_t mt = row_bt[kt / (na.nH * na.nW)], mh = row_bh[(kt / na.nW) % na.nH], mw = row_bw[kt % na.nW];
+        uint32_t plane = 0;                       // 32 keys of one t-plane: bit (lh * 8 + lw)
+#pragma unroll
+        for (int lh = 0; lh < 4; ++lh) plane |= ((mh >> lh) & 1u) ? (mw << (8 * lh)) : 0u;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) vis[c] = ((mt >> c) & 1u) ? plane : 0u;
+      }
       if (!mbar_wait(&s_full[t], j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t r[4][32];
@@ -227,13 +262,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tmem_ld32(tS + 64, r[2]);
       tmem_ld32(tS + 96, r[3]);
       tmem_ld_wait();
-      const int n_valid = Skv - j * BKV;
+      const int n_valid = NA ? BKV : Skv - j * BKV;   // neighbourhood mode works on whole tiles
       if (n_valid < BKV) {
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i >= n_valid) r[c][i] = 0xff800000u;  // -inf
+      }
+      if (NA && __any_sync(0xffffffffu, (vis[0] & vis[1] & vis[2] & vis[3]) != 0xffffffffu)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!((vis[c] >> i) & 1u)) r[c][i] = 0xff800000u;
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -262,7 +304,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tmem_st_wait();
       }
       // probabilities -> bf16 pairs over the first 64 columns of the score buffer
-      const float neg_m = -m_ref;
+      // a row that has seen no visible key yet keeps m_ref = -inf: use 0 so that its masked scores give exp2(-inf) = 0
+      const float neg_m = (NA && m_ref == -INFINITY) ? 0.f : -m_ref;
       float2 lsum2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -343,11 +386,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 using namespace cb200;
 
-template <int POLY_MOD, bool PACKED>
+template <int POLY_MOD, bool PACKED, bool NA = false>
 static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, float* lse, int B, int Sq,
-                         int Skv, int H, float scale, const SeqScatter& sc, int* err, cudaStream_t st) {
+                         int Skv, int H, float scale, const SeqScatter& sc, int* err, cudaStream_t st,
+                         const NaParams& na = NaParams{}) {
   using namespace fa;
-  auto kern = fa_fwd_kernel<POLY_MOD, PACKED>;
+  auto kern = fa_fwd_kernel<POLY_MOD, PACKED, NA>;
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
@@ -355,14 +399,15 @@ static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
     attr = true;
   }
   dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
-  kern<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, sc, err);
+  kern<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, sc, na, err);
   return (int)cudaGetLastError();
 }
 
 // q [B, Sq, H, 128]; k, v [B, Skv, H, 128]; o like q; lse [B, H, Sq] fp32.
 // variant: 0 = default; 1..: tuning variants (all produce the same result within rounding)
 static int fa_fwd_dispatch(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,
-                           float scale, int variant, const SeqScatter& sc, int* err, cudaStream_t st) {
+                           float scale, int variant, const SeqScatter& sc, int* err, cudaStream_t st,
+                           const NaParams* na = nullptr) {
   using namespace fa;
   CUtensorMap tq, tk, tv;
   auto make = [&](CUtensorMap* m, const void* p, int S) {
@@ -377,6 +422,7 @@ static int fa_fwd_dispatch(const void* q, const void* k, const void* v, void* o,
   if (rc) return rc;
   rc = make(&tv, v, Skv);
   if (rc) return rc;
+  if (na != nullptr) return launch_fa_fwd<0, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st, *na);
   switch (variant) {
     case 1: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
     case 2: return launch_fa_fwd<0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
@@ -403,4 +449,14 @@ extern "C" int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void
   sc.rank = rank;
   sc.S_loc = Sq / P;
   return fa_fwd_dispatch(q, k, v, nullptr, lse, B, Sq, Skv, H, scale, 0, sc, err, st);
+}
+
+// Neighbourhood attention on a tile-ordered token grid (see NaParams): self-attention, S = nT * nH * nW * 128 rows.
+extern "C" int cb200_fa_fwd_na(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, float scale,
+                               const int* kv_idx, const int* kv_cnt, int max_n, const uint8_t* bt, const uint8_t* bh,
+                               const uint8_t* bw, int nT, int nH, int nW, int* err, cudaStream_t st) {
+  if (nT < 1 || nH < 1 || nW < 1 || (long long)nT * nH * nW * 128 != (long long)S || max_n < 1) return -31;
+  NaParams na{kv_idx, kv_cnt, bt, bh, bw, max_n, nT, nH, nW};
+  SeqScatter sc{};
+  return fa_fwd_dispatch(q, k, v, o, lse, B, S, S, H, scale, 0, sc, err, st, &na);
 }

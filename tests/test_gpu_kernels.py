@@ -183,6 +183,25 @@ def test_flash_attention_fwd(B, Sq, Skv, H):
     _close(o, orf, 2e-2, 2e-2, "o")
 
 
+@pytest.mark.parametrize("vs,window,stride,causal", [
+    ((8, 8, 16), (4, 4, 8), 1, False),                       # 8 tiles, every visited tile partly masked
+    ((4, 12, 24), (4, 8, 16), (1, 4, 8), False),             # 9 tiles (odd: last CTA has one query tile), stride = tile
+    ((8, 8, 16), (3, 5, 7), (1, 2, 3), (True, False, False)),  # causal in time, odd windows
+    ((4, 4, 8), (4, 4, 8), 1, False),                        # one tile, whole-axis windows = dense attention
+])
+def test_neighborhood_attention_kernel(vs, window, stride, causal):
+    from cosmos_predict25_b200.modules import neighborhood_attn as na
+    torch.manual_seed(12)
+    L, H = vs[0] * vs[1] * vs[2], 3
+    q, k, v = (torch.randn(2, L, H, 128, device=DEV).bfloat16() for _ in range(3))
+    with torch.no_grad():
+        assert na.tile_kernel_supported(q, vs, (1, 1, 1))
+        got = na.neighborhood_attention(q, k, v, vs, window, stride, 1, causal)
+        _no_kernel_error()
+        want = na.neighborhood_attention_reference(q.float(), k.float(), v.float(), vs, window, stride, 1, causal)
+    _close(got, want, 2e-2, 2e-2, "neighbourhood attention")
+
+
 def test_flash_attention_large_scores_rescale():
     """Rows whose maximum keeps growing across key tiles exercise the TMEM rescale path."""
     torch.manual_seed(9)
