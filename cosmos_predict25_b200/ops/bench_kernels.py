@@ -115,7 +115,7 @@ def main():
         add("fa_fwd tcgen05", f"S={N} H={heads} hd=128", time_ms(lambda: ops.fa_fwd(q, k, v, scale), iters=3, warmup=1), fl)
         add("cudnn sdpa fwd (twin)", f"S={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, k, v, scale), iters=3, warmup=1), fl)
         if args.variants and hasattr(ops, "fa_fwd_variant"):
-            for var in range(1, 6):
+            for var in range(1, 7):
                 add(f"fa_fwd tcgen05 variant {var}", f"S={N} H={heads}",
                     time_ms(lambda: ops.fa_fwd_variant(q, k, v, scale, var), iters=3, warmup=1), fl)
         if hasattr(ops, "fa_bwd"):

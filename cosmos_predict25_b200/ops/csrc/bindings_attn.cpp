@@ -30,8 +30,14 @@ std::tuple<Tensor, Tensor> fa_fwd_variant(const Tensor& q, const Tensor& k, cons
   const int B = (int)q.size(0), Sq = (int)q.size(1), H = (int)q.size(2), Skv = (int)k.size(1);
   Tensor o = at::empty_like(q);
   Tensor lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
-  const int rc = cb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
-                              (float)scale, (int)variant, cb200_error_word(q.get_device()), at::cuda::getCurrentCUDAStream().stream());
+  // variant 6: the kernel with two threads per query row (fa_fwd_split.cu)
+  const int rc = variant == 6
+                     ? cb200_fa_fwd_split(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
+                                          (float)scale, nullptr, 0, 0, cb200_error_word(q.get_device()),
+                                          at::cuda::getCurrentCUDAStream().stream())
+                     : cb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
+                                    (float)scale, (int)variant, cb200_error_word(q.get_device()),
+                                    at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "fa_fwd launch failed with code ", rc);
   return {o, lse};
 }

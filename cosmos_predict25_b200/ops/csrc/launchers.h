@@ -46,6 +46,8 @@ int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void* v, const 
 int cb200_fa_fwd_na(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, float scale,
                     const int* kv_idx, const int* kv_cnt, int max_n, const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT,
                     int nH, int nW, int* err, cudaStream_t st);
+int cb200_fa_fwd_split(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
+                       const int64_t* out_ptrs, int P, int rank, int* err, cudaStream_t st);
 int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
                  int variant, int* err, cudaStream_t st);
 }

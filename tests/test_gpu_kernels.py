@@ -202,6 +202,21 @@ def test_neighborhood_attention_kernel(vs, window, stride, causal):
     _close(got, want, 2e-2, 2e-2, "neighbourhood attention")
 
 
+@pytest.mark.parametrize("B,Sq,Skv,H", [(1, 256, 256, 2), (2, 512, 384, 3), (1, 1000, 999, 2), (1, 300, 15, 4), (1, 300, 70, 2),
+                                        (1, 2048, 4096, 2)])
+def test_flash_attention_fwd_two_threads_per_row(B, Sq, Skv, H):
+    torch.manual_seed(9)
+    q = torch.randn(B, Sq, H, 128, device=DEV).bfloat16() * 2      # larger scores: the running maximum moves
+    k = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
+    v = torch.randn(B, Skv, H, 128, device=DEV).bfloat16()
+    scale = 1.0 / math.sqrt(128)
+    o, lse = _ops().fa_fwd_variant(q, k, v, scale, 6)
+    _no_kernel_error()
+    orf, lser = ref.attention(q.float(), k.float(), v.float(), scale)
+    _close(lse, lser, 2e-2, 1e-3, "lse")
+    _close(o, orf, 2e-2, 2e-2, "o")
+
+
 def test_flash_attention_large_scores_rescale():
     """Rows whose maximum keeps growing across key tiles exercise the TMEM rescale path."""
     torch.manual_seed(9)
