@@ -32,6 +32,10 @@ def main() -> int:
     ap.add_argument("--guidance", type=float, default=7.0)
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"])
+    ap.add_argument("--sparse-window", type=int, nargs=3, default=None, metavar=("T", "H", "W"),
+                    help="switch self-attention to neighbourhood attention with this window (e.g. 24 12 24)")
+    ap.add_argument("--sparse-stride", type=int, nargs=3, default=(1, 4, 8))
+    ap.add_argument("--dense-blocks", type=int, default=0, help="blocks that keep dense self-attention in sparse mode")
     args = ap.parse_args()
     rank, world, local_rank = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     dev = torch.device("cuda", local_rank)
@@ -53,6 +57,8 @@ def main() -> int:
     model = Video2WorldModelRectifiedFlow(cfg, device=dev, cp_group=groups.cp if world > 1 else None)
     model.net.to(torch.bfloat16)
     model.eval()
+    if args.sparse_window is not None:
+        model.net.use_sparse_attention(args.dense_blocks, {"window_size": tuple(args.sparse_window), "stride": tuple(args.sparse_stride)})
     if world > 1:
         model.net.enable_context_parallel(groups.cp)
         if args.transport == "peer":
@@ -107,7 +113,9 @@ def main() -> int:
             "decoded_frames": frames, "gpu_launches_sampling": launches, "kernel_error": int(err),
             "config": {"model": f"cosmos-predict2.5-{args.model}-video2world", "steps": args.steps, "guidance": args.guidance,
                        "cfg": "batched cond/uncond (one batch-2 forward per step)", "latent_shape": [1, 16, args.frames, args.height, args.width],
-                       "parallelism": f"cp{world}", "transport": args.transport if world > 1 else "single",
+                       "parallelism": f"cp{world}",
+                       "self_attention": "dense" if args.sparse_window is None else
+                       f"neighbourhood window={tuple(args.sparse_window)} stride={tuple(args.sparse_stride)}, {args.dense_blocks} dense blocks", "transport": args.transport if world > 1 else "single",
                        "vae": ("Wan2.1 causal Conv3d decode (cuDNN convolutions)" + (f", {world} row bands with halo exchange" if world > 1 else ""))
                        if tok is not None else "skipped"}}))
     if world > 1:

@@ -55,7 +55,7 @@ struct SeqScatterS {
   int P, rank, S_loc;
 };
 
-__global__ void __maxnreg__(112)
+__global__ void __maxnreg__(96)
 fa_fwd_split_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, int Sq, int Skv, int H,
               float scale_log2, SeqScatterS sc, int* __restrict__ err) {
@@ -243,19 +243,7 @@ fa_fwd_split_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         m_ref = mx;
         l *= alpha;
       }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // rescale this thread's 64 output columns in TMEM
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tO + half * 64 + c * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tO + half * 64 + c * 32, o);
-        }
-        tmem_st_wait();
-      }
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, need);
       const float neg_m = -m_ref;
       float2 lsum2 = make_float2(0.f, 0.f);
 #pragma unroll
@@ -273,6 +261,18 @@ fa_fwd_split_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tmem_st16(tS + half * 32 + c * 16, pk);   // keys 64*half + 32*c + [0, 32) -> packed columns 32*half + 16*c + [0, 16)
       }
       l += lsum2.x + lsum2.y;
+      if (rescale) {
+        // rescale this thread's 64 output columns in TMEM (after the probabilities: the score registers are free by now)
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[16];
+          tmem_ld16(tO + half * 64 + c * 16, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st16(tO + half * 64 + c * 16, o);
+        }
+      }
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -298,19 +298,19 @@ fa_fwd_split_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         orow = reinterpret_cast<bf16*>(sc.ptrs[dst]) + (((size_t)b * sc.S_loc + s_loc) * (sc.P * H) + sc.rank * H + h) * HD;
       }
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tO + half * 64 + c * 32, o);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[16];
+        tmem_ld16(tO + half * 64 + c * 16, o);
         tmem_ld_wait();
         if (q_row < Sq) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 2; ++q) {
             uint4 ov;
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
               o2[i] = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + half * 64 + c * 32 + q * 8) = ov;
+            *reinterpret_cast<uint4*>(orow + half * 64 + c * 16 + q * 8) = ov;
           }
         }
       }
