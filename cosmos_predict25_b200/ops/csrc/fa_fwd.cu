@@ -15,9 +15,11 @@
 // core runs the other tile's P.V and next Q.K^T (ping-pong).
 //
 // Register budget decides the shape of this kernel: 10 warps leave 168 registers per thread, enough to hold a
-// full 128-column score row; a layout with two threads per row (18 warps, 96 registers) spilled and measured
-// 1.7x slower. Template switches keep two measured alternatives for the exponentials (a degree-4 polynomial
-// on the FMA pipe for one element in POLY_MOD, packed fp32x2 scale/subtract); the plain MUFU path is fastest.
+// full 128-column score row. The layout with two threads per row (18 warps, 96 registers, fa_fwd_split.cu) runs without
+// spills but measured 53.7 ms against 48.5 ms here at S = 84,480, H = 16: the per-tile pair barrier and the doubled
+// bookkeeping cost more than the shorter exponential chain saves. Template switches keep two measured alternatives for
+// the exponentials (a degree-4 polynomial on the FMA pipe for one element in POLY_MOD, packed fp32x2 scale/subtract);
+// the plain MUFU path is fastest.
 //
 // Online softmax keeps a reference maximum per row that is only moved when the running maximum grows
 // by more than 2^8; the output accumulator is rescaled in TMEM only then (rare after the first tiles).
@@ -346,21 +348,37 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const int dst = q_row / sc.S_loc, s_loc = q_row - dst * sc.S_loc;
         orow = reinterpret_cast<bf16*>(sc.ptrs[dst]) + (((size_t)b * sc.S_loc + s_loc) * (sc.P * H) + sc.rank * H + h) * HD;
       }
+      // The finished rows go through shared memory (this tile's Q buffer is free: its last Q.K^T has completed) so that the
+      // global stores are coalesced: 16 lanes cover one 256-byte row, a warp store is two contiguous 256-byte segments.
+      // That matters most when the destination is a peer's memory: NVLink moves 256-byte writes far better than 16-byte ones.
+      uint8_t* stage_warp = sQ + t * kTileBytes + quarter * (32 * 256);
+      uint8_t* stage_row = stage_warp + lane * 256;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
         tmem_ld32(tO + c * 32, o);
         tmem_ld_wait();
-        if (q_row < Sq) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 ov;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+        for (int q = 0; q < 4; ++q) {
+          uint4 ov;
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              o2[i] = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = ov;
-          }
+          for (int i = 0; i < 4; ++i)
+            o2[i] = __floats2bfloat162_rn(__uint_as_float(o[q * 8 + 2 * i]) * inv_l, __uint_as_float(o[q * 8 + 2 * i + 1]) * inv_l);
+          *reinterpret_cast<uint4*>(stage_row + (((c * 4 + q) ^ (lane & 7)) << 4)) = ov;
+        }
+      }
+      __syncwarp();
+      {
+        const unsigned long long dst_u = reinterpret_cast<unsigned long long>(orow);
+        const int row_ok = q_row < Sq;
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+          const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
+          const unsigned long long d = __shfl_sync(0xffffffffu, dst_u, r_src);
+          const int ok_row = __shfl_sync(0xffffffffu, row_ok, r_src);
+          const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4));
+          if (ok_row) *reinterpret_cast<uint4*>(d + chunk * 16) = v;
         }
       }
       if (q_row < Sq) LSE[((size_t)b * H + h) * Sq + q_row] = (m_ref + log2f(l)) * 0.6931471805599453f;

@@ -14,6 +14,9 @@
 //   warp  16    TMA producer
 //   warp  17    MMA issuer
 //
+// Measured on a B200 at S = 84,480, H = 16: 53.7 ms against 48.5 ms for the one-thread-per-row kernel, which therefore
+// stays the default; this variant is reachable as variant 6 of the forward operator and is kept tested.
+//
 // Hazard that fixes the order of operations: P (bf16) overwrites S columns [0, 64), which are the scores of keys 0..63,
 // i.e. of half 0.  Half 0 therefore keeps its 64 scores in registers, and nobody stores P before the pair barrier that
 // follows both halves' loads.

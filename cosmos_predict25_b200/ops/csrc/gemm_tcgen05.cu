@@ -34,7 +34,8 @@ constexpr int kABytes = BM * BK * 2;  // 16 KB
 constexpr int kBBytes = BN * BK * 2;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kGemmThreads = 192;
-constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kStageOutBytes = 4 * 32 * 256;  // head-scatter epilogue: one 32-row x 256-byte staging block per epilogue warp
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kStageOutBytes;
 
 // Ulysses exchange fused into the epilogue: the output [M, N] is a projection to H = N / 128 heads of a local sequence of S
 // tokens per batch item; head h of token (b, s) is normalised (optional per-head RMSNorm), rotated (optional rotate-half
@@ -191,6 +192,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         // ---- fused head scatter: this thread owns one token row; a 256-wide tile holds two complete heads
         // tcgen05.ld is warp-collective: every lane runs every load, rows past M only skip their stores
         const bool valid = row < M;
+        uint8_t* stage_warp = smem + kStages * kStageBytes + 256 + quarter * (32 * 256);
+        uint8_t* stage_row = stage_warp + lane * 256;
         {
           const int row_c = valid ? row : M - 1;
           const int b_idx = row_c / ep.hs.S, s_idx = row_c % ep.hs.S;
@@ -254,12 +257,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                   p0[j] = __floats2bfloat162_rn(a[q * 8 + 2 * j], a[q * 8 + 2 * j + 1]);
                   p1[j] = __floats2bfloat162_rn(bb[q * 8 + 2 * j], bb[q * 8 + 2 * j + 1]);
                 }
-                if (valid) {                                                   // plain stores: local or peer memory over NVLink
-                  *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o0;
-                  *reinterpret_cast<uint4*>(dst + 64 + c * 32 + q * 8) = o1;
-                }
+                // this thread's row goes to the warp's staging block, 16-byte chunks XOR-swizzled by the row (no bank conflicts)
+                *reinterpret_cast<uint4*>(stage_row + (((c * 4 + q) ^ (lane & 7)) << 4)) = o0;
+                *reinterpret_cast<uint4*>(stage_row + (((8 + c * 4 + q) ^ (lane & 7)) << 4)) = o1;
               }
             }
+            __syncwarp();
+            // write-out: 16 lanes cover one 256-byte head row, so every store instruction of the warp is two contiguous
+            // 256-byte segments (local memory or a peer's over NVLink) instead of 32 scattered 16-byte pieces
+            const unsigned long long dst_u = reinterpret_cast<unsigned long long>(dst);
+#pragma unroll 4
+            for (int it = 0; it < 16; ++it) {
+              const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
+              const unsigned long long d = __shfl_sync(0xffffffffu, dst_u, r_src);
+              const int ok_row = __shfl_sync(0xffffffffu, (int)valid, r_src);
+              const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4));
+              if (ok_row) *reinterpret_cast<uint4*>(d + chunk * 16) = v;
+            }
+            __syncwarp();
           }
         }
         tc_fence_before();
