@@ -214,12 +214,12 @@ def main():
         tok = global_batch * tokens_per_sample * args.steps
         value = tok / (ms / 1e3)
         line = {
-            "metric": "DiT training latent-tokens/s (2B Video2World, 720p x 93 frames, device-timed, max over ranks)",
+            "metric": f"DiT training latent-tokens/s ({args.model} Video2World, 720p x 93 frames, device-timed, max over ranks)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic latents + text embeddings, random-init weights", "impl": "ours",
             "config": {"model": f"cosmos-predict2.5-{args.model}-video2world", "global_batch": global_batch,
-                       "seq_len": tokens_per_sample, "parallelism": f"fsdp{dp}" + (f"xcp{args.cp}" if args.cp > 1 else ""),
+                       "seq_len": tokens_per_sample, "parallelism": (f"fsdp{world}" if args.cp == 1 else f"fsdp{world} (masters, moments, EMA, gradients sharded over all ranks) x cp{args.cp} x dp{dp}"),
                        "latent_shape": [1, 16, args.frames, args.height, args.width], "text_context": [1, 512, ctx_dim],
                        "activation_checkpointing": args.checkpoint, "optimizer": "AdamW fp32 masters + EMA",
                        "transport": args.transport if world > 1 else "single", "attention": F_ops.settings.attention,
