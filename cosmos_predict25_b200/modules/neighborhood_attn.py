@@ -19,11 +19,12 @@ Definition used, per axis of length L with window k, stride s, dilation d (k * d
 
 A key is visible to a query iff it is visible along all three axes (the 3-D window is the product of the 1-D ones).
 
-Execution on the GPU (inference, bf16, head_dim 128, dilation 1, T % 4 == H % 4 == W % 8 == 0): tokens are re-ordered
-so that 128 consecutive rows are one 4 x 4 x 8 tile of the grid; per pair of query tiles the host builds the list of
-key tiles that contain at least one visible key; the kernel walks only that list and masks inside a tile with three
-small bit tables (one per axis). With a stride that matches the tile (e.g. (1, 4, 8)) most visited tiles are fully
-visible and skip the masking. Everything else (CPU, autograd, dilation > 1, odd grid sizes) runs the dense-masked
+Execution on the GPU (inference, bf16, head_dim 128, dilation 1, T % 4 == H % 4 == W % 8 == 0): the kernel works on
+4 x 4 x 8 (t, h, w) tiles of the token grid, fetched by TMA as 5-D boxes straight from the natural [B, T*H*W, heads, D]
+layout (no re-ordering pass); per pair of query tiles the host builds the list of key tiles that contain at least one
+visible key; the kernel walks only that list, masks inside a tile with three small bit tables (one per axis) and writes
+each output row back to its natural position. With a stride that matches the tile (e.g. (1, 4, 8)) most visited tiles are
+fully visible and skip the masking. Everything else (CPU, autograd, dilation > 1, odd grid sizes) runs the dense-masked
 PyTorch definition, which is also the oracle of the kernel tests.
 """
 
@@ -143,7 +144,8 @@ class TilePlan:
         self.visited_fraction = float(cnt.sum()) / float(block_need.shape[0] * n_tiles)
 
     def to_tiles(self, x: torch.Tensor) -> torch.Tensor:
-        """[B, T*H*W, heads, D] in (t, h, w) order -> the same tokens tile by tile."""
+        """[B, T*H*W, heads, D] in (t, h, w) order -> the same tokens tile by tile (the order in which the kernel numbers
+        its rows; the kernel itself reads the natural layout, this helper serves the host-side checks)."""
         B, L, Hh, D = x.shape
         (nT, nH, nW), (tt, th, tw) = self.n, TILE
         return x.view(B, nT, tt, nH, th, nW, tw, Hh, D).permute(0, 1, 3, 5, 2, 4, 6, 7, 8).reshape(B, L, Hh, D)
@@ -182,10 +184,10 @@ def neighborhood_attention(q, k, v, video_size, window, stride=1, dilation=1, is
         return neighborhood_attention_reference(q, k, v, video_size, window, stride, dilation, is_causal, scale)
     from ..ops import native
     plan = tile_plan(video_size, window, stride, is_causal, q.device)
-    qt, kt, vt = (plan.to_tiles(x.contiguous()) for x in (q, k, v))
-    o, _ = native.load().fa_fwd_na(qt, kt, vt, scale, plan.kv_idx, plan.kv_cnt, plan.bt, plan.bh, plan.bw)
+    o, _ = native.load().fa_fwd_na(q.contiguous(), k.contiguous(), v.contiguous(), scale, plan.kv_idx, plan.kv_cnt,
+                                   plan.bt, plan.bh, plan.bw)
     native.count_launch()
-    return plan.from_tiles(o)
+    return o
 
 
 # --------------------------------------------------------------------------------------------- module

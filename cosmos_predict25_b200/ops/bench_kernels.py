@@ -136,7 +136,7 @@ def main():
             from ..modules import neighborhood_attn as na
             vs, win, st = (24, 44, 80), (24, 12, 24), (1, 4, 8)
             plan = na.tile_plan(vs, win, st, (False, False, False), q.device)
-            qt, kt, vt = (plan.to_tiles(t) for t in (q, k, v))
+            qt, kt, vt = q, k, v                                        # natural token order: the kernel tiles by itself
             fl_na = 4.0 * N * (win[0] * win[1] * win[2]) * HD * heads
             add("fa_fwd_na tcgen05 (tile-sparse neighbourhood attention)", f"grid={vs} window={win} stride={st} H={heads}",
                 time_ms(lambda: ops.fa_fwd_na(qt, kt, vt, scale, plan.kv_idx, plan.kv_cnt, plan.bt, plan.bh, plan.bw), iters=3, warmup=1),

@@ -62,7 +62,7 @@ Tensor fa_fwd_scatter_seq_peer(const Tensor& q, const Tensor& k, const Tensor& v
   return lse;
 }
 
-// Neighbourhood attention on tile-ordered tokens (128 consecutive rows = one 4x4x8 tile of the T x H x W grid).
+// Neighbourhood attention on a T x H x W token grid in natural (t, h, w) order; the kernel tiles it 4 x 4 x 8 by itself.
 // kv_idx [n_blocks, max_n] int32, kv_cnt [n_blocks] int32 (n_blocks = ceil(n_tiles / 2)); bt/bh/bw: uint8 visibility tables
 // [T, nT], [H, nH], [W, nW].  Returns (o, lse).
 std::tuple<Tensor, Tensor> fa_fwd_na(const Tensor& q, const Tensor& k, const Tensor& v, double scale, const Tensor& kv_idx,

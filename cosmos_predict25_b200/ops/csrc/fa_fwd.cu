@@ -75,8 +75,11 @@ struct SeqScatter {
   int P, rank, S_loc;
 };
 
-// Neighbourhood (tile-sparse) attention.  The sequence is a T x H x W token grid stored tile by tile: 128 consecutive rows
-// are one 4 x 4 x 8 (t, h, w) tile, tiles in (tile_t, tile_h, tile_w) row-major order.  A CTA (two query tiles) visits only
+// Neighbourhood (tile-sparse) attention.  The sequence is a T x H x W token grid in its natural (t, h, w) order; the kernel
+// works on 4 x 4 x 8 (t, h, w) tiles of it, which TMA fetches as 5-D boxes {64 channels, 1 head, 8 w, 4 h, 4 t} straight from
+// that layout (the 128 rows land in shared memory in (t, h, w) order of the tile, the same layout a [128, 64] box has), so no
+// re-ordering pass is needed; "row" below means the position in tile order: tile index * 128 + position in the tile, tiles
+// in (tile_t, tile_h, tile_w) row-major order.  A CTA (two query tiles) visits only
 // the key tiles of its list; inside a visited tile a key is visible to a query iff it is visible along each axis, which
 // three byte tables give: bit i of bt[t_query * nT + tile_t_key] says whether key plane i of that tile is visible, etc.
 struct NaParams {
@@ -143,9 +146,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
       mbar_arrive_expect_tx(q_full, 2 * kTileBytes);
-      for (int t = 0; t < 2; ++t)
-        for (int c = 0; c < 2; ++c)
-          tma_load_4d(sQ + t * kTileBytes + c * kHalfBytes, &tm_q, q_full, c * 64, h, q_base + t * BQ, b);
+      // neighbourhood mode: tile index -> coordinates of its 5-D box (w0, h0, b * T + t0)
+      auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int tile) {
+        if (NA) {
+          const int iT = tile / (na.nH * na.nW), iH = (tile / na.nW) % na.nH, iW = tile % na.nW;
+          for (int c = 0; c < 2; ++c) tma_load_5d(dst + c * kHalfBytes, tm, bar, c * 64, h, iW * 8, iH * 4, b * (na.nT * 4) + iT * 4);
+        } else {
+          for (int c = 0; c < 2; ++c) tma_load_4d(dst + c * kHalfBytes, tm, bar, c * 64, h, tile * BKV, b);
+        }
+      };
+      for (int t = 0; t < 2; ++t) load_tile(sQ + t * kTileBytes, &tm_q, q_full, blockIdx.x * 2 + t);
       bool ok = true;
       int slot = 0;
       uint32_t ph = 0;
@@ -153,8 +163,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!mbar_wait(&r_empty[slot], ph ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&r_full[slot], kTileBytes);
         const CUtensorMap* tm = (n & 1) ? &tm_v : &tm_k;
-        const int kv_tile = NA ? kv_list[n >> 1] : (n >> 1);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sR + slot * kTileBytes + c * kHalfBytes, tm, &r_full[slot], c * 64, h, kv_tile * BKV, b);
+        load_tile(sR + slot * kTileBytes, tm, &r_full[slot], NA ? kv_list[n >> 1] : (n >> 1));
         if (++slot == kRing) { slot = 0; ph ^= 1; }
       }
       if (!ok) { atomicCAS(err, 0, 11); *abort_flag = 1; }
@@ -343,7 +352,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.f / l;
-      bf16* orow = O + (((size_t)b * Sq + q_row) * H + h) * HD;
+      int out_row = q_row;   // position of this query in the output sequence
+      if (NA && q_row < Sq) {
+        const int qt = q_row >> 7, loc = q_row & 127;
+        const int tq = (qt / (na.nH * na.nW)) * 4 + (loc >> 5), hq = ((qt / na.nW) % na.nH) * 4 + ((loc >> 3) & 3), wq = (qt % na.nW) * 8 + (loc & 7);
+        out_row = (tq * (na.nH * 4) + hq) * (na.nW * 8) + wq;
+      }
+      bf16* orow = O + (((size_t)b * Sq + out_row) * H + h) * HD;
       if (sc.P > 0 && q_row < Sq) {
         const int dst = q_row / sc.S_loc, s_loc = q_row - dst * sc.S_loc;
         orow = reinterpret_cast<bf16*>(sc.ptrs[dst]) + (((size_t)b * sc.S_loc + s_loc) * (sc.P * H) + sc.rank * H + h) * HD;
@@ -381,7 +396,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (ok_row) *reinterpret_cast<uint4*>(d + chunk * 16) = v;
         }
       }
-      if (q_row < Sq) LSE[((size_t)b * H + h) * Sq + q_row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      if (q_row < Sq) LSE[((size_t)b * H + h) * Sq + out_row] = (m_ref + log2f(l)) * 0.6931471805599453f;
     } else if (lane == 0) {
       atomicCAS(err, 0, 13);
       *abort_flag = 1;
@@ -434,11 +449,18 @@ static int fa_fwd_dispatch(const void* q, const void* k, const void* v, void* o,
     const uint32_t box[4] = {64, 1, 128, 1};
     return make_tmap_bf16(m, p, 4, dims, strides, box);
   };
-  int rc = make(&tq, q, Sq);
+  auto make_grid = [&](CUtensorMap* m, const void* p) {   // [B*T, Hg, Wg, heads, 128] seen through 4 x 4 x 8 token boxes
+    const uint64_t Wg = (uint64_t)na->nW * 8, Hg = (uint64_t)na->nH * 4, Tg = (uint64_t)na->nT * 4;
+    const uint64_t dims[5] = {(uint64_t)HD, (uint64_t)H, Wg, Hg, (uint64_t)B * Tg};
+    const uint64_t strides[4] = {(uint64_t)HD * 2, (uint64_t)H * HD * 2, Wg * H * HD * 2, Hg * Wg * H * HD * 2};
+    const uint32_t box[5] = {64, 1, 8, 4, 4};
+    return make_tmap_bf16(m, p, 5, dims, strides, box);
+  };
+  int rc = na != nullptr ? make_grid(&tq, q) : make(&tq, q, Sq);
   if (rc) return rc;
-  rc = make(&tk, k, Skv);
+  rc = na != nullptr ? make_grid(&tk, k) : make(&tk, k, Skv);
   if (rc) return rc;
-  rc = make(&tv, v, Skv);
+  rc = na != nullptr ? make_grid(&tv, v) : make(&tv, v, Skv);
   if (rc) return rc;
   if (na != nullptr) return launch_fa_fwd<0, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st, *na);
   switch (variant) {
@@ -469,7 +491,7 @@ extern "C" int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void
   return fa_fwd_dispatch(q, k, v, nullptr, lse, B, Sq, Skv, H, scale, 0, sc, err, st);
 }
 
-// Neighbourhood attention on a tile-ordered token grid (see NaParams): self-attention, S = nT * nH * nW * 128 rows.
+// Neighbourhood attention on a T x H x W token grid in natural order (see NaParams): self-attention, S = nT * nH * nW * 128.
 extern "C" int cb200_fa_fwd_na(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, float scale,
                                const int* kv_idx, const int* kv_cnt, int max_n, const uint8_t* bt, const uint8_t* bh,
                                const uint8_t* bw, int nT, int nH, int nW, int* err, cudaStream_t st) {
