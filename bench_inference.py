@@ -32,6 +32,7 @@ def main() -> int:
     ap.add_argument("--guidance", type=float, default=7.0)
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--transport", default="peer", choices=["peer", "nccl"])
+    ap.add_argument("--cp-comm", default="a2a", choices=["a2a", "p2p"], help="context-parallel exchange: Ulysses all-to-all or ring")
     ap.add_argument("--sparse-window", type=int, nargs=3, default=None, metavar=("T", "H", "W"),
                     help="switch self-attention to neighbourhood attention with this window (e.g. 24 12 24)")
     ap.add_argument("--sparse-stride", type=int, nargs=3, default=(1, 4, 8))
@@ -52,7 +53,7 @@ def main() -> int:
     groups = build_groups(world, cp_size=world)
     net_cfg = NET_PRESETS[args.model]()
     tok = None if args.no_decode else Wan2pt1VAEInterface(device=dev, dtype=torch.bfloat16)
-    cfg = Video2WorldRFConfig(net=net_cfg, precision="bfloat16", state_t=args.frames, tokenizer=tok)
+    cfg = Video2WorldRFConfig(net=net_cfg, precision="bfloat16", state_t=args.frames, tokenizer=tok, cp_comm_type=args.cp_comm)
     torch.manual_seed(1234)
     model = Video2WorldModelRectifiedFlow(cfg, device=dev, cp_group=groups.cp if world > 1 else None)
     model.net.to(torch.bfloat16)
@@ -60,7 +61,7 @@ def main() -> int:
     if args.sparse_window is not None:
         model.net.use_sparse_attention(args.dense_blocks, {"window_size": tuple(args.sparse_window), "stride": tuple(args.sparse_stride)})
     if world > 1:
-        model.net.enable_context_parallel(groups.cp)
+        model.net.enable_context_parallel(groups.cp, args.cp_comm)
         if args.transport == "peer":
             from cosmos_predict25_b200.parallel import ulysses
             from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext
@@ -113,7 +114,7 @@ def main() -> int:
             "decoded_frames": frames, "gpu_launches_sampling": launches, "kernel_error": int(err),
             "config": {"model": f"cosmos-predict2.5-{args.model}-video2world", "steps": args.steps, "guidance": args.guidance,
                        "cfg": "batched cond/uncond (one batch-2 forward per step)", "latent_shape": [1, 16, args.frames, args.height, args.width],
-                       "parallelism": f"cp{world}",
+                       "parallelism": f"cp{world}" + (" (ring)" if world > 1 and args.cp_comm == "p2p" else ""),
                        "self_attention": "dense" if args.sparse_window is None else
                        f"neighbourhood window={tuple(args.sparse_window)} stride={tuple(args.sparse_stride)}, {args.dense_blocks} dense blocks", "transport": args.transport if world > 1 else "single",
                        "vae": ("Wan2.1 causal Conv3d decode (cuDNN convolutions)" + (f", {world} row bands with halo exchange" if world > 1 else ""))

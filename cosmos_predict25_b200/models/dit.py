@@ -258,6 +258,7 @@ class Attention(nn.Module):
         self.v_proj = FusedLinear(context_dim, inner)
         self.output_proj = FusedLinear(inner, query_dim)
         self.cp_group = None
+        self.cp_comm_type = "a2a"  # "a2a": Ulysses exchange; "p2p": ring attention
         self.sparse_op = None      # NeighborhoodAttention in blocks switched to sparse self-attention
         self.video_size = None     # (T, H, W) of the whole token grid, set by the network before the blocks run
 
@@ -302,7 +303,7 @@ class Attention(nn.Module):
         B, S, _ = x.shape
         if self.is_selfattn and self.sparse_op is not None and self.video_size is not None:
             return self._sparse_forward(x, rope, return_pre_proj)
-        if (self.is_selfattn and self.cp_group is not None and self._plain_projections()
+        if (self.is_selfattn and self.cp_group is not None and self.cp_comm_type == "a2a" and self._plain_projections()
                 and ulysses.projected_attention_available(x, self.cp_group, self.head_dim)):
             # inference under context parallelism: the sequence->head exchange is the epilogue of the q/k/v GEMMs
             o = ulysses.ulysses_projected_attention(x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight,
@@ -313,7 +314,12 @@ class Attention(nn.Module):
         if self.is_selfattn:
             k = self.k_proj(x).view(B, S, self.n_heads, self.head_dim)
             v = self.v_proj(x).view(B, S, self.n_heads, self.head_dim)
-            if self.cp_group is not None:
+            if self.cp_group is not None and self.cp_comm_type == "p2p":
+                from ..parallel.ring_attention import ring_attention
+                q = ops.rmsnorm_rope(q, self.q_norm.weight, rope, self.q_norm.eps)
+                k = ops.rmsnorm_rope(k, self.k_norm.weight, rope, self.k_norm.eps)
+                o = ring_attention(q, k, v, self.cp_group)
+            elif self.cp_group is not None:
                 o = ulysses.ulysses_attention_fused(q, k, v, self.q_norm.weight, self.k_norm.weight, rope, self.cp_group,
                                                     self.q_norm.eps)
             else:
@@ -496,11 +502,15 @@ class CosmosDiT(nn.Module):
             self.img_context_proj[0].reset_parameters()
 
     # ---- context parallel ----------------------------------------------------------------
-    def enable_context_parallel(self, group):
-        """Shard the sequence by latent frames over ``group``; only self-attention communicates."""
+    def enable_context_parallel(self, group, comm_type: str = "a2a"):
+        """Shard the sequence by latent frames over ``group``; only self-attention communicates. ``comm_type``: "a2a"
+        (Ulysses all-to-all, the default) or "p2p" (ring attention: key / value shards travel round the group, no
+        constraint on the head count)."""
+        assert comm_type in ("a2a", "p2p"), comm_type
         self.cp_group = group
         for b in self.blocks:
             b.self_attn.cp_group = group
+            b.self_attn.cp_comm_type = comm_type
 
     def disable_context_parallel(self):
         self.cp_group = None

@@ -76,6 +76,7 @@ class Text2WorldRFConfig:
     use_kerras_sigma_at_inference: bool = False
     text_dropout: float = 0.2
     sharding_transport: str = "nccl"   # nccl | peer
+    cp_comm_type: str = "a2a"          # context-parallel exchange in self-attention: a2a (Ulysses) | p2p (ring)
 
 
 @dataclass
@@ -243,7 +244,7 @@ class Text2WorldModelRectifiedFlow(nn.Module):
             if t is not None:
                 t = cp.broadcast(t, group)
             condition = condition.broadcast(group)
-            self.net.enable_context_parallel(group)
+            self.net.enable_context_parallel(group, getattr(self.config, "cp_comm_type", "a2a"))
         else:
             self.net.disable_context_parallel()
         return x0, condition, eps, t

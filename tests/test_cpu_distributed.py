@@ -307,3 +307,55 @@ def test_vae_decode_row_sharded_matches_single_rank():
 
 def test_vae_decode_row_sharded_three_ranks():
     run_distributed("_vae_row_sharded", world=3)
+
+
+# ------------------------------------------------------------------------------------------------
+def _ring_attention(rank, world, tmp):
+    """Ring attention over a sequence-sharded q/k/v equals attention over the gathered sequence, forward and backward;
+    a DiT running with comm_type="p2p" equals the same DiT with the all-to-all exchange."""
+    from cosmos_predict25_b200.ops import ref
+    from cosmos_predict25_b200.parallel.ring_attention import ring_attention
+    g = dist.group.WORLD
+    torch.manual_seed(0)
+    B, S, H, D = 2, 6, 3, 8                      # 3 heads: not divisible by 2 ranks, which Ulysses could not shard
+    full = [torch.randn(B, S * world, H, D, dtype=torch.float64) for _ in range(3)]
+    go = torch.randn(B, S * world, H, D, dtype=torch.float64)
+    loc = [t[:, rank * S:(rank + 1) * S].clone().requires_grad_(True) for t in full]
+    out = ring_attention(loc[0], loc[1], loc[2], g)
+    out.backward(go[:, rank * S:(rank + 1) * S])
+    ref_in = [t.clone().requires_grad_(True) for t in full]
+    want, _ = ref.attention(*ref_in, D ** -0.5)
+    want.backward(go.to(want.dtype))
+    sl = slice(rank * S, (rank + 1) * S)
+    assert torch.allclose(out.double(), want[:, sl].double(), atol=1e-5)
+    for a, b in zip(loc, ref_in):
+        assert torch.allclose(a.grad.double(), b.grad[:, sl].double(), atol=1e-4), (a.grad - b.grad[:, sl]).abs().max()
+
+    from cosmos_predict25_b200.models.dit import NET_PRESETS, CosmosDiT
+    torch.manual_seed(1)
+    cfg = NET_PRESETS["tiny"]()
+    net = CosmosDiT(cfg).eval()
+    net.init_weights()
+    T = 2 * world
+    x = torch.randn(1, cfg.in_channels, T, 8, 8)
+    ctx_dim = cfg.crossattn_proj_in_channels if cfg.use_crossattn_projection else cfg.crossattn_emb_channels
+    kw = dict(crossattn_emb=torch.randn(1, 8, ctx_dim), fps=torch.tensor([16.0]), padding_mask=torch.zeros(1, 1, 8, 8))
+    ts = torch.full((1, T), 0.5)
+    mask = torch.zeros(1, 1, T, 8, 8)
+    tl = slice(rank * 2, rank * 2 + 2)
+    outs = {}
+    with torch.no_grad():
+        kinds = ("a2a", "p2p") if cfg.num_heads % world == 0 else ("p2p",)   # the all-to-all needs heads % ranks == 0
+        for kind in kinds:
+            net.enable_context_parallel(g, kind)
+            outs[kind] = net(x[:, :, tl], ts[:, tl], condition_video_input_mask_B_C_T_H_W=mask[:, :, tl], **kw)
+        net.disable_context_parallel()
+        whole = net(x, ts, condition_video_input_mask_B_C_T_H_W=mask, **kw)
+    if "a2a" in outs:
+        assert torch.allclose(outs["p2p"], outs["a2a"], atol=1e-4)
+    assert torch.allclose(outs["p2p"], whole[:, :, tl], atol=1e-4)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_ring_attention_matches_gathered_attention(world):
+    run_distributed("_ring_attention", world=world)

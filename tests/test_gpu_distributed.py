@@ -159,6 +159,33 @@ def test_projection_gemm_with_exchange_epilogue():
     _run("_projected_scatter_vs_unfused")
 
 
+def _ring_vs_ulysses(rank, world):
+    """Ring attention on the tcgen05 kernels (forward blocks merged by log-sum-exp, backward blocks driven by the global
+    statistics) equals the all-to-all path, forward and backward."""
+    from cosmos_predict25_b200.ops import functional as F_ops
+    from cosmos_predict25_b200.ops import native
+    from cosmos_predict25_b200.parallel import ulysses
+    from cosmos_predict25_b200.parallel.ring_attention import ring_attention
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+    torch.manual_seed(21 + rank)
+    B, S, H, D = 1, 320, 4, 128
+    q, k, v = (torch.randn(B, S, H, D, device=dev).bfloat16().requires_grad_(True) for _ in range(3))
+    go = torch.randn(B, S, H, D, device=dev).bfloat16()
+    o_ref = ulysses.ulysses_attention(q, k, v, g)
+    g_ref = torch.autograd.grad(o_ref, (q, k, v), go)
+    o = ring_attention(q, k, v, g)
+    g_ring = torch.autograd.grad(o, (q, k, v), go)
+    assert native.load().kernel_error(rank, True) == 0
+    assert (o.float() - o_ref.float()).abs().max() < 2e-2
+    for a, b in zip(g_ring, g_ref):
+        assert (a.float() - b.float()).abs().max() < 5e-2 * max(1.0, b.float().abs().max().item())
+
+
+def test_ring_attention_matches_all_to_all():
+    _run("_ring_vs_ulysses")
+
+
 def test_peer_all_to_all_matches_nccl():
     _run("_a2a_peer_vs_nccl")
 
