@@ -89,6 +89,7 @@ class QwenAttention(nn.Module):
         self.k_proj = nn.Linear(c.hidden_size, self.kv * self.hd, bias=True)
         self.v_proj = nn.Linear(c.hidden_size, self.kv * self.hd, bias=True)
         self.o_proj = nn.Linear(self.h * self.hd, c.hidden_size, bias=False)
+        self.cp_group = None   # set by QwenLanguageModel.forward for all-gather-KV context parallelism
 
     def forward(self, x, cos, sin, mask):
         B, S, _ = x.shape
@@ -98,11 +99,22 @@ class QwenAttention(nn.Module):
         v = self.v_proj(x).view(B, S, -1, self.hd).transpose(1, 2)
         q = q * cos + _rotate_half(q) * sin
         k = k * cos + _rotate_half(k) * sin
+        if self.cp_group is not None:
+            # queries stay sequence-sharded; keys / values of the whole sequence are gathered (before the GQA repeat: less traffic)
+            k, v = _gather_seq(k, self.cp_group), _gather_seq(v, self.cp_group)
         rep = self.h // self.kv
         k = k.repeat_interleave(rep, dim=1)
         v = v.repeat_interleave(rep, dim=1)
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, is_causal=mask is None)
         return self.o_proj(o.transpose(1, 2).reshape(B, S, -1))
+
+
+def _gather_seq(t: torch.Tensor, group) -> torch.Tensor:
+    """All-gather [B, heads, S_loc, hd] along the sequence in rank order."""
+    import torch.distributed as dist
+    parts = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, t.contiguous(), group=group)
+    return torch.cat(parts, dim=2)
 
 
 class QwenMLP(nn.Module):
@@ -147,18 +159,46 @@ class QwenLanguageModel(nn.Module):
         return emb.cos()[None, None].to(dtype), emb.sin()[None, None].to(dtype)
 
     @torch.no_grad()
-    def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+    def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None, cp_group=None) -> List[torch.Tensor]:
+        """Every hidden state [B, S, hidden]. With ``cp_group`` (every rank passes the same ``input_ids``) the sequence is
+        split into contiguous ranges over the group: embeddings, RoPE rows and causal-mask rows are sliced, each attention
+        all-gathers keys / values (the reference's all-gather-KV context parallelism of the VLM tower,
+        cosmos_reason1 qwen2_5_vl.py:1032-1034,1267-1281), and the hidden states are gathered back at the end."""
+        import torch.distributed as dist
+        cp = dist.get_world_size(cp_group) if cp_group is not None and dist.is_initialized() else 1
         x = self.embed_tokens(input_ids)
         B, S, _ = x.shape
         cos, sin = self.rope(S, x.device, x.dtype)
         mask = None
-        if attention_mask is not None:
+        if attention_mask is not None or cp > 1:
             causal = torch.ones(S, S, dtype=torch.bool, device=x.device).tril()
-            mask = causal[None, None] & attention_mask[:, None, None, :].bool()
-        hidden = [x]
-        for i, layer in enumerate(self.layers):
-            x = layer(x, cos, sin, mask)
-            hidden.append(self.norm(x) if i == len(self.layers) - 1 else x)
+            mask = causal[None, None].expand(B, 1, S, S)
+            if attention_mask is not None:
+                mask = mask & attention_mask[:, None, None, :].bool()
+        if cp > 1:
+            assert S % cp == 0, f"sequence {S} does not divide over {cp} ranks"
+            r, n = dist.get_rank(cp_group), S // cp
+            x, mask = x[:, r * n:(r + 1) * n], mask[:, :, r * n:(r + 1) * n]
+            cos_q, sin_q = cos[:, :, r * n:(r + 1) * n], sin[:, :, r * n:(r + 1) * n]
+        else:
+            cos_q, sin_q = cos, sin
+        for layer in self.layers:
+            layer.self_attn.cp_group = cp_group if cp > 1 else None
+        try:
+            hidden = [x]
+            for i, layer in enumerate(self.layers):
+                x = layer(x, cos_q, sin_q, mask)   # keys are rotated with their own (local) positions before the gather
+                hidden.append(self.norm(x) if i == len(self.layers) - 1 else x)
+        finally:
+            for layer in self.layers:
+                layer.self_attn.cp_group = None
+        if cp > 1:
+            gathered = []
+            for h in hidden:
+                parts = [torch.empty_like(h) for _ in range(cp)]
+                dist.all_gather(parts, h.contiguous(), group=cp_group)
+                gathered.append(torch.cat(parts, dim=1))
+            hidden = gathered
         return hidden
 
     def load_hf_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:

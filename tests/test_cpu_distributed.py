@@ -359,3 +359,30 @@ def _ring_attention(rank, world, tmp):
 @pytest.mark.parametrize("world", [2, 3])
 def test_ring_attention_matches_gathered_attention(world):
     run_distributed("_ring_attention", world=world)
+
+
+# ------------------------------------------------------------------------------------------------
+def _qwen_allgather_kv_cp(rank, world, tmp):
+    """The language tower with all-gather-KV context parallelism returns the single-rank hidden states."""
+    from cosmos_predict25_b200.models.text_encoder import QwenConfig, QwenLanguageModel
+    torch.manual_seed(0)
+    cfg = QwenConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2)
+    lm = QwenLanguageModel(cfg).eval()
+    ids = torch.randint(0, 64, (2, 6 * world))
+    att = torch.ones(2, 6 * world, dtype=torch.long)
+    att[1, -4:] = 0                                        # right padding on one sample
+    want = lm(ids, att)
+    got = lm(ids, att, cp_group=dist.group.WORLD)
+    assert len(got) == len(want) == 3
+    valid = att.bool()[..., None]
+    for a, b in zip(got, want):
+        assert a.shape == b.shape
+        assert torch.allclose(a * valid, b * valid, atol=1e-5)
+    nomask = lm(ids, None, cp_group=dist.group.WORLD)
+    assert torch.allclose(nomask[-1], lm(ids, None)[-1], atol=1e-5)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_text_tower_all_gather_kv_context_parallel(world):
+    run_distributed("_qwen_allgather_kv_cp", world=world)
