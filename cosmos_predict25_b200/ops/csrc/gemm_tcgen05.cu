@@ -284,6 +284,109 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         continue;
       }
       const float* gate_row = (ep.gate != nullptr && row < M) ? ep.gate + (size_t)(row / ep.L) * N : nullptr;
+      if (vec_ok && n0 + BN <= N) {
+        // ---- full-width tile: every global access of the epilogue goes through the warp's 8 KB staging block, so that a
+        // warp instruction moves two contiguous 256-byte row segments instead of 32 scattered 16-byte pieces (the scattered
+        // form made K = 2048 GEMMs epilogue-bound).  Two passes of 128 columns; TMEM loads stay warp-uniform.
+        uint8_t* stage_warp = smem + kStages * kStageBytes + 256 + quarter * (32 * 256);
+        uint8_t* stage_row = stage_warp + lane * 256;
+        const int row0 = m0 + quarter * 32;
+        auto write_out = [&](bf16* base, int colbase) {       // staged [32 rows x 128 cols] -> base[row, colbase ...]
+          __syncwarp();
+#pragma unroll 4
+          for (int it = 0; it < 16; ++it) {
+            const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
+            const uint4 v4 = *reinterpret_cast<const uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4));
+            if (row0 + r_src < M) *reinterpret_cast<uint4*>(base + (size_t)(row0 + r_src) * N + colbase + chunk * 8) = v4;
+          }
+          __syncwarp();
+        };
+        auto stage_chunk = [&](int c, const float (&v)[32]) {   // this thread's columns [32c, 32c + 32) of the pass
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(stage_row + (((c * 4 + q) ^ (lane & 7)) << 4)) = o;
+          }
+        };
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+          const int colbase = n0 + pass * 128;
+          if (ep.gate != nullptr) {                             // residual rows in, coalesced
+#pragma unroll 4
+            for (int it = 0; it < 16; ++it) {
+              const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
+              uint4 v4 = make_uint4(0, 0, 0, 0);
+              if (row0 + r_src < M) v4 = *reinterpret_cast<const uint4*>(ep.resid + (size_t)(row0 + r_src) * N + colbase + chunk * 8);
+              *reinterpret_cast<uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4)) = v4;
+            }
+            __syncwarp();
+          }
+          if (ep.act == 1 && ep.pre != nullptr) {               // pre-activation output first (TMEM is read again below)
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tmem_ld32(t_row + pass * 128 + c * 32, r);
+              tmem_ld_wait();
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              if (ep.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(ep.bias[colbase + c * 32 + j]);
+              }
+              stage_chunk(c, v);
+            }
+            write_out(ep.pre, colbase);
+          }
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld32(t_row + pass * 128 + c * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            const int col0 = colbase + c * 32;
+            if (ep.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += __bfloat162float(ep.bias[col0 + j]);
+            }
+            if (ep.act == 1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+            }
+            if (ep.gate != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(stage_row + (((c * 4 + q) ^ (lane & 7)) << 4));
+                const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+                float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (gate_row != nullptr) {
+                  const float4 g0 = *reinterpret_cast<const float4*>(gate_row + col0 + q * 8);
+                  const float4 g1 = *reinterpret_cast<const float4*>(gate_row + col0 + q * 8 + 4);
+                  g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 rf = __bfloat1622float2(r2[j]);
+                  v[q * 8 + 2 * j] = rf.x + g[2 * j] * v[q * 8 + 2 * j];
+                  v[q * 8 + 2 * j + 1] = rf.y + g[2 * j + 1] * v[q * 8 + 2 * j + 1];
+                }
+              }
+            }
+            stage_chunk(c, v);                                  // in place: a thread only ever touches its own row here
+          }
+          write_out(ep.C, colbase);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];

@@ -133,9 +133,10 @@ def test_gemm_transposed_operands():
     _close(c, want, 2e-2, 2e-2, "gemm trans_a trans_b")
 
 
-def test_gemm_epilogues():
+@pytest.mark.parametrize("M,N,L", [(640, 1024, 40), (600, 1024, 40), (600, 1000, 40)])   # full, ragged rows, ragged rows + columns
+def test_gemm_epilogues(M, N, L):
     torch.manual_seed(6)
-    M, N, K, L = 640, 1024, 512, 40
+    K = 512
     a = torch.randn(M, K, device=DEV).bfloat16()
     b = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
     bias = torch.randn(N, device=DEV).bfloat16()
