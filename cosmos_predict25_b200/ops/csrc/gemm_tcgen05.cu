@@ -33,8 +33,8 @@ constexpr int kStages = 4;
 constexpr int kABytes = BM * BK * 2;  // 16 KB
 constexpr int kBBytes = BN * BK * 2;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kGemmThreads = 192;
-constexpr int kStageOutBytes = 4 * 32 * 256;  // head-scatter epilogue: one 32-row x 256-byte staging block per epilogue warp
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter, 128 columns each)
+constexpr int kStageOutBytes = 8 * 32 * 128;  // one 32-row x 128-byte staging block per epilogue warp
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kStageOutBytes;
 
 // Ulysses exchange fused into the epilogue: the output [M, N] is a projection to H = N / 128 heads of a local sequence of S
@@ -89,7 +89,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);
+      mbar_init(&acc_empty[a], 8);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -177,7 +177,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int quarter = warp & 3;      // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int part = (warp - 2) >> 2;  // accumulator columns [128*part, 128*part + 128)
+    uint8_t* stage_warp = smem + kStages * kStageBytes + 256 + (warp - 2) * (32 * 128);
+    uint8_t* stage_row = stage_warp + lane * 128;
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
@@ -192,13 +195,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         // ---- fused head scatter: this thread owns one token row; a 256-wide tile holds two complete heads
         // tcgen05.ld is warp-collective: every lane runs every load, rows past M only skip their stores
         const bool valid = row < M;
-        uint8_t* stage_warp = smem + kStages * kStageBytes + 256 + quarter * (32 * 256);
-        uint8_t* stage_row = stage_warp + lane * 256;
         {
           const int row_c = valid ? row : M - 1;
           const int b_idx = row_c / ep.hs.S, s_idx = row_c % ep.hs.S;
-#pragma unroll 1
-          for (int hh = 0; hh < BN / 128; ++hh) {
+          for (int hh = part; hh == part; ++hh) {      // this warp's head of the tile
             const int head = (n0 + hh * 128) >> 7;
             if ((head + 1) * 128 > N) break;
             const uint32_t t_head = t_row + hh * 128;
@@ -257,24 +257,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                   p0[j] = __floats2bfloat162_rn(a[q * 8 + 2 * j], a[q * 8 + 2 * j + 1]);
                   p1[j] = __floats2bfloat162_rn(bb[q * 8 + 2 * j], bb[q * 8 + 2 * j + 1]);
                 }
-                // this thread's row goes to the warp's staging block, 16-byte chunks XOR-swizzled by the row (no bank conflicts)
-                *reinterpret_cast<uint4*>(stage_row + (((c * 4 + q) ^ (lane & 7)) << 4)) = o0;
-                *reinterpret_cast<uint4*>(stage_row + (((8 + c * 4 + q) ^ (lane & 7)) << 4)) = o1;
+                // this thread's row goes to the warp's staging block, 16-byte chunks XOR-swizzled by the row (no bank conflicts):
+                // chunks 0-3 = columns [32c, 32c + 32), chunks 4-7 = their rotation partners [64 + 32c, 64 + 32c + 32)
+                *reinterpret_cast<uint4*>(stage_row + ((q ^ (lane & 7)) << 4)) = o0;
+                *reinterpret_cast<uint4*>(stage_row + (((4 + q) ^ (lane & 7)) << 4)) = o1;
               }
-            }
-            __syncwarp();
-            // write-out: 16 lanes cover one 256-byte head row, so every store instruction of the warp is two contiguous
-            // 256-byte segments (local memory or a peer's over NVLink) instead of 32 scattered 16-byte pieces
-            const unsigned long long dst_u = reinterpret_cast<unsigned long long>(dst);
+              __syncwarp();
+              // write-out: 4 lanes cover a 64-byte run of a head row, so a warp store is eight contiguous 64-byte segments
+              // (local memory or a peer's over NVLink) instead of 32 scattered 16-byte pieces
+              const unsigned long long dst_u = reinterpret_cast<unsigned long long>(dst);
 #pragma unroll 4
-            for (int it = 0; it < 16; ++it) {
-              const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
-              const unsigned long long d = __shfl_sync(0xffffffffu, dst_u, r_src);
-              const int ok_row = __shfl_sync(0xffffffffu, (int)valid, r_src);
-              const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4));
-              if (ok_row) *reinterpret_cast<uint4*>(d + chunk * 16) = v;
+              for (int it = 0; it < 8; ++it) {
+                const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
+                const unsigned long long d = __shfl_sync(0xffffffffu, dst_u, r_src);
+                const int ok_row = __shfl_sync(0xffffffffu, (int)valid, r_src);
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4));
+                const int col = (chunk < 4 ? c * 32 + chunk * 8 : 64 + c * 32 + (chunk - 4) * 8);
+                if (ok_row) *reinterpret_cast<uint4*>(d + col * 2) = v;
+              }
+              __syncwarp();
             }
-            __syncwarp();
           }
         }
         tc_fence_before();
@@ -285,18 +287,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       const float* gate_row = (ep.gate != nullptr && row < M) ? ep.gate + (size_t)(row / ep.L) * N : nullptr;
       if (vec_ok && n0 + BN <= N) {
-        // ---- full-width tile: every global access of the epilogue goes through the warp's 8 KB staging block, so that a
-        // warp instruction moves two contiguous 256-byte row segments instead of 32 scattered 16-byte pieces (the scattered
-        // form made K = 2048 GEMMs epilogue-bound).  Two passes of 128 columns; TMEM loads stay warp-uniform.
-        uint8_t* stage_warp = smem + kStages * kStageBytes + 256 + quarter * (32 * 256);
-        uint8_t* stage_row = stage_warp + lane * 256;
+        // ---- full-width tile: every global access of the epilogue goes through the warp's 4 KB staging block, so that a
+        // warp instruction moves four contiguous 128-byte row segments instead of 32 scattered 16-byte pieces (the scattered
+        // form made K = 2048 GEMMs epilogue-bound).  This warp owns 128 columns: two passes of 64; TMEM loads stay
+        // warp-uniform.
         const int row0 = m0 + quarter * 32;
-        auto write_out = [&](bf16* base, int colbase) {       // staged [32 rows x 128 cols] -> base[row, colbase ...]
+        auto write_out = [&](bf16* base, int colbase) {       // staged [32 rows x 64 cols] -> base[row, colbase ...]
           __syncwarp();
 #pragma unroll 4
-          for (int it = 0; it < 16; ++it) {
-            const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
-            const uint4 v4 = *reinterpret_cast<const uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4));
+          for (int it = 0; it < 8; ++it) {
+            const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
+            const uint4 v4 = *reinterpret_cast<const uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4));
             if (row0 + r_src < M) *reinterpret_cast<uint4*>(base + (size_t)(row0 + r_src) * N + colbase + chunk * 8) = v4;
           }
           __syncwarp();
@@ -313,22 +314,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         };
 #pragma unroll 1
         for (int pass = 0; pass < 2; ++pass) {
-          const int colbase = n0 + pass * 128;
+          const int coff = part * 128 + pass * 64;              // column offset inside the tile
+          const int colbase = n0 + coff;
           if (ep.gate != nullptr) {                             // residual rows in, coalesced
 #pragma unroll 4
-            for (int it = 0; it < 16; ++it) {
-              const int r_src = it * 2 + (lane >> 4), chunk = lane & 15;
+            for (int it = 0; it < 8; ++it) {
+              const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
               uint4 v4 = make_uint4(0, 0, 0, 0);
               if (row0 + r_src < M) v4 = *reinterpret_cast<const uint4*>(ep.resid + (size_t)(row0 + r_src) * N + colbase + chunk * 8);
-              *reinterpret_cast<uint4*>(stage_warp + r_src * 256 + ((chunk ^ (r_src & 7)) << 4)) = v4;
+              *reinterpret_cast<uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4)) = v4;
             }
             __syncwarp();
           }
           if (ep.act == 1 && ep.pre != nullptr) {               // pre-activation output first (TMEM is read again below)
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
               uint32_t r[32];
-              tmem_ld32(t_row + pass * 128 + c * 32, r);
+              tmem_ld32(t_row + coff + c * 32, r);
               tmem_ld_wait();
               float v[32];
 #pragma unroll
@@ -342,9 +344,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             write_out(ep.pre, colbase);
           }
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t r[32];
-            tmem_ld32(t_row + pass * 128 + c * 32, r);
+            tmem_ld32(t_row + coff + c * 32, r);
             tmem_ld_wait();
             float v[32];
 #pragma unroll
@@ -388,7 +390,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = part * 4; c < part * 4 + 4; ++c) {
         uint32_t r[32];
         tmem_ld32(t_row + c * 32, r);
         tmem_ld_wait();
