@@ -386,3 +386,32 @@ def _qwen_allgather_kv_cp(rank, world, tmp):
 @pytest.mark.parametrize("world", [2, 3])
 def test_text_tower_all_gather_kv_context_parallel(world):
     run_distributed("_qwen_allgather_kv_cp", world=world)
+
+
+# ------------------------------------------------------------------------------------------------
+def _sparse_attention_under_cp(rank, world, tmp):
+    """Neighbourhood attention in a DiT under context parallelism (q/k/v exchanged to whole-sequence / local-heads, operator
+    applied on the full T x H x W grid, output exchanged back) equals the single-rank sparse network."""
+    from cosmos_predict25_b200.models.dit import NET_PRESETS, CosmosDiT, replace_selfattn_op_with_sparse_attn_op
+    g = dist.group.WORLD
+    torch.manual_seed(2)
+    cfg = NET_PRESETS["tiny"]()
+    net = CosmosDiT(cfg).eval()
+    net.init_weights()
+    replace_selfattn_op_with_sparse_attn_op(net, 0, {"window_size": (2, 3, 3), "stride": (1, 1, 2)})
+    T = 2 * world
+    x = torch.randn(1, cfg.in_channels, T, 8, 8)
+    ctx_dim = cfg.crossattn_proj_in_channels if cfg.use_crossattn_projection else cfg.crossattn_emb_channels
+    kw = dict(crossattn_emb=torch.randn(1, 8, ctx_dim), fps=torch.tensor([16.0]), padding_mask=torch.zeros(1, 1, 8, 8))
+    ts = torch.full((1, T), 0.5)
+    mask = torch.zeros(1, 1, T, 8, 8)
+    tl = slice(rank * 2, rank * 2 + 2)
+    with torch.no_grad():
+        whole = net(x, ts, condition_video_input_mask_B_C_T_H_W=mask, **kw)
+        net.enable_context_parallel(g)
+        part = net(x[:, :, tl], ts[:, tl], condition_video_input_mask_B_C_T_H_W=mask[:, :, tl], **kw)
+    assert torch.allclose(part, whole[:, :, tl], atol=1e-4), (part - whole[:, :, tl]).abs().max()
+
+
+def test_sparse_attention_under_context_parallel():
+    run_distributed("_sparse_attention_under_cp", world=2)
