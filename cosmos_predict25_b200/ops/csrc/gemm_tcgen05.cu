@@ -237,8 +237,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                   bb[j] *= rstd * ep.hs.w[64 + c * 32 + j];
                 }
                 if (ep.hs.cosv != nullptr) {
-                  const float* cs = ep.hs.cosv + (size_t)s_idx * 64 + c * 32;
-                  const float* sn = ep.hs.sinv + (size_t)s_idx * 64 + c * 32;
+                  // this row's 32 cosines and sines come in through the staging block with coalesced loads (8 lanes per
+                  // 128-byte run, 4 rows per instruction); reading them per thread straight from global memory would be
+                  // 32 scattered 16-byte loads per instruction
+                  float cs[32], sn[32];
+                  auto fetch_rows = [&](const float* table, float (&out)[32]) {
+#pragma unroll 4
+                    for (int it = 0; it < 8; ++it) {
+                      const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
+                      const int s_src = __shfl_sync(0xffffffffu, s_idx, r_src);
+                      const uint4 v4 = *reinterpret_cast<const uint4*>(table + (size_t)s_src * 64 + c * 32 + chunk * 4);
+                      *reinterpret_cast<uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4)) = v4;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                      const float4 f = *reinterpret_cast<const float4*>(stage_row + ((q ^ (lane & 7)) << 4));
+                      out[q * 4] = f.x; out[q * 4 + 1] = f.y; out[q * 4 + 2] = f.z; out[q * 4 + 3] = f.w;
+                    }
+                    __syncwarp();
+                  };
+                  fetch_rows(ep.hs.cosv, cs);
+                  fetch_rows(ep.hs.sinv, sn);
 #pragma unroll
                   for (int j = 0; j < 32; ++j) {
                     const float x0 = a[j], x1 = bb[j], cc = cs[j], s1 = sn[j];
