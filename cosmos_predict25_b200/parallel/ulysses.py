@@ -166,6 +166,14 @@ def projected_attention_available(x: torch.Tensor, group, head_dim: int) -> bool
             and settings.gemm == "native")
 
 
+def _attention_exchange_mode() -> str:
+    """How the attention output returns to sequence layout in the inference path: "store" = the attention kernel writes every
+    finished row into its owner's shard (one barrier, no extra kernel); "gather" = attention, then the stand-alone gather kernel
+    (two barriers). Both are exact; COSMOS_B200_ATTN_EXCHANGE selects, the default is the one that measured faster end to end."""
+    import os
+    return os.environ.get("COSMOS_B200_ATTN_EXCHANGE", "store")
+
+
 def ulysses_projected_attention(x, wq, wk, wv, q_norm_weight, k_norm_weight, rope, group, eps: float = 1e-6,
                                 scale: Optional[float] = None):
     """Inference self-attention on a sequence shard ``x [B, S_loc, D]``: the three projection GEMMs write their
@@ -180,7 +188,9 @@ def ulysses_projected_attention(x, wq, wk, wv, q_norm_weight, k_norm_weight, rop
         x2d = x2d.contiguous()
     qh, kh, vh = t.project_scatter_heads(x2d, [wq, wk, wv], [q_norm_weight, k_norm_weight, None], rope, B, S, eps)
     scale = scale if scale is not None else 1.0 / math.sqrt(qh.shape[-1])
-    return t.attention_scatter_seq(qh, kh, vh, scale)
+    if _attention_exchange_mode() == "store":
+        return t.attention_scatter_seq(qh, kh, vh, scale)
+    return t.head_to_seq(ops.attention(qh, kh, vh, scale))
 
 
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: Optional[float] = None):
