@@ -96,7 +96,7 @@ class PtCheckpointer:
         if "scheduler" in resume and scheduler is not None and os.path.exists(base + "_scheduler.pt"):
             scheduler.load_state_dict(torch.load(base + "_scheduler.pt", map_location="cpu", weights_only=False))
             if iteration:
-                scheduler.load_state_dict({"last_epoch": iteration})
+                scheduler.last_epoch = iteration
         log.info(f"loaded checkpoint {base} at iteration {iteration}")
         return iteration
 
@@ -104,3 +104,100 @@ class PtCheckpointer:
         if self._thread is not None:
             self._thread.join()
             self._thread = None
+
+
+class ModelParallelPtCheckpointer(PtCheckpointer):
+    """``PtCheckpointer`` for models split over a model-parallel group: every model-parallel rank of the first data-parallel
+    replica writes its own ``iter_%09d_{model,optim}_mp_{rank}.pt``; scheduler and trainer state are written once
+    (cosmos_predict2/_src/imaginaire/checkpointer/tp.py:20-42). ``mp_rank`` / ``dp_rank`` are callables so that the class
+    works with any group layout (and without a process group in tests)."""
+
+    def __init__(self, config_checkpoint, job_dir: str, callbacks=None, mp_rank=lambda: 0, dp_rank=lambda: 0):
+        super().__init__(config_checkpoint, job_dir, callbacks)
+        self.mp_rank, self.dp_rank = mp_rank, dp_rank
+
+    def _suffix(self, key: str) -> str:
+        return f"_{key}_mp_{self.mp_rank()}.pt" if key in ("model", "optim") else f"_{key}.pt"
+
+    def _extra_model_state(self, model) -> dict:
+        return {}
+
+    def _load_extra_model_state(self, model, sd: dict) -> dict:
+        return sd
+
+    def save(self, model, optimizer, scheduler, iteration, grad_scaler=None, trainer=None):
+        self.finalize()
+        name = f"iter_{iteration:09d}"
+        cpu = lambda sd: {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in sd.items()}
+        model_sd = cpu(model.state_dict())
+        model_sd.update(self._extra_model_state(model))
+        parts = {"model": model_sd, "optim": cpu(optimizer.state_dict()) if optimizer is not None else {},
+                 "scheduler": scheduler.state_dict() if scheduler is not None else {}}
+        first_replica, first_mp = self.dp_rank() == 0, self.mp_rank() == 0
+
+        def work():
+            if not first_replica:
+                return
+            os.makedirs(self.dir, exist_ok=True)
+            for k in ("model", "optim"):
+                torch.save(parts[k], os.path.join(self.dir, name + self._suffix(k)))
+            if first_mp:
+                torch.save(parts["scheduler"], os.path.join(self.dir, name + self._suffix("scheduler")))
+                torch.save({"iteration": iteration, "grad_scaler": {}}, os.path.join(self.dir, f"{name}.pt"))
+                with open(os.path.join(self.dir, "latest_checkpoint.txt"), "w") as f:
+                    f.write(name + "\n")
+
+        self._thread = threading.Thread(target=work, daemon=True)
+        self._thread.start()
+
+    def load(self, model, optimizer=None, scheduler=None, grad_scaler=None, trainer=None) -> int:
+        latest = self._latest()
+        if latest is None:
+            return 0
+        base = os.path.join(self.dir, latest)
+        sd = torch.load(base + self._suffix("model"), map_location="cpu", weights_only=False)
+        sd = self._load_extra_model_state(model, sd)
+        model.load_state_dict(sd, strict=self.strict_resume)
+        if optimizer is not None and os.path.exists(base + self._suffix("optim")):
+            optimizer.load_state_dict(torch.load(base + self._suffix("optim"), map_location="cpu", weights_only=False))
+        iteration = int(torch.load(base + ".pt", map_location="cpu", weights_only=False)["iteration"])
+        if scheduler is not None and os.path.exists(base + self._suffix("scheduler")):
+            scheduler.load_state_dict(torch.load(base + self._suffix("scheduler"), map_location="cpu", weights_only=False))
+        return iteration
+
+
+class ModelParallelEmaPtCheckpointer(ModelParallelPtCheckpointer):
+    """Model-parallel checkpointer whose model file also carries the EMA weights under the key ``ema``
+    (cosmos_predict2/_src/imaginaire/checkpointer/tp_ema.py:26-90). ``get_ema`` / ``set_ema`` read and write the EMA state
+    dict of the model (by default ``model.ema_state_dict()`` / ``model.load_ema_state_dict(sd)`` when present)."""
+
+    def __init__(self, *a, get_ema=None, set_ema=None, **k):
+        super().__init__(*a, **k)
+        self.get_ema, self.set_ema = get_ema, set_ema
+
+    def _extra_model_state(self, model) -> dict:
+        getter = self.get_ema or getattr(model, "ema_state_dict", None)
+        if getter is None:
+            return {}
+        ema = getter() if self.get_ema is None else getter(model)
+        return {"ema": {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in ema.items()}}
+
+    def _load_extra_model_state(self, model, sd: dict) -> dict:
+        sd = dict(sd)
+        ema = sd.pop("ema", None)
+        if ema is not None:
+            if self.set_ema is not None:
+                self.set_ema(model, ema)
+            elif hasattr(model, "load_ema_state_dict"):
+                model.load_ema_state_dict(ema)
+        return sd
+
+
+def broadcast_object(obj, src: int = 0, group=None):
+    """Broadcast a picklable object; a no-op without a process group (checkpointer/safe_broadcast.py:27 of the reference
+    guards the same call against un-initialised process groups)."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return obj
+    box = [obj]
+    dist.broadcast_object_list(box, src=src, group=group)
+    return box[0]
