@@ -1,0 +1,128 @@
+"""Data and I/O helpers: mock datasets, local video dataset, video read / write / resize, composite loaders, small utilities."""
+
+import os
+import time
+
+import pytest
+import torch
+
+from cosmos_predict25_b200.data import loaders as L
+from cosmos_predict25_b200.data import mock
+from cosmos_predict25_b200.utils import misc, video_io
+
+
+def test_mock_datasets_are_deterministic_and_shaped():
+    ds = mock.MockVideoLatentDataset(num_frames=3, height=8, width=6, text_dim=16, text_len=5, length=10)
+    a, b = ds[3], ds[3]
+    assert a["latents"].shape == (16, 3, 8, 6) and torch.equal(a["latents"], b["latents"]) and not torch.equal(a["latents"], ds[4]["latents"])
+    assert a["t5_text_embeddings"].dtype == torch.bfloat16 and a["padding_mask"].shape == (1, 8, 6)
+    px = mock.MockVideoPixelDataset(num_frames=5, height=16, width=24, text_dim=8, text_len=4, length=4)[0]
+    assert px["video"].dtype == torch.uint8 and px["video"].shape == (3, 5, 16, 24) and px["image_size"].tolist() == [16, 24, 16, 24]
+    im = mock.MockImageDataset(height=8, width=8, text_dim=8, text_len=4, length=4)[1]
+    assert im["images"].shape == (3, 8, 8) and im["dataset_name"] == "mock_image"
+    dl = mock.build_dataloader(ds, batch_size=2, dp_size=2, dp_rank=1, shuffle=False)
+    batch = next(iter(dl))
+    assert batch["latents"].shape == (2, 16, 3, 8, 6)
+    assert torch.equal(batch["latents"][0], ds[1]["latents"])          # rank 1 of 2 starts at sample 1
+
+
+def test_resize_cover_and_center_crop():
+    x = torch.zeros(1, 3, 40, 100, dtype=torch.uint8)
+    x[..., :, 40:60] = 255                                             # a vertical bar in the middle
+    y = video_io.resize_input(x, (20, 20))
+    assert y.shape == (1, 3, 20, 20) and y.dtype == torch.uint8
+    assert y[0, 0, 10, 10] > 200 and y[0, 0, 10, 0] < 50               # scaled by 0.5, cropped around the centre: bar survives
+    f = video_io.resize_input(torch.rand(2, 3, 10, 10), (20, 30))
+    assert f.shape == (2, 3, 20, 30) and f.dtype == torch.float32
+
+
+def test_video_and_image_write_read_roundtrip(tmp_path):
+    t = torch.linspace(0, 1, 9).view(1, 9, 1, 1).expand(3, 9, 32, 48).contiguous()
+    path = video_io.save_img_or_video(t, str(tmp_path / "clip"), fps=12)
+    assert path.endswith(".mp4") and os.path.getsize(path) > 0
+    frames, fps = video_io._read_video(path)
+    assert frames.shape == (9, 32, 48, 3) and abs(fps - 12) < 0.5
+    assert abs(float(frames[-1].mean()) - 255.0) < 12 and float(frames[0].mean()) < 12
+    clip = video_io.read_and_process_video(path, (16, 24), num_video_frames=13, num_latent_conditional_frames=2)
+    assert clip.shape == (1, 3, 13, 16, 24) and clip.dtype == torch.uint8
+    assert torch.equal(clip[0, :, 5:], clip[0, :, 4:5].expand(-1, 8, -1, -1))   # padded with the last conditioning frame
+    with pytest.raises(ValueError):
+        video_io.read_and_process_video(path, (16, 24), 13, num_latent_conditional_frames=4)   # needs 13 frames, clip has 9
+    img = video_io.save_img_or_video(t[:, :1] * 0 + 0.5, str(tmp_path / "still"))
+    assert img.endswith(".jpg")
+    vid = video_io.read_and_process_image(img, (16, 24), num_video_frames=5)
+    assert vid.shape == (1, 3, 5, 16, 24) and abs(int(vid[0, 0, 0, 8, 8]) - 128) <= 3 and int(vid[0, :, 1:].max()) == 0
+
+
+def test_local_video_dataset(tmp_path):
+    from cosmos_predict25_b200.data.video_dataset import VideoDataset
+    root = tmp_path / "ds"
+    os.makedirs(root / "videos")
+    os.makedirs(root / "metas")
+    os.makedirs(root / "t5_xxl")
+    clip = torch.rand(3, 12, 32, 48)
+    video_io.save_img_or_video(clip, str(root / "videos" / "a"), fps=10)
+    (root / "metas" / "a.txt").write_text("a red cube\n")
+    torch.save(torch.randn(7, 16), root / "t5_xxl" / "a.pt")
+    ds = VideoDataset(str(root), num_frames=8, video_size=(16, 24), embedding_dir="t5_xxl", text_len=10)
+    assert len(ds) == 1
+    s = ds[0]
+    assert s["video"].shape == (3, 8, 16, 24) and s["video"].dtype == torch.uint8 and s["ai_caption"] == "a red cube"
+    assert s["t5_text_embeddings"].shape == (10, 16) and float(s["t5_text_embeddings"][7:].abs().sum()) == 0.0
+    assert 0 <= s["frame_start"] <= 4 and s["frame_end"] - s["frame_start"] == 8
+    too_long = VideoDataset(str(root), num_frames=50, video_size=(16, 24), max_retries=2)
+    with pytest.raises(RuntimeError):
+        too_long[0]
+
+
+def test_joint_loader_ratios_and_tags():
+    img = [{"images": i} for i in range(3)]
+    vid = [{"video": i} for i in range(100)]
+    joint = L.IterativeJointDataLoader({"image": {"dataloader": img, "ratio": 1}, "video": {"dataloader": vid, "ratio": 2},
+                                        "off": {"dataloader": [], "ratio": 0}})
+    it = iter(joint)
+    names = [next(it)["dataset_name"] for _ in range(9)]
+    assert names == ["image", "video", "video"] * 3
+    assert next(it)["dataset_name"] == "image"                       # the exhausted image loader restarts
+
+
+def test_cached_replay_loader_replays_augments_and_reports_errors():
+    base = [{"x": i} for i in range(4)]
+    aug = lambda b: [b, {"x": b["x"] + 100}]
+    dl = L.CachedReplayDataLoader(base, cache_size=3, cache_replay_n=2, cache_augmentation_fn=aug)
+    got = [b["x"] for b in dl]
+    assert got == [0, 0, 100, 100, 1, 1, 101, 101, 2, 2, 102, 102, 3, 3, 103, 103] and len(dl) == 8
+    shuffled = sorted(b["x"] for b in L.CachedReplayDataLoader(base, cache_size=2, shuffle_cache=True))
+    assert shuffled == [0, 1, 2, 3]
+
+    def broken():
+        yield {"x": 0}
+        raise OSError("disk went away")
+
+    with pytest.raises(OSError):
+        list(L.CachedReplayDataLoader(broken(), cache_size=2))
+
+
+def test_operation_watchdog_warns_only_when_slow():
+    with L.OperationWatchdog("fast", warning_threshold=5.0, interval=0.05) as w:
+        time.sleep(0.1)
+    assert w.warnings == 0
+    with L.OperationWatchdog("slow", warning_threshold=0.1, interval=0.05) as w:
+        time.sleep(0.35)
+    assert w.warnings >= 1
+
+
+def test_misc_helpers():
+    a = misc.arch_invariant_rand((2, 3), torch.float32, "cpu", seed=5)
+    assert torch.equal(a, misc.arch_invariant_rand((2, 3), torch.float32, "cpu", seed=5)) and a.shape == (2, 3)
+    moved = misc.to({"a": torch.ones(2), "b": [torch.zeros(1), "s"], "c": 3}, dtype=torch.float64)
+    assert moved["a"].dtype == torch.float64 and moved["b"][1] == "s" and moved["c"] == 3
+    assert misc.get_data_batch_size({"k": "v", "t": torch.zeros(5, 2)}) == 5
+    timer = misc.TrainingTimer()
+    with timer("forward"):
+        time.sleep(0.01)
+    with timer("forward"):
+        time.sleep(0.01)
+    avg = timer.compute_average_results()
+    assert 0.005 < avg["forward"] < 0.2
+    assert misc.count_params(torch.nn.Linear(3, 2)) == 8
