@@ -205,6 +205,11 @@ class Text2WorldModelRectifiedFlow(nn.Module):
 
     @torch.no_grad()
     def encode(self, state: torch.Tensor) -> torch.Tensor:
+        """Pixels -> latent. With ``shard_vae_encode`` set (the inference pipeline sets it: there every rank of the
+        context-parallel group holds the same conditioning clip) the ranks encode one horizontal band each."""
+        if getattr(self, "shard_vae_encode", False) and self.cp_group is not None and cp._size_rank(self.cp_group)[0] > 1 \
+                and hasattr(self.tokenizer, "encode_parallel"):
+            return self.tokenizer.encode_parallel(state, self.cp_group)
         return self.tokenizer.encode(state)
 
     @torch.no_grad()

@@ -10,6 +10,7 @@ context-parallel (cosmos_predict2/_src/predict2/models/text2world_model_rectifie
     zeros);
   * the single-head spatial attention of the middle block attends from the local rows to the keys / values of the
     whole frame (all-gather of k and v, 14k tokens x 384 channels per frame at 720p);
+  * the encoder's stride-2 convolutions (zero padding on the bottom / right only) take one boundary row from the next rank;
   * everything else (RMS norm over channels, SiLU, nearest 2x up-sampling, causal time convolutions and their
     chunk-to-chunk caches) is local to a pixel column or a row and needs no communication.
 
@@ -49,28 +50,30 @@ def _global(group, r: int) -> int:
     return dist.get_global_rank(group, r) if group is not None and group is not dist.group.WORLD else r
 
 
-def exchange_rows(x: torch.Tensor, dim: int, n: int) -> torch.Tensor:
-    """``x`` extended along ``dim`` by the last ``n`` rows of the previous rank and the first ``n`` rows of the next
-    one; zeros where there is no neighbour (they stand for the convolution's zero padding at the frame border)."""
+def exchange_rows(x: torch.Tensor, dim: int, n: int, top: bool = True, bottom: bool = True) -> torch.Tensor:
+    """``x`` extended along ``dim`` by the last ``n`` rows of the previous rank (``top``) and the first ``n`` rows of the next
+    one (``bottom``); zeros where there is no neighbour (they stand for the convolution's zero padding at the frame border).
+    The messages always flow both ways (every rank runs the same exchange); a side that is switched off is just not attached."""
     if _active is None or n == 0:
         return x
     group, r, P = _active
     size = x.shape[dim]
     assert size >= n, "band thinner than the halo"
-    top = x.narrow(dim, 0, n).contiguous()
-    bot = x.narrow(dim, size - n, n).contiguous()
-    from_prev = torch.zeros_like(top)
-    from_next = torch.zeros_like(bot)
+    first = x.narrow(dim, 0, n).contiguous()
+    last = x.narrow(dim, size - n, n).contiguous()
+    from_prev = torch.zeros_like(first)
+    from_next = torch.zeros_like(last)
     ops = []
     if r > 0:
-        ops.append(dist.P2POp(dist.isend, top, _global(group, r - 1), group))
+        ops.append(dist.P2POp(dist.isend, first, _global(group, r - 1), group))
         ops.append(dist.P2POp(dist.irecv, from_prev, _global(group, r - 1), group))
     if r < P - 1:
-        ops.append(dist.P2POp(dist.isend, bot, _global(group, r + 1), group))
+        ops.append(dist.P2POp(dist.isend, last, _global(group, r + 1), group))
         ops.append(dist.P2POp(dist.irecv, from_next, _global(group, r + 1), group))
     for req in dist.batch_isend_irecv(ops):
         req.wait()
-    return torch.cat([from_prev, x, from_next], dim)
+    parts = ([from_prev] if top else []) + [x] + ([from_next] if bottom else [])
+    return torch.cat(parts, dim)
 
 
 def gather_tokens(x: torch.Tensor, dim: int) -> torch.Tensor:
@@ -96,6 +99,17 @@ def can_shard(latent_rows: int, group) -> bool:
         return False
     P = dist.get_world_size(group)
     return P > 1 and latent_rows % P == 0 and latent_rows // P >= 1
+
+
+def encode_row_sharded(encode_fn, video: torch.Tensor, group) -> torch.Tensor:
+    """Run ``encode_fn`` (pixels [B,3,T,H,W] -> latent [B,C,T',H/8,W/8]) on this rank's band of pixel rows and gather the
+    latent rows on every rank. Band heights must stay even through the three stride-2 stages: H divisible by 8 * ranks."""
+    band = split_rows(video, 3, group)
+    with row_sharded(group):
+        lat = encode_fn(band).contiguous()
+    parts = [torch.empty_like(lat) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, lat, group=group)
+    return torch.cat(parts, 3)
 
 
 def decode_row_sharded(decode_fn, latent: torch.Tensor, group, dst: Optional[int] = None) -> Optional[torch.Tensor]:

@@ -150,8 +150,14 @@ class Resample(nn.Module):
             conv = self.resample[1]
             x = vae_parallel.exchange_rows(self.resample[0](x), 2, 1)
             x = F.conv2d(x, conv.weight, conv.bias, padding=(0, 1))
+        elif vae_parallel.active() is not None and self.mode in ("downsample2d", "downsample3d"):
+            # stride-2 convolution padded on the bottom / right only: output row j reads input rows 2j .. 2j+2, so an even band
+            # needs exactly one row of the next rank below it (zeros at the bottom of the frame)
+            assert x.shape[2] % 2 == 0, "row bands must keep an even height through every down-sampling stage"
+            conv = self.resample[1]
+            x = vae_parallel.exchange_rows(x, 2, 1, top=False)
+            x = F.conv2d(F.pad(x, (0, 1, 0, 0)), conv.weight, conv.bias, stride=2)
         else:
-            assert vae_parallel.active() is None or self.mode == "none", "row sharding covers the decoder only"
             x = self.resample(x)
         x = x.reshape(b, t, *x.shape[1:]).permute(0, 2, 1, 3, 4)
         if self.mode == "downsample3d" and state is not None:
@@ -431,6 +437,17 @@ class Wan2pt1VAEInterface(VideoTokenizerInterface):
         if not vae_parallel.can_shard(latent.shape[3], group):
             return self.decode(latent)
         return vae_parallel.decode_row_sharded(self.decode, latent, group, dst)
+
+    @torch.no_grad()
+    def encode_parallel(self, state: torch.Tensor, group) -> torch.Tensor:
+        """``encode`` with the frame split into horizontal bands over ``group`` (every rank passes the same video); exact.
+        Falls back to ``encode`` when the pixel rows do not divide into bands of a multiple of 8 rows."""
+        import torch.distributed as dist
+        ok = group is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1 \
+            and state.shape[3] % (8 * dist.get_world_size(group)) == 0
+        if not ok:
+            return self.encode(state)
+        return vae_parallel.encode_row_sharded(self.encode, state, group)
 
     def get_latent_num_frames(self, num_pixel_frames: int) -> int:
         return 1 + (num_pixel_frames - 1) // 4

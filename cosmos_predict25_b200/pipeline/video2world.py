@@ -45,6 +45,7 @@ class Video2WorldInference:
         self.model, self.config = model, config
         self.model.cp_group = cp_group
         if cp_group is not None:
+            self.model.shard_vae_encode = True     # every rank reads the same conditioning clip: encode it in row bands
             self.model.net.enable_context_parallel(cp_group)
             self._attach_peer_exchange(cp_group)
         self.device = self.model.device_

@@ -299,6 +299,14 @@ def _vae_row_sharded(rank, world, tmp):
     # rows that do not divide over the group: plain decode on every rank
     odd = tok.decode_parallel(torch.randn(1, 16, 1, 3, 4), dist.group.WORLD)
     assert odd.shape == (1, 3, 1, 24, 32)
+    # encoder: bands of 16 pixel rows (even through the three stride-2 stages), one row from the next rank per stage
+    torch.manual_seed(2)
+    vid = torch.rand(1, 3, 5, 16 * world, 24) * 2 - 1
+    lat_full = tok.encode(vid)
+    lat_par = tok.encode_parallel(vid, dist.group.WORLD)
+    assert lat_par.shape == lat_full.shape == (1, 16, 2, 2 * world, 3)
+    assert (lat_par - lat_full).abs().max() < 1e-4 * max(1.0, lat_full.abs().max().item())
+    assert tok.encode_parallel(vid[:, :, :, :24], dist.group.WORLD).shape[3] == 3       # 24 rows: no even bands, plain encode
 
 
 def test_vae_decode_row_sharded_matches_single_rank():
