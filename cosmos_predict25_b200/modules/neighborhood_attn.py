@@ -175,12 +175,70 @@ def tile_kernel_supported(q: torch.Tensor, video_size, dilation) -> bool:
             and native.available() and hasattr(native.load(), "fa_fwd_na"))
 
 
+def _group_starts(L: int, k: int, s: int) -> torch.Tensor:
+    """First visible key of every stride group of a non-causal, undilated axis (all queries of a group share the window)."""
+    g = torch.arange(L // s)
+    leader = torch.clamp(g * s + s // 2, max=L - 1)
+    return torch.clamp(leader - k // 2, min=0, max=L - k)
+
+
+def grouped_attention_supported(video_size, window, stride, dilation, is_causal) -> bool:
+    return (all(d == 1 for d in dilation) and not any(is_causal)
+            and all(L % s == 0 and k <= L for L, k, s in zip(video_size, window, stride)))
+
+
+def neighborhood_attention_grouped(q, k, v, video_size, window, stride, scale: Optional[float] = None,
+                                   max_keys_per_chunk: int = 1 << 24) -> torch.Tensor:
+    """Differentiable neighbourhood attention whose cost follows the window, not the sequence: the queries of one stride group
+    share one box of keys, so each group is a small dense attention over its gathered box (``scaled_dot_product_attention`` on
+    [groups, heads, queries per group, keys per box]); autograd scatters the key / value gradients back through the gather.
+    Non-causal, dilation 1, axis lengths divisible by the strides. Groups are processed in chunks to bound the gathered size."""
+    import torch.nn.functional as F
+    B, L, Hh, D = q.shape
+    T, H, W = video_size
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    (kt, kh, kw), (st, sh, sw) = window, stride
+    Gt, Gh, Gw = T // st, H // sh, W // sw
+    dev = q.device
+    it = (_group_starts(T, kt, st)[:, None] + torch.arange(kt)[None]).to(dev)        # [Gt, kt]
+    ih = (_group_starts(H, kh, sh)[:, None] + torch.arange(kh)[None]).to(dev)        # [Gh, kh]
+    iw = (_group_starts(W, kw, sw)[:, None] + torch.arange(kw)[None]).to(dev)        # [Gw, kw]
+    q6 = q.view(B, Gt, st, Gh, sh, Gw, sw, Hh, D).permute(0, 1, 3, 5, 7, 2, 4, 6, 8)   # [B,Gt,Gh,Gw,heads,st,sh,sw,D]
+    k5, v5 = k.view(B, T, H, W, Hh, D), v.view(B, T, H, W, Hh, D)
+    nq, nk = st * sh * sw, kt * kh * kw
+    rows_per_chunk = max(1, max_keys_per_chunk // max(1, B * Gw * nk * Hh))          # (gt, gh) pairs per chunk
+    out = q.new_empty(B, Gt, Gh, Gw, Hh, nq, D)
+    pairs = [(a, b) for a in range(Gt) for b in range(Gh)]
+    for c0 in range(0, len(pairs), rows_per_chunk):
+        chunk = pairs[c0:c0 + rows_per_chunk]
+        ga = torch.tensor([a for a, _ in chunk], device=dev)
+        gb = torch.tensor([b for _, b in chunk], device=dev)
+        n = len(chunk)
+        # key boxes of the groups (ga[i], gb[i], every gw): [B, n, Gw, kt, kh, kw, heads, D]
+        tt = it[ga][:, None, :, None, None]                                          # [n,1,kt,1,1]
+        hh = ih[gb][:, None, None, :, None]                                          # [n,1,1,kh,1]
+        ww = iw[None, :, None, None, :]                                              # [1,Gw,1,1,kw]
+        kb = k5[:, tt, hh, ww]
+        vb = v5[:, tt, hh, ww]
+        kb = kb.reshape(B * n * Gw, nk, Hh, D).transpose(1, 2)
+        vb = vb.reshape(B * n * Gw, nk, Hh, D).transpose(1, 2)
+        qb = q6[:, ga, gb].reshape(B * n * Gw, Hh, nq, D)
+        ob = F.scaled_dot_product_attention(qb, kb, vb, scale=scale).view(B, n, Gw, Hh, nq, D)
+        out[:, ga, gb] = ob
+    o = out.view(B, Gt, Gh, Gw, Hh, st, sh, sw, D).permute(0, 1, 5, 2, 6, 3, 7, 4, 8)
+    return o.reshape(B, L, Hh, D)
+
+
 def neighborhood_attention(q, k, v, video_size, window, stride=1, dilation=1, is_causal=False,
                            scale: Optional[float] = None) -> torch.Tensor:
     """q, k, v: [B, T*H*W, heads, D] -> [B, T*H*W, heads, D]."""
     stride, dilation, is_causal = _triple(stride, int), _triple(dilation, int), _triple(is_causal, bool)
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not tile_kernel_supported(q, video_size, dilation) or k.requires_grad or v.requires_grad:
+        # training / CPU: gather the shared key box of every stride group when the configuration allows it (cost follows the
+        # window), otherwise the dense-masked definition
+        if grouped_attention_supported(video_size, window, stride, dilation, is_causal) and q.shape[1] > 4096:
+            return neighborhood_attention_grouped(q, k, v, video_size, window, stride, scale)
         return neighborhood_attention_reference(q, k, v, video_size, window, stride, dilation, is_causal, scale)
     from ..ops import native
     plan = tile_plan(video_size, window, stride, is_causal, q.device)

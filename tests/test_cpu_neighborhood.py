@@ -116,3 +116,22 @@ def test_dit_blocks_switch_to_sparse_attention():
         assert local.shape == dense.shape and torch.isfinite(local).all() and not torch.allclose(local, dense, atol=1e-4)
     with pytest.raises(ValueError):
         replace_selfattn_op_with_sparse_attn_op(net, 0, None)
+
+
+@pytest.mark.parametrize("window,stride", [((4, 4, 8), (1, 1, 1)), ((8, 4, 16), (1, 4, 8)), ((5, 7, 9), (2, 3, 4)), ((8, 12, 16), (2, 2, 2))])
+def test_grouped_gather_path_matches_definition_with_gradients(window, stride):
+    torch.manual_seed(4)
+    vs = (8, 12, 16)
+    assert na.grouped_attention_supported(vs, window, stride, (1, 1, 1), (False, False, False))
+    L = vs[0] * vs[1] * vs[2]
+    q, k, v = (torch.randn(1, L, 2, 8, dtype=torch.float64, requires_grad=True) for _ in range(3))
+    go = torch.randn(1, L, 2, 8, dtype=torch.float64)
+    got = na.neighborhood_attention_grouped(q, k, v, vs, window, stride, max_keys_per_chunk=1 << 14)   # several chunks
+    g1 = torch.autograd.grad(got, (q, k, v), go)
+    want = na.neighborhood_attention_reference(q, k, v, vs, window, stride)
+    g2 = torch.autograd.grad(want, (q, k, v), go)
+    assert torch.allclose(got, want.double(), atol=1e-5)
+    for a, b in zip(g1, g2):
+        assert torch.allclose(a, b.double(), atol=1e-4), (a - b).abs().max()
+    assert not na.grouped_attention_supported(vs, window, stride, (1, 1, 1), (True, False, False))
+    assert not na.grouped_attention_supported((9, 12, 16), (4, 4, 8), (2, 1, 1), (1, 1, 1), (False, False, False))
