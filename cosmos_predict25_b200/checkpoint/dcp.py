@@ -229,6 +229,20 @@ class DistributedCheckpointer:
             return 0
         if _dist_on():
             dist.barrier()
+        try:
+            iteration = self._load_parts(model, optimizer, scheduler, keys, path)
+        except BaseException as e:
+            # torch's CheckpointException derives from BaseException; callers that guard with ``except Exception`` must see it
+            if isinstance(e, (Exception, KeyboardInterrupt, SystemExit)):
+                raise
+            raise RuntimeError(f"checkpoint {path} is damaged or incomplete: {e}") from e
+        log.info(f"loaded checkpoint {path} (keys {sorted(keys)}), iteration {iteration}")
+        if self.callbacks is not None:
+            self.callbacks.on_load_checkpoint_end(model, iteration=iteration, checkpoint_path=path)
+        return iteration
+
+    def _load_parts(self, model, optimizer, scheduler, keys, path: str) -> int:
+        iteration = 0
         for key in KEYS:
             if key not in keys:
                 continue
@@ -259,9 +273,6 @@ class DistributedCheckpointer:
                 sd = {"iteration": torch.tensor(0), "grad_scaler_scale": torch.tensor(1.0)}
                 dcp.load(sd, storage_reader=reader, planner=_TolerantLoadPlanner())
                 iteration = int(sd["iteration"])
-        log.info(f"loaded checkpoint {path} (keys {sorted(keys)}), iteration {iteration}")
-        if self.callbacks is not None:
-            self.callbacks.on_load_checkpoint_end(model, iteration=iteration, checkpoint_path=path)
         return iteration
 
     # ---- save --------------------------------------------------------------------------------------------------
