@@ -120,6 +120,21 @@ class Trainer:
         self.callbacks.on_train_start(self.model, iteration=self.iteration)
         log.info(f"training from iteration {self.iteration} to {cfg.max_iter}")
         done = self.iteration >= cfg.max_iter
+        try:
+            self._loop(dataloader_train, dataloader_val, done)
+        finally:
+            if cfg.timeout_period > 0:
+                signal.alarm(0)   # a pending alarm must not outlive the loop, whichever way it ends
+        if self.checkpointer is not None and cfg.save_iter:
+            if self.iteration % cfg.save_iter != 0:  # otherwise the loop has just written this iteration
+                self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
+            self.checkpointer.finalize()
+        self.callbacks.on_train_end(self.model, iteration=self.iteration)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+
+    def _loop(self, dataloader_train: Iterable, dataloader_val: Optional[Iterable], done: bool) -> None:
+        cfg = self.config
         while not done:
             data_iter = iter(dataloader_train)
             while True:
@@ -141,15 +156,6 @@ class Trainer:
                 if self.iteration >= cfg.max_iter:
                     done = True
                     break
-        if cfg.timeout_period > 0:
-            signal.alarm(0)
-        if self.checkpointer is not None and cfg.save_iter:
-            if self.iteration % cfg.save_iter != 0:  # otherwise the loop has just written this iteration
-                self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
-            self.checkpointer.finalize()
-        self.callbacks.on_train_end(self.model, iteration=self.iteration)
-        if dist.is_available() and dist.is_initialized():
-            dist.barrier()
 
     @torch.no_grad()
     def validate(self, dataloader_val: Iterable) -> float:

@@ -1,0 +1,60 @@
+"""Host-side failure tests of the training loop: a hung step trips the watchdog, a failing dataloader surfaces, and no alarm
+is left armed afterwards."""
+
+import signal
+import time
+
+import pytest
+import torch
+
+from cosmos_predict25_b200.models.dit import dit_tiny
+from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+from cosmos_predict25_b200.trainer.callbacks import Callback
+from cosmos_predict25_b200.trainer.optim import OptimizerConfig
+from cosmos_predict25_b200.trainer.trainer import Trainer, TrainerConfig
+
+
+def _batches(n, fail_at=None):
+    g = torch.Generator().manual_seed(0)
+    for i in range(n):
+        if fail_at is not None and i == fail_at:
+            raise OSError("storage backend went away")
+        yield {"latents": torch.randn(1, 16, 4, 16, 16, generator=g), "t5_text_embeddings": torch.randn(1, 32, 256, generator=g),
+               "fps": torch.tensor([16.0]), "padding_mask": torch.zeros(1, 1, 16, 16)}
+
+
+def _trainer(tmp_path, callbacks=None, **kw):
+    torch.manual_seed(0)
+    model = Video2WorldModelRectifiedFlow(Video2WorldRFConfig(net=dit_tiny(), precision="float32", state_t=4), device=torch.device("cpu"))
+    return Trainer(TrainerConfig(output_dir=str(tmp_path), logging_iter=1, **kw), model, OptimizerConfig(lr=1e-3), callbacks=callbacks)
+
+
+class _Stall(Callback):
+    def __init__(self, at, seconds):
+        self.at, self.seconds = at, seconds
+
+    def on_training_step_end(self, model, data_batch, output_batch, loss, iteration=0):
+        if iteration == self.at:
+            time.sleep(self.seconds)      # a rank that stops making progress (hung collective, dead storage, ...)
+
+
+def test_watchdog_raises_on_a_hung_step_and_disarms(tmp_path):
+    t = _trainer(tmp_path, callbacks=[_Stall(at=2, seconds=5.0)], max_iter=5, timeout_period=1)
+    t0 = time.time()
+    with pytest.raises(TimeoutError):
+        t.train(list(_batches(5)))
+    assert time.time() - t0 < 4.5 and t.iteration == 2
+    assert signal.alarm(0) == 0           # nothing left armed
+
+
+def test_dataloader_failure_surfaces_and_disarms(tmp_path):
+    t = _trainer(tmp_path, max_iter=5, timeout_period=30)
+    with pytest.raises(OSError, match="went away"):
+        t.train(_batches(5, fail_at=2))
+    assert t.iteration == 2 and signal.alarm(0) == 0
+
+
+def test_loop_without_faults_runs_to_max_iter(tmp_path):
+    t = _trainer(tmp_path, max_iter=3, timeout_period=30)
+    t.train(list(_batches(2)))            # the loader is shorter than max_iter: it is restarted
+    assert t.iteration == 3 and signal.alarm(0) == 0
