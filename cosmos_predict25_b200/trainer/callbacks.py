@@ -280,9 +280,25 @@ class WandbCallback(Callback):
         if self.mode == "online" and _rank() == 0:
             try:
                 import wandb
-                self._wandb = wandb.init(project=self.project, name=self.name, resume="allow")
+                self._wandb = wandb.init(project=self.project, name=self.name, resume="allow", id=self._run_id())
             except Exception as e:  # no network: keep the JSONL sink
                 log.warning(f"wandb unavailable ({e}); logging to metrics.jsonl only")
+
+    def _run_id(self) -> str:
+        """The run id lives next to the checkpoints, so a job restarted from its checkpoint continues the same run
+        (cosmos_predict2/_src/imaginaire/utils/wandb_util.py:36-118)."""
+        import uuid
+        out_dir = self.config.output_dir if self.config else "."
+        path = os.path.join(out_dir, "checkpoints", "wandb_id.txt")
+        if os.path.exists(path):
+            rid = open(path).read().strip()
+            if rid:
+                return rid
+        rid = uuid.uuid4().hex[:8]
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        with open(path, "w") as f:
+            f.write(rid + "\n")
+        return rid
 
     def on_training_step_end(self, model, data, output, loss, iteration: int = 0):
         l = loss.detach().float()

@@ -58,3 +58,35 @@ def test_loop_without_faults_runs_to_max_iter(tmp_path):
     t = _trainer(tmp_path, max_iter=3, timeout_period=30)
     t.train(list(_batches(2)))            # the loader is shorter than max_iter: it is restarted
     assert t.iteration == 3 and signal.alarm(0) == 0
+
+
+def test_wandb_run_id_survives_a_restart(tmp_path, monkeypatch):
+    import sys
+    import types
+
+    from cosmos_predict25_b200.trainer.callbacks import WandbCallback
+    calls = []
+    fake = types.ModuleType("wandb")
+
+    class _Run:
+        def log(self, rec, step=None):
+            calls.append(("log", step))
+
+        def finish(self):
+            calls.append(("finish",))
+
+    def init(**kw):
+        calls.append(("init", kw["id"], kw["resume"]))
+        return _Run()
+
+    fake.init = init
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    ids = []
+    for _ in range(2):                                   # the second trainer stands for the restarted job
+        cb = WandbCallback(logging_iter=1, mode="online")
+        t = _trainer(tmp_path, callbacks=[cb], max_iter=1)
+        t.train(list(_batches(1)))
+        ids.append([c for c in calls if c[0] == "init"][-1][1])
+    assert ids[0] == ids[1] and len(ids[0]) == 8
+    assert (tmp_path / "checkpoints" / "wandb_id.txt").read_text().strip() == ids[0]
+    assert ("log", 1) in calls and ("finish",) in calls and (tmp_path / "metrics.jsonl").exists()
