@@ -140,8 +140,9 @@ def ulysses_attention_fused(q_raw, k_raw, v, q_norm_weight, k_norm_weight, rope,
                             scale: Optional[float] = None):
     """Self-attention on un-normalised q/k projections with the q/k epilogue chain (RMSNorm, RoPE) fused into
     the peer-memory all-to-all. Falls back to the unfused composition when no peer transport is attached."""
+    from ..ops import native
     t = _peer_transports.get(id(group))
-    if t is None or not q_raw.is_cuda:
+    if t is None or not q_raw.is_cuda or native.forward_mode():
         q = ops.rmsnorm_rope(q_raw, q_norm_weight, rope, eps)
         k = ops.rmsnorm_rope(k_raw, k_norm_weight, rope, eps)
         return ulysses_attention(q, k, v, group, scale)
@@ -193,11 +194,26 @@ def ulysses_projected_attention(x, wq, wk, wv, q_norm_weight, k_norm_weight, rop
     return t.head_to_seq(ops.attention(qh, kh, vh, scale))
 
 
+def _exchange_dual(fn, x: torch.Tensor) -> torch.Tensor:
+    """Apply the linear map ``fn`` to a (possibly dual) tensor: value and tangent are mapped one after the other."""
+    import torch.autograd.forward_ad as fwAD
+    primal, tangent = fwAD.unpack_dual(x)
+    y = fn(primal.contiguous())
+    if tangent is None:
+        return y
+    return fwAD.make_dual(y, fn(tangent.contiguous()))
+
+
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: Optional[float] = None):
     """Self-attention over a sequence sharded on dim 1 across ``group``."""
     P, _ = group_size_rank(group)
     if P == 1:
         return ops.attention(q, k, v, scale)
+    from ..ops import native
+    if native.forward_mode():
+        # forward-mode AD (consistency distillation): the exchanges are linear, so primal and tangent travel separately
+        qh, kh, vh = (_exchange_dual(lambda x: seq_to_head(x, group), x) for x in (q, k, v))
+        return _exchange_dual(lambda x: head_to_seq(x, group), ops.attention(qh, kh, vh, scale))
     qh = _SeqToHead.apply(q, group)
     kh = _SeqToHead.apply(k, group)
     vh = _SeqToHead.apply(v, group)

@@ -423,3 +423,36 @@ def _sparse_attention_under_cp(rank, world, tmp):
 
 def test_sparse_attention_under_context_parallel():
     run_distributed("_sparse_attention_under_cp", world=2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _network_jvp_under_cp(rank, world, tmp):
+    """Forward-mode (JVP) network pass under context parallelism equals the T-slice of the single-rank pass."""
+    from cosmos_predict25_b200.models.distill import network_jvp
+    from cosmos_predict25_b200.models.dit import NET_PRESETS, CosmosDiT
+    g = dist.group.WORLD
+    torch.manual_seed(3)
+    cfg = NET_PRESETS["tiny"]()
+    net = CosmosDiT(cfg).eval()
+    net.init_weights()
+    for p in net.parameters():                   # AdaLN output layers start at zero: perturb so that every path carries signal
+        if p.abs().sum() == 0:
+            torch.nn.init.normal_(p, std=0.02)
+    T = 2 * world
+    x, tx = torch.randn(1, cfg.in_channels, T, 8, 8), torch.randn(1, cfg.in_channels, T, 8, 8)
+    ts, tt = torch.full((1, T), 0.4), torch.ones(1, T)
+    ctx_dim = cfg.crossattn_proj_in_channels if cfg.use_crossattn_projection else cfg.crossattn_emb_channels
+    kw = dict(crossattn_emb=torch.randn(1, 8, ctx_dim), fps=torch.tensor([16.0]), padding_mask=torch.zeros(1, 1, 8, 8))
+    mask = torch.zeros(1, 1, T, 8, 8)
+    F_full, dF_full = network_jvp(net, x, ts, tx, tt, condition_video_input_mask_B_C_T_H_W=mask, **kw)
+    tl = slice(rank * 2, rank * 2 + 2)
+    net.enable_context_parallel(g)
+    F_loc, dF_loc = network_jvp(net, x[:, :, tl], ts[:, tl], tx[:, :, tl], tt[:, tl], condition_video_input_mask_B_C_T_H_W=mask[:, :, tl], **kw)
+    net.disable_context_parallel()
+    assert dF_full.abs().max() > 1e-4
+    assert torch.allclose(F_loc, F_full[:, :, tl], atol=1e-4)
+    assert torch.allclose(dF_loc, dF_full[:, :, tl], atol=1e-4), (dF_loc - dF_full[:, :, tl]).abs().max()
+
+
+def test_network_jvp_under_context_parallel():
+    run_distributed("_network_jvp_under_cp", world=2)
