@@ -22,6 +22,8 @@ from typing import Optional
 import torch
 from torch.utils.checkpoint import CheckpointPolicy, checkpoint, create_selective_checkpoint_contexts
 
+from ..ops import native
+
 CHECKPOINT_MODES = ("none", "block_wise", "save_attention", "mm_only", "save_attention_some_mm")
 
 # reference mode names accepted as aliases
@@ -62,9 +64,10 @@ def _mm_ops():
 
 def _make_policy(mode: str):
     attn, mm = _attention_ops(), _mm_ops()
+    own = {op for op in (attn | mm) if "cosmos_b200" in str(op)}   # operators whose front-ends count kernel launches
     counter = {False: 0, True: 0}  # forward pass / recompute pass must take identical decisions
 
-    def policy(ctx, op, *args, **kwargs):
+    def decide(ctx, op):
         if mode in ("save_attention", "save_attention_some_mm") and op in attn:
             return CheckpointPolicy.MUST_SAVE
         if mode == "mm_only" and (op in mm or op in attn):
@@ -74,6 +77,13 @@ def _make_policy(mode: str):
             if counter[bool(ctx.is_recompute)] % 16 in (1, 6, 11):
                 return CheckpointPolicy.MUST_SAVE
         return CheckpointPolicy.PREFER_RECOMPUTE
+
+    def policy(ctx, op, *args, **kwargs):
+        d = decide(ctx, op)
+        if d == CheckpointPolicy.MUST_SAVE and ctx.is_recompute and op in own:
+            # the recompute pass takes this result from the cache: the front-end still counted a launch that never happens
+            native.count_launch(-1)
+        return d
 
     return policy
 
