@@ -126,3 +126,33 @@ def test_misc_helpers():
     avg = timer.compute_average_results()
     assert 0.005 < avg["forward"] < 0.2
     assert misc.count_params(torch.nn.Linear(3, 2)) == 8
+
+
+def test_item_datasets_with_media_and_rank_split(tmp_path):
+    import pickle
+
+    from PIL import Image
+
+    from cosmos_predict25_b200.data.item_dataset import PromptImageItemDataset, PromptVideoItemDataset, calculate_indices
+    assert calculate_indices(10, 4, 0) == (0, 3, False) and calculate_indices(10, 4, 1) == (3, 6, False)
+    assert calculate_indices(10, 4, 3) == (8, 10, False) and calculate_indices(2, 4, 3) == (0, 1, True)
+    covered = [i for r in range(4) for i in range(*calculate_indices(10, 4, r)[:2])]
+    assert covered == list(range(10))
+    for i, name in enumerate(["b", "a"]):
+        with open(tmp_path / f"{name}.pkl", "wb") as f:
+            pickle.dump({"prompt": f"prompt {name}", "t5_text_embeddings": torch.randn(3 + i, 8).numpy()}, f)
+        Image.fromarray((torch.rand(20, 30, 3) * 255).byte().numpy()).save(tmp_path / f"{name}.jpg")
+        video_io.save_img_or_video(torch.rand(3, 4 + i, 20, 30), str(tmp_path / name), fps=8)
+    (tmp_path / "orphan.jpg").write_bytes((tmp_path / "a.jpg").read_bytes())          # no pickle: ignored
+    img = PromptImageItemDataset(str(tmp_path), num_video_frames=5, height=16, width=24, max_t5_length=6)
+    assert len(img) == 2 and img.stems == ["a", "b"]
+    it = img[0]
+    assert it["prompt"] == "prompt a" and it["video"].shape == (3, 5, 16, 24) and int(it["video"][:, 1:].max()) == 0
+    assert int(it["video"][:, 0].max()) > 0 and it["t5_text_embeddings"].shape == (6, 8) and int(it["t5_text_mask"].sum()) == 4
+    vid = PromptVideoItemDataset(str(tmp_path), num_video_frames=6, height=16, width=24, start_index=1)
+    assert len(vid) == 1
+    iv = vid[0]
+    assert iv["__file__"] == "b" and iv["video"].shape == (3, 6, 16, 24) and iv["num_frames"] == 4
+    assert int(iv["video"][:, 4:].max()) == 0 and abs(float(iv["fps"]) - 8) < 0.5
+    with pytest.raises(IndexError):
+        vid[1]
