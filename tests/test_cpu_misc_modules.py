@@ -164,3 +164,26 @@ def test_profiling_contexts(tmp_path):
     with maybe_enable_memory_snapshot(ProfilingConfig(enable_memory_snapshot=True, profile_freq=2), str(tmp_path)) as mp:
         mp.step(); mp.step()
     assert os.path.exists(tmp_path / "memory_snapshot" / "iteration_2" / "rank0_memory_snapshot.pickle")
+
+
+def test_config_yaml_round_trip_with_type_markers(tmp_path):
+    import enum
+
+    import torch
+
+    from cosmos_predict25_b200.config import InferenceType
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig
+    from cosmos_predict25_b200.utils.lazy_config import LazyCall as L
+    from cosmos_predict25_b200.utils.lazy_config import LazyConfig, instantiate
+    cfg = {"precision": torch.bfloat16, "kind": InferenceType.VIDEO2WORLD, "optimizer": OptimizerConfig(lr=3e-4, weight_decay=0.1),
+           "net": L(torch.nn.Linear)(in_features=4, out_features=2, bias=False), "nested": {"sizes": (1, 2, 3), "none": None, "flag": True}}
+    path = str(tmp_path / "config.yaml")
+    LazyConfig.save_yaml(cfg, path)
+    text = open(path).read()
+    assert "__type__: torch.dtype" in text and "torch.nn.modules.linear.Linear" in text
+    back = LazyConfig.load_yaml(path)
+    assert back["precision"] is torch.bfloat16 and back["kind"] is InferenceType.VIDEO2WORLD
+    assert isinstance(back["optimizer"], OptimizerConfig) and back["optimizer"].lr == 3e-4 and back["optimizer"].weight_decay == 0.1
+    assert back["nested"]["sizes"] == [1, 2, 3] and back["nested"]["none"] is None and back["nested"]["flag"] is True
+    lin = instantiate(back["net"])
+    assert isinstance(lin, torch.nn.Linear) and lin.weight.shape == (2, 4) and lin.bias is None
