@@ -22,6 +22,17 @@ def _rank():
     return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
 
 
+def _optim_state(optimizer) -> dict:
+    """Optimizer state that ONE file can restore on every rank. A sharded optimizer's ``state_dict`` holds only the
+    calling rank's rows; writing rank 0's copy and loading it everywhere would put rank 0's rows into every shard.
+    Such optimizers expose ``consolidated_state_dict`` (a collective that gathers full tensors), used here."""
+    if optimizer is None:
+        return {}
+    if hasattr(optimizer, "consolidated_state_dict"):
+        return optimizer.consolidated_state_dict()
+    return optimizer.state_dict()
+
+
 class DummyCheckpointer:
     def __init__(self, *a, **k):
         pass
@@ -55,7 +66,7 @@ class PtCheckpointer:
         self.finalize()
         name = f"iter_{iteration:09d}"
         cpu = lambda sd: {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in sd.items()}
-        parts = {"model": cpu(model.state_dict()), "optim": cpu(optimizer.state_dict()) if optimizer is not None else {},
+        parts = {"model": cpu(model.state_dict()), "optim": cpu(_optim_state(optimizer)),
                  "scheduler": scheduler.state_dict() if scheduler is not None else {}}
         trainer_state = {"iteration": iteration, "grad_scaler": {}}
 
@@ -131,7 +142,7 @@ class ModelParallelPtCheckpointer(PtCheckpointer):
         cpu = lambda sd: {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in sd.items()}
         model_sd = cpu(model.state_dict())
         model_sd.update(self._extra_model_state(model))
-        parts = {"model": model_sd, "optim": cpu(optimizer.state_dict()) if optimizer is not None else {},
+        parts = {"model": model_sd, "optim": cpu(_optim_state(optimizer)),
                  "scheduler": scheduler.state_dict() if scheduler is not None else {}}
         first_replica, first_mp = self.dp_rank() == 0, self.mp_rank() == 0
 

@@ -30,9 +30,19 @@ def launch(config: Config, args) -> None:
         config.save(out_dir)
         log.init_loguru_file(os.path.join(out_dir, "stdout.log"))
     dev = torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu")
-    groups = build_groups(cp_size=config["model_parallel"]["context_parallel_size"])
-    model = instantiate(config["model"], device=dev, fsdp_group=groups.fsdp, cp_group=groups.cp)
     t = config["trainer"]
+    cp_size = config["model_parallel"]["context_parallel_size"]
+    world = distributed.get_world_size()
+    if t["distributed_parallelism"] == "ddp":
+        shard_size = cp_size                     # nothing sharded beyond the ranks that share a sample
+    else:
+        mcfg = config["model"].get("config") if hasattr(config["model"], "get") else None
+        shard_size = int((mcfg or {}).get("fsdp_shard_size", 0) or 0)
+        if shard_size <= 1 or shard_size > world or world % shard_size != 0 or shard_size % cp_size != 0:
+            shard_size = world                   # unset (or not a divisor of this job): shard over all ranks
+    groups = build_groups(cp_size=cp_size, shard_size=shard_size)
+    model = instantiate(config["model"], device=dev, fsdp_group=groups.fsdp, cp_group=groups.cp,
+                        replicate_group=groups.replicate)
     callbacks = [instantiate(v) for v in (t.get("callbacks") or {}).values() if v is not None]
     ckpt_cls = config["checkpoint"].get("type")
     checkpointer = None

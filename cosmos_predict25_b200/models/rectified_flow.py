@@ -100,9 +100,11 @@ def ema_exp_coefficient(rate: float) -> float:
 class Text2WorldModelRectifiedFlow(nn.Module):
     condition_is_video2world = False
 
-    def __init__(self, config: Text2WorldRFConfig, device: Optional[torch.device] = None, fsdp_group=None, cp_group=None):
+    def __init__(self, config: Text2WorldRFConfig, device: Optional[torch.device] = None, fsdp_group=None, cp_group=None,
+                 replicate_group=None):
         super().__init__()
         self.config = config
+        self.replicate_group = replicate_group
         self.precision = _PRECISION[config.precision]
         self.device_ = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                                   else torch.device("cpu"))
@@ -140,10 +142,13 @@ class Text2WorldModelRectifiedFlow(nn.Module):
                     if not p.requires_grad and p.is_floating_point():
                         p.data = p.data.to(self.precision)
             make = ShardedEngine
-            if self.config.sharding_transport == "peer" and self.device_.type == "cuda":
+            import torch.distributed as dist
+            n_shard = dist.get_world_size(self.fsdp_group) if (self.fsdp_group is not None and dist.is_initialized()) else 1
+            # peer kernels address one NVSwitch domain (2..8 ranks); anything else goes through NCCL
+            if self.config.sharding_transport == "peer" and self.device_.type == "cuda" and 2 <= n_shard <= 8:
                 from ..parallel.peer_fsdp import PeerShardedEngine as make
             self.engine = make(self.net, group=self.fsdp_group, compute_dtype=self.precision,
-                               use_ema=self.config.ema.enabled,
+                               use_ema=self.config.ema.enabled, replicate_group=self.replicate_group,
                                transport="nccl" if make is ShardedEngine else "peer")
         if self.tokenizer is not None and hasattr(self.tokenizer, "reset_dtype"):
             self.tokenizer.reset_dtype()
@@ -265,18 +270,19 @@ class Text2WorldModelRectifiedFlow(nn.Module):
         B = x0.shape[0]
         u = self.rectified_flow.sample_train_time(B).to(**self.tensor_kwargs_fp32).view(B, 1)
         x0, condition, eps, u = self.broadcast_split_for_model_parallelsim(x0, condition, eps, u)
-        idx = self.rectified_flow.indices(u.cpu())
+        # the time tables live on the device, so the index never comes back to the host (no synchronisation per step)
+        table_t, table_s = self._rf_tables()
+        idx = self.rectified_flow.indices(u)
         if cfg.use_high_sigma_strategy:
-            table_t = self.rectified_flow.timesteps
             cand = torch.nonzero((table_t >= cfg.high_sigma_timesteps_min) & (table_t <= cfg.high_sigma_timesteps_max)).view(-1)
             if len(cand) == 0:
                 raise ValueError("no candidate timesteps for the high-sigma strategy")
-            pick = torch.rand(idx.shape) < cfg.high_sigma_ratio
-            idx = torch.where(pick, cand[torch.randint(0, len(cand), idx.shape)], idx)
+            pick = torch.rand(idx.shape, device=idx.device) < cfg.high_sigma_ratio
+            idx = torch.where(pick, cand[torch.randint(0, len(cand), idx.shape, device=idx.device)], idx)
             if cp._size_rank(self.cp_group)[0] > 1:
                 idx = cp.broadcast(idx, self.cp_group)
-        timesteps = self.rectified_flow.timesteps[idx].to(**self.tensor_kwargs_fp32).view(B, 1)
-        sigmas = self.rectified_flow.sigmas[idx].to(**self.tensor_kwargs_fp32).view(B, 1)
+        timesteps = table_t[idx].view(B, 1)
+        sigmas = table_s[idx].view(B, 1)
         xt, vt = self.rectified_flow.interpolate(eps, x0, sigmas)
         v_pred = self.denoise(eps, xt.to(**self.tensor_kwargs), timesteps, condition)
         w = self.rectified_flow.loss_weight(timesteps.view(-1))
@@ -284,6 +290,13 @@ class Text2WorldModelRectifiedFlow(nn.Module):
         loss = torch.mean(w * per_instance)
         out = {"x0": x0, "xt": xt, "sigma": sigmas, "condition": condition, "model_pred": v_pred, "edm_loss": loss}
         return out, loss
+
+    def _rf_tables(self):
+        """(timesteps, sigmas) of the training schedule as fp32 tensors on the model's device (copied once)."""
+        if getattr(self, "_rf_tables_dev", None) is None:
+            self._rf_tables_dev = (self.rectified_flow.timesteps.to(**self.tensor_kwargs_fp32),
+                                   self.rectified_flow.sigmas.to(**self.tensor_kwargs_fp32))
+        return self._rf_tables_dev
 
     def _net_kwargs(self, condition: Text2WorldCondition) -> Dict[str, Any]:
         return {"crossattn_emb": condition.crossattn_emb.to(self.precision) if condition.crossattn_emb is not None else None,

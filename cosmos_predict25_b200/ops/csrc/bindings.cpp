@@ -28,7 +28,7 @@ inline void check_f32(const Tensor& t, const char* name) {
 }
 
 constexpr int kRowsPerCta = 32;
-constexpr int kRowsPerWarp = 64;
+constexpr int kRowsPerWarp = CB200_RMSNORM_BWD_ROWS_PER_WARP;
 
 }  // namespace
 
@@ -136,8 +136,20 @@ std::tuple<Tensor, Tensor> rmsnorm_rope_bwd(const Tensor& dy, const Tensor& x, c
                                             const c10::optional<Tensor>& cosv, const c10::optional<Tensor>& sinv) {
   check_bf16(dy, "dy");
   check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 4 && dy.sizes() == x.sizes() && dy.device() == x.device(), "dy must have the shape and device of x [B, S, H, D]");
   c10::cuda::CUDAGuard g(x.device());
   const int64_t B = x.size(0), S = x.size(1), H = x.size(2), HD = x.size(3);
+  TORCH_CHECK(HD == 128 || HD == 64, "head_dim must be 64 or 128");
+  TORCH_CHECK(w.numel() == HD && w.device() == x.device(), "w must hold head_dim values on the device of x");
+  check_f32(rstd, "rstd");
+  TORCH_CHECK(rstd.numel() == B * S * H && rstd.device() == x.device(), "rstd must be [B, S, H] on the device of x");
+  TORCH_CHECK(cosv.has_value() == sinv.has_value(), "cos and sin come together");
+  if (cosv.has_value()) {
+    check_f32(*cosv, "cos");
+    check_f32(*sinv, "sin");
+    TORCH_CHECK(cosv->dim() == 2 && cosv->size(0) == S && cosv->size(1) == HD / 2 && sinv->sizes() == cosv->sizes() &&
+                    cosv->device() == x.device() && sinv->device() == x.device(), "cos/sin must be [S, D/2] on the device of x");
+  }
   Tensor wf = w.to(at::kFloat).contiguous();
   const float* cp = cosv.has_value() ? cosv->data_ptr<float>() : nullptr;
   const float* sp = sinv.has_value() ? sinv->data_ptr<float>() : nullptr;

@@ -17,6 +17,30 @@ using at::Tensor;
 
 inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+// every operand that a kernel indexes through a raw pointer is checked here: a wrong dtype, device, layout or size must be a
+// Python error, not an out-of-bounds access to this GPU's or a peer's memory
+void check_shard(const Tensor& t, const char* name, const Tensor& like) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), name, " must be a contiguous fp32 CUDA tensor");
+  TORCH_CHECK(t.device() == like.device() && t.numel() == like.numel(), name, " must match the master shard in device and size");
+}
+
+void check_segs(const Tensor& segs, const Tensor& like) {
+  TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kLong && segs.is_contiguous() && segs.dim() == 2 && segs.size(1) == 4 &&
+                  segs.size(0) >= 1,
+              "segment table must be a contiguous int64 CUDA tensor [n, 4]");
+  TORCH_CHECK(segs.device() == like.device(), "segment table is on another device than the shard");
+}
+
+void check_rope(const c10::optional<Tensor>& cosv, const c10::optional<Tensor>& sinv, int64_t S, int64_t HD, const Tensor& x) {
+  TORCH_CHECK(cosv.has_value() == sinv.has_value(), "cos and sin come together");
+  if (!cosv.has_value()) return;
+  for (const Tensor* t : {&*cosv, &*sinv}) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->device() == x.device(),
+                "cos/sin must be contiguous fp32 CUDA tensors on the device of x");
+    TORCH_CHECK(t->dim() == 2 && t->size(0) == S && t->size(1) == HD / 2, "cos/sin must be [S, D/2] for the local sequence slice");
+  }
+}
+
 std::vector<int64_t> ptr_vec(c10::ArrayRef<int64_t> v) {
   TORCH_CHECK(v.size() >= 1 && v.size() <= 8, "1..8 peers supported");
   return std::vector<int64_t>(v.begin(), v.end());
@@ -31,9 +55,16 @@ void peer_barrier(c10::ArrayRef<int64_t> flag_ptrs, int64_t rank, int64_t epoch,
 // segs: int64 CUDA tensor [nseg, 4] = (full_offset, stride, shard_offset, numel)
 void rs_cast_norm_peer(c10::ArrayRef<int64_t> grad_ptrs, const Tensor& segs, Tensor g32, Tensor unit_sumsq,
                        const c10::optional<Tensor>& total_sumsq, int64_t rank, double scale) {
-  TORCH_CHECK(segs.is_cuda() && segs.scalar_type() == at::kLong && segs.is_contiguous() && segs.size(1) == 4, "bad segment table");
+  TORCH_CHECK(g32.is_cuda() && g32.scalar_type() == at::kFloat && g32.is_contiguous(), "g32 must be a contiguous fp32 CUDA tensor");
+  check_segs(segs, g32);
+  check_shard(unit_sumsq, "unit_sumsq", unit_sumsq);
+  TORCH_CHECK(unit_sumsq.numel() >= 1 && unit_sumsq.device() == g32.device(), "unit_sumsq: one float on the device of g32");
+  if (total_sumsq.has_value())
+    TORCH_CHECK(total_sumsq->is_cuda() && total_sumsq->scalar_type() == at::kFloat && total_sumsq->numel() >= 1 &&
+                    total_sumsq->device() == g32.device(), "total_sumsq: one float on the device of g32");
   c10::cuda::CUDAGuard g(g32.device());
   auto p = ptr_vec(grad_ptrs);
+  TORCH_CHECK(rank >= 0 && rank < (int64_t)p.size(), "rank out of range");
   const int nseg = (int)segs.size(0);
   Tensor partials = at::empty({(int64_t)cb200_rs_blocks_x() * nseg}, g32.options());
   cb200_rs_cast_norm_peer(p.data(), segs.data_ptr(), nseg, g32.data_ptr<float>(), partials.data_ptr<float>(),
@@ -45,10 +76,20 @@ void adamw_push_peer(c10::ArrayRef<int64_t> full_ptrs, c10::ArrayRef<int64_t> su
                      const Tensor& grad, Tensor m, Tensor v, const c10::optional<Tensor>& ema, int64_t rank, double max_norm,
                      double lr, double beta1, double beta2, double eps, double wd, int64_t step, double ema_beta,
                      const c10::optional<Tensor>& norm_out) {
+  check_shard(master, "master", master);
+  check_shard(grad, "grad", master);
+  check_shard(m, "exp_avg", master);
+  check_shard(v, "exp_avg_sq", master);
+  if (ema.has_value()) check_shard(*ema, "ema", master);
+  check_segs(segs, master);
+  if (norm_out.has_value())
+    TORCH_CHECK(norm_out->is_cuda() && norm_out->scalar_type() == at::kFloat && norm_out->numel() >= 1 &&
+                    norm_out->device() == master.device(), "norm_out: one float on the device of the shard");
   c10::cuda::CUDAGuard g(master.device());
   auto fp = ptr_vec(full_ptrs);
   auto sp = ptr_vec(sumsq_ptrs);
   TORCH_CHECK(fp.size() == sp.size(), "pointer lists differ in length");
+  TORCH_CHECK(rank >= 0 && rank < (int64_t)fp.size(), "rank out of range");
   cb200_adamw_push_peer(fp.data(), sp.data(), segs.data_ptr(), (int)segs.size(0), master.data_ptr<float>(), grad.data_ptr<float>(),
                         m.data_ptr<float>(), v.data_ptr<float>(), ema.has_value() ? ema->data_ptr<float>() : nullptr, (int)rank,
                         (int)fp.size(), (float)max_norm, (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, step,
@@ -63,6 +104,13 @@ Tensor a2a_scatter_heads_peer(const Tensor& x, c10::ArrayRef<int64_t> out_ptrs, 
   auto p = ptr_vec(out_ptrs);
   const int64_t B = x.size(0), S = x.size(1), H = x.size(2), HD = x.size(3);
   TORCH_CHECK((HD == 128 || HD == 64) && H % (int64_t)p.size() == 0, "head_dim 64/128 and heads divisible by peers");
+  TORCH_CHECK(rank >= 0 && rank < (int64_t)p.size(), "rank out of range");
+  if (w.has_value()) {
+    TORCH_CHECK(w->is_cuda() && w->device() == x.device() && w->numel() == HD, "norm weight must hold head_dim values on the device of x");
+    check_rope(cosv, sinv, S, HD, x);
+  } else {
+    TORCH_CHECK(!cosv.has_value() && !sinv.has_value(), "RoPE is applied only together with the norm");
+  }
   Tensor rstd = at::empty({w.has_value() ? B * S * H : 0}, x.options().dtype(at::kFloat));
   Tensor wf;
   const float* wp = nullptr;
@@ -79,8 +127,11 @@ Tensor a2a_scatter_heads_peer(const Tensor& x, c10::ArrayRef<int64_t> out_ptrs, 
 
 Tensor a2a_gather_seq_peer(c10::ArrayRef<int64_t> src_ptrs, int64_t B, int64_t S, int64_t H, int64_t HD, int64_t rank,
                            const Tensor& like) {
+  TORCH_CHECK(like.is_cuda(), "like must be a CUDA tensor");
   c10::cuda::CUDAGuard g(like.device());
   auto p = ptr_vec(src_ptrs);
+  TORCH_CHECK(rank >= 0 && rank < (int64_t)p.size() && B >= 1 && S >= 1 && H >= 1 && (HD == 64 || HD == 128) &&
+                  H % (int64_t)p.size() == 0, "bad exchange shape");
   Tensor out = at::empty({B, S, H, HD}, like.options().dtype(at::kBFloat16));
   cb200_a2a_gather_seq_peer(p.data(), out.data_ptr(), B, (int)S, (int)H, (int)HD, (int)rank, (int)p.size(), stream());
   return out;

@@ -3,6 +3,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// rows of the RMSNorm/RoPE backward that one warp reduces before it writes a weight-gradient partial (a CTA has 8 warps). The
+// torch operator and the allocation-free entry point both pass this value, which is what makes their results bit-identical.
+#define CB200_RMSNORM_BWD_ROWS_PER_WARP 64
+
 extern "C" {
 // elementwise.cu
 int cb200_ln_groups_per_frame(int L, int rows_per_cta);

@@ -20,7 +20,10 @@ static __device__ __align__(256) float g_noalloc_scratch[CB200_NOALLOC_SCRATCH_F
 namespace {
 
 constexpr int kMaxDevices = 64;
-constexpr int kRowsPerWarp = 64;  // must match the torch operator so both produce bit-identical results
+constexpr int kRowsPerWarp = CB200_RMSNORM_BWD_ROWS_PER_WARP;  // shared with the torch operator: same grouping, same bits
+static_assert(CB200_NOALLOC_ROWS_PER_CTA == 8 * kRowsPerWarp, "noalloc.h states the rows per CTA of the backward kernel (8 warps)");
+static_assert(CB200_NOALLOC_MAX_ROWS == (long)(CB200_NOALLOC_SCRATCH_FLOATS / 128) * CB200_NOALLOC_ROWS_PER_CTA,
+              "the row limit follows from the scratch size at head_dim 128");
 
 float* g_scratch_addr[kMaxDevices] = {nullptr};
 std::mutex g_setup_mutex;
@@ -70,6 +73,13 @@ extern "C" int cb200_rmsnorm_rope_bwd_noalloc(const void* dy, const void* x, con
   cudaError_t e = scratch_for_current_device(&scratch);
   if (e != cudaSuccess) {
     set_error(errbuf, errbuf_len, "rmsnorm_rope_bwd_noalloc: cudaGetSymbolAddress failed with CUDA error %ld", (long)e);
+    return CB200_NOALLOC_ERR_CUDA;
+  }
+  // An error left behind by earlier, unrelated work must not be reported (and cleared) as this call's launch failure.
+  e = cudaPeekAtLastError();
+  if (e != cudaSuccess) {
+    set_error(errbuf, errbuf_len, "rmsnorm_rope_bwd_noalloc: the CUDA context already carries error %ld from earlier work; nothing launched",
+              (long)e);
     return CB200_NOALLOC_ERR_CUDA;
   }
   // every partial slot [0, ctas) x [0, HD) is written by the first kernel before the second one sums it

@@ -28,6 +28,8 @@
 //   * All calls on a device share the one array and it keeps whatever the previous call left in it. Each call
 //     overwrites every slot it later reads, so nothing has to be cleared between calls; but two calls that
 //     overlap on the GPU (different streams, no ordering between them) race on it. Serialise them.
+//   * `stream` must be a stream of the device that is current when the call is made (or 0): the scratch address used is
+//     the current device's, and a stream of another device would run the kernels against the wrong GPU's copy.
 //   * No cudaMalloc / cudaFree / allocating library routine is called, on any path.
 //
 // Returns 0 on success, a negative CB200_NOALLOC_ERR_* code otherwise. errbuf (may be NULL) receives a

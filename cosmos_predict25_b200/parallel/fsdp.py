@@ -9,11 +9,13 @@ for a 180 GB-per-GPU machine:
     ``ceil(rows/P)``-row chunks (the FSDP2 / DTensor ``Shard(0)`` layout, so checkpoints interoperate).
   * Each rank owns, per unit, one contiguous shard holding its chunk of every parameter:
     fp32 master weights, Adam moments, an optional fp32 EMA, and the fp32 reduced gradient.
-  * ``resident`` policy (default): the full bf16 parameters of all units stay in HBM (4 GB for 2B,
-    29 GB for 14B). The all-gather moves out of the forward pass: the optimizer kernel writes each
-    updated bf16 chunk straight into every peer's full buffer. ``reshard`` policy gathers a unit
-    right before it is used and drops it after (needs activation checkpointing so that backward
-    re-gathers).
+  * The full bf16 parameters of all units stay resident in HBM (4 GB for 2B, 29 GB for 14B). The
+    all-gather moves out of the forward pass: the optimizer kernel writes each updated bf16 chunk
+    straight into every peer's full buffer.
+  * HSDP / DDP: with a ``replicate_group`` the reduced gradient shard is summed once more over the
+    ranks that hold the same shard in other replicas (cosmos_predict2/_src/common/utils/fsdp_helper.py:97-159).
+    A shard group of one rank plus a replicate group over the world is plain data parallelism
+    (cosmos_predict2/_src/imaginaire/utils/distributed.py:173-264): every rank keeps the whole state.
   * Gradients are accumulated by autograd directly into a flat bf16 buffer with the full-parameter
     layout (``param.grad`` are views). When a unit's backward is complete, its reduce-scatter runs
     on a side stream: either NCCL/gloo ``reduce_scatter`` (the baseline twin) or the peer-memory
@@ -182,6 +184,12 @@ class FlatUnit:
             raise ValueError(f"transport {transport!r} is handled by PeerFlatUnit")
         self.reduced = True
 
+    @torch.no_grad()
+    def all_reduce_replicas(self, group):
+        """HSDP / DDP: sum the reduced shard over the replicas (the 1/replicas factor is part of ``scale``)."""
+        dist.all_reduce(self.grad_shard, group=group)
+        self.sumsq.copy_(self.grad_shard.pow(2).sum().view(1))
+
     def _local_grad_to_shard(self, scale: float):
         if self.device.type == "cuda":
             ops = native.load()
@@ -239,15 +247,19 @@ class ShardedEngine:
 
     def __init__(self, net: nn.Module, group=None, compute_dtype: torch.dtype = torch.bfloat16, use_ema: bool = True,
                  transport: str = "nccl", units: Optional[List[nn.Module]] = None, device: Optional[torch.device] = None,
-                 grad_divide: Optional[float] = None):
+                 grad_divide: Optional[float] = None, replicate_group=None):
         self.net = net
         self.group = group
         self.P, self.rank = _group_size_rank(group)
+        self.replicate_group = replicate_group
+        self.R = _group_size_rank(replicate_group)[0]
+        if self.R == 1:
+            self.replicate_group = None
         self.transport = transport
         self.compute_dtype = compute_dtype
         first = next(net.parameters())
         self.device = device or first.device
-        self.grad_scale = 1.0 / (grad_divide if grad_divide is not None else self.P)
+        self.grad_scale = 1.0 / (grad_divide if grad_divide is not None else self.P * self.R)
         unit_modules = units if units is not None else (net.fsdp_units() if hasattr(net, "fsdp_units") else [])
         claimed = set()
         self.units: List[FlatUnit] = []
@@ -292,12 +304,20 @@ class ShardedEngine:
         self._sync_grads = flag
 
     def _reduce_unit(self, unit: FlatUnit):
+        def run():
+            unit.reduce_scatter_grads(self.transport, self.grad_scale)
+            if self.replicate_group is not None:
+                unit.all_reduce_replicas(self.replicate_group)
         if self._comm_stream is not None:
             self._comm_stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self._comm_stream):
-                unit.reduce_scatter_grads(self.transport, self.grad_scale)
+                run()
         else:
-            unit.reduce_scatter_grads(self.transport, self.grad_scale)
+            run()
+
+    def check_health(self) -> None:
+        """Raise if a kernel of this engine recorded an error. The collectives of this class are host-checked library
+        calls; engines whose collectives are kernels with bounded waits override this."""
 
     def finish_backward(self):
         """Reduce any unit whose hook did not fire (unused parameters) and join the comm stream."""

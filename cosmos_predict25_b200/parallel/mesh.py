@@ -63,6 +63,8 @@ def build_groups(world_size: Optional[int] = None, cp_size: int = 1, shard_size:
         g.dp = dist.group.WORLD
     if shard_size == W:
         g.fsdp = dist.group.WORLD
+    elif shard_size == 1:
+        g.fsdp, g.replicate = None, dist.group.WORLD   # plain data parallelism: nothing is sharded
     else:
         for i in range(W // shard_size):
             ranks = list(range(i * shard_size, (i + 1) * shard_size))

@@ -31,6 +31,21 @@ from .fsdp import FlatUnit, ShardedEngine, _group_size_rank
 from .symm import PeerContext, SymmetricArena
 
 
+def check_segment_table(segs: torch.Tensor, world: int, full_numel: int, shard_numel: int) -> None:
+    """Bound every (full_offset, rank_stride, shard_offset, chunk_numel) row of a unit's segment table against the buffers
+    the kernels will index with it. Runs once on the host copy when a unit is built: the kernels themselves take the table
+    on trust, and a row that runs past a buffer would be an out-of-bounds access to a peer's memory."""
+    for i, (full_off, stride, shard_off, n) in enumerate(segs.tolist()):
+        if min(full_off, stride, shard_off, n) < 0 or stride < n:
+            raise ValueError(f"segment {i}: negative field or rank stride {stride} below the chunk size {n}")
+        if n % 8 != 0 or full_off % 8 != 0 or shard_off % 4 != 0:
+            raise ValueError(f"segment {i}: offsets and sizes must keep 16-byte alignment")
+        if full_off + (world - 1) * stride + n > full_numel:
+            raise ValueError(f"segment {i} runs past the full buffer ({full_off} + {world - 1} * {stride} + {n} > {full_numel})")
+        if shard_off + n > shard_numel:
+            raise ValueError(f"segment {i} runs past the shard ({shard_off} + {n} > {shard_numel})")
+
+
 class PeerFlatUnit(FlatUnit):
     def __init__(self, *args, peer_alloc=None, **kwargs):
         self._peer_alloc = peer_alloc
@@ -40,7 +55,9 @@ class PeerFlatUnit(FlatUnit):
             if s.chunk_numel % 8 != 0:
                 raise ValueError(f"parameter {s.name}: per-rank chunk of {s.chunk_numel} elements is not a multiple of 8; "
                                  "use sharding_transport='nccl'")
-        self.segs = self.segment_table().to(self.device)
+        table = self.segment_table()
+        check_segment_table(table, self.P, self.full_numel, self.shard_numel)
+        self.segs = table.to(self.device)
         self.full_ptrs = self._ptrs[id(self.full)]
         self.grad_ptrs = self._ptrs[id(self.grad_full)]
 
@@ -52,7 +69,8 @@ class PeerFlatUnit(FlatUnit):
 
 class PeerShardedEngine(ShardedEngine):
     def __init__(self, net, group=None, compute_dtype: torch.dtype = torch.bfloat16, use_ema: bool = True,
-                 transport: str = "peer", units=None, device: Optional[torch.device] = None, grad_divide=None):
+                 transport: str = "peer", units=None, device: Optional[torch.device] = None, grad_divide=None,
+                 replicate_group=None):
         P, _ = _group_size_rank(group)
         dev = device or next(net.parameters()).device
         assert dev.type == "cuda" and P > 1, "the peer engine needs CUDA devices and more than one rank"
@@ -65,7 +83,7 @@ class PeerShardedEngine(ShardedEngine):
         self.sumsq_slot = self.arena.alloc(64, torch.float32)
         self.norm_out = torch.zeros(1, dtype=torch.float32, device=dev)
         super().__init__(net, group=group, compute_dtype=compute_dtype, use_ema=use_ema, transport="peer", units=units,
-                         device=dev, grad_divide=grad_divide)
+                         device=dev, grad_divide=grad_divide, replicate_group=replicate_group)
         torch.cuda.synchronize(dev)
         dist.barrier(self.ctx.group)  # every rank's buffers are initialised before any peer touches them
 
@@ -82,7 +100,18 @@ class PeerShardedEngine(ShardedEngine):
             ops.rs_cast_norm_peer(unit.grad_ptrs, unit.segs, unit.grad_shard, unit.sumsq, self.sumsq_slot.tensor[:1],
                                   self.rank, float(self.grad_scale))
             native.count_launch(2)
+            if self.replicate_group is not None:
+                # HSDP: the kernel has added this unit's squared sum to the published slot; swap it for the replica-summed one
+                self.sumsq_slot.tensor[:1].sub_(unit.sumsq)
+                unit.all_reduce_replicas(self.replicate_group)
+                self.sumsq_slot.tensor[:1].add_(unit.sumsq)
         unit.reduced = True
+
+    def check_health(self) -> None:
+        """A device barrier that ran out of time only records an error word and returns, and the kernels after it would
+        then work on stale peer data. The trainer calls this wherever it synchronises anyway (logging, before a
+        checkpoint is written, end of training) so that such a run stops instead of saving a damaged state."""
+        self.ctx.check()
 
     @torch.no_grad()
     def grad_norm(self) -> torch.Tensor:

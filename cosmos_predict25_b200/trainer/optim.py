@@ -69,6 +69,9 @@ class ShardedAdamW:
         for which in ("exp_avg", "exp_avg_sq", "master"):
             for name, (local, shape, row0) in self.engine.sharded_state(which).items():
                 out[f"state.{name}.{which}"] = local
+        return self._hyper(out)
+
+    def _hyper(self, out: Dict[str, Any]) -> Dict[str, Any]:
         out["state.step"] = torch.tensor(self.engine.step_count, dtype=torch.int64)
         g = self.param_groups[0]
         out["param_groups.lr"] = g["lr"]
@@ -77,12 +80,38 @@ class ShardedAdamW:
         out["param_groups.weight_decay"] = g["weight_decay"]
         return out
 
+    def consolidated_state_dict(self) -> Dict[str, Any]:
+        """The same keys as ``state_dict`` but with every tensor gathered to its full (unsharded) shape. A collective
+        over the shard group: every rank calls it and every rank gets the whole state, so a single-file checkpoint
+        written by one rank restores all shards (the per-shard ``state_dict`` of one rank does not)."""
+        out: Dict[str, Any] = {"consolidated": True}
+        for which in ("exp_avg", "exp_avg_sq", "master"):
+            for name, t in self.engine.full_state_dict(which).items():
+                out[f"state.{name}.{which}"] = t
+        return self._hyper(out)
+
+    def load_consolidated_state_dict(self, sd: Dict[str, Any]):
+        """Inverse of ``consolidated_state_dict``: every rank cuts its own rows out of the full tensors."""
+        for which in ("exp_avg", "exp_avg_sq", "master"):
+            part = {k[len("state."):-len(which) - 1]: v for k, v in sd.items()
+                    if k.startswith("state.") and k.endswith("." + which)}
+            if part:
+                self.engine.load_full_state_dict(part, which=which, strict=False)
+        self._load_hyper(sd)
+        self.engine.restore_params()
+
     def load_state_dict(self, sd: Dict[str, Any]):
+        if sd.get("consolidated", False):
+            return self.load_consolidated_state_dict(sd)
         for which in ("exp_avg", "exp_avg_sq", "master"):
             for name, (local, shape, row0) in self.engine.sharded_state(which).items():
                 key = f"state.{name}.{which}"
                 if key in sd:
                     local.copy_(sd[key].to(local))
+        self._load_hyper(sd)
+        self.engine.restore_params()
+
+    def _load_hyper(self, sd: Dict[str, Any]):
         if "state.step" in sd:
             self.engine.step_count = int(sd["state.step"])
         g = self.param_groups[0]
@@ -91,7 +120,6 @@ class ShardedAdamW:
                 g[k] = float(sd[f"param_groups.{k}"])
         if "param_groups.betas" in sd:
             g["betas"] = tuple(float(b) for b in sd["param_groups.betas"])
-        self.engine.restore_params()
 
 
 class LambdaLinearScheduler:

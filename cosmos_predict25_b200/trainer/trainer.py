@@ -38,7 +38,7 @@ class TrainerConfig:
     seed: int = 0
     timeout_period: int = 0            # seconds; 0 disables the SIGALRM watchdog
     run_validation: bool = False
-    distributed_parallelism: str = "fsdp"   # fsdp | ddp (ddp = fsdp engine with replicated grouping)
+    distributed_parallelism: str = "fsdp"   # fsdp | ddp: read by cli/train.py, which turns it into the shard / replicate groups
     cudnn_deterministic: bool = False
     memory_format: str = "preserve"
     profile: bool = False
@@ -62,6 +62,8 @@ class Trainer:
         os.makedirs(config.output_dir, exist_ok=True)
         self.callbacks = CallBackGroup(callbacks or [], trainer=self, config=config)
         self.checkpointer = checkpointer
+        if checkpointer is not None and getattr(checkpointer, "callbacks", 0) is None:
+            checkpointer.callbacks = self.callbacks   # on_save_checkpoint_* / on_load_checkpoint_* reach the callback bus
         self.timer = misc.TrainingTimer()
         model.on_train_start()
         self.optimizer, self.scheduler = model.init_optimizer_scheduler(optimizer_config or OptimizerConfig(),
@@ -111,8 +113,21 @@ class Trainer:
                 model.on_before_zero_grad(self.optimizer, self.scheduler, iteration=self.iteration)
             self.grad_accum_count = 0
             self.iteration += 1
+        if last_micro and cfg.logging_iter and self.iteration % cfg.logging_iter == 0:
+            self.check_health()   # the logging callbacks synchronise on this iteration anyway
         self.callbacks.on_training_step_end(model, batch, out, loss, iteration=self.iteration)
         return loss.detach() if return_loss_tensor else float(loss.detach().float().item())
+
+    def check_health(self) -> None:
+        """Raise if a kernel with a bounded wait (peer barrier, exchange) gave up: its successors ran on stale data, so the
+        run must stop before anything is saved."""
+        engine = getattr(self.model, "engine", None)
+        if engine is not None and hasattr(engine, "check_health"):
+            engine.check_health()
+
+    def _save(self) -> None:
+        self.check_health()
+        self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
 
     # ---- full loop ---------------------------------------------------------------------------------------------
     def train(self, dataloader_train: Iterable, dataloader_val: Optional[Iterable] = None):
@@ -127,8 +142,9 @@ class Trainer:
                 signal.alarm(0)   # a pending alarm must not outlive the loop, whichever way it ends
         if self.checkpointer is not None and cfg.save_iter:
             if self.iteration % cfg.save_iter != 0:  # otherwise the loop has just written this iteration
-                self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
+                self._save()
             self.checkpointer.finalize()
+        self.check_health()
         self.callbacks.on_train_end(self.model, iteration=self.iteration)
         if dist.is_available() and dist.is_initialized():
             dist.barrier()
@@ -149,7 +165,7 @@ class Trainer:
                 self.train_step(batch, return_loss_tensor=True)
                 if self.iteration != before:
                     if cfg.save_iter and self.checkpointer is not None and self.iteration % cfg.save_iter == 0:
-                        self.checkpointer.save(self.model, self.optimizer, self.scheduler, self.iteration, trainer=self)
+                        self._save()
                     if cfg.run_validation and cfg.validation_iter and dataloader_val is not None \
                             and self.iteration % cfg.validation_iter == 0:
                         self.validate(dataloader_val)

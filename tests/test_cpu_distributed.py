@@ -168,6 +168,90 @@ def test_sharded_engine_two_ranks_equals_one():
     run_distributed("_engine")
 
 
+def _pt_checkpoint_resume(rank, world, tmp):
+    """Single-file checkpoint of a 2-rank sharded run: after save -> perturb -> load every rank has its OWN rows of the
+    masters and moments back (not rank 0's), the parameters are bit-identical and the next step gives the same loss."""
+    from cosmos_predict25_b200.checkpoint.simple import PtCheckpointer
+    from cosmos_predict25_b200.parallel.fsdp import ShardedEngine
+    from cosmos_predict25_b200.trainer.optim import ShardedAdamW
+    job = [tmp]
+    dist.broadcast_object_list(job, src=0)   # every rank uses rank 0's directory
+
+    def make():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.GELU(), torch.nn.Linear(40, 8, bias=False))
+
+    torch.manual_seed(1)
+    data = torch.randn(world, 5, 24)
+    net = make()
+    eng = ShardedEngine(net, group=dist.group.WORLD, compute_dtype=torch.float32, use_ema=False, units=[net[0]])
+    opt = ShardedAdamW(eng, lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01)
+    for _ in range(2):
+        net(data[rank]).pow(2).mean().backward()
+        opt.step()
+    before = [p.detach().clone() for p in net.parameters()]
+    shard_before = {w: [getattr(u, w).clone() for u in eng.units] for w in ("master", "exp_avg", "exp_avg_sq")}
+    ck = PtCheckpointer({}, job[0])
+    ck.save(net, opt, None, 2)
+    ck.finalize()
+    dist.barrier()
+    net(data[rank]).pow(2).mean().backward()
+    opt.step()
+    loss_ref = net(data[rank]).pow(2).mean().item()
+    # a fresh process would start from the initial weights: emulate it with a new engine
+    net2 = make()
+    eng2 = ShardedEngine(net2, group=dist.group.WORLD, compute_dtype=torch.float32, use_ema=False, units=[net2[0]])
+    opt2 = ShardedAdamW(eng2, lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01)
+    assert PtCheckpointer({}, job[0]).load(net2, opt2, None) == 2
+    for a, b in zip(before, net2.parameters()):
+        assert torch.equal(a, b)
+    for w, bufs in shard_before.items():
+        for u, ref_buf in zip(eng2.units, bufs):
+            assert torch.equal(getattr(u, w), ref_buf), (w, rank)
+    net2(data[rank]).pow(2).mean().backward()
+    opt2.step()
+    assert net2(data[rank]).pow(2).mean().item() == loss_ref
+
+
+def test_pt_checkpointer_resume_two_ranks():
+    run_distributed("_pt_checkpoint_resume")
+
+
+def _hsdp(rank, world, tmp, shard_size):
+    """Hybrid sharding (shard groups of ``shard_size`` ranks, replicated ``world / shard_size`` times) and plain data
+    parallelism (``shard_size`` 1) give the same parameters as one process that sees the whole batch."""
+    from cosmos_predict25_b200.parallel.fsdp import ShardedEngine
+    from cosmos_predict25_b200.parallel.mesh import build_groups
+
+    def make():
+        torch.manual_seed(0)
+        return torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.GELU(), torch.nn.Linear(40, 8, bias=False))
+
+    torch.manual_seed(3)
+    data = torch.randn(world, 5, 24)
+    g = build_groups(cp_size=1, shard_size=shard_size)
+    assert g.shard_size == shard_size and g.replicate_size == world // shard_size and g.replicate is not None
+    net1 = make()
+    eng1 = ShardedEngine(net1, group=None, compute_dtype=torch.float32, use_ema=False, units=[net1[0]])
+    netP = make()
+    engP = ShardedEngine(netP, group=g.fsdp, compute_dtype=torch.float32, use_ema=False, units=[netP[0]],
+                         replicate_group=g.replicate)
+    assert engP.P == shard_size and engP.R == world // shard_size
+    for step in range(3):
+        sum(net1(data[r]).pow(2).mean() for r in range(world)).div(world).backward()
+        n1 = eng1.step(lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01, max_grad_norm=0.5)
+        netP(data[rank]).pow(2).mean().backward()
+        nP = engP.step(lr=1e-2, betas=(0.9, 0.99), weight_decay=0.01, max_grad_norm=0.5)
+        assert torch.allclose(n1, nP, atol=1e-5), (n1, nP)
+        for p1, pP in zip(net1.parameters(), netP.parameters()):
+            assert torch.allclose(p1, pP, atol=1e-6), step
+
+
+@pytest.mark.parametrize("shard_size", [2, 1])
+def test_hybrid_sharding_and_data_parallel_four_ranks(shard_size):
+    run_distributed("_hsdp", world=4, shard_size=shard_size)
+
+
 def _model_fsdp_cp(rank, world, tmp):
     """Full model with parameter sharding + context parallelism over the same two ranks: both ranks see the
     same loss (one sample, sequence-sharded) and the step keeps parameters identical across ranks."""

@@ -90,3 +90,47 @@ def test_wandb_run_id_survives_a_restart(tmp_path, monkeypatch):
     assert ids[0] == ids[1] and len(ids[0]) == 8
     assert (tmp_path / "checkpoints" / "wandb_id.txt").read_text().strip() == ids[0]
     assert ("log", 1) in calls and ("finish",) in calls and (tmp_path / "metrics.jsonl").exists()
+
+
+class _RecordingCheckpointer:
+    callbacks = None
+
+    def __init__(self):
+        self.saved = []
+
+    def load(self, *a, **k):
+        return 0
+
+    def save(self, model, optimizer, scheduler, iteration, trainer=None):
+        self.saved.append(iteration)
+
+    def finalize(self):
+        pass
+
+
+def test_kernel_error_word_stops_the_run_before_a_checkpoint(tmp_path):
+    """A bounded device wait that gave up is reported through the engine's health check (here a fake of the error word that
+    turns non-zero after step 2): the trainer raises at the next check and writes no checkpoint after the failure."""
+    ck = _RecordingCheckpointer()
+    torch.manual_seed(0)
+    model = Video2WorldModelRectifiedFlow(Video2WorldRFConfig(net=dit_tiny(), precision="float32", state_t=4), device=torch.device("cpu"))
+    t = Trainer(TrainerConfig(output_dir=str(tmp_path), logging_iter=0, max_iter=6, save_iter=2), model, OptimizerConfig(lr=1e-3),
+                checkpointer=ck)
+    assert ck.callbacks is t.callbacks            # checkpoint callbacks reach the trainer's callback bus
+    state = {"code": 0}
+
+    def check_health():
+        if state["code"]:
+            raise RuntimeError(f"a peer-memory kernel gave up waiting (error code {state['code']})")
+
+    model.engine.check_health = check_health
+
+    class _Break(Callback):
+        def on_training_step_end(self, model, data_batch, output_batch, loss, iteration=0):
+            if iteration == 3:
+                state["code"] = 101
+
+    t.callbacks.append(_Break())
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        t.train(list(_batches(6)))
+    assert ck.saved == [2]                        # iteration 4's save was refused

@@ -5,7 +5,8 @@ device memory to its own pool, and therefore cannot let an operator allocate scr
 library exports one C function that keeps its scratch in a fixed array inside the library image. This test calls
 that function through its exported symbol with raw device pointers, twice in a row with different data (the
 shared scratch still holds the first call's partial sums when the second one starts), and checks both results
-against ``torch.ops.cosmos_b200.rmsnorm_rope_bwd``. It also checks that an over-sized problem is refused with a
+against ``torch.ops.cosmos_b200.rmsnorm_rope_bwd`` - bit for bit, because both run the same kernels with the same row
+grouping - and against a plain PyTorch fp32 evaluation of the same backward within the tolerance of the kernel tests. It also checks that an over-sized problem is refused with a
 message instead of being launched. This file is named to be collected last.
 """
 
@@ -14,7 +15,7 @@ import ctypes
 import pytest
 import torch
 
-from cosmos_predict25_b200.ops import native
+from cosmos_predict25_b200.ops import native, ref
 
 pytestmark = pytest.mark.gpu
 
@@ -53,10 +54,11 @@ def test_no_alloc_entry_point_matches_operator_twice(HD, use_rope):
         x = torch.randn(B, S, H, HD, device=dev).bfloat16()
         dy = torch.randn(B, S, H, HD, device=dev).bfloat16() * (1 + call)
         w = (1 + 0.1 * torch.randn(HD, device=dev)).float().contiguous()
-        cos = sin = None
+        cos = sin = angles = None
         if use_rope:
             ang = torch.rand(S, HD // 2, device=dev) * 40
             cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+            angles = torch.cat([ang, ang], dim=-1)      # rotate-half pairs (i, i + HD/2) share one angle
         _, rstd = ops.rmsnorm_rope_fwd(x, w, cos, sin, 1e-6)
         want_dx, want_dw = ops.rmsnorm_rope_bwd(dy, x, w, rstd, cos, sin)
         dx = torch.empty_like(x)
@@ -66,8 +68,12 @@ def test_no_alloc_entry_point_matches_operator_twice(HD, use_rope):
                 ctypes.c_void_p(stream.cuda_stream), err, 256)
         assert rc == 0, err.value.decode()
         torch.cuda.synchronize()
-        _close(dx, want_dx, 3e-2, 3e-2)
-        _close(dw, want_dw, 0.3, 3e-2)
+        assert torch.equal(dx, want_dx) and torch.equal(dw, want_dw)
+        # fp32 oracle: autograd through the PyTorch definition of the forward
+        xr, wr = x.float().requires_grad_(True), w.clone().requires_grad_(True)
+        ref.rmsnorm_rope(xr, wr, angles, 1e-6).backward(dy.float())
+        _close(dx, xr.grad, 3e-2, 3e-2)
+        _close(dw, wr.grad, 0.3, 3e-2)
 
 
 def test_no_alloc_entry_point_rejects_oversized_problem():
