@@ -11,6 +11,12 @@ Two timed regions of K steps each, both bracketed by barrier + synchronize and t
   value      inputs already on the device
   e2e.value  through ``Trainer.train_step`` with the step's inputs copied from pinned host memory and the
              loss read back to the host every step
+After them, in the same process and on the same model object:
+  library_twin  3 warm-up + 3 timed steps with every contraction switched to the libraries the reference selects on this
+                GPU (cuDNN SDPA, cuBLAS GEMMs); ``vs_baseline`` is value / twin value (the reference publishes no number)
+  inference     the other half of the headline metric: Video2World sampling through ``generate_samples_from_batch`` with all
+                N ranks as one context-parallel group (a few UniPC steps, classifier-free guidance 7, batched) + the full VAE
+                decode; reports seconds per denoising step, decode seconds and the 35-step seconds per video they imply
 `python bench.py --impl reference` reports why the unmodified reference cannot run offline.
 """
 
@@ -44,6 +50,9 @@ def parse():
     ap.add_argument("--gemm", default=None, choices=[None, "native", "cublas"])
     ap.add_argument("--checkpoint", default="save_attention")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-twin", action="store_true", help="skip the cuDNN + cuBLAS twin of the training step")
+    ap.add_argument("--no-inference", action="store_true", help="skip the Video2World sampling + decode block")
+    ap.add_argument("--inference-steps", type=int, default=3, help="UniPC steps timed in the inference block")
     return ap.parse_args()
 
 
@@ -210,13 +219,44 @@ def main():
     err = native.load().kernel_error(local_rank, True)
     last_loss = float(losses[-1]) if losses else float("nan")
 
+    # ---- library twin: the same model, optimizer and data with cuDNN attention and cuBLAS GEMMs (the reference's choice on sm_100)
+    twin = None
+    if not args.no_twin and args.attention is None and args.gemm is None and args.model in ("2B", "14B"):
+        saved = (F_ops.settings.attention, F_ops.settings.gemm)
+        F_ops.settings.attention, F_ops.settings.gemm = "cudnn", "cublas"
+        try:
+            for _ in range(3):
+                step_device()
+            twin_ms = timed(3, step_device)
+            twin = {"tokens_s": global_batch * tokens_per_sample * 3 / (twin_ms / 1e3), "ms_per_step": twin_ms / 3, "steps": 3,
+                    "warmup": 3, "attention": "cudnn sdpa", "gemm": "cublas", "same_process": True}
+        finally:
+            F_ops.settings.attention, F_ops.settings.gemm = saved
+
+    # ---- inference half of the metric: all ranks form one context-parallel group
+    inference = None
+    if not args.no_inference and args.model == "2B" and args.cp == 1 and args.frames % world == 0:
+        del trainer, model, device_batch
+        losses.clear()
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        from bench_inference import run_inference
+        rec = run_inference(model_name=args.model, frames=args.frames, height=args.height, width=args.width,
+                            steps=args.inference_steps, transport=args.transport)
+        inference = {k: rec[k] for k in ("s_per_denoising_step", "vae_decode_s", "s_per_video_35_steps", "decoded_frames",
+                                         "gpu_launches_sampling", "kernel_error")}
+        inference.update(unit="s", timed_unipc_steps=args.inference_steps, guidance=7.0, parallelism=rec["config"]["parallelism"],
+                         transport=rec["config"]["transport"], vae=rec["config"]["vae"])
+
     if rank == 0:
         tok = global_batch * tokens_per_sample * args.steps
         value = tok / (ms / 1e3)
         line = {
             "metric": f"DiT training latent-tokens/s ({args.model} Video2World, 720p x 93 frames, device-timed, max over ranks)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / twin["tokens_s"]) if twin else None,
             "dtype": "bf16", "data": "synthetic latents + text embeddings, random-init weights", "impl": "ours",
             "config": {"model": f"cosmos-predict2.5-{args.model}-video2world", "global_batch": global_batch,
                        "seq_len": tokens_per_sample, "parallelism": (f"fsdp{world}" if args.cp == 1 else f"fsdp{world} (masters, moments, EMA, gradients sharded over all ranks) x cp{args.cp} x dp{dp}"),
@@ -228,6 +268,10 @@ def main():
                        "l2": "per-step working set (>10 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches, "kernel_error": int(err), "final_loss": last_loss,
         }
+        if twin:
+            line["library_twin"] = twin
+        if inference:
+            line["inference"] = inference
         if e2e_ms is not None:
             line["e2e"] = {"value": tok / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                            "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4}

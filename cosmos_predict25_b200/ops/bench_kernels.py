@@ -6,6 +6,11 @@ Each row: kernel, shape, CUDA-event time (median of timed iterations after warm-
 iterations by writing a 256 MB buffer), achieved TFLOP/s or GB/s, and the fraction of the measured
 peak (``MEASURED_PEAKS.json`` at the repository root when present, otherwise 6.65 TB/s and
 1.59 PFLOP/s). The library twin (cuBLAS / cuDNN via torch) is timed next to each contraction.
+
+``--reference`` adds the reference arm of the attention rows: the reference repository's own, unmodified
+``cosmos_predict2/_src/predict2/networks/attention.py`` (its dispatcher) and
+``cosmos_predict2/_src/predict2/utils/flash_attention_jvp_triton.py`` (its Triton forward-mode kernel) are loaded by file
+path from ``baseline/_ref`` (a copy of the reference tree) and timed on the same tensors.
 """
 
 from __future__ import annotations
@@ -59,8 +64,22 @@ def time_ms(fn, iters=5, warmup=3):
     return statistics.median(ts)
 
 
+def _load_reference_module(rel_path: str, name: str):
+    """Import one file of the reference tree under ``baseline/_ref`` as a stand-alone module (None when it is absent)."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "baseline", "_ref", rel_path)
+    if not os.path.exists(path):
+        return None
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", action="store_true", help="also time the reference repository's own attention code (baseline/_ref)")
     ap.add_argument("--quick", action="store_true", help="1/8 of the tokens (fast sanity pass)")
     ap.add_argument("--only", default=None)
     ap.add_argument("--json", default=None)
@@ -115,7 +134,7 @@ def main():
         add("fa_fwd tcgen05", f"S={N} H={heads} hd=128", time_ms(lambda: ops.fa_fwd(q, k, v, scale), iters=3, warmup=1), fl)
         add("cudnn sdpa fwd (twin)", f"S={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, k, v, scale), iters=3, warmup=1), fl)
         if args.variants and hasattr(ops, "fa_fwd_variant"):
-            for var in range(1, 7):
+            for var in (1, 2, 3, 4, 5, 6, 9, 10, 11):
                 add(f"fa_fwd tcgen05 variant {var}", f"S={N} H={heads}",
                     time_ms(lambda: ops.fa_fwd_variant(q, k, v, scale, var), iters=3, warmup=1), fl)
         if hasattr(ops, "fa_bwd"):
@@ -123,8 +142,10 @@ def main():
             do = torch.randn_like(o)
             add("fa_bwd tcgen05 two-kernel (7 GEMM)", f"S={N} H={heads}",
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 1), iters=3, warmup=1), 2.5 * fl)
-            add("fa_bwd tcgen05 single-pass (5 GEMM)", f"S={N} H={heads}",
+            add("fa_bwd tcgen05 single-pass, 128x64 sub-tiles (5 GEMM)", f"S={N} H={heads}",
                 time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 2), iters=3, warmup=1), 2.5 * fl)
+            add("fa_bwd tcgen05 single-pass, 128x128 tiles (5 GEMM)", f"S={N} H={heads}",
+                time_ms(lambda: ops.fa_bwd_variant(do, q, k, v, o, lse, scale, 3), iters=3, warmup=1), 2.5 * fl)
         if hasattr(ops, "fa_jvp"):
             tq, tk, tv = (torch.randn_like(t) for t in (q, k, v))
             # useful work: S, tS (2 GEMMs), P V (forward), A V, P tV = 6 GEMM units of 2 S^2 D H each
@@ -141,14 +162,6 @@ def main():
             add("fa_fwd_na tcgen05 (tile-sparse neighbourhood attention)", f"grid={vs} window={win} stride={st} H={heads}",
                 time_ms(lambda: ops.fa_fwd_na(qt, kt, vt, scale, plan.kv_idx, plan.kv_cnt, plan.bt, plan.bh, plan.bw), iters=3, warmup=1),
                 fl_na, note=f"visited key tiles: {plan.visited_fraction:.3f} of dense; dense fa_fwd above is the baseline")
-        if hasattr(ops, "red_f32_bench"):
-            # L2 reduction rate that bounds the dQ accumulation of the single-pass backward: one head's dQ matrix [S, 128] fp32,
-            # 660 key tiles adding into it = the traffic of one head of the S=84480 problem
-            acc = torch.zeros(N, 128, device=dev)
-            n_ctas = (N + 127) // 128
-            ms = time_ms(lambda: ops.red_f32_bench(acc, n_ctas), iters=3, warmup=1)
-            gb = n_ctas * N * 512 / 1e9
-            add("red.global.add.f32 rate (one head of dQ accumulation)", f"rows={N} ctas={n_ctas}", ms, bytes_=gb * 1e9)
         qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
         og = F_ops._sdpa(qg, kg, vg, scale)
         dog = torch.randn_like(og)
@@ -157,6 +170,31 @@ def main():
         kc, vc = (torch.randn(1, 512, heads, HD, device=dev).bfloat16() for _ in range(2))
         add("fa_fwd tcgen05 cross (Skv=512)", f"Sq={N} H={heads}", time_ms(lambda: ops.fa_fwd(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
         add("cudnn sdpa cross (twin)", f"Sq={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
+        if args.variants:
+            for var in (7, 8, 4, 1):
+                add(f"fa_fwd tcgen05 cross variant {var}", f"Sq={N} H={heads}",
+                    time_ms(lambda: ops.fa_fwd_variant(q, kc, vc, scale, var)), 4.0 * N * 512 * HD * heads)
+        if args.reference:
+            ref_attn = _load_reference_module("cosmos_predict2/_src/predict2/networks/attention.py", "reference_attention")
+            if ref_attn is None:
+                print(json.dumps({"reference": "baseline/_ref is absent"}), flush=True)
+            else:
+                add("reference attention() dispatcher fwd", f"S={N} H={heads}",
+                    time_ms(lambda: ref_attn.attention(q, k, v, softmax_scale=scale), iters=3, warmup=1), fl)
+                add("reference attention() dispatcher cross (Skv=512)", f"Sq={N} H={heads}",
+                    time_ms(lambda: ref_attn.attention(q, kc, vc, softmax_scale=scale)), 4.0 * N * 512 * HD * heads)
+            try:
+                ref_jvp = _load_reference_module("cosmos_predict2/_src/predict2/utils/flash_attention_jvp_triton.py", "reference_jvp")
+            except Exception as e:   # the file imports triton and flash_attn
+                ref_jvp = None
+                print(json.dumps({"reference_jvp": f"import failed: {type(e).__name__}: {e}"}), flush=True)
+            if ref_jvp is not None:
+                # the Triton kernel wants [B, H, S, D]; same tensors, transposed views made contiguous once outside the timing
+                qh, kh, vh = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+                tqh, tkh, tvh = (torch.randn_like(t) for t in (qh, kh, vh))
+                add("reference Triton JVP attention (forward + tangent)", f"S={N} H={heads}",
+                    time_ms(lambda: ref_jvp.attention(qh, kh, vh, tqh, tkh, tvh, False, scale), iters=3, warmup=2), 3.0 * fl)
+                del qh, kh, vh, tqh, tkh, tvh
         del q, k, v
     if want("elementwise"):
         x = torch.randn(1, T, L, D, device=dev).bfloat16()

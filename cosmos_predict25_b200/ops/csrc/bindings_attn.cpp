@@ -30,14 +30,9 @@ std::tuple<Tensor, Tensor> fa_fwd_variant(const Tensor& q, const Tensor& k, cons
   const int B = (int)q.size(0), Sq = (int)q.size(1), H = (int)q.size(2), Skv = (int)k.size(1);
   Tensor o = at::empty_like(q);
   Tensor lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
-  // variant 6: the kernel with two threads per query row (fa_fwd_split.cu)
-  const int rc = variant == 6
-                     ? cb200_fa_fwd_split(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
-                                          (float)scale, nullptr, 0, 0, cb200_error_word(q.get_device()),
-                                          at::cuda::getCurrentCUDAStream().stream())
-                     : cb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
-                                    (float)scale, (int)variant, cb200_error_word(q.get_device()),
-                                    at::cuda::getCurrentCUDAStream().stream());
+  const int rc = cb200_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Skv, H,
+                              (float)scale, (int)variant, cb200_error_word(q.get_device()),
+                              at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "fa_fwd launch failed with code ", rc);
   return {o, lse};
 }
@@ -98,7 +93,8 @@ std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor
 }
 
 // gradients of softmax(q k^T scale) v given the forward's output and log-sum-exp
-// variant 0: by problem size; 1: two deterministic kernels; 2: single pass with fp32 dQ accumulation
+// variant 0: by problem size; 1: two deterministic kernels; 2: single pass, 128 x 64 sub-tiles; 3: single pass, 128 x 128 tiles
+// (2 and 3 accumulate dQ in fp32 with reductions in global memory: run-to-run differences of the last bit are possible)
 std::tuple<Tensor, Tensor, Tensor> fa_bwd_variant(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
                                                   const Tensor& lse, double scale, int64_t variant) {
   check_qkv(d_o, "do");
@@ -153,21 +149,6 @@ std::tuple<Tensor, Tensor, Tensor> fa_jvp(const Tensor& q, const Tensor& k, cons
   return {o, fa_jvp_tangent(q, k, v, tq, tk, tv, o, lse, scale), lse};
 }
 
-// event trace (SM clocks, [256 sub-tiles, 8 events]) of CTA 0 of the single-pass backward; for performance analysis
-Tensor fa_bwd_fused_trace(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse, double scale) {
-  Tensor tr = at::zeros({256, 8}, q.options().dtype(at::kLong));
-  cb200_fa_bwd_fused_set_trace(reinterpret_cast<long long*>(tr.data_ptr<int64_t>()));
-  fa_bwd_variant(d_o, q, k, v, o, lse, scale, 2);
-  cb200_fa_bwd_fused_set_trace(nullptr);
-  return tr;
-}
-// hardware-rate probe: n_ctas CTAs each add 1.0 into every element of acc [rows, 128]
-void red_f32_bench(Tensor acc, int64_t n_ctas) {
-  TORCH_CHECK(acc.is_cuda() && acc.scalar_type() == at::kFloat && acc.is_contiguous() && acc.dim() == 2 && acc.size(1) == 128);
-  c10::cuda::CUDAGuard g(acc.device());
-  const int rc = cb200_red_f32_bench(acc.data_ptr<float>(), (int)acc.size(0), (int)n_ctas, at::cuda::getCurrentCUDAStream().stream());
-  TORCH_CHECK(rc == 0, "red_f32_bench launch failed with code ", rc);
-}
 }  // namespace
 
 void register_attention_ops(torch::Library& m) {
@@ -182,8 +163,6 @@ void register_attention_ops(torch::Library& m) {
   m.def("fa_fwd_variant(Tensor q, Tensor k, Tensor v, float scale, int variant) -> (Tensor, Tensor)");
   m.def("fa_jvp(Tensor q, Tensor k, Tensor v, Tensor tq, Tensor tk, Tensor tv, float scale) -> (Tensor, Tensor, Tensor)");
   m.def("fa_jvp_tangent(Tensor q, Tensor k, Tensor v, Tensor tq, Tensor tk, Tensor tv, Tensor o, Tensor lse, float scale) -> Tensor");
-  m.def("fa_bwd_fused_trace(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> Tensor");
-  m.def("red_f32_bench(Tensor(a!) acc, int n_ctas) -> ()");
   m.def("fa_bwd_variant(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, int variant) -> (Tensor, Tensor, Tensor)");
 }
 
@@ -192,8 +171,6 @@ TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
   m.impl("fa_bwd", &fa_bwd);
   m.impl("fa_fwd_variant", &fa_fwd_variant);
   m.impl("fa_bwd_variant", &fa_bwd_variant);
-  m.impl("red_f32_bench", &red_f32_bench);
-  m.impl("fa_bwd_fused_trace", &fa_bwd_fused_trace);
   m.impl("fa_jvp", &fa_jvp);
   m.impl("fa_jvp_tangent", &fa_jvp_tangent);
 }

@@ -28,6 +28,8 @@
 namespace cb200 {
 using namespace sm100;
 
+constexpr int kFaBwdDefaultLong = 2;   // kernel used for long key sequences when the caller does not choose
+
 namespace fab {
 constexpr int HD = 128;
 constexpr int kBig = 128 * HD * 2;    // 32 KB: 128-row tile
@@ -552,19 +554,25 @@ extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const voi
                                        const float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Skv, int H,
                                        int S_pad, float scale, int dbg, int* err, cudaStream_t st);
 
-// variant 10 + bits: timing experiments on the single-pass kernel with parts of the dQ path switched off (results wrong)
-// variant 0: choose by problem size; 1: two deterministic kernels (7 GEMMs); 2: single pass with fp32 dQ accumulation (5 GEMMs)
-static bool fa_bwd_use_fused(int Skv, int variant) { return variant == 2 || variant >= 10 || (variant == 0 && Skv >= 2048); }
+extern "C" int cb200_fa_bwd_tile_main(const void* d_o, const void* q, const void* k, const void* v, const float* lse2,
+                                      const float* delta, float* dq_acc, void* dk, void* dv, int B, int Sq, int Skv, int H, int S_pad,
+                                      float scale, int* err, cudaStream_t st);
+extern "C" void cb200_fa_bwd_dq_convert(const float* acc, void* dq, int B, int S, int H, float scale, cudaStream_t st);
+
+// variant 0: choose by problem size; 1: two deterministic kernels (7 GEMMs, no atomics); 2: single pass over 128 x 64 sub-tiles with
+// fp32 dQ accumulation (5 GEMMs); 3: single pass over 128 x 128 tiles (5 GEMMs, every MMA N = 128)
+static int fa_bwd_pick(int Skv, int variant) { return variant != 0 ? variant : (Skv >= 2048 ? kFaBwdDefaultLong : 1); }
+static bool fa_bwd_use_fused(int Skv, int variant) { return fa_bwd_pick(Skv, variant) >= 2; }
 
 extern "C" long cb200_fa_bwd_scratch_floats_v(int B, int Sq, int Skv, int H, int variant) {
-  const long S_pad = (Sq + 63) / 64 * 64;
+  const long S_pad = (Sq + 127) / 128 * 128;
   long n = 2L * B * H * S_pad;
   if (fa_bwd_use_fused(Skv, variant)) n += (long)B * Sq * H * 128;
   return n;
 }
 
 extern "C" int cb200_fa_bwd_scratch_floats(int B, int Sq, int H) {
-  const int S_pad = (Sq + 63) / 64 * 64;
+  const int S_pad = (Sq + 127) / 128 * 128;
   return 2 * B * H * S_pad;
 }
 
@@ -584,7 +592,7 @@ extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, con
                               void* dk, void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int variant, int* err,
                               cudaStream_t st) {
   using namespace fab;
-  const int S_pad = (Sq + 63) / 64 * 64;
+  const int S_pad = (Sq + 127) / 128 * 128;
   float* delta = scratch;
   float* lse2 = scratch + (size_t)B * H * S_pad;
   {
@@ -592,9 +600,16 @@ extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, con
     fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, lse, delta, lse2, B, Sq, H, S_pad,
                                                                    fa_bwd_use_fused(Skv, variant) ? -1.f : 1.f);
   }
+  if (fa_bwd_pick(Skv, variant) == 3) {
+    float* acc = scratch + 2 * (size_t)B * H * S_pad;
+    const int rc = cb200_fa_bwd_tile_main(d_o, q, k, v, lse2, delta, acc, dk, dv, B, Sq, Skv, H, S_pad, scale, err, st);
+    if (rc) return rc;
+    cb200_fa_bwd_dq_convert(acc, dq, B, Sq, H, scale, st);
+    return (int)cudaGetLastError();
+  }
   if (fa_bwd_use_fused(Skv, variant))
     return cb200_fa_bwd_fused_main(d_o, q, k, v, lse2, delta, scratch + 2 * (size_t)B * H * S_pad, dq, dk, dv, B, Sq, Skv, H, S_pad, scale,
-                                   variant >= 10 ? variant - 10 : 0, err, st);
+                                   0, err, st);
   auto make = [&](CUtensorMap* m, const void* p, int S, int box_rows) {
     const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)HD * 2, (uint64_t)H * HD * 2, (uint64_t)S * H * HD * 2};

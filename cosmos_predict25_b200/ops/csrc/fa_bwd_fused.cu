@@ -24,6 +24,8 @@
 
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100.cuh"
@@ -57,11 +59,8 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dQacc,
                     bf16* __restrict__ dK, bf16* __restrict__ dV, int Sq, int Skv, int H, int Sq_pad, float scale,
-                    long long* __restrict__ trace, int* __restrict__ err) {
+                    int* __restrict__ err) {
   using namespace faf;
-  // optional event trace of CTA (0,0,0): trace[i*8 + k] = SM clock at event k of sub-tile i (i < 256); see the call sites
-  const bool tracing = trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define FAF_TRACE(i_, k_) do { if (tracing && (i_) < 256) trace[(i_) * 8 + (k_)] = clock64(); } while (0)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -218,7 +217,6 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int u = i & 1;
         const uint32_t par = (i >> 1) & 1;
         if (!wait_all(&p_ready[u], par)) { ok = false; break; }
-        if (lane == 0) FAF_TRACE(i, 4);
         tc_fence_after();
         issue_dq(u);
         umma_commit_w(&dq_full[u], leader);
@@ -232,13 +230,10 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           // columns that hold dQ^T of this sub-tile, so it waits for the read-back (hidden behind dV / dK / S^T).
           tc_fence_after();
           issue_st(u, qs[u]);
-          if (lane == 0) FAF_TRACE(i, 5);
           if (!wait_all(&dq_free[u], par)) { ok = false; break; }
-          if (lane == 0) FAF_TRACE(i, 6);
           tc_fence_after();
           issue_dpt(u, ds[u]);
           umma_commit_w(&s_full[u], leader);
-          if (lane == 0) FAF_TRACE(i, 7);
         }
       }
       if (ok) umma_commit_w(done, leader);
@@ -264,7 +259,6 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int qslot = n % kRing;
       if (!mbar_wait(&s_full[u], par, abort_flag)) { ok = false; break; }
       if (!mbar_wait(&r_full[qslot], (n / kRing) & 1, abort_flag)) { ok = false; break; }  // row statistics landed
-      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 0);
       tc_fence_after();
       const float4* l4 = reinterpret_cast<const float4*>(sStat + qslot * (kStat / 4)) + half * 8;
       const float4* d4 = l4 + 16;
@@ -309,11 +303,9 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[u]);
-      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 1);
 
       // ---- read this warp's half of dQ^T back (lane = d) and add it into the fp32 dQ buffer
       if (!mbar_wait(&dq_full[u], par, abort_flag)) { ok = false; break; }
-      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 2);
       tc_fence_after();
       uint32_t a[32];
       tmem_ld32(tST + 64 + half * 32, a);
@@ -321,7 +313,6 @@ fa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_free[u]);
-      if ((warp & 7) == 0 && lane == 0) FAF_TRACE(i, 3);
       const int q0 = i * 64 + half * 32;
       // head-major accumulator [B, H, Sq, 128]: consecutive queries are 512 bytes apart, so every reduction below is one
       // instruction with an immediate offset from a single base pointer
@@ -406,9 +397,10 @@ __global__ void __launch_bounds__(256) fa_bwd_dq_convert_kernel(const float* __r
 
 using namespace cb200;
 
-static long long* g_faf_trace = nullptr;
-// device buffer of 256*8 int64 that receives the event trace of the next launches (nullptr switches tracing off)
-extern "C" void cb200_fa_bwd_fused_set_trace(long long* buf) { g_faf_trace = buf; }
+extern "C" void cb200_fa_bwd_dq_convert(const float* acc, void* dq, int B, int S, int H, float scale, cudaStream_t st) {
+  const long n8 = (long)B * S * H * 16;
+  fa_bwd_dq_convert_kernel<<<(unsigned)std::min<long>((n8 + 255) / 256, 148 * 16), 256, 0, st>>>(acc, (bf16*)dq, B, S, H, scale);
+}
 
 // Runs after the preprocessing kernel has produced lse2 / delta (padded to S_pad rows per (b, h)).
 // dq_acc: B*Sq*H*128 floats of scratch, zeroed here.
@@ -437,7 +429,7 @@ extern "C" int cb200_fa_bwd_fused_main(const void* d_o, const void* q, const voi
   if (e != cudaSuccess) return 400 + (int)e;
   dim3 grid((Skv + 127) / 128, H, B);
   fa_bwd_fused_kernel<<<grid, kThreads, kSmem, st>>>(q64, do64, k128, v128, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, Sq, Skv, H, S_pad,
-                                                     scale, g_faf_trace, err);
+                                                     scale, err);
   const long n8 = (long)(n / 8);
   fa_bwd_dq_convert_kernel<<<(unsigned)std::min<long>((n8 + 255) / 256, 148 * 16), 256, 0, st>>>(dq_acc, (bf16*)dq, B, Sq, H, scale);
   return (int)cudaGetLastError();

@@ -14,12 +14,18 @@
 // them from there, so probabilities never visit shared memory. While one tile is in softmax the tensor
 // core runs the other tile's P.V and next Q.K^T (ping-pong).
 //
-// Register budget decides the shape of this kernel: 10 warps leave 168 registers per thread, enough to hold a
-// full 128-column score row. The layout with two threads per row (18 warps, 96 registers, fa_fwd_split.cu) runs without
-// spills but measured 53.7 ms against 48.5 ms here at S = 84,480, H = 16: the per-tile pair barrier and the doubled
-// bookkeeping cost more than the shorter exponential chain saves. Template switches keep two measured alternatives for
-// the exponentials (a degree-4 polynomial on the FMA pipe for one element in POLY_MOD, packed fp32x2 scale/subtract);
-// the plain MUFU path is fastest.
+// Register budget decides the shape of this kernel: one thread per query row holds the whole 128-column score row.
+//
+// Three pipes are needed for exactly the same time per 128 x 128 tile at full rate - the tensor pipe (2 x 512 clocks), the
+// exponential unit (16,384 ex2 at 16 per clock) and, for the Q.K^T half, shared-memory operand bandwidth - so the kernel is
+// tuned by taking work off the exponential unit and by shortening the softmax -> MMA hand-off:
+//   * EXPM of every 4 element pairs compute 2^x on the FMA pipe instead (round-to-nearest split, degree-3 polynomial in
+//     packed fp32x2 arithmetic, exponent add; relative error 1e-4, a twentieth of a bf16 half-ulp);
+//   * the row maximum uses the three-input max;
+//   * SPLITP: the probabilities of keys 0..63 are published on their own barrier, so the first half of P.V runs while
+//     the second half of the row is still being exponentiated.
+// QT = 1 is the shape for short key sequences (cross-attention, 512 keys): one query tile, 192 threads, 97 KB of shared memory and 256
+// TMEM columns per CTA, so that two CTAs share an SM and fill each other's prologue / epilogue gaps.
 //
 // Online softmax keeps a reference maximum per row that is only moved when the running maximum grows
 // by more than 2^8; the output accumulator is rescaled in TMEM only then (rare after the first tiles).
@@ -41,11 +47,21 @@ constexpr int BQ = 128;          // query rows per tile (two tiles per CTA)
 constexpr int BKV = 128;         // keys per tile
 constexpr int kTileBytes = 128 * HD * 2;  // 32 KB
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kRing = 5;         // K/V ring slots
-constexpr int kThreads = 320;
-constexpr int kMmaWarp = 9, kTmaWarp = 8;
-constexpr size_t kSmem = (2 + kRing) * (size_t)kTileBytes + 1024 + 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// shape of a CTA with QT query tiles: 4 softmax warps per tile, then the TMA warp and the MMA warp
+// REGS: the CTA is padded to whole warpgroups (12 warps) and re-divides its registers at start: the warpgroup of the TMA / MMA warps
+// gives registers back (setmaxnreg.dec) and the softmax warpgroups take them (setmaxnreg.inc), which removes the spills of the
+// 128-value score row.
+template <int QT, bool REGS = false>
+struct Shape {
+  static constexpr int kRing = QT == 2 ? 5 : 2;           // K/V ring slots
+  static constexpr int kTmaWarp = 4 * QT, kMmaWarp = 4 * QT + 1;
+  static constexpr int kThreads = REGS ? (4 * QT + 4) * 32 : (4 * QT + 2) * 32;
+  static constexpr int kRegsSoftmax = 224, kRegsOther = 56;
+  static constexpr int kMinCtas = QT == 2 ? 1 : 2;
+  static constexpr uint32_t kTmemCols = 256 * QT;
+  static constexpr size_t kSmem = (QT + kRing) * (size_t)kTileBytes + 1024 + 256;
+};
 }  // namespace fa
 
 __device__ __forceinline__ float ex2(float x) {
@@ -54,17 +70,30 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// 2^x for x <= ~8 on the FMA/ALU pipes: round to nearest integer with the 1.5*2^23 trick, degree-4
-// polynomial for 2^f on [-0.5, 0.5] (relative error < 5e-5, far below bf16 resolution), exponent add.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 0.00961813f, 0.0555041f);
-  p = fmaf(p, f, 0.240227f);
-  p = fmaf(p, f, 0.693147f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + ((__float_as_int(t) - 0x4B400000) << 23));
+// 2^x for a pair of values, x <= ~100, on the FMA / ALU pipes: t = x + 1.5 * 2^23 rounds x to the nearest integer n (kept in
+// the low mantissa bits of t), f = x - n lies in [-0.5, 0.5], 2^f comes from a degree-3 polynomial fitted for a relative
+// error of 1.0e-4, and n is added to the exponent field (t << 23 drops everything but n; x is clamped at -126 so that the
+// result stays a normal number). Packed fp32x2 instructions halve the issue slots of the six additions / multiply-adds.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  const float2 t = add2(x, magic);
+  const float2 n = add2(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = fma2(f, make_float2(0.05500893f, 0.05500893f), make_float2(0.24221095f, 0.24221095f));
+  p = fma2(p, f, make_float2(0.6932829f, 0.6932829f));
+  p = fma2(p, f, make_float2(1.f, 1.f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 // Ulysses head->sequence exchange fused into the output store: this rank holds heads [rank*H, rank*H + H) of the whole
@@ -91,47 +120,59 @@ struct NaParams {
   int max_n, nT, nH, nW;
 };
 
-template <int POLY_MOD, bool PACKED, bool NA>
-__global__ void __launch_bounds__(fa::kThreads, 1)
+template <int QT, int EXPM, bool SPLITP, bool NA, bool REGS>
+__global__ void __launch_bounds__(fa::Shape<QT, REGS>::kThreads, fa::Shape<QT, REGS>::kMinCtas)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, int Sq, int Skv, int H,
               float scale_log2, SeqScatter sc, NaParams na, int* __restrict__ err) {
   using namespace fa;
+  using Sh = Shape<QT, REGS>;
+  constexpr int kRing = Sh::kRing, kMmaWarp = Sh::kMmaWarp, kTmaWarp = Sh::kTmaWarp;
+  static_assert(!REGS || QT == 2, "register re-division needs whole warpgroups per role");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;                     // 2 tiles
-  uint8_t* sR = smem + 2 * kTileBytes;    // ring of kRing tiles: K_0 V_0 K_1 V_1 ...
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + kRing) * kTileBytes);
+  uint8_t* sQ = smem;                      // QT tiles
+  uint8_t* sR = smem + QT * kTileBytes;    // ring of kRing tiles: K_0 V_0 K_1 V_1 ...
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (QT + kRing) * kTileBytes);
   uint64_t* q_full = bars;                 // [1]
   uint64_t* r_full = bars + 1;             // [kRing]
   uint64_t* r_empty = bars + 1 + kRing;    // [kRing]
-  uint64_t* s_full = bars + 1 + 2 * kRing; // [2]  scores of tile t ready (also: all earlier MMAs complete)
-  uint64_t* p_ready = s_full + 2;          // [2]  probabilities of tile t written to TMEM
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_ready + 2);
+  uint64_t* s_full = bars + 1 + 2 * kRing; // [QT]  scores of tile t ready (also: all earlier MMAs complete)
+  uint64_t* p_ready = s_full + QT;         // [QT]  probabilities of tile t written to TMEM
+  uint64_t* p_half = p_ready + QT;         // [QT]  probabilities of keys 0..63 of tile t written (SPLITP)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_half + QT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // the shuffle makes the warp index (and every role branch below) provably warp-uniform for the compiler
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int h = blockIdx.y, b = blockIdx.z;
-  const int q_base = blockIdx.x * 2 * BQ;
+  const int q_base = blockIdx.x * QT * BQ;
   const int n_kv = NA ? na.kv_cnt[blockIdx.x] : (Skv + BKV - 1) / BKV;
   const int* kv_list = NA ? na.kv_idx + (size_t)blockIdx.x * na.max_n : nullptr;
+  constexpr uint32_t kOBase = QT * 128;    // TMEM: S_t at t * 128, O_t at kOBase + t * 128
 
+  // A CTA that starts after another one has reported an error leaves at once (the whole grid then drains in microseconds
+  // instead of running every CTA into its own wait limit). One thread reads the word so that the decision is CTA-uniform.
+  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int*>(err);
+  __syncthreads();
+  if (*abort_flag != 0) return;
+  __syncthreads();
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < kRing; ++i) {
       mbar_init(&r_full[i], 1);
       mbar_init(&r_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < QT; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 4);
+      mbar_init(&p_half[i], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, Sh::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -139,13 +180,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // With REGS every role branch starts by re-dividing the registers of its warpgroup (the instruction has to sit inside the
+  // branch: the compiler takes the smallest limit that reaches a join point as the limit of everything after it).
   if (warp == kTmaWarp) {
     // -------------------------------------------------------------------- TMA producer
+    if (REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Sh::kRegsOther));
     if (lane == 0) {
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
-      mbar_arrive_expect_tx(q_full, 2 * kTileBytes);
+      mbar_arrive_expect_tx(q_full, QT * kTileBytes);
       // neighbourhood mode: tile index -> coordinates of its 5-D box (w0, h0, b * T + t0)
       auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int tile) {
         if (NA) {
@@ -155,7 +199,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int c = 0; c < 2; ++c) tma_load_4d(dst + c * kHalfBytes, tm, bar, c * 64, h, tile * BKV, b);
         }
       };
-      for (int t = 0; t < 2; ++t) load_tile(sQ + t * kTileBytes, &tm_q, q_full, blockIdx.x * 2 + t);
+      for (int t = 0; t < QT; ++t) load_tile(sQ + t * kTileBytes, &tm_q, q_full, blockIdx.x * QT + t);
       bool ok = true;
       int slot = 0;
       uint32_t ph = 0;
@@ -170,6 +214,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------------- MMA issuer
+    if (REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Sh::kRegsOther));
     {
       // The whole warp runs this code with identical values and only the elected lane issues: warp-uniform control flow
       // and descriptor arithmetic stay on the uniform datapath, which roughly halves the issue cost per MMA.
@@ -189,11 +234,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           umma_ss_w(tmem_base + t * 128, bq + off, bk + off, idesc_qk, kk > 0 ? 1u : 0u, leader);
         }
       };
-      auto issue_pv = [&](int t, int slot, bool accumulate) {
+      // O_t += P_t[:, 16 kk0 .. 16 kk1) V[16 kk0 .. 16 kk1, :]
+      auto issue_pv = [&](int t, int slot, bool accumulate, int kk0, int kk1) {
         const uint64_t bv = dR_mn + (uint64_t)(slot * (kTileBytes >> 4));
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          umma_ts_w(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8, bv + (uint32_t)(kk * (2048 >> 4)), idesc_pv,
+        for (int kk = kk0; kk < kk1; ++kk) {
+          umma_ts_w(tmem_base + kOBase + t * 128, tmem_base + t * 128 + kk * 8, bv + (uint32_t)(kk * (2048 >> 4)), idesc_pv,
                     (accumulate || kk > 0) ? 1u : 0u, leader);
         }
       };
@@ -204,10 +250,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) ok = wait_all(&r_full[slot], ph);
       if (ok) {
         tc_fence_after();
-        issue_qk(0, slot);
-        umma_commit_w(&s_full[0], leader);
-        issue_qk(1, slot);
-        umma_commit_w(&s_full[1], leader);
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+          issue_qk(t, slot);
+          umma_commit_w(&s_full[t], leader);
+        }
         umma_commit_w(&r_empty[slot], leader);
         advance();
       }
@@ -221,26 +268,37 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (!wait_all(&r_full[k_slot], ph)) { ok = false; break; }
           advance();
         }
-        for (int t = 0; t < 2; ++t) {
-          if (!wait_all(&p_ready[t], j & 1)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(t, v_slot, j > 0);
-          if (t == 1) umma_commit_w(&r_empty[v_slot], leader);
+#pragma unroll
+        for (int t = 0; t < QT; ++t) {
+          if (SPLITP) {
+            if (!wait_all(&p_half[t], j & 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, v_slot, j > 0, 0, 4);
+            if (!wait_all(&p_ready[t], j & 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, v_slot, true, 4, 8);
+          } else {
+            if (!wait_all(&p_ready[t], j & 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, v_slot, j > 0, 0, 8);
+          }
+          if (t == QT - 1) umma_commit_w(&r_empty[v_slot], leader);
           if (has_next) issue_qk(t, k_slot);
-          if (t == 1 && has_next) umma_commit_w(&r_empty[k_slot], leader);
+          if (t == QT - 1 && has_next) umma_commit_w(&r_empty[k_slot], leader);
           umma_commit_w(&s_full[t], leader);
         }
       }
       if (!ok && lane == 0) { atomicCAS(err, 0, 12); *abort_flag = 1; }
     }
-  } else {
+  } else if (warp < 4 * QT) {
     // -------------------------------------------------------------------- softmax warpgroups
+    if (REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Sh::kRegsSoftmax));
     const int t = warp >> 2;       // query tile
     const int quarter = warp & 3;  // TMEM lane quarter
     const int q_row = q_base + t * BQ + quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem_base + t * 128 + lane_off;
-    const uint32_t tO = tmem_base + 256 + t * 128 + lane_off;
+    const uint32_t tO = tmem_base + kOBase + t * 128 + lane_off;
     float m_ref = -INFINITY;  // reference maximum used in the exponent (log2 domain)
     float l = 0.f;
     bool ok = true;
@@ -288,11 +346,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int i = 0; i < 32; ++i)
             if (!((vis[c] >> i) & 1u)) r[c][i] = 0xff800000u;
       }
+      // row maximum: four independent chains of three-input max instructions
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[c][i]));
+        for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       const bool need = mx > m_ref + kRescaleThreshold;
       float alpha = 1.f;
@@ -317,30 +376,32 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // probabilities -> bf16 pairs over the first 64 columns of the score buffer
       // a row that has seen no visible key yet keeps m_ref = -inf: use 0 so that its masked scores give exp2(-inf) = 0
       const float neg_m = (NA && m_ref == -INFINITY) ? 0.f : -m_ref;
+      const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_m, neg_m);
       float2 lsum2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float2 x;
-          if (PACKED) {
-            x = fma2(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
-                     make_float2(scale_log2, scale_log2), make_float2(neg_m, neg_m));
-          } else {
-            x.x = fmaf(__uint_as_float(r[c][2 * i]), scale_log2, neg_m);
-            x.y = fmaf(__uint_as_float(r[c][2 * i + 1]), scale_log2, neg_m);
-          }
+          const float2 x = fma2(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), sc2, nm2);
           float2 p;
-          const bool poly = (POLY_MOD > 0) && ((i % (POLY_MOD > 0 ? POLY_MOD : 1)) == 0);
-          p.x = poly ? exp2_poly(x.x) : ex2(x.x);
-          p.y = poly ? exp2_poly(x.y) : ex2(x.y);
-          lsum2.x += p.x;
-          lsum2.y += p.y;
+          if ((i & 3) < EXPM) {
+            p = exp2_poly2(x);
+          } else {
+            p.x = ex2(x.x);
+            p.y = ex2(x.y);
+          }
+          lsum2 = add2(lsum2, p);
           __nv_bfloat162 pb = __floats2bfloat162_rn(p.x, p.y);
           pk[i] = *reinterpret_cast<uint32_t*>(&pb);
         }
         tmem_st16(tS + c * 16, pk);
+        if (SPLITP && c == 1) {
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_half[t]);
+        }
       }
       l += lsum2.x + lsum2.y;
       tmem_st_wait();
@@ -401,6 +462,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       atomicCAS(err, 0, 13);
       *abort_flag = 1;
     }
+  } else {
+    if (REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Sh::kRegsOther));   // the two padding warps of the third warpgroup
   }
 
   __syncwarp();
@@ -411,7 +474,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, Sh::kTmemCols);
   }
 }
 
@@ -419,22 +482,28 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 using namespace cb200;
 
-template <int POLY_MOD, bool PACKED, bool NA = false>
+template <int QT, int EXPM, bool SPLITP, bool NA = false, bool REGS = false>
 static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, float* lse, int B, int Sq,
                          int Skv, int H, float scale, const SeqScatter& sc, int* err, cudaStream_t st,
                          const NaParams& na = NaParams{}) {
   using namespace fa;
-  auto kern = fa_fwd_kernel<POLY_MOD, PACKED, NA>;
+  using Sh = Shape<QT, REGS>;
+  auto kern = fa_fwd_kernel<QT, EXPM, SPLITP, NA, REGS>;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::kSmem);
     if (e != cudaSuccess) return 100 + (int)e;
     attr = true;
   }
-  dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
-  kern<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, sc, na, err);
+  dim3 grid((Sq + QT * BQ - 1) / (QT * BQ), H, B);
+  kern<<<grid, Sh::kThreads, Sh::kSmem, st>>>(tq, tk, tv, (bf16*)o, lse, Sq, Skv, H, scale * 1.4426950408889634f, sc, na, err);
   return (int)cudaGetLastError();
 }
+
+// the variant the operators use: exponentials split between the special-function unit and the FMA pipe, half-row hand-off
+constexpr int kDefaultExpm = 2;
+constexpr bool kDefaultSplit = true;
+constexpr int kShortKeys = 1024;   // at most this many keys: the one-tile shape with two CTAs per SM
 
 // q [B, Sq, H, 128]; k, v [B, Skv, H, 128]; o like q; lse [B, H, Sq] fp32.
 // variant: 0 = default; 1..: tuning variants (all produce the same result within rounding)
@@ -462,15 +531,23 @@ static int fa_fwd_dispatch(const void* q, const void* k, const void* v, void* o,
   if (rc) return rc;
   rc = na != nullptr ? make_grid(&tv, v) : make(&tv, v, Skv);
   if (rc) return rc;
-  if (na != nullptr) return launch_fa_fwd<0, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st, *na);
+  if (na != nullptr) return launch_fa_fwd<2, kDefaultExpm, kDefaultSplit, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st, *na);
   switch (variant) {
-    case 1: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 2: return launch_fa_fwd<0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 3: return launch_fa_fwd<2, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 4: return launch_fa_fwd<3, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 5: return launch_fa_fwd<4, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    default: return launch_fa_fwd<0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 1: return launch_fa_fwd<2, 0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);   // all ex2, whole-row hand-off
+    case 2: return launch_fa_fwd<2, 0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 3: return launch_fa_fwd<2, 1, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 4: return launch_fa_fwd<2, 2, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 5: return launch_fa_fwd<2, 2, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 6: return launch_fa_fwd<2, 3, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 7: return launch_fa_fwd<1, kDefaultExpm, kDefaultSplit>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);  // one tile, 2 CTAs / SM
+    case 8: return launch_fa_fwd<1, 0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 9: return launch_fa_fwd<2, 2, true, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);   // + register re-division
+    case 10: return launch_fa_fwd<2, 1, true, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 11: return launch_fa_fwd<2, 0, false, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    default: break;
   }
+  if (sc.P == 0 && Skv <= kShortKeys) return launch_fa_fwd<1, kDefaultExpm, kDefaultSplit>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+  return launch_fa_fwd<2, kDefaultExpm, kDefaultSplit>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
 }
 
 extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,

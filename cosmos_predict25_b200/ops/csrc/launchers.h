@@ -50,8 +50,6 @@ int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void* v, const 
 int cb200_fa_fwd_na(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, float scale,
                     const int* kv_idx, const int* kv_cnt, int max_n, const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT,
                     int nH, int nW, int* err, cudaStream_t st);
-int cb200_fa_fwd_split(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
-                       const int64_t* out_ptrs, int P, int rank, int* err, cudaStream_t st);
 int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
                  int variant, int* err, cudaStream_t st);
 }
@@ -73,12 +71,9 @@ void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S
 }
 
 extern "C" {
-void cb200_fa_bwd_fused_set_trace(long long* buf);
 // fa_jvp.cu
 int cb200_fa_jvp(const void* q, const void* k, const void* v, const void* tq, const void* tk, const void* tv, const void* o,
                  const float* lse, void* to, int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st);
-// microbench.cu
-int cb200_red_f32_bench(float* acc, int rows, int n_ctas, cudaStream_t st);
 
 // fa_bwd.cu
 int cb200_fa_bwd_scratch_floats(int B, int Sq, int H);
@@ -87,4 +82,12 @@ int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, const void* v,
                    void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int variant, int* err, cudaStream_t st);
 int cb200_fa_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq, void* dk,
                  void* dv, float* scratch, int B, int Sq, int Skv, int H, float scale, int* err, cudaStream_t st);
+}
+
+extern "C" {
+// conv3d_cl.cu
+int cb200_conv_cl(const void* x, int T_in, int H_in, int W_in, int Cin, const void* w, int n_rows, int n_tile, int Cout,
+                  const int* taps, int ntaps, int T_out, int H_out, int W_out, const int* out_map, void* y, const void* resid,
+                  const float* bias, int* err, int sms, cudaStream_t st);
+int cb200_rmsnorm_silu_cl(const void* x, const float* gamma, void* y, long n_vox, int C, int silu, cudaStream_t st);
 }

@@ -316,8 +316,12 @@ class ShardedEngine:
             run()
 
     def check_health(self) -> None:
-        """Raise if a kernel of this engine recorded an error. The collectives of this class are host-checked library
-        calls; engines whose collectives are kernels with bounded waits override this."""
+        """Raise if a kernel recorded an error in the device's error word (a bounded wait that ran out: the kernel returned
+        early and its output is not valid). Synchronises the device; the trainer calls it where it synchronises anyway."""
+        if self.device.type == "cuda" and native.available():
+            code = int(native.load().kernel_error(self.device.index, True))
+            if code != 0:
+                raise RuntimeError(f"a kernel gave up a bounded wait (error code {code}); the step's results are not valid")
 
     def finish_backward(self):
         """Reduce any unit whose hook did not fire (unused parameters) and join the comm stream."""
