@@ -14,7 +14,9 @@ temporal up-sampler is skipped on the first chunk); encode is deterministic (mu 
 (mu - mean) / std scaling.
 
 The streaming state is an explicit ``StreamState`` object keyed by module instead of a positional list that
-is threaded through every forward call. Convolutions run on cuDNN through torch. Under
+is threaded through every forward call. On a GPU, bf16 decodes of one video run channels-last on this package's
+implicit-GEMM convolution kernel (``vae_wan_cl.DecoderCL``); the module tree below is the definition, the CPU / fp32 path and
+the row-sharded path, with convolutions on cuDNN through torch. Under
 ``vae_parallel.row_sharded`` the decoder works on a horizontal band of the frame per rank and swaps boundary
 rows with its neighbours (``Wan2pt1VAEInterface.decode_parallel``).
 """
@@ -338,10 +340,33 @@ class WanVAE_(nn.Module):
         else:
             z = z / inv_std + mean
         x = self.conv2(z)
+        cl = self._kernel_decoder(x)
+        if cl is not None:
+            # channels-last decoder on this package's convolution kernel; it keeps its own stream state
+            if clear_decoder_cache or cl.state is None:
+                cl.reset()
+            outs = [cl.step(x[:, :, i: i + 1]) for i in range(z.shape[2])]
+            if clear_decoder_cache:
+                cl.state = None
+                self._dec_state = None
+            return torch.cat(outs, 2)
         outs = [self.decoder(x[:, :, i: i + 1], st) for i in range(z.shape[2])]
         if clear_decoder_cache:
             self._dec_state = None
         return torch.cat(outs, 2)
+
+    def _kernel_decoder(self, x):
+        """The channels-last kernel decoder for this input, or None when the torch / cuDNN path has to serve it (CPU tensors,
+        fp32, batches, row-sharded decode, ``settings.conv == "cudnn"``). Weights are repacked when they change."""
+        from ..ops import functional as F_ops
+        from . import vae_wan_cl
+        if F_ops.settings.conv != "native" or vae_parallel.active() is not None or not vae_wan_cl.supported(self.decoder, x):
+            return None
+        sig = tuple((p.data_ptr(), p._version) for p in self.decoder.parameters())
+        if getattr(self, "_dec_cl", None) is None or self._dec_cl_sig != sig:
+            self._dec_cl = vae_wan_cl.DecoderCL(self.decoder, x.device)
+            self._dec_cl_sig = sig
+        return self._dec_cl
 
     def forward(self, x, scale=(0.0, 1.0)):
         mu = self.encode(x, scale)

@@ -132,7 +132,8 @@ def main():
         fl = 4.0 * N * N * HD * heads
         scale = 1 / math.sqrt(HD)
         add("fa_fwd tcgen05", f"S={N} H={heads} hd=128", time_ms(lambda: ops.fa_fwd(q, k, v, scale), iters=3, warmup=1), fl)
-        add("cudnn sdpa fwd (twin)", f"S={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, k, v, scale), iters=3, warmup=1), fl)
+        if not args.no_twin:
+            add("cudnn sdpa fwd (twin)", f"S={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, k, v, scale), iters=3, warmup=1), fl)
         if args.variants and hasattr(ops, "fa_fwd_variant"):
             for var in (1, 2, 3, 4, 5, 6, 9, 10, 11):
                 add(f"fa_fwd tcgen05 variant {var}", f"S={N} H={heads}",
@@ -162,14 +163,16 @@ def main():
             add("fa_fwd_na tcgen05 (tile-sparse neighbourhood attention)", f"grid={vs} window={win} stride={st} H={heads}",
                 time_ms(lambda: ops.fa_fwd_na(qt, kt, vt, scale, plan.kv_idx, plan.kv_cnt, plan.bt, plan.bh, plan.bw), iters=3, warmup=1),
                 fl_na, note=f"visited key tiles: {plan.visited_fraction:.3f} of dense; dense fa_fwd above is the baseline")
-        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
-        og = F_ops._sdpa(qg, kg, vg, scale)
-        dog = torch.randn_like(og)
-        add("cudnn sdpa bwd (twin)", f"S={N} H={heads}",
-            time_ms(lambda: torch.autograd.grad(og, (qg, kg, vg), dog, retain_graph=True), iters=3, warmup=1), 2.5 * fl)
+        if not args.no_twin:
+            qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+            og = F_ops._sdpa(qg, kg, vg, scale)
+            dog = torch.randn_like(og)
+            add("cudnn sdpa bwd (twin)", f"S={N} H={heads}",
+                time_ms(lambda: torch.autograd.grad(og, (qg, kg, vg), dog, retain_graph=True), iters=3, warmup=1), 2.5 * fl)
         kc, vc = (torch.randn(1, 512, heads, HD, device=dev).bfloat16() for _ in range(2))
         add("fa_fwd tcgen05 cross (Skv=512)", f"Sq={N} H={heads}", time_ms(lambda: ops.fa_fwd(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
-        add("cudnn sdpa cross (twin)", f"Sq={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
+        if not args.no_twin:
+            add("cudnn sdpa cross (twin)", f"Sq={N} H={heads}", time_ms(lambda: F_ops._sdpa(q, kc, vc, scale)), 4.0 * N * 512 * HD * heads)
         if args.variants:
             for var in (7, 8, 4, 1):
                 add(f"fa_fwd tcgen05 cross variant {var}", f"Sq={N} H={heads}",

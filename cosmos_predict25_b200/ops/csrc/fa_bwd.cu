@@ -28,7 +28,7 @@
 namespace cb200 {
 using namespace sm100;
 
-constexpr int kFaBwdDefaultLong = 2;   // kernel used for long key sequences when the caller does not choose
+constexpr int kFaBwdDefaultLong = 3;   // kernel used for long key sequences when the caller does not choose
 
 namespace fab {
 constexpr int HD = 128;

@@ -22,8 +22,8 @@
 //   * EXPM of every 4 element pairs compute 2^x on the FMA pipe instead (round-to-nearest split, degree-3 polynomial in
 //     packed fp32x2 arithmetic, exponent add; relative error 1e-4, a twentieth of a bf16 half-ulp);
 //   * the row maximum uses the three-input max;
-//   * SPLITP: the probabilities of keys 0..63 are published on their own barrier, so the first half of P.V runs while
-//     the second half of the row is still being exponentiated.
+//   * SPLITP = 2 or 4: the probabilities are published in halves / quarters of the key tile on their own barriers, so P.V of
+//     the first keys runs while the rest of the row is still being exponentiated.
 // QT = 1 is the shape for short key sequences (cross-attention, 512 keys): one query tile, 192 threads, 97 KB of shared memory and 256
 // TMEM columns per CTA, so that two CTAs share an SM and fill each other's prologue / epilogue gaps.
 //
@@ -51,13 +51,17 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 // shape of a CTA with QT query tiles: 4 softmax warps per tile, then the TMA warp and the MMA warp
 // REGS: the CTA is padded to whole warpgroups (12 warps) and re-divides its registers at start: the warpgroup of the TMA / MMA warps
 // gives registers back (setmaxnreg.dec) and the softmax warpgroups take them (setmaxnreg.inc), which removes the spills of the
-// 128-value score row.
+// 128-value score row. The padding also pays for a second MMA issuer: each query tile gets its own issuing warp, so a wait
+// on one tile's probabilities never delays the other tile's MMAs.
 template <int QT, bool REGS = false>
 struct Shape {
   static constexpr int kRing = QT == 2 ? 5 : 2;           // K/V ring slots
   static constexpr int kTmaWarp = 4 * QT, kMmaWarp = 4 * QT + 1;
+  static constexpr int kIssuers = REGS ? QT : 1;          // MMA issuer warps kMmaWarp .. kMmaWarp + kIssuers - 1
   static constexpr int kThreads = REGS ? (4 * QT + 4) * 32 : (4 * QT + 2) * 32;
-  static constexpr int kRegsSoftmax = 224, kRegsOther = 56;
+  // register re-division: launched with kRegsLaunch per thread (12 warps); the CTA can only re-divide that allocation
+  static constexpr int kRegsLaunch = 168, kRegsSoftmax = 224, kRegsOther = 56;
+  static_assert(!REGS || (8 * kRegsSoftmax + 4 * kRegsOther <= 12 * kRegsLaunch), "setmaxnreg budget: increases must be covered by decreases");
   static constexpr int kMinCtas = QT == 2 ? 1 : 2;
   static constexpr uint32_t kTmemCols = 256 * QT;
   static constexpr size_t kSmem = (QT + kRing) * (size_t)kTileBytes + 1024 + 256;
@@ -120,7 +124,7 @@ struct NaParams {
   int max_n, nT, nH, nW;
 };
 
-template <int QT, int EXPM, bool SPLITP, bool NA, bool REGS>
+template <int QT, int EXPM, int SPLITP, bool NA, bool REGS>
 __global__ void __launch_bounds__(fa::Shape<QT, REGS>::kThreads, fa::Shape<QT, REGS>::kMinCtas)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, int Sq, int Skv, int H,
@@ -139,8 +143,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint64_t* r_empty = bars + 1 + kRing;    // [kRing]
   uint64_t* s_full = bars + 1 + 2 * kRing; // [QT]  scores of tile t ready (also: all earlier MMAs complete)
   uint64_t* p_ready = s_full + QT;         // [QT]  probabilities of tile t written to TMEM
-  uint64_t* p_half = p_ready + QT;         // [QT]  probabilities of keys 0..63 of tile t written (SPLITP)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_half + QT);
+  uint64_t* p_part = p_ready + QT;         // [QT][3] probabilities of the first 1, 2, 3 key quarters of tile t written (SPLITP > 1)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_part + 3 * QT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // the shuffle makes the warp index (and every role branch below) provably warp-uniform for the compiler
@@ -161,12 +165,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(q_full, 1);
     for (int i = 0; i < kRing; ++i) {
       mbar_init(&r_full[i], 1);
-      mbar_init(&r_empty[i], 1);
+      mbar_init(&r_empty[i], Sh::kIssuers);   // every issuer has finished reading the slot
     }
     for (int i = 0; i < QT; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 4);
-      mbar_init(&p_half[i], 4);
+      for (int k = 0; k < 3; ++k) mbar_init(&p_part[i * 3 + k], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -212,9 +216,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       if (!ok) { atomicCAS(err, 0, 11); *abort_flag = 1; }
     }
-  } else if (warp == kMmaWarp) {
-    // -------------------------------------------------------------------- MMA issuer
+  } else if (warp >= kMmaWarp && warp < kMmaWarp + Sh::kIssuers) {
+    // -------------------------------------------------------------------- MMA issuer(s): tiles [t_lo, t_hi) of this warp
     if (REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Sh::kRegsOther));
+    const int t_lo = Sh::kIssuers == 1 ? 0 : warp - kMmaWarp, t_hi = Sh::kIssuers == 1 ? QT : t_lo + 1;
     {
       // The whole warp runs this code with identical values and only the elected lane issues: warp-uniform control flow
       // and descriptor arithmetic stay on the uniform datapath, which roughly halves the issue cost per MMA.
@@ -250,8 +255,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) ok = wait_all(&r_full[slot], ph);
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int t = 0; t < QT; ++t) {
+        for (int t = t_lo; t < t_hi; ++t) {
           issue_qk(t, slot);
           umma_commit_w(&s_full[t], leader);
         }
@@ -268,23 +272,26 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (!wait_all(&r_full[k_slot], ph)) { ok = false; break; }
           advance();
         }
+        for (int t = t_lo; t < t_hi; ++t) {
+          if (SPLITP > 1) {
+            // the softmax publishes its row in SPLITP parts; P.V follows part by part
+            constexpr int kPer = 8 / SPLITP;
 #pragma unroll
-        for (int t = 0; t < QT; ++t) {
-          if (SPLITP) {
-            if (!wait_all(&p_half[t], j & 1)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, v_slot, j > 0, 0, 4);
-            if (!wait_all(&p_ready[t], j & 1)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, v_slot, true, 4, 8);
+            for (int part = 0; part < SPLITP; ++part) {
+              uint64_t* bar = part == SPLITP - 1 ? &p_ready[t] : &p_part[t * 3 + (part + 1) * (4 / SPLITP) - 1];
+              if (!wait_all(bar, j & 1)) { ok = false; break; }
+              tc_fence_after();
+              issue_pv(t, v_slot, j > 0 || part > 0, part * kPer, (part + 1) * kPer);
+            }
+            if (!ok) break;
           } else {
             if (!wait_all(&p_ready[t], j & 1)) { ok = false; break; }
             tc_fence_after();
             issue_pv(t, v_slot, j > 0, 0, 8);
           }
-          if (t == QT - 1) umma_commit_w(&r_empty[v_slot], leader);
+          if (t == t_hi - 1) umma_commit_w(&r_empty[v_slot], leader);
           if (has_next) issue_qk(t, k_slot);
-          if (t == QT - 1 && has_next) umma_commit_w(&r_empty[k_slot], leader);
+          if (t == t_hi - 1 && has_next) umma_commit_w(&r_empty[k_slot], leader);
           umma_commit_w(&s_full[t], leader);
         }
       }
@@ -396,11 +403,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           pk[i] = *reinterpret_cast<uint32_t*>(&pb);
         }
         tmem_st16(tS + c * 16, pk);
-        if (SPLITP && c == 1) {
+        if (SPLITP > 1 && c < 3 && ((c + 1) % (4 / SPLITP)) == 0) {
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&p_half[t]);
+          if (lane == 0) mbar_arrive(&p_part[t * 3 + c]);
         }
       }
       l += lsum2.x + lsum2.y;
@@ -482,7 +489,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
 using namespace cb200;
 
-template <int QT, int EXPM, bool SPLITP, bool NA = false, bool REGS = false>
+template <int QT, int EXPM, int SPLITP, bool NA = false, bool REGS = false>
 static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* o, float* lse, int B, int Sq,
                          int Skv, int H, float scale, const SeqScatter& sc, int* err, cudaStream_t st,
                          const NaParams& na = NaParams{}) {
@@ -493,6 +500,12 @@ static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::kSmem);
     if (e != cudaSuccess) return 100 + (int)e;
+    if (REGS) {   // the register re-division inside the kernel is computed for exactly this launch allocation
+      cudaFuncAttributes fa{};
+      e = cudaFuncGetAttributes(&fa, kern);
+      if (e != cudaSuccess) return 100 + (int)e;
+      if (fa.numRegs != Sh::kRegsLaunch) return -43;
+    }
     attr = true;
   }
   dim3 grid((Sq + QT * BQ - 1) / (QT * BQ), H, B);
@@ -501,8 +514,8 @@ static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUt
 }
 
 // the variant the operators use: exponentials split between the special-function unit and the FMA pipe, half-row hand-off
-constexpr int kDefaultExpm = 2;
-constexpr bool kDefaultSplit = true;
+constexpr int kDefaultExpm = 1;     // one pair in four on the FMA pipe
+constexpr int kDefaultSplit = 2;    // probabilities published in two halves
 constexpr int kShortKeys = 1024;   // at most this many keys: the one-tile shape with two CTAs per SM
 
 // q [B, Sq, H, 128]; k, v [B, Skv, H, 128]; o like q; lse [B, H, Sq] fp32.
@@ -531,23 +544,23 @@ static int fa_fwd_dispatch(const void* q, const void* k, const void* v, void* o,
   if (rc) return rc;
   rc = na != nullptr ? make_grid(&tv, v) : make(&tv, v, Skv);
   if (rc) return rc;
-  if (na != nullptr) return launch_fa_fwd<2, kDefaultExpm, kDefaultSplit, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st, *na);
+  if (na != nullptr) return launch_fa_fwd<2, kDefaultExpm, kDefaultSplit, true, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st, *na);
   switch (variant) {
-    case 1: return launch_fa_fwd<2, 0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);   // all ex2, whole-row hand-off
-    case 2: return launch_fa_fwd<2, 0, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 3: return launch_fa_fwd<2, 1, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 4: return launch_fa_fwd<2, 2, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 5: return launch_fa_fwd<2, 2, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 6: return launch_fa_fwd<2, 3, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 1: return launch_fa_fwd<2, 0, 1>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);   // all ex2, whole-row hand-off
+    case 2: return launch_fa_fwd<2, 1, 2>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 3: return launch_fa_fwd<2, 1, 1, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);   // from here: register re-division, two issuers
+    case 4: return launch_fa_fwd<2, 1, 2, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 5: return launch_fa_fwd<2, 1, 4, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 6: return launch_fa_fwd<2, 0, 2, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
     case 7: return launch_fa_fwd<1, kDefaultExpm, kDefaultSplit>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);  // one tile, 2 CTAs / SM
-    case 8: return launch_fa_fwd<1, 0, false>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 9: return launch_fa_fwd<2, 2, true, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);   // + register re-division
-    case 10: return launch_fa_fwd<2, 1, true, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-    case 11: return launch_fa_fwd<2, 0, false, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 8: return launch_fa_fwd<1, 0, 1>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 9: return launch_fa_fwd<2, 2, 2, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 10: return launch_fa_fwd<2, 2, 4, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+    case 11: return launch_fa_fwd<2, 0, 4, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
     default: break;
   }
   if (sc.P == 0 && Skv <= kShortKeys) return launch_fa_fwd<1, kDefaultExpm, kDefaultSplit>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
-  return launch_fa_fwd<2, kDefaultExpm, kDefaultSplit>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
+  return launch_fa_fwd<2, kDefaultExpm, kDefaultSplit, false, true>(tq, tk, tv, o, lse, B, Sq, Skv, H, scale, sc, err, st);
 }
 
 extern "C" int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H,

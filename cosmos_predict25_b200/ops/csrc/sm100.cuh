@@ -1,7 +1,10 @@
 // Thin inline-PTX layer over the Blackwell (sm_100a) primitives used by the contraction kernels:
 // mbarrier, TMA tiled loads (each load lands in the issuing CTA's own shared memory only), tcgen05 MMA / TMEM alloc / TMEM load,
-// UMMA shared-memory and instruction descriptors. Every wait is bounded: after `kSpinLimit` failed
-// probes the caller gets `false`, records an error code and leaves through its normal exit path.
+// UMMA shared-memory and instruction descriptors. Every mbarrier wait is bounded in time (`kWaitLimitNs`): the caller then
+// gets `false`, records an error code and leaves through its normal exit path. One wait is NOT bounded and must be made
+// impossible to miss by construction: `setmaxnreg.inc` blocks until the CTA's OWN register allocation (threads x registers at
+// launch; the SM's unallocated registers do not count) has enough free registers, i.e. until other warpgroups of the CTA have
+// released them with `setmaxnreg.dec`. Kernels that use it assert their register budget at compile time.
 #pragma once
 
 #include <cuda.h>
@@ -12,7 +15,15 @@
 namespace cb200 {
 namespace sm100 {
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // probes; each try_wait may itself block for a while
+// Bound of every mbarrier wait, in nanoseconds of the global timer. A probe count is not a bound one can rely on: a single
+// try_wait may block for a system-dependent time, and 2^24 of them added up to minutes per wait on B200.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -57,11 +68,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: false on timeout or when `abort_flag` (shared memory) has been raised by another role.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
   }
-  return false;
 }
 
 // ---- TMA -----------------------------------------------------------------------------------------

@@ -28,11 +28,13 @@ class OpSettings:
                (torch SDPA pinned to the cuDNN backend: what the reference selects on sm_100,
                cosmos_predict2/_src/predict2/networks/attention.py:132-138).
     gemm:      "native" (tcgen05/TMA GEMM with fused epilogues) or "cublas" (torch.matmul).
+    conv:      "native" (channels-last implicit-GEMM convolution kernel: the VAE decoder) or "cudnn" (torch convolutions).
     """
 
     attention: str = os.environ.get("COSMOS_B200_ATTENTION", "native")
     gemm: str = os.environ.get("COSMOS_B200_GEMM", "native")
     attention_bwd: str = os.environ.get("COSMOS_B200_ATTENTION_BWD", "native")
+    conv: str = os.environ.get("COSMOS_B200_CONV", "native")
 
 
 settings = OpSettings()
