@@ -45,7 +45,7 @@ def parse():
     ap.add_argument("--height", type=int, default=88)
     ap.add_argument("--width", type=int, default=160)
     ap.add_argument("--cp", type=int, default=1, help="context-parallel size (Ulysses)")
-    ap.add_argument("--transport", default=os.environ.get("COSMOS_B200_TRANSPORT", "peer"), choices=["peer", "nccl"])
+    ap.add_argument("--transport", default=os.environ.get("COSMOS_B200_TRANSPORT", "peer"), choices=["peer", "nccl", "peer_reshard"])
     ap.add_argument("--attention", default=None, choices=[None, "native", "cudnn"])
     ap.add_argument("--gemm", default=None, choices=[None, "native", "cublas"])
     ap.add_argument("--checkpoint", default="save_attention")
@@ -219,6 +219,9 @@ def main():
     err = native.load().kernel_error(local_rank, True)
     last_loss = float(losses[-1]) if losses else float("nan")
 
+    resident_bytes = int(model.engine.resident_parameter_bytes()) if hasattr(model.engine, "resident_parameter_bytes") else \
+        int(sum(u.full_numel for u in model.engine.units) * 2)
+
     # ---- library twin: the same model, optimizer and data with cuDNN attention and cuBLAS GEMMs (the reference's choice on sm_100)
     twin = None
     if not args.no_twin and args.attention is None and args.gemm is None and args.model in ("2B", "14B"):
@@ -243,7 +246,7 @@ def main():
         torch.cuda.empty_cache()
         from bench_inference import run_inference
         rec = run_inference(model_name=args.model, frames=args.frames, height=args.height, width=args.width,
-                            steps=args.inference_steps, transport=args.transport)
+                            steps=args.inference_steps, transport="peer" if args.transport.startswith("peer") else args.transport)
         inference = {k: rec[k] for k in ("s_per_denoising_step", "vae_decode_s", "s_per_video_35_steps", "decoded_frames",
                                          "gpu_launches_sampling", "kernel_error")}
         inference.update(unit="s", timed_unipc_steps=args.inference_steps, guidance=7.0, parallelism=rec["config"]["parallelism"],
@@ -267,6 +270,7 @@ def main():
                        "gemm": F_ops.settings.gemm,
                        "l2": "per-step working set (>10 GB of activations) exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks, "gpu_launches": launches, "kernel_error": int(err), "final_loss": last_loss,
+            "resident_parameter_bytes": resident_bytes, "max_memory_allocated_bytes": int(torch.cuda.max_memory_allocated(dev)),
         }
         if twin:
             line["library_twin"] = twin

@@ -21,6 +21,11 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
+def _conv_native() -> bool:
+    from cosmos_predict25_b200.ops import functional as F_ops
+    return F_ops.settings.conv == "native"
+
+
 def run_inference(*, model_name="2B", frames=24, height=88, width=160, steps=35, guidance=7.0, decode=True, transport="peer",
                   cp_comm="a2a", sparse_window=None, sparse_stride=(1, 4, 8), dense_blocks=0, warmup_steps=2) -> dict:
     """Video2World sampling (+ VAE decode) through ``generate_samples_from_batch`` / ``decode`` on the current process group, the
@@ -107,7 +112,8 @@ def run_inference(*, model_name="2B", frames=24, height=88, width=160, steps=35,
                    "parallelism": f"cp{world}" + (" (ring)" if world > 1 and args.cp_comm == "p2p" else ""),
                    "self_attention": "dense" if args.sparse_window is None else
                    f"neighbourhood window={tuple(args.sparse_window)} stride={tuple(args.sparse_stride)}, {args.dense_blocks} dense blocks", "transport": args.transport if world > 1 else "single",
-                   "vae": ("Wan2.1 causal Conv3d decode (cuDNN convolutions)" + (f", {world} row bands with halo exchange" if world > 1 else ""))
+                   "vae": ("Wan2.1 causal Conv3d decode (" + ("channels-last implicit-GEMM kernel" if _conv_native() else "cuDNN convolutions") + ")"
+                           + (f", {world} row bands with halo exchange" if world > 1 else ""))
                    if tok is not None else "skipped"}}
 
 

@@ -439,7 +439,7 @@ class FinalLayer(nn.Module):
         lora2 = lora[..., : 2 * D] if lora is not None else None
         shift, scale = _run_adaln(self.adaln_modulation, emb, lora2, self.cfg.use_wan_fp32_strategy).chunk(2, dim=-1)
         h = ops.ln_modulate(x, shift, scale)
-        return F.linear(h, self.linear.weight)
+        return ops.linear(h, self.linear.weight)
 
 
 @dataclass
@@ -550,7 +550,14 @@ class CosmosDiT(nn.Module):
             parts.append(pm.expand(B, 1, T, H, W))
         x = torch.cat(parts, dim=1)
         lin = self.x_embedder.proj[1]
-        return F.linear(self.x_embedder.proj[0](x).to(lin.weight.dtype), lin.weight)
+        tokens = self.x_embedder.proj[0](x).to(lin.weight.dtype)
+        K = tokens.shape[-1]
+        if tokens.is_cuda and tokens.dtype == torch.bfloat16 and K % 64 != 0:
+            # the patch vector (72 values for 18 channels x 2 x 2) is zero-padded to the GEMM's 64-element k-block so that the
+            # embedding runs on the tcgen05 GEMM like every other projection (minimal_v4_dit.py:867-877)
+            pad = (-K) % 64
+            return ops.linear(F.pad(tokens, (0, pad)), F.pad(lin.weight, (0, pad)))
+        return ops.linear(tokens, lin.weight)
 
     def forward(self, x_B_C_T_H_W: torch.Tensor, timesteps_B_T: torch.Tensor, crossattn_emb: Optional[torch.Tensor],
                 condition_video_input_mask_B_C_T_H_W: Optional[torch.Tensor] = None,

@@ -75,7 +75,7 @@ class Text2WorldRFConfig:
     high_sigma_timesteps_max: int = 1000
     use_kerras_sigma_at_inference: bool = False
     text_dropout: float = 0.2
-    sharding_transport: str = "nccl"   # nccl | peer
+    sharding_transport: str = "nccl"   # nccl | peer | peer_reshard
     cp_comm_type: str = "a2a"          # context-parallel exchange in self-attention: a2a (Ulysses) | p2p (ring)
 
 
@@ -145,7 +145,10 @@ class Text2WorldModelRectifiedFlow(nn.Module):
             import torch.distributed as dist
             n_shard = dist.get_world_size(self.fsdp_group) if (self.fsdp_group is not None and dist.is_initialized()) else 1
             # peer kernels address one NVSwitch domain (2..8 ranks); anything else goes through NCCL
-            if self.config.sharding_transport == "peer" and self.device_.type == "cuda" and 2 <= n_shard <= 8:
+            if self.config.sharding_transport == "peer_reshard" and self.device_.type == "cuda" and 2 <= n_shard <= 8:
+                # block parameters are not kept resident: their all-gather is fused into the consuming GEMMs
+                from ..parallel.reshard_fsdp import ReshardEngine as make
+            elif self.config.sharding_transport in ("peer", "peer_reshard") and self.device_.type == "cuda" and 2 <= n_shard <= 8:
                 from ..parallel.peer_fsdp import PeerShardedEngine as make
             self.engine = make(self.net, group=self.fsdp_group, compute_dtype=self.precision,
                                use_ema=self.config.ema.enabled, replicate_group=self.replicate_group,

@@ -357,10 +357,10 @@ class WanVAE_(nn.Module):
 
     def _kernel_decoder(self, x):
         """The channels-last kernel decoder for this input, or None when the torch / cuDNN path has to serve it (CPU tensors,
-        fp32, batches, row-sharded decode, ``settings.conv == "cudnn"``). Weights are repacked when they change."""
+        fp32, batches, ``settings.conv == "cudnn"``). Weights are repacked when they change."""
         from ..ops import functional as F_ops
         from . import vae_wan_cl
-        if F_ops.settings.conv != "native" or vae_parallel.active() is not None or not vae_wan_cl.supported(self.decoder, x):
+        if F_ops.settings.conv != "native" or not vae_wan_cl.supported(self.decoder, x):
             return None
         sig = tuple((p.data_ptr(), p._version) for p in self.decoder.parameters())
         if getattr(self, "_dec_cl", None) is None or self._dec_cl_sig != sig:

@@ -26,6 +26,7 @@ import torch.nn.functional as F
 
 from ..ops import functional as F_ops
 from ..ops import native
+from . import vae_parallel
 
 CACHE_T = 2
 
@@ -54,17 +55,25 @@ class ConvCL:
         self.w = w.view(rows, ntaps * cpad).contiguous()
         self.bias = bias.detach().to(device=device, dtype=torch.float32).contiguous() if bias is not None else None
         self.taps = [int(v) for t in taps for v in t]
+        self.spatial = any(t[1] != 0 for t in taps)            # reads neighbouring rows: needs halo rows under row sharding
+        self.taps_halo = [int(v) for t in taps for v in (t[0], t[1] + 1, t[2])]
 
     def __call__(self, x: torch.Tensor, t_out: int, out: Optional[torch.Tensor] = None, out_map: Optional[List[int]] = None,
                  resid: Optional[torch.Tensor] = None, h_out: Optional[int] = None, w_out: Optional[int] = None) -> torch.Tensor:
-        """x [T_in, H, W, C_in]. Default output: a new [t_out, H, W, C_out] tensor with the identity mapping."""
+        """x [T_in, H, W, C_in]. Default output: a new [t_out, H, W, C_out] tensor with the identity mapping. Under row-sharded
+        decoding (``vae_parallel.row_sharded``) a convolution that reads neighbouring rows first receives one boundary row from
+        each neighbouring rank (zeros at the frame border) and reads its input shifted by that row."""
         _, H, W, _ = x.shape
         h_out, w_out = h_out or H, w_out or W
+        taps = self.taps
+        if self.spatial and vae_parallel.active() is not None:
+            x = vae_parallel.exchange_rows(x, 1, 1)
+            taps = self.taps_halo
         if out is None:
             out = torch.empty(t_out, h_out, w_out, self.cout, dtype=torch.bfloat16, device=x.device)
         if out_map is None:
             out_map = [1, 0, 1, 0, 1, 0, out.shape[1], out.shape[2], out.shape[3], 0]
-        native.load().conv_cl(x, self.w, self.n_tile, self.cout, self.taps, t_out, h_out, w_out, out_map, out, resid, self.bias)
+        native.load().conv_cl(x, self.w, self.n_tile, self.cout, taps, t_out, h_out, w_out, out_map, out, resid, self.bias)
         native.count_launch()
         return out
 
@@ -153,6 +162,8 @@ class _AttnCL:
         native.count_launch()
         qkv = F_ops.linear(y.view(T * H * W, C), self.w_qkv, self.b_qkv).view(T, H * W, 3, C)
         q, k, v = (qkv[:, :, i].unsqueeze(1) for i in range(3))          # [T, 1, HW, C]
+        if vae_parallel.active() is not None:                             # local rows attend to the whole frame
+            k, v = vae_parallel.gather_tokens(k.contiguous(), 2), vae_parallel.gather_tokens(v.contiguous(), 2)
         o = F.scaled_dot_product_attention(q, k, v)                       # single head of dimension C
         o = F_ops.linear(o.squeeze(1).reshape(T * H * W, C), self.w_proj, self.b_proj)
         return o.view(T, H, W, C) + x
@@ -251,6 +262,6 @@ class DecoderCL:
 
 
 def supported(decoder, z: torch.Tensor) -> bool:
-    """The kernel path serves bf16 CUDA decodes of one video whose frame is at least one 8 x 16 tile."""
+    """The kernel path serves bf16 CUDA decodes of one video (whole frames or, under ``vae_parallel.row_sharded``, row bands)."""
     return (z.is_cuda and z.dtype == torch.bfloat16 and z.shape[0] == 1 and native.available()
             and hasattr(native.load(), "conv_cl") and not native.forward_mode())

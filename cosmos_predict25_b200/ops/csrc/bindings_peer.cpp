@@ -137,9 +137,69 @@ Tensor a2a_gather_seq_peer(c10::ArrayRef<int64_t> src_ptrs, int64_t B, int64_t S
   return out;
 }
 
+int sm_count_peer(int device) {
+  static int cache[64] = {0};
+  if (cache[device] == 0) cache[device] = at::cuda::getDeviceProperties(device)->multiProcessorCount;
+  return cache[device];
+}
+
+// Small parameters of a unit, all-gathered by peer reads: segs [n, 4] as for the other segment kernels; `full` is the local
+// full-layout buffer that receives every rank's chunk.
+void gather_slots_peer(c10::ArrayRef<int64_t> shard_ptrs, const Tensor& segs, Tensor full) {
+  TORCH_CHECK(full.is_cuda() && full.scalar_type() == at::kBFloat16 && full.is_contiguous(), "full must be a contiguous CUDA bf16 tensor");
+  check_segs(segs, full);
+  c10::cuda::CUDAGuard g(full.device());
+  auto p = ptr_vec(shard_ptrs);
+  cb200_gather_slots_peer(p.data(), segs.data_ptr(), (int)segs.size(0), full.data_ptr(), (int)p.size(), stream());
+}
+
+// FSDP all-gather fused into the consuming GEMM. `ws` [rows, ld] is the local full-size home of a weight whose rows are sharded
+// over the ranks (shard_ptrs[r]: rank r's rows [r * chunk_rows, ...), row-major); the kernel fills it while it computes.
+//   trans_b = false: returns x [M, ld] @ W^T  (+ bias, optional GELU; `pre` receives the pre-activation when given)
+//   trans_b = true : returns x [M, rows] @ W  (dgrad)
+Tensor gemm_bf16_gather(const Tensor& x, Tensor ws, c10::ArrayRef<int64_t> shard_ptrs, int64_t chunk_rows, Tensor counters,
+                        const c10::optional<Tensor>& bias, int64_t act, bool trans_b, const c10::optional<Tensor>& pre) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x must be contiguous CUDA bf16 [M, K]");
+  TORCH_CHECK(ws.is_cuda() && ws.scalar_type() == at::kBFloat16 && ws.is_contiguous() && ws.dim() == 2 && ws.device() == x.device(),
+              "ws must be contiguous CUDA bf16 [rows, ld] on the device of x");
+  const int64_t rows = ws.size(0), ld = ws.size(1), M = x.size(0);
+  TORCH_CHECK(x.size(1) == (trans_b ? rows : ld), "contraction dims differ");
+  TORCH_CHECK(ld % 8 == 0 && x.size(1) % 8 == 0, "row strides must be multiples of 16 bytes");
+  auto p = ptr_vec(shard_ptrs);
+  TORCH_CHECK(chunk_rows >= 1 && chunk_rows * (int64_t)p.size() >= rows, "shards do not cover the weight");
+  const int64_t n_groups = (rows + 255) / 256;
+  TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.is_contiguous() && counters.numel() >= n_groups &&
+                  counters.device() == x.device(), "counters: CUDA int32, one per 256 rows");
+  c10::cuda::CUDAGuard g(x.device());
+  Tensor c = at::empty({M, trans_b ? ld : rows}, x.options());
+  Tensor bias_c;
+  const void* bias_p = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(!trans_b, "bias belongs to the forward form");
+    bias_c = bias->to(at::kBFloat16).contiguous();
+    TORCH_CHECK(bias_c.numel() == rows && bias_c.device() == x.device(), "bias must be [rows]");
+    bias_p = bias_c.data_ptr();
+  }
+  void* pre_p = nullptr;
+  if (pre.has_value()) {
+    TORCH_CHECK(pre->is_cuda() && pre->scalar_type() == at::kBFloat16 && pre->is_contiguous() && pre->numel() == c.numel() && act == 1,
+                "pre: bf16 tensor of the output's size, only with the GELU epilogue");
+    pre_p = pre->data_ptr();
+  }
+  const int dev = x.get_device();
+  const int rc = cb200_gemm_bf16_gather(x.data_ptr(), ws.data_ptr(), c.data_ptr(), (int)M, (int)rows, (int)ld, trans_b ? 1 : 0, p.data(),
+                                        (int)p.size(), (int)chunk_rows, counters.data_ptr<int>(), bias_p, (int)act, pre_p,
+                                        cb200_error_word(dev), sm_count_peer(dev), stream());
+  TORCH_CHECK(rc == 0, "gather GEMM launch failed with code ", rc);
+  return c;
+}
+
 }  // namespace
 
 void register_peer_ops(torch::Library& m) {
+  m.def("gather_slots_peer(int[] shard_ptrs, Tensor segs, Tensor(a!) full) -> ()", &gather_slots_peer);
+  m.def("gemm_bf16_gather(Tensor x, Tensor(a!) ws, int[] shard_ptrs, int chunk_rows, Tensor(b!) counters, Tensor? bias, int act, "
+        "bool trans_b, Tensor(c!)? pre) -> Tensor", &gemm_bf16_gather);
   m.def("peer_barrier(int[] flag_ptrs, int rank, int epoch, int device, int max_spins) -> ()", &peer_barrier);
   m.def("rs_cast_norm_peer(int[] grad_ptrs, Tensor segs, Tensor(a!) g32, Tensor(b!) unit_sumsq, Tensor(c!)? total_sumsq, int rank, "
         "float scale) -> ()", &rs_cast_norm_peer);

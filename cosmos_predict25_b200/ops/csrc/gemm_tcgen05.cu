@@ -15,6 +15,14 @@
 // Fused epilogues: + bias, exact GELU (optionally also writing the pre-activation for backward),
 // and the AdaLN gated residual  out = resid + gate[row / L, col] * acc.
 //
+// FSDP all-gather fused into the GEMM (template flag GATHER): the B operand is a weight [rows, ld] whose rows are sharded over P
+// ranks (rank r holds rows [r * chunk_rows, (r + 1) * chunk_rows) in its own memory). Four extra warps per CTA pull the shards -
+// plain 16-byte loads from the owners' memory, local or over NVLink - into a local full-size copy, in groups of 256 rows cut into
+// slices, and publish every finished slice with a release increment of the group's counter. The TMA producer acquires the
+// counter of the group a B box lies in before it issues the load, so tiles are computed while later groups are still in
+// flight and every remote row crosses NVLink exactly once. The same code serves the forward GEMM (groups along N) and dgrad
+// (groups along the contraction dimension).
+//
 // All mbarrier waits are bounded; on timeout the CTA records an error code in `err`, lets in-flight
 // copies land, frees its TMEM and returns.
 
@@ -62,10 +70,30 @@ struct GemmEpilogue {
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
-template <int A_MN, int B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// Row-sharded B operand gathered inside the kernel (see the header comment).
+constexpr int kGatherWarps = 4;
+constexpr int kGatherGroupRows = 256;
+struct GatherB {
+  int64_t ptrs[8];     // rank r: its rows [r * chunk_rows, ...) of the weight, row-major with `ld` elements per row
+  bf16* ws;            // local full copy [rows, ld]; the B tensor map is built on it
+  int* counters;       // one per 256-row group, zeroed by the host before the launch
+  int P, chunk_rows, rows, ld;
+  int slices;          // pieces a group is cut into; a group is complete when its counter reaches this value
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int A_MN, int B_MN, bool GATHER>
+__global__ void __launch_bounds__(kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, int M, int N, int K,
-                 GemmEpilogue ep, int* __restrict__ err) {
+                 GemmEpilogue ep, GatherB gb, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -111,9 +139,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      // GATHER: groups of B rows whose gather this thread has already seen complete (a bit per group, 128 groups)
+      unsigned long long seen[2] = {0ull, 0ull};
+      auto group_ready = [&](int row) -> bool {
+        const int g = row / kGatherGroupRows;
+        if (g < 128 && ((seen[g >> 6] >> (g & 63)) & 1ull)) return true;
+        const unsigned long long t0 = global_timer_ns();
+        while (ld_acquire_gpu(gb.counters + g) < gb.slices) {
+          __nanosleep(64);
+          if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) return false;
+        }
+        fence_proxy_async_all();    // the rows were written by ordinary stores; the TMA load below reads them through the async proxy
+        if (g < 128) seen[g >> 6] |= 1ull << (g & 63);
+        return true;
+      };
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          if (GATHER) {
+            // rows of the weight this stage reads: an N tile of 256 rows (forward) or 64 rows of the contraction dimension (dgrad)
+            if (B_MN == 0) {
+              if (kb == 0 && !group_ready(n0)) { ok = false; break; }
+            } else if (!group_ready(kb * BK)) { ok = false; break; }
+          }
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + s * kStageBytes;
           uint8_t* sb = sa + kABytes;
@@ -174,6 +222,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
       }
       if (!ok && lane == 0) { atomicCAS(err, 0, 2); *abort_flag = 1; }
+    }
+  } else if (GATHER && warp >= 10) {
+    // ------------------------------------------------------------------ gather warps (128 threads)
+    // item = (group, slice); CTA b takes items b, b + grid, ...; item i works on group i % n_groups, so the CTAs' first
+    // items cover every group at once and the group of a CTA's own first tile is among the first to complete
+    const int tid = threadIdx.x - 10 * 32;
+    const int n_groups = (gb.rows + kGatherGroupRows - 1) / kGatherGroupRows;
+    const int n_items = n_groups * gb.slices;
+    const int row_vecs = gb.ld >> 3;                       // 16-byte pieces per row
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const int g = item % n_groups, sl = item / n_groups;
+      const int g_lo = g * kGatherGroupRows, g_hi = min(gb.rows, g_lo + kGatherGroupRows);
+      const int per = (g_hi - g_lo + gb.slices - 1) / gb.slices;
+      const int r_lo = min(g_hi, g_lo + sl * per), r_hi = min(g_hi, r_lo + per);
+      const long n_vec = (long)(r_hi - r_lo) * row_vecs;
+      // 8 independent 16-byte loads per thread and round: enough bytes in flight per SM to cover the NVLink round trip
+      for (long v0 = (long)tid * 8; v0 < n_vec; v0 += (long)kGatherWarps * 32 * 8) {
+        uint4 buf[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long v = v0 + u;
+          if (v < n_vec) {
+            const int row = r_lo + (int)(v / row_vecs), piece = (int)(v % row_vecs);
+            const int owner = row / gb.chunk_rows;
+            const bf16* src = reinterpret_cast<const bf16*>(gb.ptrs[owner]) + (size_t)(row - owner * gb.chunk_rows) * gb.ld;
+            buf[u] = *(reinterpret_cast<const uint4*>(src) + piece);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const long v = v0 + u;
+          if (v < n_vec) {
+            const int row = r_lo + (int)(v / row_vecs), piece = (int)(v % row_vecs);
+            *(reinterpret_cast<uint4*>(gb.ws + (size_t)row * gb.ld) + piece) = buf[u];
+          }
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kGatherWarps * 32) : "memory");   // all 128 threads have stored and fenced
+      if (tid == 0) red_release_gpu_add(gb.counters + g, 1);
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -505,9 +593,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
 using namespace cb200;
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, bool GATHER = false>
 static int launch_gemm(const void* A, const void* B, int M, int N, int K, const GemmEpilogue& ep, int* err, int sms,
-                       cudaStream_t st) {
+                       cudaStream_t st, const GatherB& gb = GatherB{}) {
   CUtensorMap ta, tb;
   int rc;
   // A: K-major [M,K] -> dims {K, M}, box {64, 128};  MN-major stored [K,M] -> dims {M, K}, box {64, 64}
@@ -517,16 +605,17 @@ static int launch_gemm(const void* A, const void* B, int M, int N, int K, const 
   if (B_MN == 0) rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BN);
   else rc = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, BK);
   if (rc) return rc;
-  static bool attr_set[4] = {false, false, false, false};
-  auto kern = gemm_bf16_kernel<A_MN, B_MN>;
-  if (!attr_set[A_MN * 2 + B_MN]) {
+  static bool attr_set = false;      // one flag per template instantiation
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, GATHER>;
+  if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return 100 + (int)e;
-    attr_set[A_MN * 2 + B_MN] = true;
+    attr_set = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, kGemmThreads, kSmemBytes, st>>>(ta, tb, M, N, K, ep, err);
+  // with a gather every SM takes part (its gather warps work even when it has no tile): the grid is the whole machine
+  const int grid = GATHER ? sms : (tiles < sms ? tiles : sms);
+  kern<<<grid, kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), kSmemBytes, st>>>(ta, tb, M, N, K, ep, gb, err);
   return (int)cudaGetLastError();
 }
 
@@ -567,4 +656,33 @@ extern "C" int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M
   ep.hs.eps = eps;
   ep.L = 1;
   return launch_gemm<0, 0>(A, W, M, N, K, ep, err, sms, st);
+}
+
+// C = epilogue(A @ op(W)) where W [rows, ld] is sharded by rows over P ranks (rank r: shard_ptrs[r] holds rows [r * chunk_rows, ...)).
+// b_mn = 0: forward, C[M, rows] = A[M, ld] @ W^T; b_mn = 1: dgrad, C[M, ld] = A[M, rows] @ W. `ws` [rows, ld] receives the gathered
+// weight (and stays valid after the call); `counters`: ceil(rows / 256) ints of scratch.
+extern "C" int cb200_gemm_bf16_gather(const void* A, void* ws, void* C, int M, int rows, int ld, int b_mn, const int64_t* shard_ptrs,
+                                      int P, int chunk_rows, int* counters, const void* bias, int act, void* pre, int* err, int sms,
+                                      cudaStream_t st) {
+  if (P < 1 || P > 8 || chunk_rows < 1 || (long)chunk_rows * P < rows || ld % 8 != 0) return -31;
+  GemmEpilogue ep{};
+  ep.C = (bf16*)C;
+  ep.pre = (bf16*)pre;
+  ep.bias = (const bf16*)bias;
+  ep.act = act;
+  ep.L = 1;
+  GatherB gb{};
+  for (int i = 0; i < P; ++i) gb.ptrs[i] = shard_ptrs[i];
+  gb.ws = (bf16*)ws;
+  gb.counters = counters;
+  gb.P = P;
+  gb.chunk_rows = chunk_rows;
+  gb.rows = rows;
+  gb.ld = ld;
+  const int n_groups = (rows + kGatherGroupRows - 1) / kGatherGroupRows;
+  gb.slices = sms / n_groups < 1 ? 1 : (sms / n_groups > 16 ? 16 : sms / n_groups);
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)n_groups * sizeof(int), st);
+  if (e != cudaSuccess) return 400 + (int)e;
+  if (b_mn == 0) return launch_gemm<0, 0, true>(A, ws, M, rows, ld, ep, err, sms, st, gb);
+  return launch_gemm<0, 1, true>(A, ws, M, ld, rows, ep, err, sms, st, gb);
 }

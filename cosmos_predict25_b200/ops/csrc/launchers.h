@@ -38,6 +38,8 @@ void cb200_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t st);
 // gemm_tcgen05.cu
 int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn, const void* bias,
                     int act, void* pre, const void* resid, const float* gate, int L, int* err, int sms, cudaStream_t st);
+int cb200_gemm_bf16_gather(const void* A, void* ws, void* C, int M, int rows, int ld, int b_mn, const int64_t* shard_ptrs, int P,
+                           int chunk_rows, int* counters, const void* bias, int act, void* pre, int* err, int sms, cudaStream_t st);
 int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M, int N, int K, const int64_t* ptrs, int P, int rank, int S,
                                   const float* norm_w, const float* cosv, const float* sinv, float eps, int* err, int sms,
                                   cudaStream_t st);
@@ -68,6 +70,7 @@ void cb200_a2a_scatter_heads_peer(const void* x, const int64_t* out_ptrs, const 
                                   float* rstd, long n_rows, int S, int H, int HD, int rank, int P, int norm, float eps,
                                   cudaStream_t st);
 void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S, int H, int HD, int rank, int P, cudaStream_t st);
+void cb200_gather_slots_peer(const int64_t* shard_ptrs, const void* segs, int nseg, void* full, int P, cudaStream_t st);
 }
 
 extern "C" {

@@ -231,6 +231,18 @@ __global__ void __launch_bounds__(256) a2a_gather_seq_peer_kernel(PeerPtrs srcs,
   }
 }
 
+// All-gather of small parameters by peer reads: for every segment (full_offset, rank_stride, shard_offset, numel) and every
+// rank r, the chunk of `numel` bf16 values at shards[r] + shard_offset is copied to full + full_offset + r * rank_stride.
+// grid = (blocks, segments, ranks); every count is a multiple of 8 elements (16-byte vectors).
+__global__ void __launch_bounds__(256) gather_slots_peer_kernel(PeerPtrs shards, const Segment* __restrict__ segs, bf16* __restrict__ full) {
+  const Segment sg = segs[blockIdx.y];
+  const int r = blockIdx.z;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(reinterpret_cast<const bf16*>(shards.p[r]) + sg.shard_offset);
+  bf16x8* dst = reinterpret_cast<bf16x8*>(full + sg.full_offset + (long)r * sg.stride);
+  const long nvec = sg.numel >> 3;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace cb200
 
 using namespace cb200;
@@ -281,6 +293,11 @@ void cb200_a2a_scatter_heads_peer(const void* x, const int64_t* out_ptrs, const 
     if (norm) LAUNCH(64, true); else LAUNCH(64, false);
   }
 #undef LAUNCH
+}
+
+void cb200_gather_slots_peer(const int64_t* shard_ptrs, const void* segs, int nseg, void* full, int P, cudaStream_t st) {
+  dim3 grid(8, nseg, P);
+  gather_slots_peer_kernel<<<grid, 256, 0, st>>>(make_ptrs(shard_ptrs, P), (const Segment*)segs, (bf16*)full);
 }
 
 void cb200_a2a_gather_seq_peer(const int64_t* src_ptrs, void* out, long B, int S, int H, int HD, int rank, int P, cudaStream_t st) {

@@ -345,10 +345,61 @@ class _Linear(torch.autograd.Function):
         return dx, dw, db, None
 
 
+class _LinearGather(torch.autograd.Function):
+    """``_Linear`` for a weight whose rows are sharded over the ranks of the sharding group (``parallel/reshard_fsdp.py``): the
+    all-gather runs inside the forward GEMM and again inside the input-gradient GEMM (``gemm_bf16_gather``); ``w`` is the
+    parameter's view into the engine's workspace, which the kernel fills."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, act, info):
+        ops = native.load()
+        x2d = x.reshape(-1, x.shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        pre = torch.empty(x2d.shape[0], w.shape[0], dtype=x2d.dtype, device=x2d.device) if act == "gelu" else None
+        y = ops.gemm_bf16_gather(x2d, w, info.shard_ptrs, info.chunk_rows, info.counters, bias, _ACT_CODE[act], False, pre)
+        native.count_launch()
+        if act == "gelu":
+            ctx.save_for_backward(x2d, w, pre)
+        else:
+            ctx.save_for_backward(x2d, w)
+        ctx.act, ctx.has_bias, ctx.x_shape, ctx.info = act, bias is not None, x.shape, info
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        ops = native.load()
+        dy2d = dy.reshape(-1, dy.shape[-1])
+        if not dy2d.is_contiguous():
+            dy2d = dy2d.contiguous()
+        if ctx.act == "gelu":
+            x2d, w, pre = ctx.saved_tensors
+            dy2d = ops.gelu_bwd(dy2d, pre)
+            native.count_launch()
+        else:
+            x2d, w = ctx.saved_tensors
+        info = ctx.info
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # the workspace may hold another unit's weights by now: the input-gradient GEMM gathers the rows again
+            dx = ops.gemm_bf16_gather(dy2d, w, info.shard_ptrs, info.chunk_rows, info.counters, None, 0, True, None).view(ctx.x_shape)
+            native.count_launch()
+        if ctx.needs_input_grad[1]:
+            dw = gemm_nt(dy2d, x2d, None, "none", True, True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2d.float().sum(0).to(dy.dtype)
+        return dx, dw, db, None, None
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act: str = "none") -> torch.Tensor:
     """act(x @ w.T + bias); act in {none, gelu(erf)}."""
     x2d_shape_ok = x.shape[-1] == w.shape[1]
     assert x2d_shape_ok, (x.shape, w.shape)
+    info = getattr(w, "_cb200_gather", None)
+    if info is not None:
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and not native.forward_mode()):
+            raise RuntimeError("a resharded weight can only be used by the bf16 CUDA GEMM (its values live on other ranks)")
+        return _LinearGather.apply(x, w, bias, act, info)
     if x.is_cuda and _native_gemm_ok(x.reshape(-1, x.shape[-1]), w) and x.shape[-1] % 64 == 0 \
             and x.numel() // x.shape[-1] % 8 == 0:
         return _Linear.apply(x, w, bias, act)
@@ -365,7 +416,8 @@ def linear_gate_residual(h: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, 
     B, T, L, D = resid.shape
     needs_grad = torch.is_grad_enabled() and (h.requires_grad or w.requires_grad or resid.requires_grad or gate.requires_grad)
     h2d = h.reshape(-1, h.shape[-1])
-    if resid.is_cuda and not needs_grad and _native_gemm_ok(h2d, w) and h2d.shape[0] % 8 == 0:
+    if resid.is_cuda and not needs_grad and _native_gemm_ok(h2d, w) and h2d.shape[0] % 8 == 0 \
+            and getattr(w, "_cb200_gather", None) is None:
         out = native.load().gemm_bf16_gate_residual(h2d.contiguous(), w, resid.contiguous().view(-1, D),
                                                     gate.float().contiguous().view(B * T, D), L)
         native.count_launch()

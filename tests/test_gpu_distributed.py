@@ -264,6 +264,120 @@ def test_model_step_with_peer_engine_and_fused_context_parallel():
     _run("_model_step_peer")
 
 
+def _gather_gemm(rank, world):
+    """The all-gather fused into the GEMM against torch: forward (x @ W^T + bias, GELU) and input gradient (dy @ W), with the weight's
+    rows sharded over the two ranks; the workspace must hold the whole weight afterwards."""
+    from cosmos_predict25_b200.ops import native
+    from cosmos_predict25_b200.parallel.symm import SymmetricArena
+    ops = native.load()
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+    arena = SymmetricArena(64 << 20, g, dev)
+    for rows, K, M in ((1024, 512, 384), (2048, 2048, 1000), (768, 256, 64)):
+        torch.manual_seed(1)
+        W = (torch.randn(rows, K, device=dev) * 0.05).bfloat16()          # identical on both ranks
+        chunk = rows // world
+        shard = arena.alloc(chunk * K, torch.bfloat16)
+        shard.tensor.copy_(W[rank * chunk:(rank + 1) * chunk].reshape(-1))
+        torch.cuda.synchronize()
+        dist.barrier()
+        ws = torch.zeros(rows, K, device=dev, dtype=torch.bfloat16)
+        counters = torch.zeros((rows + 255) // 256, dtype=torch.int32, device=dev)
+        torch.manual_seed(2 + rank)
+        x = torch.randn(M, K, device=dev).bfloat16()
+        bias = torch.randn(rows, device=dev).bfloat16()
+        y = ops.gemm_bf16_gather(x, ws, shard.ptrs, chunk, counters, bias, 0, False, None)
+        torch.cuda.synchronize()
+        assert torch.equal(ws, W), "the workspace does not hold the gathered weight"
+        want = x.float() @ W.float().T + bias.float()
+        assert (y.float() - want).abs().max() <= 2e-2 * want.abs().max() + 1e-2
+        ws.zero_()
+        dy = torch.randn(M, rows, device=dev).bfloat16()
+        dx = ops.gemm_bf16_gather(dy, ws, shard.ptrs, chunk, counters, None, 0, True, None)
+        torch.cuda.synchronize()
+        assert torch.equal(ws, W)
+        want = dy.float() @ W.float()
+        assert (dx.float() - want).abs().max() <= 2e-2 * want.abs().max() + 1e-2
+        dist.barrier()
+    assert native_error(rank) == 0
+
+
+def test_all_gather_fused_into_gemm():
+    _run("_gather_gemm")
+
+
+def _reshard_engine_vs_resident(rank, world):
+    """Mini Video2World model trained two steps with the resharded engine (block parameters gathered inside their GEMMs) and with the
+    resident peer engine: same losses, same masters after the steps, fewer resident parameter bytes."""
+    from cosmos_predict25_b200.models.dit import dit_mini
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig
+    from cosmos_predict25_b200.trainer.trainer import Trainer, TrainerConfig
+    dev = torch.device("cuda", rank)
+    g = dist.group.WORLD
+    results = {}
+    for transport in ("peer", "peer_reshard"):
+        torch.manual_seed(0)
+        cfg = Video2WorldRFConfig(net=dit_mini(crossattn_proj_in_channels=2048, checkpoint_mode="save_attention", num_blocks=4),
+                                  state_t=4, sharding_transport=transport)
+        model = Video2WorldModelRectifiedFlow(cfg, device=dev, fsdp_group=g).train()
+        trainer = Trainer(TrainerConfig(output_dir=f"/tmp/cosmos_b200_rs{rank}", logging_iter=0), model, OptimizerConfig(lr=1e-4))
+        torch.manual_seed(5 + rank)
+        batch = {"latents": torch.randn(1, 16, 4, 32, 32), "t5_text_embeddings": torch.randn(1, 64, 2048).bfloat16(),
+                 "fps": torch.tensor([16.0]), "padding_mask": torch.zeros(1, 1, 32, 32), "num_conditional_frames": 1}
+        torch.manual_seed(9 + rank)
+        losses = [trainer.train_step(dict(batch)) for _ in range(2)]
+        model.engine.ctx.check()
+        masters = {k: v.clone() for k, v in model.engine.full_state_dict("master").items()}
+        resident = model.engine.resident_parameter_bytes() if hasattr(model.engine, "resident_parameter_bytes") else \
+            sum(u.full_numel for u in model.engine.units) * 2
+        results[transport] = (losses, masters, resident)
+        del trainer, model
+        torch.cuda.empty_cache()
+    (la, ma, ra), (lb, mb, rb) = results["peer"], results["peer_reshard"]
+    assert all(abs(a - b) <= 2e-3 * max(abs(a), 1.0) for a, b in zip(la, lb)), (la, lb)
+    # Adam normalises every gradient to about +-lr, so an element whose gradient is rounding noise (zero-initialised projections, the
+    # unordered dQ reductions of the attention backward) may move by lr in either direction: two steps of 1e-4 bound the difference
+    for k in ma:
+        assert (ma[k] - mb[k]).abs().max() <= 1e-3 * ma[k].abs().max() + 2.5e-4, k
+    # 4 blocks on 2 ranks: 4 resident blocks against 4 half shards + one workspace block
+    assert rb < 0.85 * ra, (ra, rb)
+
+
+def test_reshard_engine_matches_resident_engine():
+    _run("_reshard_engine_vs_resident")
+
+
+def _vae_kernel_decode_row_sharded(rank, world):
+    """Row-band decode on the convolution kernel (halo rows exchanged before every spatial convolution) against the same decode of
+    the whole frame on one rank."""
+    from cosmos_predict25_b200.models.vae_wan import Wan2pt1VAEInterface
+    torch.manual_seed(0)
+    dev = torch.device("cuda", rank)
+    tok = Wan2pt1VAEInterface(device=dev, dtype=torch.bfloat16, dim=32)
+    for p in tok.model.parameters():                      # same weights on both ranks
+        dist.broadcast(p.data, 0)
+    z = torch.randn(1, 16, 3, 16, 32, device=dev).bfloat16()
+    dist.broadcast(z, 0)
+    whole = tok.decode(z)
+    assert getattr(tok.model, "_dec_cl", None) is not None, "the kernel decoder did not serve the decode"
+    banded = tok.decode_parallel(z, dist.group.WORLD)
+    assert banded.shape == whole.shape
+    err = (banded.float() - whole.float()).abs().max().item()
+    assert err <= 2e-2 * whole.float().abs().max().item() + 1e-3, f"row-sharded decode differs by {err}"
+    assert native_error(rank) == 0
+
+
+def native_error(rank):
+    from cosmos_predict25_b200.ops import native
+    torch.cuda.synchronize()
+    return int(native.load().kernel_error(rank, True))
+
+
+def test_vae_kernel_decode_row_sharded_matches_whole_frame():
+    _run("_vae_kernel_decode_row_sharded")
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """A flag that nothing ever sets: the barrier kernel gives up after its bound (well under a second),
     records which peer was missing and returns; the context stays usable."""
