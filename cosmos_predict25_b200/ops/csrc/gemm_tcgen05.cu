@@ -71,7 +71,8 @@ struct GemmEpilogue {
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
 // Row-sharded B operand gathered inside the kernel (see the header comment).
-constexpr int kGatherWarps = 4;
+constexpr int kGatherWarps = 2;   // with the 10 GEMM warps: three warpgroups, 168 registers per thread (four more warps
+                                  // would cap the epilogue at 128 registers and make it spill)
 constexpr int kGatherGroupRows = 256;
 struct GatherB {
   int64_t ptrs[8];     // rank r: its rows [r * chunk_rows, ...) of the weight, row-major with `ld` elements per row
@@ -224,7 +225,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       if (!ok && lane == 0) { atomicCAS(err, 0, 2); *abort_flag = 1; }
     }
   } else if (GATHER && warp >= 10) {
-    // ------------------------------------------------------------------ gather warps (128 threads)
+    // ------------------------------------------------------------------ gather warps
     // item = (group, slice); CTA b takes items b, b + grid, ...; item i works on group i % n_groups, so the CTAs' first
     // items cover every group at once and the group of a CTA's own first tile is among the first to complete
     const int tid = threadIdx.x - 10 * 32;
@@ -237,11 +238,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int per = (g_hi - g_lo + gb.slices - 1) / gb.slices;
       const int r_lo = min(g_hi, g_lo + sl * per), r_hi = min(g_hi, r_lo + per);
       const long n_vec = (long)(r_hi - r_lo) * row_vecs;
-      // 8 independent 16-byte loads per thread and round: enough bytes in flight per SM to cover the NVLink round trip
-      for (long v0 = (long)tid * 8; v0 < n_vec; v0 += (long)kGatherWarps * 32 * 8) {
-        uint4 buf[8];
+      // 16 independent 16-byte loads per thread and round: enough bytes in flight per SM to cover the NVLink round trip
+      constexpr int kInFlight = 16;
+      for (long v0 = (long)tid * kInFlight; v0 < n_vec; v0 += (long)kGatherWarps * 32 * kInFlight) {
+        uint4 buf[kInFlight];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < kInFlight; ++u) {
           const long v = v0 + u;
           if (v < n_vec) {
             const int row = r_lo + (int)(v / row_vecs), piece = (int)(v % row_vecs);
@@ -251,7 +253,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
         }
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < kInFlight; ++u) {
           const long v = v0 + u;
           if (v < n_vec) {
             const int row = r_lo + (int)(v / row_vecs), piece = (int)(v % row_vecs);
@@ -260,7 +262,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
       __threadfence();
-      asm volatile("bar.sync 1, %0;" ::"n"(kGatherWarps * 32) : "memory");   // all 128 threads have stored and fenced
+      asm volatile("bar.sync 1, %0;" ::"n"(kGatherWarps * 32) : "memory");   // every gather thread has stored and fenced
       if (tid == 0) red_release_gpu_add(gb.counters + g, 1);
     }
   } else {

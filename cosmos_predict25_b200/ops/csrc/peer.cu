@@ -125,23 +125,41 @@ __global__ void __launch_bounds__(256) adamw_push_peer_kernel(
   const Segment sg = segs[blockIdx.y];
   const long nvec = sg.numel >> 3;
   const long dst0 = sg.full_offset + (long)rank * sg.stride;
+  const float decay = 1.f - lr * wd, step_size = lr / bc1, omb1 = 1.f - beta1, omb2 = 1.f - beta2;
+  const bool do_ema = ema != nullptr && ema_beta >= 0.f;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
-    const long s0 = sg.shard_offset + i * 8;
-    float o[8];
+    const long s0 = sg.shard_offset + i * 8;     // a multiple of 4 elements: 16-byte vector accesses throughout
+    float gq[8], pq[8], mq[8], vq[8], eq[8];
+    auto ld8 = [&](const float* src, float (&dst)[8]) {
+      const float4 a = *reinterpret_cast<const float4*>(src + s0), b = *reinterpret_cast<const float4*>(src + s0 + 4);
+      dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w; dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+    };
+    auto st8 = [&](float* dst, const float (&src)[8]) {
+      *reinterpret_cast<float4*>(dst + s0) = make_float4(src[0], src[1], src[2], src[3]);
+      *reinterpret_cast<float4*>(dst + s0 + 4) = make_float4(src[4], src[5], src[6], src[7]);
+    };
+    ld8(grad, gq);
+    ld8(master, pq);
+    ld8(m, mq);
+    ld8(v, vq);
+    if (do_ema) ld8(ema, eq);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float g = grad[s0 + j] * clip;
-      float p = master[s0 + j] * (1.f - lr * wd);
-      const float mi = beta1 * m[s0 + j] + (1.f - beta1) * g;
-      const float vi = beta2 * v[s0 + j] + (1.f - beta2) * g * g;
-      p -= (lr / bc1) * (mi / (sqrtf(vi) * rsqrt_bc2 + eps));
-      master[s0 + j] = p;
-      m[s0 + j] = mi;
-      v[s0 + j] = vi;
-      if (ema != nullptr && ema_beta >= 0.f) ema[s0 + j] = ema_beta * ema[s0 + j] + (1.f - ema_beta) * p;
-      o[j] = p;
+      const float g = gq[j] * clip;
+      float p = pq[j] * decay;
+      const float mi = beta1 * mq[j] + omb1 * g;
+      const float vi = beta2 * vq[j] + omb2 * g * g;
+      p -= step_size * (mi / (sqrtf(vi) * rsqrt_bc2 + eps));
+      pq[j] = p;
+      mq[j] = mi;
+      vq[j] = vi;
+      if (do_ema) eq[j] = ema_beta * eq[j] + (1.f - ema_beta) * p;
     }
-    const bf16x8 packed = pack8(o);
+    st8(master, pq);
+    st8(m, mq);
+    st8(v, vq);
+    if (do_ema) st8(ema, eq);
+    const bf16x8 packed = pack8(pq);
 #pragma unroll 1
     for (int q = 0; q < P; ++q) {
       const int r = (rank + q) % P;
