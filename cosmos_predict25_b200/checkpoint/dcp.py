@@ -7,7 +7,9 @@ distributed, so torch DCP can reshard on load. Parity target: ``DistributedCheck
 (cosmos_predict2/_src/predict2/checkpointer/dcp.py:16-732) incl. resume priority (``latest_checkpoint.txt``
 beats ``load_path``), ``load_training_state`` / ``only_load_scheduler_state`` / ``keys_not_to_resume`` /
 ``strict_resume``, ``load_ema_to_reg``, skipping of ``_extra_state`` keys, size-mismatch-tolerant loading and the
-asynchronous save path (staging to host memory, write in the background, success callback).
+asynchronous save path (staging to shared pinned host memory, write by a child process per rank whose group is separate from
+the trainer's - ``async_writer.py`` -, success callback; ``dcp_async_writer: "thread"`` keeps the write in a thread of the
+trainer's process instead).
 
 Unlike the reference the optimizer state contains the fp32 master weights, so resuming is bit-exact.
 """
@@ -167,6 +169,10 @@ class DistributedCheckpointer:
         self.load_ema_to_reg = c.get("load_ema_to_reg", False)
         self.allow_mismatched = c.get("dcp_allow_mismatched_size", False)
         self.async_mode = bool(c.get("dcp_async_mode_enabled", False)) and not disable_async
+        self.async_writer = str(c.get("dcp_async_writer", "process"))
+        if self.async_writer not in ("process", "thread"):
+            raise ValueError(f"dcp_async_writer must be 'process' or 'thread', got {self.async_writer!r}")
+        self._writer = None                       # ProcessWriter, created on the first asynchronous save
         self._bg: Optional[threading.Thread] = None
         self._bg_error: Optional[BaseException] = None
         self._cpu_group = None
@@ -328,7 +334,16 @@ class DistributedCheckpointer:
             self.callbacks.on_save_checkpoint_start(model, iteration)
         name = self.iter_name(iteration)
         sds = self._state_dicts(model, optimizer, scheduler, iteration)
-        if self.async_mode:
+        if self.async_mode and self.async_writer == "process":
+            self.finalize()  # one save in flight at a time
+            if self._writer is None:
+                from .async_writer import ProcessWriter
+                self._writer = ProcessWriter()
+            try:
+                self._writer.submit(sds, self.ckpt_dir, name)
+            except BaseException as e:  # a writer that cannot start must not end the training run
+                self._bg_error = e
+        elif self.async_mode:
             self.finalize()  # one save in flight at a time
             staged = {k: self._to_host(v) for k, v in sds.items()}
             if _dist_on() and self._cpu_group is None:
@@ -348,12 +363,38 @@ class DistributedCheckpointer:
             self.callbacks.on_save_checkpoint_end(model, iteration)
 
     def finalize(self) -> None:
+        """Wait for the save in flight; report (never raise) its failure. Collective when the job is distributed: a failure on
+        one rank makes every rank restart its writer, so the writers' group stays in step."""
+        if self._writer is not None:
+            msg = self._writer.wait()
+            failed = msg is not None and msg[1] is not None
+            if _dist_on() and (msg is not None or self._bg_error is not None):
+                flags = [None] * dist.get_world_size()
+                dist.all_gather_object(flags, bool(failed or self._bg_error is not None))
+                if any(flags) and not failed:
+                    self._writer.close()
+                    failed_elsewhere = True
+                else:
+                    failed_elsewhere = False
+                if failed_elsewhere and self._bg_error is None:
+                    self._bg_error = RuntimeError("checkpoint save failed on another rank")
+            if failed:
+                self._bg_error = RuntimeError(msg[1])
+            elif msg is not None and self._bg_error is None and self.callbacks is not None:
+                self.callbacks.on_save_checkpoint_success(iteration=int(msg[0].split("_")[1]), elapsed_time=msg[2])
         if self._bg is not None:
             self._bg.join()
             self._bg = None
         if self._bg_error is not None:
             e, self._bg_error = self._bg_error, None
             log.error(f"asynchronous checkpoint save failed: {e!r}")
+
+    def close(self) -> None:
+        """Finish the save in flight and end the writer process."""
+        self.finalize()
+        if self._writer is not None:
+            self._writer.close()
+            self._writer = None
 
 
 def convert_distcp_to_pt(dcp_model_dir: str, out_dir: str) -> Dict[str, str]:

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import List, Optional, Tuple
+from typing import Sequence, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -165,8 +165,14 @@ class TimestepEmbedding(nn.Module):
 
     def forward(self, sample):
         w1, w2 = self.linear_1.weight, self.linear_2.weight
-        h = F.linear(sample, w1.to(sample.dtype), None if self.linear_1.bias is None else self.linear_1.bias.to(sample.dtype))
-        emb = F.linear(self.activation(h), w2.to(sample.dtype))
+        if self.linear_1.bias is None and sample.is_cuda and type(self.linear_1) is nn.Linear and type(self.linear_2) is nn.Linear:
+            # two launches of the few-row fp32 GEMM kernel; the SiLU is applied while the second one loads its input
+            lead = sample.shape[:-1]
+            h = ops.skinny_linears(sample.reshape(-1, sample.shape[-1]), [w1])
+            emb = ops.skinny_linears(h, [w2], silu=True)[0].view(*lead, -1).to(sample.dtype)
+        else:
+            h = F.linear(sample, w1.to(sample.dtype), None if self.linear_1.bias is None else self.linear_1.bias.to(sample.dtype))
+            emb = F.linear(self.activation(h), w2.to(sample.dtype))
         if self.use_adaln_lora:
             return sample, emb
         return emb, None
@@ -368,6 +374,27 @@ def _run_adaln(mlp: nn.Sequential, emb: torch.Tensor, lora: Optional[torch.Tenso
     return h
 
 
+def _plain_adaln(mlp: nn.Sequential) -> bool:
+    return all(type(m) in (nn.Linear, nn.SiLU) for m in mlp)
+
+
+def run_adaln_many(mlps: Sequence[nn.Sequential], emb: torch.Tensor, lora: Optional[torch.Tensor], fp32: bool) -> torch.Tensor:
+    """The modulation MLPs ``mlps`` (same shapes) on one embedding in two launches of the few-row fp32 GEMM kernel:
+    SiLU(emb) @ W1[z]^T for every z, then @ W2[z]^T + the shared LoRA term. Returns [Z, *emb.shape[:-1], n * D]
+    (minimal_v4_dit.py:1131-1162)."""
+    lead = emb.shape[:-1]
+    e2 = emb.reshape(-1, emb.shape[-1])
+    l2 = None if lora is None else lora.reshape(-1, lora.shape[-1])
+    lins = [[m for m in mlp if isinstance(m, nn.Linear)] for mlp in mlps]
+    if len(lins[0]) == 2:
+        h = ops.skinny_linears(e2, [l[0].weight for l in lins], silu=True)
+        out = ops.skinny_linears(h, [l[1].weight for l in lins], add=l2)
+    else:
+        out = ops.skinny_linears(e2, [l[0].weight for l in lins], silu=True, add=l2)
+    out = out.view(len(mlps), *lead, out.shape[-1])
+    return out if fp32 else out.to(emb.dtype)
+
+
 class Block(nn.Module):
     """x += g1*SA(LNmod(x)); x += g2*CA(LNmod(x), ctx); x += g3*MLP(LNmod(x)) (minimal_v4_dit.py:993-1242)."""
 
@@ -382,11 +409,14 @@ class Block(nn.Module):
         self.adaln_modulation_cross_attn = _adaln_mlp(D, cfg.adaln_lora_dim, 3, cfg.use_adaln_lora)
         self.adaln_modulation_mlp = _adaln_mlp(D, cfg.adaln_lora_dim, 3, cfg.use_adaln_lora)
 
+    def adaln_mlps(self) -> Tuple[nn.Sequential, nn.Sequential, nn.Sequential]:
+        return self.adaln_modulation_self_attn, self.adaln_modulation_cross_attn, self.adaln_modulation_mlp
+
     def init_weights(self):
         self.self_attn.init_weights()
         self.cross_attn.init_weights()
         self.mlp.init_weights()
-        for mlp in (self.adaln_modulation_self_attn, self.adaln_modulation_cross_attn, self.adaln_modulation_mlp):
+        for mlp in self.adaln_mlps():
             lins = [m for m in mlp if isinstance(m, nn.Linear)]
             for lin in lins[:-1]:
                 _trunc_normal_(lin.weight, 1.0 / math.sqrt(lin.in_features))
@@ -394,15 +424,21 @@ class Block(nn.Module):
 
     def forward(self, x: torch.Tensor, emb: torch.Tensor, context: torch.Tensor, rope: Optional[torch.Tensor],
                 lora: Optional[torch.Tensor], extra_pos: Optional[torch.Tensor] = None,
-                cross_kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
-        """x: [B,T,L,D] (L = H*W tokens of one latent frame); emb [B,T,D]; lora [B,T,3D]."""
+                cross_kv: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, mods: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: [B,T,L,D] (L = H*W tokens of one latent frame); emb [B,T,D]; lora [B,T,3D]; ``mods`` [3,B,T,3D]: the block's three
+        modulation outputs when the caller has computed those of all blocks in one launch."""
         if extra_pos is not None:
             x = x + extra_pos
         fp32 = self.cfg.use_wan_fp32_strategy
         B, T, L, D = x.shape
-        sh1, sc1, g1 = _run_adaln(self.adaln_modulation_self_attn, emb, lora, fp32).chunk(3, dim=-1)
-        sh2, sc2, g2 = _run_adaln(self.adaln_modulation_cross_attn, emb, lora, fp32).chunk(3, dim=-1)
-        sh3, sc3, g3 = _run_adaln(self.adaln_modulation_mlp, emb, lora, fp32).chunk(3, dim=-1)
+        if mods is None and emb.is_cuda and all(_plain_adaln(m) for m in self.adaln_mlps()):
+            mods = run_adaln_many(self.adaln_mlps(), emb, lora, fp32)
+        if mods is not None:
+            (sh1, sc1, g1), (sh2, sc2, g2), (sh3, sc3, g3) = (mods[i].chunk(3, dim=-1) for i in range(3))
+        else:
+            sh1, sc1, g1 = _run_adaln(self.adaln_modulation_self_attn, emb, lora, fp32).chunk(3, dim=-1)
+            sh2, sc2, g2 = _run_adaln(self.adaln_modulation_cross_attn, emb, lora, fp32).chunk(3, dim=-1)
+            sh3, sc3, g3 = _run_adaln(self.adaln_modulation_mlp, emb, lora, fp32).chunk(3, dim=-1)
 
         h = ops.ln_modulate(x, sh1, sc1)
         o = self.self_attn(h.view(B, T * L, D), None, rope, return_pre_proj=True)
@@ -437,7 +473,10 @@ class FinalLayer(nn.Module):
     def forward(self, x, emb, lora):
         D = self.cfg.model_channels
         lora2 = lora[..., : 2 * D] if lora is not None else None
-        shift, scale = _run_adaln(self.adaln_modulation, emb, lora2, self.cfg.use_wan_fp32_strategy).chunk(2, dim=-1)
+        if emb.is_cuda and _plain_adaln(self.adaln_modulation):
+            shift, scale = run_adaln_many([self.adaln_modulation], emb, lora2, self.cfg.use_wan_fp32_strategy)[0].chunk(2, dim=-1)
+        else:
+            shift, scale = _run_adaln(self.adaln_modulation, emb, lora2, self.cfg.use_wan_fp32_strategy).chunk(2, dim=-1)
         h = ops.ln_modulate(x, shift, scale)
         return ops.linear(h, self.linear.weight)
 
@@ -596,9 +635,15 @@ class CosmosDiT(nn.Module):
         for block in self.blocks:
             block.self_attn.video_size = (T * cp_size, H, W)
 
+        all_mods = None
+        if (not torch.is_grad_enabled() and emb.is_cuda and not getattr(self, "_params_sharded", False)
+                and all(_plain_adaln(m) for b in self.blocks for m in b.adaln_mlps())):
+            # the modulation vectors depend only on the timestep embedding: all 3 x L MLPs in two launches, once per forward
+            all_mods = run_adaln_many([m for b in self.blocks for m in b.adaln_mlps()], emb, lora, cfg.use_wan_fp32_strategy)
         for i, block in enumerate(self.blocks):
             kv = cross_kv[i] if cross_kv else None
-            x = run_block(block, cfg.checkpoint_mode if self.training else "none", x, emb, context, rope, lora, extra, kv)
+            mods = None if all_mods is None else all_mods[3 * i: 3 * i + 3]
+            x = run_block(block, cfg.checkpoint_mode if self.training else "none", x, emb, context, rope, lora, extra, kv, mods)
         out = self.final_layer(x, emb, lora).view(B, T, H, W, -1)
         return self.unpatchify(out)
 

@@ -342,6 +342,51 @@ void gemm_scatter_heads_peer(const Tensor& x, const Tensor& w, c10::ArrayRef<int
   TORCH_CHECK(rc == 0, "tcgen05 GEMM (head-scatter epilogue) launch failed with code ", rc);
 }
 
+// Z small fp32 GEMMs in one launch (skinny.cu). ``a``: fp32 storage addressed as a[z*a_z + r*a_r + k*a_k]; B: either ``b_ptrs``
+// (int64 device tensor with one base address per problem) or the tensor ``b`` addressed as b[z*b_z + n*b_n + k*b_k], bf16 or
+// fp32; result [Z, R, N] contiguous in ``out_bf16 ? bf16 : fp32``; with ``ksplit`` > 1 the result is [Z * ksplit, R, N] fp32:
+// partial sums over ``ksplit`` ranges of k, to be added by the caller (few tiles, long reduction: more CTAs in flight).
+Tensor skinny_bgemm(const Tensor& a, int64_t a_z, int64_t a_r, int64_t a_k, const c10::optional<Tensor>& b_ptrs,
+                    const c10::optional<Tensor>& b, int64_t b_z, int64_t b_n, int64_t b_k, bool b_bf16,
+                    const c10::optional<Tensor>& add, int64_t add_cols, int64_t Z, int64_t R, int64_t N, int64_t K, bool silu_a,
+                    bool silu_b, bool out_bf16, int64_t ksplit) {
+  check_f32(a, "a");
+  c10::cuda::CUDAGuard g(a.device());
+  TORCH_CHECK(Z > 0 && R > 0 && N > 0 && K > 0 && ksplit >= 1 && Z * ksplit <= 65535, "skinny_bgemm: bad problem size");
+  TORCH_CHECK(ksplit == 1 || !out_bf16, "skinny_bgemm: partial sums (ksplit > 1) are fp32");
+  TORCH_CHECK(a_z >= 0 && a_r >= 0 && a_k >= 0 && b_z >= 0 && b_n >= 0 && b_k >= 0, "skinny_bgemm: strides must not be negative");
+  TORCH_CHECK((Z - 1) * a_z + (R - 1) * a_r + (K - 1) * a_k < a.numel(), "skinny_bgemm: A strides reach past the tensor");
+  TORCH_CHECK(b_ptrs.has_value() != b.has_value(), "skinny_bgemm: give exactly one of b_ptrs and b");
+  const long long* bp = nullptr;
+  const void* bb = nullptr;
+  if (b_ptrs.has_value()) {
+    TORCH_CHECK(b_ptrs->is_cuda() && b_ptrs->scalar_type() == at::kLong && b_ptrs->is_contiguous() && b_ptrs->numel() >= Z,
+                "b_ptrs must be a contiguous int64 CUDA tensor with one entry per problem");
+    bp = reinterpret_cast<const long long*>(b_ptrs->data_ptr<int64_t>());
+  } else {
+    TORCH_CHECK(b->is_cuda() && b->is_contiguous() && b->scalar_type() == (b_bf16 ? at::kBFloat16 : at::kFloat),
+                "b must be a contiguous CUDA tensor of the stated dtype");
+    TORCH_CHECK((Z - 1) * b_z + (N - 1) * b_n + (K - 1) * b_k < b->numel(), "skinny_bgemm: B strides reach past the tensor");
+    bb = b->data_ptr();
+  }
+  const float* addp = nullptr;
+  int ld_add = 0;
+  if (add.has_value()) {
+    check_f32(*add, "add");
+    TORCH_CHECK(add->dim() == 2 && add->size(0) == R && add_cols >= 0 && add_cols <= add->size(1) && add_cols <= N,
+                "add must be [R, >= add_cols] with add_cols <= N");
+    addp = add->data_ptr<float>();
+    ld_add = (int)add->size(1);
+  }
+  Tensor c = at::empty({Z * ksplit, R, N}, a.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  const int rc = cb200_skinny_bgemm(a.data_ptr<float>(), a_z, a_r, a_k, bp, bb, b_z, b_n, b_k, b_bf16 ? 1 : 0, c.data_ptr(), R * N,
+                                    (int)N, out_bf16 ? 1 : 0, addp, ld_add, (int)add_cols, (int)Z, (int)R, (int)N, (int)K,
+                                    silu_a ? 1 : 0, silu_b ? 1 : 0, (int)ksplit, stream());
+  TORCH_CHECK(rc == 0, "skinny_bgemm launch refused with code ", rc);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return c;
+}
+
 int64_t kernel_error(int64_t device, bool clear) {
   int v = 0;
   int* w = error_word((int)device);
@@ -380,6 +425,8 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor");
   m.def("gemm_scatter_heads_peer(Tensor x, Tensor w, int[] out_ptrs, Tensor? norm_w, Tensor? cos, Tensor? sin, int S, int rank, "
         "float eps) -> ()", &gemm_scatter_heads_peer);
+  m.def("skinny_bgemm(Tensor a, int a_z, int a_r, int a_k, Tensor? b_ptrs, Tensor? b, int b_z, int b_n, int b_k, bool b_bf16, "
+        "Tensor? add, int add_cols, int Z, int R, int N, int K, bool silu_a, bool silu_b, bool out_bf16, int ksplit) -> Tensor", &skinny_bgemm);
   m.def("kernel_error(int device, bool clear) -> int", &kernel_error);
   register_attention_ops(m);
   register_peer_ops(m);

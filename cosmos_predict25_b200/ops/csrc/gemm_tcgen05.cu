@@ -240,11 +240,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const long n_vec = (long)(r_hi - r_lo) * row_vecs;
       // 16 independent 16-byte loads per thread and round: enough bytes in flight per SM to cover the NVLink round trip
       constexpr int kInFlight = 16;
-      for (long v0 = (long)tid * kInFlight; v0 < n_vec; v0 += (long)kGatherWarps * 32 * kInFlight) {
+      // consecutive lanes take consecutive 16-byte pieces: one warp load is 512 contiguous bytes on the link
+      constexpr int kGatherThreads = kGatherWarps * 32;
+      for (long v0 = tid; v0 < n_vec; v0 += (long)kGatherThreads * kInFlight) {
         uint4 buf[kInFlight];
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
-          const long v = v0 + u;
+          const long v = v0 + (long)u * kGatherThreads;
           if (v < n_vec) {
             const int row = r_lo + (int)(v / row_vecs), piece = (int)(v % row_vecs);
             const int owner = row / gb.chunk_rows;
@@ -254,7 +256,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
-          const long v = v0 + u;
+          const long v = v0 + (long)u * kGatherThreads;
           if (v < n_vec) {
             const int row = r_lo + (int)(v / row_vecs), piece = (int)(v % row_vecs);
             *(reinterpret_cast<uint4*>(gb.ws + (size_t)row * gb.ld) + piece) = buf[u];

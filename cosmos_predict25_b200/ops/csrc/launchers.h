@@ -35,6 +35,12 @@ void cb200_adamw_ema_shard(float* master, const float* grad, float* m, float* v,
                            float ema_beta, long n, cudaStream_t st);
 void cb200_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t st);
 
+// skinny.cu: Z small fp32 GEMMs C[z][r,n] = sum_k fa(A[z][r,k]) fb(B[z][n,k]) (+ add[r,n], n < add_cols) with element strides;
+// ksplit > 1: C is [Z * ksplit, R, N] partial sums over ranges of k (the caller adds them)
+int cb200_skinny_bgemm(const float* a, long a_z, long a_r, long a_k, const long long* b_ptrs, const void* b_base, long b_z, long b_n,
+                       long b_k, int b_is_bf16, void* c, long c_z, int ldc, int c_is_bf16, const float* add, int ld_add, int add_cols,
+                       int Z, int R, int N, int K, int silu_a, int silu_b, int ksplit, cudaStream_t st);
+
 // gemm_tcgen05.cu
 int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn, const void* bias,
                     int act, void* pre, const void* resid, const float* gate, int L, int* err, int sms, cudaStream_t st);

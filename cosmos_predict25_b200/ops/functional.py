@@ -12,7 +12,7 @@ from __future__ import annotations
 import math
 import os
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -428,6 +428,116 @@ def linear_gate_residual(h: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, 
 # --------------------------------------------------------------------------------------
 # small fused elementwise ops used by sampling
 # --------------------------------------------------------------------------------------
+# --------------------------------------------------------------------------------------
+# Few-row fp32 linears, many weights per launch (AdaLN-LoRA modulation MLPs, timestep embedder)
+# --------------------------------------------------------------------------------------
+_ptr_tables: dict = {}
+
+
+def _ptr_table(weights: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Device tensor with the base address of every weight; cached per address tuple (parameter storages do not move)."""
+    key = tuple(w.data_ptr() for w in weights)
+    t = _ptr_tables.get(key)
+    if t is None:
+        if len(_ptr_tables) > 4096:
+            _ptr_tables.clear()
+        t = torch.tensor(key, dtype=torch.int64, device=weights[0].device)
+        _ptr_tables[key] = t
+    return t
+
+
+def _skinny_ok(a: torch.Tensor, weights: Sequence[torch.Tensor]) -> bool:
+    if native.forward_mode() or settings.gemm != "native" or not a.is_cuda or not native.available():
+        return False
+    w0 = weights[0]
+    return (w0.dtype in (torch.bfloat16, torch.float32) and all(w.shape == w0.shape and w.dtype == w0.dtype and w.is_contiguous()
+                                                                   for w in weights) and hasattr(native.load(), "skinny_bgemm"))
+
+
+def _skinny_split(Z: int, R: int, N: int, K: int) -> int:
+    """Ranges of the reduction per problem: enough CTAs to fill the GPU when the output is a few tiles and K is long."""
+    tiles = Z * ((R + 63) // 64) * ((N + 63) // 64)
+    return max(1, min((K + 255) // 256, 296 // max(tiles, 1), 65535 // Z))
+
+
+def _skinny_call(ops, Z, R, N, K, *args):
+    """args = the operator's arguments up to ``out_bf16``; splits long reductions and adds the partial sums."""
+    out_bf16 = args[-1]
+    S = 1 if out_bf16 else _skinny_split(Z, R, N, K)
+    out = ops.skinny_bgemm(*args, S)
+    native.count_launch()
+    return out if S == 1 else out.view(Z, S, R, N).sum(1)
+
+
+class _SkinnyLinears(torch.autograd.Function):
+    """``out[z] = f(a[z]) @ W[z]^T (+ add)`` for Z weights of one shape in one launch; ``a`` is [R, K] (shared by every z) or
+    [Z, R, K]; f is identity or SiLU. fp32 accumulate, fp32 result. Backward: two more launches of the same kernel."""
+
+    @staticmethod
+    def forward(ctx, a, add, silu, *weights):
+        ops = native.load()
+        Z = len(weights)
+        N, K = weights[0].shape
+        shared = a.dim() == 2
+        R = a.shape[-2]
+        a32 = a.float().contiguous()
+        add32 = None if add is None else add.float().contiguous()
+        bf16 = weights[0].dtype == torch.bfloat16
+        out = _skinny_call(ops, Z, R, N, K, a32, 0 if shared else R * K, K, 1, _ptr_table(weights), None, 0, K, 1, bf16, add32,
+                           0 if add32 is None else add32.shape[1], Z, R, N, K, bool(silu), False, False)
+        ctx.save_for_backward(a32, *weights)
+        ctx.meta = (Z, R, N, K, shared, bool(silu), bf16, None if add is None else (add.shape, add.dtype), a.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ops = native.load()
+        a32, *weights = ctx.saved_tensors
+        Z, R, N, K, shared, silu, bf16, add_meta, a_dtype = ctx.meta
+        dout = dout.float().contiguous()
+        da = dadd = None
+        if ctx.needs_input_grad[0]:
+            # da[z][r, k] = sum_n dout[z][r, n] W[z][n, k]: the weight is read along its rows (k contiguous in the output)
+            da = _skinny_call(ops, Z, R, K, N, dout, R * N, N, 1, _ptr_table(weights), None, 0, 1, K, bf16, None, 0, Z, R, K, N, False,
+                              False, False)
+            if silu:
+                sg = torch.sigmoid(a32)
+                da = da * (sg * (1 + a32 * (1 - sg)))
+            if shared:
+                da = da.sum(0)
+            da = da.to(a_dtype)
+        if add_meta is not None and ctx.needs_input_grad[1]:
+            dadd = dout.sum(0)
+            if add_meta[0][1] < N:
+                dadd = dadd[:, : add_meta[0][1]]
+            dadd = dadd.to(add_meta[1])
+        dws: Tuple = (None,) * Z
+        if any(ctx.needs_input_grad[3:]):
+            # dW[z][n, k] = sum_r dout[z][r, n] f(a[z][r, k]): the reduction runs over the few rows
+            dw = _skinny_call(ops, Z, N, K, R, dout, R * N, 1, N, None, a32, 0 if shared else R * K, 1, K, False, None, 0, Z, N, K, R, False,
+                              silu, bf16)
+            dws = tuple(dw[z] for z in range(Z))
+        return (da, dadd, None) + dws
+
+
+def skinny_linears(a: torch.Tensor, weights: Sequence[torch.Tensor], silu: bool = False,
+                   add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``stack_z( f(a[z]) @ weights[z]^T ) + add`` in fp32 -> [Z, R, N]. ``a``: [R, K] shared by all weights or [Z, R, K];
+    ``add``: [R, <= N] added to the leading columns of every z (the shared AdaLN-LoRA term)."""
+    if _skinny_ok(a, weights):
+        return _SkinnyLinears.apply(a, add, silu, *weights)
+    h = a.float()
+    if silu:
+        h = torch.nn.functional.silu(h)
+    outs = []
+    for z, w in enumerate(weights):
+        o = torch.nn.functional.linear(h if h.dim() == 2 else h[z], w.float())
+        if add is not None:
+            o = torch.cat([o[:, : add.shape[1]] + add.float(), o[:, add.shape[1]:]], dim=1) if add.shape[1] < o.shape[1] else o + add.float()
+        outs.append(o)
+    return torch.stack(outs)
+
+
 def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, guidance: float) -> torch.Tensor:
     if cond.is_cuda and native.available() and hasattr(native.load(), "cfg_combine"):
         native.count_launch()

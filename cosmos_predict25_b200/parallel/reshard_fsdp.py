@@ -49,7 +49,9 @@ class GatherInfo:
 class ReshardFlatUnit(PeerFlatUnit):
     """A unit whose full-layout parameter buffer is the engine's shared workspace."""
 
-    def __init__(self, *args, workspace_alloc=None, **kwargs):
+    def __init__(self, *args, workspace_alloc=None, gather_ids=None, **kwargs):
+        """``gather_ids``: ids of the parameters whose consumer is ``ops.functional.linear`` (the only caller that can bring a
+        weight in through the gather GEMM); every other parameter is gathered when the unit is entered."""
         self._workspace_alloc = workspace_alloc
         self._alloc_calls = 0
         super().__init__(*args, **kwargs)
@@ -62,7 +64,8 @@ class ReshardFlatUnit(PeerFlatUnit):
         small_rows = []
         self.big_slots = []
         for s in self.slots:
-            big = len(s.shape) == 2 and s.param.numel() >= BIG_NUMEL and s.rows % (8 * P) == 0 and s.cols % 64 == 0
+            big = (len(s.shape) == 2 and s.param.numel() >= BIG_NUMEL and s.rows % (8 * P) == 0 and s.cols % 64 == 0
+                   and (gather_ids is None or id(s.param) in gather_ids))
             if big:
                 self.big_slots.append(s)
                 n_groups = (s.rows + 255) // 256
@@ -108,6 +111,7 @@ class ReshardEngine(PeerShardedEngine):
         super().__init__(net, group=group, compute_dtype=compute_dtype, use_ema=use_ema, transport=transport, units=unit_modules,
                          device=device, grad_divide=grad_divide, replicate_group=replicate_group)
         self._current: Optional[ReshardFlatUnit] = None
+        net._params_sharded = True            # code that reads several blocks' parameters in one kernel must not run
         for u in self.units:
             if isinstance(u, ReshardFlatUnit):
                 mod = u.module
@@ -126,9 +130,13 @@ class ReshardEngine(PeerShardedEngine):
     def _make_unit(self, name, named, use_ema, alloc):
         idx = int(name[4:]) if name.startswith("unit") else -1
         if idx in self._reshard_ids:
+            from ..models.dit import FusedLinear
+            mod = self._unit_modules[idx]
+            gather_ids = {id(m.weight) for m in mod.modules() if isinstance(m, FusedLinear)}
             u = ReshardFlatUnit(name, named, self.group, self.compute_dtype, use_ema, self.device,
-                                peer_alloc=lambda n, dt: self.arena.alloc(n, dt), workspace_alloc=self._workspace_alloc)
-            u.module = self._unit_modules[idx]
+                                peer_alloc=lambda n, dt: self.arena.alloc(n, dt), workspace_alloc=self._workspace_alloc,
+                                gather_ids=gather_ids)
+            u.module = mod
             return u
         return super()._make_unit(name, named, use_ema, alloc)
 

@@ -143,7 +143,7 @@ class Trainer:
         if self.checkpointer is not None and cfg.save_iter:
             if self.iteration % cfg.save_iter != 0:  # otherwise the loop has just written this iteration
                 self._save()
-            self.checkpointer.finalize()
+            getattr(self.checkpointer, "close", self.checkpointer.finalize)()   # waits for the save in flight, ends a writer process
         self.check_health()
         self.callbacks.on_train_end(self.model, iteration=self.iteration)
         if dist.is_available() and dist.is_initialized():

@@ -277,3 +277,22 @@ def test_state_dict_roundtrip_with_ema_prefixes():
     m2.load_state_dict(sd, strict=False)
     for (n1, p1), (n2, p2) in zip(m.net.named_parameters(), m2.net.named_parameters()):
         assert torch.equal(p1, p2), n1
+
+
+def test_batched_adaln_equals_per_mlp_modulation():
+    """All modulation MLPs in one call (the few-row batched GEMM front-end; its torch fallback on CPU) equal the per-MLP path,
+    with and without the LoRA bottleneck, for the 3-chunk block MLPs and the 2-chunk final layer; gradients reach every weight."""
+    from cosmos_predict25_b200.models.dit import _adaln_mlp, _run_adaln, run_adaln_many
+    torch.manual_seed(0)
+    D, r = 64, 16
+    emb = torch.randn(2, 3, D)
+    for use_lora, chunks in ((True, 3), (False, 3), (True, 2)):
+        mlps = [_adaln_mlp(D, r, chunks, use_lora) for _ in range(4)]
+        lora = torch.randn(2, 3, chunks * D, requires_grad=True) if use_lora else None
+        many = run_adaln_many(mlps, emb, lora, True)
+        assert many.shape == (4, 2, 3, chunks * D)
+        for z, mlp in enumerate(mlps):
+            assert torch.allclose(many[z], _run_adaln(mlp, emb, lora, True), atol=1e-5)
+        many.square().sum().backward()
+        assert all(p.grad is not None and p.grad.abs().sum() > 0 for m in mlps for p in m.parameters())
+        assert lora is None or lora.grad is not None

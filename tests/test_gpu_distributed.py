@@ -313,9 +313,13 @@ def _reshard_engine_vs_resident(rank, world):
     from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
     from cosmos_predict25_b200.trainer.optim import OptimizerConfig
     from cosmos_predict25_b200.trainer.trainer import Trainer, TrainerConfig
+    from cosmos_predict25_b200.parallel import reshard_fsdp
     dev = torch.device("cuda", rank)
     g = dist.group.WORLD
     results = {}
+    # a low size bar makes the mini network's projections take the in-GEMM gather, and shows that matrices of the same size whose
+    # consumer is not the GEMM front-end (the AdaLN modulation weights) are still gathered when the block is entered
+    reshard_fsdp.BIG_NUMEL = 1 << 14
     for transport in ("peer", "peer_reshard"):
         torch.manual_seed(0)
         cfg = Video2WorldRFConfig(net=dit_mini(crossattn_proj_in_channels=2048, checkpoint_mode="save_attention", num_blocks=4),

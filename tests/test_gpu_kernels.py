@@ -337,6 +337,49 @@ def test_attention_autograd():
     _close(v.grad, vr.grad, 3e-2, 3e-2, "dv")
 
 
+@pytest.mark.parametrize("Z,R,K,N,wdtype,shared,silu,add_cols", [
+    (3, 24, 2048, 256, torch.bfloat16, True, True, 0),         # AdaLN-LoRA first stage of one block
+    (3, 24, 256, 6144, torch.bfloat16, False, False, 6144),    # second stage + shared LoRA term
+    (1, 48, 256, 4096, torch.bfloat16, False, False, 4096),    # final layer: 2 chunks
+    (5, 7, 100, 70, torch.float32, True, False, 33),           # ragged everything, fp32 weights, partial add
+    (2, 130, 96, 200, torch.bfloat16, False, True, 0),         # more rows than one tile
+])
+def test_skinny_linears_fwd_bwd(Z, R, K, N, wdtype, shared, silu, add_cols):
+    """The few-row batched fp32 GEMM (forward, input gradient, weight gradient, shared-term gradient) against torch fp32."""
+    torch.manual_seed(0)
+    ws = [(torch.randn(N, K, device=DEV) / math.sqrt(K)).to(wdtype).requires_grad_(True) for _ in range(Z)]
+    a = torch.randn(*((R, K) if shared else (Z, R, K)), device=DEV).requires_grad_(True)
+    add = torch.randn(R, add_cols, device=DEV).requires_grad_(True) if add_cols else None
+    before = native.launches()
+    out = F_ops.skinny_linears(a, ws, silu=silu, add=add)
+    assert native.launches() == before + 1, "the skinny GEMM kernel did not serve the call"
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ar = a.detach().clone().requires_grad_(True)
+    wr = [w.detach().float().requires_grad_(True) for w in ws]
+    addr = add.detach().clone().requires_grad_(True) if add is not None else None
+    h = torch.nn.functional.silu(ar) if silu else ar
+    outs = []
+    for z in range(Z):
+        o = (h if shared else h[z]) @ wr[z].t()
+        if addr is not None:
+            o = torch.cat([o[:, :add_cols] + addr, o[:, add_cols:]], 1)
+        outs.append(o)
+    want = torch.stack(outs)
+    want.backward(dout)
+    assert out.dtype == torch.float32
+    _close(out, want, 1e-4, 1e-4, "out")
+    _close(a.grad, ar.grad, 1e-3, 1e-3, "da")
+    gtol = 2e-2 if wdtype == torch.bfloat16 else 1e-4
+    for z in range(Z):
+        assert ws[z].grad.dtype == wdtype
+        _close(ws[z].grad, wr[z].grad, gtol * math.sqrt(R), gtol, f"dW[{z}]")
+    if add is not None:
+        _close(add.grad, addr.grad, 1e-4, 1e-4, "dadd")
+    again = F_ops.skinny_linears(a, ws, silu=silu, add=add)
+    assert torch.equal(out, again), "the skinny GEMM is not bitwise repeatable"
+
+
 def test_optimizer_kernels():
     torch.manual_seed(11)
     n = 100_003 * 8
