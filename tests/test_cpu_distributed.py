@@ -217,6 +217,63 @@ def test_pt_checkpointer_resume_two_ranks():
     run_distributed("_pt_checkpoint_resume")
 
 
+def _dcp_writer_processes(rank, world, tmp):
+    """Asynchronous DCP save of a 2-rank sharded model through the per-rank writer processes (own gloo group): the trainer ranks
+    keep stepping while the files are written, a fresh pair of ranks resumes bit-exactly, and a save that cannot be written on
+    rank 0 is reported on every rank and the next save works again."""
+    from cosmos_predict25_b200.checkpoint.dcp import DistributedCheckpointer
+    from cosmos_predict25_b200.models.dit import dit_tiny
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig, SchedulerConfig
+    job = [tmp]
+    dist.broadcast_object_list(job, src=0)
+    cfg = Video2WorldRFConfig(net=dit_tiny(), precision="float32", state_t=4)
+
+    def make():
+        torch.manual_seed(0)
+        m = Video2WorldModelRectifiedFlow(cfg, device=torch.device("cpu"), fsdp_group=dist.group.WORLD)
+        o, s = m.init_optimizer_scheduler(OptimizerConfig(lr=1e-3), SchedulerConfig(kind="constant"))
+        return m, o, s
+
+    torch.manual_seed(3 + rank)
+    batch = {"latents": torch.randn(1, 16, 4, 16, 16), "t5_text_embeddings": torch.randn(1, 32, 256), "fps": torch.tensor([16.0]),
+             "padding_mask": torch.zeros(1, 1, 16, 16)}
+    m, o, s = make()
+    _, loss = m.training_step(dict(batch), 0)
+    loss.backward()
+    o.step()
+    ck = DistributedCheckpointer({"dcp_async_mode_enabled": True}, job[0])
+    ck.save(m, o, s, iteration=1)
+    masters = [u.master.clone() for u in m.engine.units]
+    _, loss = m.training_step(dict(batch), 1)      # the trainer goes on while the children write
+    loss.backward()
+    o.step()
+    ck.finalize()
+    dist.barrier()
+    latest = os.path.join(job[0], "checkpoints", "latest_checkpoint.txt")
+    assert open(latest).read().strip() == "iter_000000001"
+    m2, o2, s2 = make()
+    assert DistributedCheckpointer({}, job[0]).load(m2, o2, s2) == 1
+    for a, u in zip(masters, m2.engine.units):
+        assert torch.equal(a, u.master), rank
+    # rank 0 cannot create the directory of iteration 2: every rank learns of the failure, the pointer stays
+    if rank == 0:
+        with open(os.path.join(job[0], "checkpoints", "iter_000000002"), "w") as f:
+            f.write("taken")
+    dist.barrier()
+    ck.save(m, o, s, iteration=2)
+    ck.finalize()
+    assert ck._bg_error is None and open(latest).read().strip() == "iter_000000001"
+    ck.save(m, o, s, iteration=3)
+    ck.close()
+    dist.barrier()
+    assert open(latest).read().strip() == "iter_000000003"
+
+
+def test_dcp_async_save_through_writer_processes():
+    run_distributed("_dcp_writer_processes", world=2)
+
+
 def _hsdp(rank, world, tmp, shard_size):
     """Hybrid sharding (shard groups of ``shard_size`` ranks, replicated ``world / shard_size`` times) and plain data
     parallelism (``shard_size`` 1) give the same parameters as one process that sees the whole batch."""
