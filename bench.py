@@ -40,6 +40,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="train", choices=["train", "distill"],
+                    help="train: rectified-flow training step (the headline); distill: sCM / rCM consistency-distillation step "
+                         "(teacher forward, student forward-mode JVP on the JVP attention kernel, student forward + backward, optimizer)")
     ap.add_argument("--model", default="2B", choices=["2B", "14B", "mini", "tiny"])
     ap.add_argument("--frames", type=int, default=24, help="latent frames per sample")
     ap.add_argument("--height", type=int, default=88)
@@ -146,11 +149,14 @@ def main():
     groups = build_groups(world, cp_size=args.cp)
     ctx_dim = 256 if args.model == "tiny" else 100352
     net_cfg = NET_PRESETS[args.model](checkpoint_mode=args.checkpoint)
-    cfg = Video2WorldRFConfig(net=net_cfg, precision="bfloat16", state_t=args.frames,
-                              conditional_frames_probs={0: 0.5, 1: 0.25, 2: 0.25},
-                              sharding_transport=args.transport if world > 1 else "nccl")
+    model_kw = dict(net=net_cfg, precision="bfloat16", state_t=args.frames, conditional_frames_probs={0: 0.5, 1: 0.25, 2: 0.25},
+                    sharding_transport=args.transport if world > 1 else "nccl")
     torch.manual_seed(1234 + rank)
-    model = Video2WorldModelRectifiedFlow(cfg, device=dev, fsdp_group=groups.fsdp, cp_group=groups.cp)
+    if args.mode == "distill":
+        from cosmos_predict25_b200.models.distill import ConsistencyDistillModel, DistillConfig
+        model = ConsistencyDistillModel(DistillConfig(**model_kw), device=dev, fsdp_group=groups.fsdp, cp_group=groups.cp)
+    else:
+        model = Video2WorldModelRectifiedFlow(Video2WorldRFConfig(**model_kw), device=dev, fsdp_group=groups.fsdp, cp_group=groups.cp)
     model.train()
     if args.cp > 1 and args.transport == "peer":
         from cosmos_predict25_b200.parallel import ulysses
@@ -224,7 +230,7 @@ def main():
 
     # ---- library twin: the same model, optimizer and data with cuDNN attention and cuBLAS GEMMs (the reference's choice on sm_100)
     twin = None
-    if not args.no_twin and args.attention is None and args.gemm is None and args.model in ("2B", "14B"):
+    if args.mode == "train" and not args.no_twin and args.attention is None and args.gemm is None and args.model in ("2B", "14B"):
         saved = (F_ops.settings.attention, F_ops.settings.gemm)
         F_ops.settings.attention, F_ops.settings.gemm = "cudnn", "cublas"
         try:
@@ -238,7 +244,7 @@ def main():
 
     # ---- inference half of the metric: all ranks form one context-parallel group
     inference = None
-    if not args.no_inference and args.model == "2B" and args.cp == 1 and args.frames % world == 0:
+    if args.mode == "train" and not args.no_inference and args.model == "2B" and args.cp == 1 and args.frames % world == 0:
         del trainer, model, device_batch
         losses.clear()
         import gc
@@ -256,7 +262,10 @@ def main():
         tok = global_batch * tokens_per_sample * args.steps
         value = tok / (ms / 1e3)
         line = {
-            "metric": f"DiT training latent-tokens/s ({args.model} Video2World, 720p x 93 frames, device-timed, max over ranks)",
+            "metric": (f"DiT training latent-tokens/s ({args.model} Video2World, 720p x 93 frames, device-timed, max over ranks)"
+                       if args.mode == "train" else
+                       f"sCM / rCM distillation step latent-tokens/s ({args.model} Video2World student and teacher, 720p x 93 frames, "
+                       "teacher forward + student forward-mode JVP + student forward / backward + optimizer, device-timed, max over ranks)"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / twin["tokens_s"]) if twin else None,

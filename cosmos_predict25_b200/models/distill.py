@@ -71,7 +71,8 @@ class ConsistencyDistillModel(Video2WorldModelRectifiedFlow):
 
     def __init__(self, config: DistillConfig, **kw):
         super().__init__(config, **kw)
-        self.teacher = copy.deepcopy(self.net).requires_grad_(False).eval()
+        # the teacher is frozen and never enters the sharded engine: it is held in the compute precision
+        self.teacher = copy.deepcopy(self.net).requires_grad_(False).eval().to(self.precision)
         self.fake_score = copy.deepcopy(self.net) if config.dmd_weight > 0 else None
         self._phase = "student"
 

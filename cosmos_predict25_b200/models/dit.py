@@ -316,6 +316,14 @@ class Attention(nn.Module):
                                                     self.q_norm.weight, self.k_norm.weight, rope, self.cp_group, self.q_norm.eps)
             o = o.reshape(B, S, self.n_heads * self.head_dim)
             return o if return_pre_proj else self.output_proj(o)
+        if (self.is_selfattn and self.cp_group is not None and self.cp_comm_type == "a2a" and self._plain_projections()
+                and all(getattr(p.weight, "_cb200_gather", None) is None for p in (self.q_proj, self.k_proj, self.v_proj))
+                and ulysses.projected_attention_train_available(x, self.cp_group, self.head_dim)):
+            # training under context parallelism: same GEMM-epilogue exchange, with the raw projections kept for the backward
+            o = ulysses.ulysses_projected_attention_train(x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight,
+                                                          self.q_norm.weight, self.k_norm.weight, rope, self.cp_group, self.q_norm.eps)
+            o = o.reshape(B, S, self.n_heads * self.head_dim)
+            return o if return_pre_proj else self.output_proj(o)
         q = self.q_proj(x).view(B, S, self.n_heads, self.head_dim)
         if self.is_selfattn:
             k = self.k_proj(x).view(B, S, self.n_heads, self.head_dim)

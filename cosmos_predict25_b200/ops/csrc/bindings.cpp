@@ -309,9 +309,12 @@ Tensor gemm_bf16_gate_residual(const Tensor& a, const Tensor& b, const Tensor& r
 
 // x [B*S, K] @ w [H*128, K]^T with the Ulysses sequence->head exchange as the epilogue: nothing is returned, head h of token
 // (b, s) lands in out_ptrs[h / (H/P)] (a staging buffer of that rank, [B, P*S, H/P, 128]) after optional RMSNorm and RoPE.
-void gemm_scatter_heads_peer(const Tensor& x, const Tensor& w, c10::ArrayRef<int64_t> out_ptrs, const c10::optional<Tensor>& norm_w,
-                             const c10::optional<Tensor>& cosv, const c10::optional<Tensor>& sinv, int64_t S, int64_t rank,
-                             double eps) {
+// ``keep_raw`` (training; needs norm_w): also returns the un-normalised projection [B*S, H*128] and the reciprocal RMS [B*S, H]
+// that the RMSNorm backward needs; otherwise two empty tensors.
+std::tuple<Tensor, Tensor> gemm_scatter_heads_peer(const Tensor& x, const Tensor& w, c10::ArrayRef<int64_t> out_ptrs,
+                                                   const c10::optional<Tensor>& norm_w, const c10::optional<Tensor>& cosv,
+                                                   const c10::optional<Tensor>& sinv, int64_t S, int64_t rank, double eps,
+                                                   bool keep_raw) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "operands must be contiguous");
@@ -335,11 +338,77 @@ void gemm_scatter_heads_peer(const Tensor& x, const Tensor& w, c10::ArrayRef<int
       sp = sinv->data_ptr<float>();
     }
   }
+  TORCH_CHECK(rank >= 0 && rank < (int64_t)out_ptrs.size(), "rank out of range");
+  TORCH_CHECK(!keep_raw || wp != nullptr, "keep_raw needs a norm weight (without normalisation the output is the raw projection)");
+  Tensor raw = at::empty({keep_raw ? (int64_t)d.M : 0, keep_raw ? (int64_t)d.N : 0}, x.options());
+  Tensor rstd = at::empty({keep_raw ? (int64_t)d.M : 0, keep_raw ? (int64_t)d.N / 128 : 0}, x.options().dtype(at::kFloat));
   std::vector<int64_t> p(out_ptrs.begin(), out_ptrs.end());
   const int dev = x.get_device();
   const int rc = cb200_gemm_bf16_scatter_heads(x.data_ptr(), w.data_ptr(), d.M, d.N, d.K, p.data(), (int)p.size(), (int)rank, (int)S,
-                                               wp, cp, sp, (float)eps, error_word(dev), sm_count(dev), stream());
+                                               wp, cp, sp, (float)eps, keep_raw ? raw.data_ptr() : nullptr,
+                                               keep_raw ? rstd.data_ptr<float>() : nullptr, error_word(dev), sm_count(dev), stream());
   TORCH_CHECK(rc == 0, "tcgen05 GEMM (head-scatter epilogue) launch failed with code ", rc);
+  return {raw, rstd};
+}
+
+std::tuple<Tensor, Tensor> ln_modulate_jvp(const Tensor& x, const Tensor& tx, const Tensor& shift, const Tensor& scale,
+                                           const c10::optional<Tensor>& tshift, const c10::optional<Tensor>& tscale, int64_t L,
+                                           double eps) {
+  check_bf16(x, "x");
+  check_bf16(tx, "tx");
+  check_f32(shift, "shift");
+  check_f32(scale, "scale");
+  TORCH_CHECK(x.dim() == 2 && tx.sizes() == x.sizes() && tx.device() == x.device(), "tx must have the shape and device of x [rows, D]");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t rows = x.size(0), D = x.size(1);
+  TORCH_CHECK(D % 8 == 0 && D <= 8192, "channel dim must be a multiple of 8 and <= 8192");
+  TORCH_CHECK(L > 0 && rows % L == 0 && shift.dim() == 2 && shift.size(0) == rows / L && shift.size(1) == D &&
+                  scale.sizes() == shift.sizes(), "shift/scale must be [rows/L, D]");
+  TORCH_CHECK(tshift.has_value() == tscale.has_value(), "give both modulation tangents or neither");
+  const float* tsp = nullptr;
+  const float* tcp = nullptr;
+  if (tshift.has_value()) {
+    check_f32(*tshift, "tshift");
+    check_f32(*tscale, "tscale");
+    TORCH_CHECK(tshift->sizes() == shift.sizes() && tscale->sizes() == shift.sizes(), "modulation tangents must be [rows/L, D]");
+    tsp = tshift->data_ptr<float>();
+    tcp = tscale->data_ptr<float>();
+  }
+  // value and tangent rows in one allocation, tangent after value: a following GEMM can take both as one [2 rows, D] operand
+  Tensor both = at::empty({2, rows, D}, x.options());
+  Tensor y = both.select(0, 0), ty = both.select(0, 1);
+  cb200_ln_modulate_jvp(x.data_ptr(), tx.data_ptr(), shift.data_ptr<float>(), scale.data_ptr<float>(), tsp, tcp, y.data_ptr(),
+                        ty.data_ptr(), rows, (int)D, (int)L, (float)eps, stream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {y, ty};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_rope_jvp(const Tensor& x, const Tensor& tx, const Tensor& w, const c10::optional<Tensor>& cosv,
+                                            const c10::optional<Tensor>& sinv, double eps) {
+  check_bf16(x, "x");
+  check_bf16(tx, "tx");
+  TORCH_CHECK(x.dim() == 4 && tx.sizes() == x.sizes() && tx.device() == x.device(), "tx must have the shape and device of x [B, S, H, D]");
+  c10::cuda::CUDAGuard g(x.device());
+  const int64_t B = x.size(0), S = x.size(1), H = x.size(2), HD = x.size(3);
+  TORCH_CHECK(HD == 128 || HD == 64, "head_dim must be 64 or 128");
+  TORCH_CHECK(w.numel() == HD && w.device() == x.device(), "w must hold head_dim values on the device of x");
+  Tensor wf = w.to(at::kFloat).contiguous();
+  const float* cp = nullptr;
+  const float* sp = nullptr;
+  TORCH_CHECK(cosv.has_value() == sinv.has_value(), "give both rotation tables or neither");
+  if (cosv.has_value()) {
+    check_f32(*cosv, "cos");
+    check_f32(*sinv, "sin");
+    TORCH_CHECK(cosv->dim() == 2 && cosv->size(0) == S && cosv->size(1) == HD / 2 && sinv->sizes() == cosv->sizes(),
+                "cos/sin must be [S, D/2]");
+    cp = cosv->data_ptr<float>();
+    sp = sinv->data_ptr<float>();
+  }
+  Tensor y = at::empty_like(x), ty = at::empty_like(x);
+  cb200_rmsnorm_rope_jvp(x.data_ptr(), tx.data_ptr(), wf.data_ptr<float>(), cp, sp, y.data_ptr(), ty.data_ptr(), B * S * H, (int)S,
+                         (int)H, (int)HD, (float)eps, stream());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {y, ty};
 }
 
 // Z small fp32 GEMMs in one launch (skinny.cu). ``a``: fp32 storage addressed as a[z*a_z + r*a_r + k*a_k]; B: either ``b_ptrs``
@@ -424,7 +493,10 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_bf16_gelu_pre(Tensor a, Tensor b, Tensor? bias) -> (Tensor, Tensor)");
   m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor");
   m.def("gemm_scatter_heads_peer(Tensor x, Tensor w, int[] out_ptrs, Tensor? norm_w, Tensor? cos, Tensor? sin, int S, int rank, "
-        "float eps) -> ()", &gemm_scatter_heads_peer);
+        "float eps, bool keep_raw) -> (Tensor, Tensor)", &gemm_scatter_heads_peer);
+  m.def("ln_modulate_jvp(Tensor x, Tensor tx, Tensor shift, Tensor scale, Tensor? tshift, Tensor? tscale, int L, float eps) -> "
+        "(Tensor, Tensor)", &ln_modulate_jvp);
+  m.def("rmsnorm_rope_jvp(Tensor x, Tensor tx, Tensor w, Tensor? cos, Tensor? sin, float eps) -> (Tensor, Tensor)", &rmsnorm_rope_jvp);
   m.def("skinny_bgemm(Tensor a, int a_z, int a_r, int a_k, Tensor? b_ptrs, Tensor? b, int b_z, int b_n, int b_k, bool b_bf16, "
         "Tensor? add, int add_cols, int Z, int R, int N, int K, bool silu_a, bool silu_b, bool out_bf16, int ksplit) -> Tensor", &skinny_bgemm);
   m.def("kernel_error(int device, bool clear) -> int", &kernel_error);

@@ -25,6 +25,12 @@
 //
 // Shared memory (7 tiles of 32 KB): K, V, three Q stages (a Q tile lives from S^T(i) to dK(i)), one dO stage (dP^T(i) to dV(i)),
 // dS^T. Row statistics (-lse*log2e, -delta) travel in their own two-stage ring. All waits are bounded and report through `err`.
+//
+// Neighbourhood (tile-sparse) mode, template flag NA: the tensors arrive in tile order (every 128-row tile is one 4 x 4 x 8 box of
+// video tokens, row = dt * 32 + dh * 8 + dw), a CTA walks the list of query tiles that see its key tile instead of all of them,
+// and phase 1 clears the entries of P^T whose (key, query) pair is not visible: per axis a byte table indexed by
+// (key coordinate, query tile) holds the visibility bits of the tile's 4 / 4 / 8 query coordinates, and a pair is visible when its
+// three bits are set. Tiles that are visible as a whole (list entry with the top bit set) skip the masking.
 
 #include <math.h>
 
@@ -51,6 +57,15 @@ constexpr size_t kSmem = (size_t)(2 + kQStages + 1 + 1) * kTile + 2 * kStatBytes
 constexpr uint32_t X = 0, Y = 128, DV = 256, DK = 384;   // TMEM columns
 }  // namespace fat
 
+struct NaBwdPlan {
+  const int* q_list;       // [key tiles][max_n]: query tile index, top bit = the whole tile pair is visible
+  const int* q_cnt;        // [key tiles]
+  const uint8_t* bt;       // [T][nT], [H][nH], [W][nW]: visibility bits of a query tile's coordinates for one key coordinate
+  const uint8_t* bh;
+  const uint8_t* bw;
+  int max_n, nT, nH, nW;
+};
+
 __device__ __forceinline__ float ex2t(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -60,12 +75,13 @@ __device__ __forceinline__ void red_add_f32t(float* p, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
 
+template <bool NA>
 __global__ void __launch_bounds__(fat::kThreads, 1)
 fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const float* __restrict__ lse2, const float* __restrict__ delta, float* __restrict__ dQacc,
                    bf16* __restrict__ dK, bf16* __restrict__ dV, int Sq, int Skv, int H, int Sq_pad, float scale,
-                   int* __restrict__ err) {
+                   NaBwdPlan na, int* __restrict__ err) {
   using namespace fat;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
@@ -96,7 +112,10 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int h = blockIdx.y, b = blockIdx.z;
   const int kv_base = blockIdx.x * 128;
-  const int n_q = (Sq + 127) / 128;
+  // query tiles this CTA visits, and the tile index of visit i
+  const int n_q = NA ? na.q_cnt[blockIdx.x] : (Sq + 127) / 128;
+  const int* my_list = NA ? na.q_list + (size_t)blockIdx.x * na.max_n : nullptr;
+  auto q_tile = [&](int i) -> int { return NA ? (my_list[i] & 0x7fffffff) : i; };
   const float scale_log2 = scale * 1.4426950408889634f;
 
   // The 128-byte swizzle of TMA and of the UMMA descriptors is a function of the shared-memory address, so every tile must
@@ -158,17 +177,18 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       bool ok = true;
       for (int i = 0; i < n_q && ok; ++i) {
         const int qs = i % kQStages, ss = i & 1;
+        const int q0 = q_tile(i) * 128;
         if (!mbar_wait(&q_empty[qs], ((i / kQStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&q_full[qs], kTile);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sQ + qs * kTile + c * kHalf, &tm_q, &q_full[qs], c * 64, h, i * 128, b);
+        for (int c = 0; c < 2; ++c) tma_load_4d(sQ + qs * kTile + c * kHalf, &tm_q, &q_full[qs], c * 64, h, q0, b);
         if (!mbar_wait(&st_empty[ss], ((i >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&st_full[ss], kStatBytes);
         float* st = sStat + ss * 256;
-        bulk_load_1d(st, lse2 + bh * Sq_pad + (size_t)i * 128, 512, &st_full[ss]);
-        bulk_load_1d(st + 128, delta + bh * Sq_pad + (size_t)i * 128, 512, &st_full[ss]);
+        bulk_load_1d(st, lse2 + bh * Sq_pad + (size_t)q0, 512, &st_full[ss]);
+        bulk_load_1d(st + 128, delta + bh * Sq_pad + (size_t)q0, 512, &st_full[ss]);
         if (!mbar_wait(do_empty, (i & 1) ^ 1, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(do_full, kTile);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sDO + c * kHalf, &tm_do, do_full, c * 64, h, i * 128, b);
+        for (int c = 0; c < 2; ++c) tma_load_4d(sDO + c * kHalf, &tm_do, do_full, c * 64, h, q0, b);
       }
       if (!ok) { atomicCAS(err, 0, 51); *abort_flag = 1; }
     }
@@ -221,14 +241,14 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         umma_ss_w(tmem_base + DK, dDS_km + km_off(kk), bq + mn_off(kk), idesc_kn, (accumulate || kk > 0) ? 1u : 0u, leader);
     };
     bool ok = wait_all(kv_full, 0);
-    if (ok) ok = wait_all(&q_full[0], 0);
-    if (ok) {
+    if (ok && n_q > 0) ok = wait_all(&q_full[0], 0);
+    if (ok && n_q > 0) {
       tc_fence_after();
       issue_st(0);
       umma_commit_w(s_full, leader);
       ok = wait_all(do_full, 0);
     }
-    if (ok) {
+    if (ok && n_q > 0) {
       tc_fence_after();
       issue_dpt();
       umma_commit_w(dp_full, leader);
@@ -262,7 +282,7 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         umma_commit_w(dp_full, leader);
       }
     }
-    if (ok) umma_commit_w(done, leader);
+    if (ok && n_q > 0) umma_commit_w(done, leader);
     if (!ok && lane == 0) { atomicCAS(err, 0, 52); *abort_flag = 1; }
   } else if (warp >= kEwWarps) {
     // ------------------------------------------------------------------------------------------ dQ^T drain warps
@@ -284,7 +304,7 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           __syncwarp();
           if (lane == 0) mbar_arrive(dq_free);
         }
-        const int q0 = i * 128 + half * 64;
+        const int q0 = q_tile(i) * 128 + half * 64;
         // head-major accumulator [B, H, Sq, 128]: consecutive queries are 512 bytes apart, so every reduction below is one
         // instruction with an immediate offset from a single base pointer
         float* qrow = dQacc + (bh * Sq + (size_t)q0) * HD + d;
@@ -317,10 +337,34 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint8_t* ds_row = sDS + (cg >> 1) * kHalf + row * 128;
     const int sw = row & 7, chunk0 = (cg & 1) * 4;
     const float2 sc2 = make_float2(scale_log2, scale_log2);
+    // NA: this thread's key coordinates (tile blockIdx.x, row dt * 32 + dh * 8 + dw)
+    int k_t = 0, k_h = 0, k_w = 0;
+    if (NA) {
+      const int kt = blockIdx.x;
+      k_t = (kt / (na.nH * na.nW)) * 4 + (row >> 5);
+      k_h = ((kt / na.nW) % na.nH) * 4 + ((row >> 3) & 3);
+      k_w = (kt % na.nW) * 8 + (row & 7);
+    }
     bool ok = true;
     for (int i = 0; i < n_q; ++i) {
       const uint32_t par = i & 1;
       const int ss = i & 1;
+      // visibility of this thread's 32 queries (dt = cg, bit dh * 8 + dw): all ones for a fully visible tile pair
+      uint32_t vis = 0xffffffffu;
+      if (NA) {
+        const int entry = my_list[i];
+        if (entry >= 0) {
+          const int qt = entry;
+          const uint32_t mt = na.bt[k_t * na.nT + qt / (na.nH * na.nW)];
+          const uint32_t mh = na.bh[k_h * na.nH + (qt / na.nW) % na.nH];
+          const uint32_t mw = na.bw[k_w * na.nW + qt % na.nW];
+          vis = 0u;
+          if ((mt >> cg) & 1u) {
+#pragma unroll
+            for (int dh = 0; dh < 4; ++dh) vis |= ((mh >> dh) & 1u) ? (mw << (dh * 8)) : 0u;
+          }
+        }
+      }
       if (!mbar_wait(&st_full[ss], (i >> 1) & 1, abort_flag)) { ok = false; break; }
       if (!mbar_wait(s_full, par, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -337,7 +381,13 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           const float4 nl = l4[g];
           const float2 x0 = fma2(make_float2(__uint_as_float(p[g * 4]), __uint_as_float(p[g * 4 + 1])), sc2, make_float2(nl.x, nl.y));
           const float2 x1 = fma2(make_float2(__uint_as_float(p[g * 4 + 2]), __uint_as_float(p[g * 4 + 3])), sc2, make_float2(nl.z, nl.w));
-          const float e0 = ex2t(x0.x), e1 = ex2t(x0.y), e2 = ex2t(x1.x), e3 = ex2t(x1.y);
+          float e0 = ex2t(x0.x), e1 = ex2t(x0.y), e2 = ex2t(x1.x), e3 = ex2t(x1.y);
+          if (NA && vis != 0xffffffffu) {
+            e0 = ((vis >> (g * 4)) & 1u) ? e0 : 0.f;
+            e1 = ((vis >> (g * 4 + 1)) & 1u) ? e1 : 0.f;
+            e2 = ((vis >> (g * 4 + 2)) & 1u) ? e2 : 0.f;
+            e3 = ((vis >> (g * 4 + 3)) & 1u) ? e3 : 0.f;
+          }
           p[g * 4] = __float_as_uint(e0);
           p[g * 4 + 1] = __float_as_uint(e1);
           p[g * 4 + 2] = __float_as_uint(e2);
@@ -389,7 +439,7 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         mbar_arrive(&st_empty[ss]);
       }
     }
-    if (ok) ok = mbar_wait(done, 0, abort_flag);
+    if (ok && n_q > 0) ok = mbar_wait(done, 0, abort_flag);
     if (ok) {
       tc_fence_after();
       // warps with cg 0,1 write dV, cg 2,3 write dK (scaled); the two warps of a lane quarter take 64 columns each
@@ -404,6 +454,10 @@ fa_bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         uint32_t o[32];
         tmem_ld32(tAcc + c * 32, o);
         tmem_ld_wait();
+        if (n_q == 0) {               // no query sees this key tile: its gradients are zero (the accumulators were never written)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
         if (kv_row < Skv) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -456,7 +510,7 @@ extern "C" int cb200_fa_bwd_tile_main(const void* d_o, const void* q, const void
   if (rc) return rc;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(fa_bwd_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    cudaError_t e = cudaFuncSetAttribute(fa_bwd_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
     if (e != cudaSuccess) return 300 + (int)e;
     attr = true;
   }
@@ -464,7 +518,39 @@ extern "C" int cb200_fa_bwd_tile_main(const void* d_o, const void* q, const void
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, n * sizeof(float), st);
   if (e != cudaSuccess) return 400 + (int)e;
   dim3 grid((Skv + 127) / 128, H, B);
-  fa_bwd_tile_kernel<<<grid, kThreads, kSmem, st>>>(tq, tdo, tk, tv, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, Sq, Skv, H, S_pad, scale,
-                                                    err);
+  fa_bwd_tile_kernel<false><<<grid, kThreads, kSmem, st>>>(tq, tdo, tk, tv, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, Sq, Skv, H, S_pad,
+                                                           scale, NaBwdPlan{}, err);
+  return (int)cudaGetLastError();
+}
+
+// Neighbourhood attention backward. q, k, v, d_o and the outputs are in tile order ([B, S, H, 128] with S = nT * nH * nW tiles of 128
+// rows, row dt * 32 + dh * 8 + dw inside a tile); lse2 / delta as above, in the same order. q_list [S / 128][max_n] int32 (top bit:
+// whole tile pair visible), q_cnt [S / 128]; bt / bh / bw: uint8 tables [4 nT][nT], [4 nH][nH], [8 nW][nW].
+extern "C" int cb200_fa_bwd_tile_na(const void* d_o, const void* q, const void* k, const void* v, const float* lse2, const float* delta,
+                                    float* dq_acc, void* dk, void* dv, int B, int S, int H, float scale, const int* q_list,
+                                    const int* q_cnt, int max_n, const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT, int nH,
+                                    int nW, int* err, cudaStream_t st) {
+  using namespace fat;
+  if (S != nT * nH * nW * 128 || max_n < 1) return -42;
+  auto make = [&](CUtensorMap* m, const void* p) {
+    const uint64_t dims[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+    const uint64_t strides[3] = {(uint64_t)HD * 2, (uint64_t)H * HD * 2, (uint64_t)S * H * HD * 2};
+    const uint32_t box[4] = {64, 1, 128, 1};
+    return make_tmap_bf16(m, p, 4, dims, strides, box);
+  };
+  CUtensorMap tq, tdo, tk, tv;
+  int rc = make(&tq, q) | make(&tdo, d_o) | make(&tk, k) | make(&tv, v);
+  if (rc) return rc;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(fa_bwd_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr = true;
+  }
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)B * S * H * HD * sizeof(float), st);
+  if (e != cudaSuccess) return 400 + (int)e;
+  dim3 grid(S / 128, H, B);
+  fa_bwd_tile_kernel<true><<<grid, kThreads, kSmem, st>>>(tq, tdo, tk, tv, lse2, delta, dq_acc, (bf16*)dk, (bf16*)dv, S, S, H, S, scale,
+                                                          NaBwdPlan{q_list, q_cnt, bt, bh, bw, max_n, nT, nH, nW}, err);
   return (int)cudaGetLastError();
 }

@@ -55,6 +55,8 @@ struct HeadScatter {
   const float* sinv;
   int S, Hl, P, rank;
   float eps;
+  bf16* raw;          // optional [M, N]: the un-normalised projection, kept locally for the RMSNorm backward (training)
+  float* rstd_out;    // optional [M, N / 128]: reciprocal RMS of every (token, head), with ``raw``
 };
 
 struct GemmEpilogue {
@@ -306,10 +308,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 for (int j = 0; j < 32; ++j) ss = fmaf(__uint_as_float(r[j]), __uint_as_float(r[j]), ss);
               }
               rstd = rsqrtf(ss * (1.f / 128.f) + ep.hs.eps);
+              if (ep.hs.rstd_out != nullptr && valid) ep.hs.rstd_out[(size_t)row * (N >> 7) + head] = rstd;
             }
+            const unsigned long long raw_u =
+                ep.hs.raw != nullptr ? reinterpret_cast<unsigned long long>(ep.hs.raw + (size_t)row_c * N + (size_t)head * 128) : 0ull;
             const int dst_rank = head / ep.hs.Hl, hl = head - dst_rank * ep.hs.Hl;
             bf16* dst = reinterpret_cast<bf16*>(ep.hs.ptrs[dst_rank]) +
                         ((((size_t)b_idx * ep.hs.P + ep.hs.rank) * ep.hs.S + s_idx) * ep.hs.Hl + hl) * 128;
+            int c_cur = 0;
+            // this thread's row (columns [32c, 32c + 32) in ``lo32`` and their rotation partners [64 + 32c, ...) in ``hi32``) goes to
+            // the warp's staging block, 16-byte chunks XOR-swizzled by the row (no bank conflicts); then 4 lanes cover a 64-byte
+            // run of a head row, so a warp store is eight contiguous 64-byte segments (local memory or a peer's over NVLink)
+            // instead of 32 scattered 16-byte pieces
+            auto emit = [&](const float (&lo32)[32], const float (&hi32)[32], unsigned long long dst_u) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o0, o1;
+                __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&o0);
+                __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  p0[j] = __floats2bfloat162_rn(lo32[q * 8 + 2 * j], lo32[q * 8 + 2 * j + 1]);
+                  p1[j] = __floats2bfloat162_rn(hi32[q * 8 + 2 * j], hi32[q * 8 + 2 * j + 1]);
+                }
+                *reinterpret_cast<uint4*>(stage_row + ((q ^ (lane & 7)) << 4)) = o0;
+                *reinterpret_cast<uint4*>(stage_row + (((4 + q) ^ (lane & 7)) << 4)) = o1;
+              }
+              __syncwarp();
+#pragma unroll 4
+              for (int it = 0; it < 8; ++it) {
+                const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
+                const unsigned long long d = __shfl_sync(0xffffffffu, dst_u, r_src);
+                const int ok_row = __shfl_sync(0xffffffffu, (int)valid, r_src);
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4));
+                const int col = (chunk < 4 ? c_cur * 32 + chunk * 8 : 64 + c_cur * 32 + (chunk - 4) * 8);
+                if (ok_row) *reinterpret_cast<uint4*>(d + col * 2) = v;
+              }
+              __syncwarp();
+            };
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {      // pass 2: columns [32c, 32c+32) and their rotation partners [64+32c, 64+32c+32)
               uint32_t lo[32], hi[32];
@@ -322,6 +358,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 a[j] = __uint_as_float(lo[j]);
                 bb[j] = __uint_as_float(hi[j]);
               }
+              c_cur = c;
+              if (raw_u != 0ull) emit(a, bb, raw_u);        // warp-uniform: every lane of the kernel sees the same ep.hs.raw
               if (ep.hs.w != nullptr) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -359,35 +397,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                   }
                 }
               }
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 o0, o1;
-                __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&o0);
-                __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  p0[j] = __floats2bfloat162_rn(a[q * 8 + 2 * j], a[q * 8 + 2 * j + 1]);
-                  p1[j] = __floats2bfloat162_rn(bb[q * 8 + 2 * j], bb[q * 8 + 2 * j + 1]);
-                }
-                // this thread's row goes to the warp's staging block, 16-byte chunks XOR-swizzled by the row (no bank conflicts):
-                // chunks 0-3 = columns [32c, 32c + 32), chunks 4-7 = their rotation partners [64 + 32c, 64 + 32c + 32)
-                *reinterpret_cast<uint4*>(stage_row + ((q ^ (lane & 7)) << 4)) = o0;
-                *reinterpret_cast<uint4*>(stage_row + (((4 + q) ^ (lane & 7)) << 4)) = o1;
-              }
-              __syncwarp();
-              // write-out: 4 lanes cover a 64-byte run of a head row, so a warp store is eight contiguous 64-byte segments
-              // (local memory or a peer's over NVLink) instead of 32 scattered 16-byte pieces
-              const unsigned long long dst_u = reinterpret_cast<unsigned long long>(dst);
-#pragma unroll 4
-              for (int it = 0; it < 8; ++it) {
-                const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
-                const unsigned long long d = __shfl_sync(0xffffffffu, dst_u, r_src);
-                const int ok_row = __shfl_sync(0xffffffffu, (int)valid, r_src);
-                const uint4 v = *reinterpret_cast<const uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4));
-                const int col = (chunk < 4 ? c * 32 + chunk * 8 : 64 + c * 32 + (chunk - 4) * 8);
-                if (ok_row) *reinterpret_cast<uint4*>(d + col * 2) = v;
-              }
-              __syncwarp();
+              emit(a, bb, reinterpret_cast<unsigned long long>(dst));
             }
           }
         }
@@ -645,9 +655,10 @@ extern "C" int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int
 // [b, rank * S + s, head % Hl, :].  The buffers may live on peer GPUs (plain stores over NVLink).
 extern "C" int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M, int N, int K, const int64_t* ptrs, int P,
                                              int rank, int S, const float* norm_w, const float* cosv, const float* sinv,
-                                             float eps, int* err, int sms, cudaStream_t st) {
+                                             float eps, void* raw, float* rstd_out, int* err, int sms, cudaStream_t st) {
   if (P < 1 || P > 8 || N % 128 != 0 || (N / 128) % P != 0 || S <= 0 || M % S != 0) return -21;
   if (cosv != nullptr && norm_w == nullptr) return -22;
+  if ((raw != nullptr) != (rstd_out != nullptr) || (raw != nullptr && norm_w == nullptr)) return -23;
   GemmEpilogue ep{};
   for (int i = 0; i < P; ++i) ep.hs.ptrs[i] = ptrs[i];
   ep.hs.w = norm_w;
@@ -658,6 +669,8 @@ extern "C" int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M
   ep.hs.P = P;
   ep.hs.rank = rank;
   ep.hs.eps = eps;
+  ep.hs.raw = (bf16*)raw;
+  ep.hs.rstd_out = rstd_out;
   ep.L = 1;
   return launch_gemm<0, 0>(A, W, M, N, K, ep, err, sms, st);
 }

@@ -35,6 +35,12 @@ void cb200_adamw_ema_shard(float* master, const float* grad, float* m, float* v,
                            float ema_beta, long n, cudaStream_t st);
 void cb200_cast_f32_bf16(const float* src, void* dst, long n, cudaStream_t st);
 
+// tangent.cu: value and directional derivative in one pass (forward-mode variants)
+void cb200_ln_modulate_jvp(const void* x, const void* tx, const float* shift, const float* scale, const float* tshift,
+                           const float* tscale, void* y, void* ty, long rows, int D, int L, float eps, cudaStream_t st);
+void cb200_rmsnorm_rope_jvp(const void* x, const void* tx, const float* w, const float* cosv, const float* sinv, void* y, void* ty,
+                            long n_rows, int S, int H, int HD, float eps, cudaStream_t st);
+
 // skinny.cu: Z small fp32 GEMMs C[z][r,n] = sum_k fa(A[z][r,k]) fb(B[z][n,k]) (+ add[r,n], n < add_cols) with element strides;
 // ksplit > 1: C is [Z * ksplit, R, N] partial sums over ranges of k (the caller adds them)
 int cb200_skinny_bgemm(const float* a, long a_z, long a_r, long a_k, const long long* b_ptrs, const void* b_base, long b_z, long b_n,
@@ -47,7 +53,7 @@ int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
 int cb200_gemm_bf16_gather(const void* A, void* ws, void* C, int M, int rows, int ld, int b_mn, const int64_t* shard_ptrs, int P,
                            int chunk_rows, int* counters, const void* bias, int act, void* pre, int* err, int sms, cudaStream_t st);
 int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M, int N, int K, const int64_t* ptrs, int P, int rank, int S,
-                                  const float* norm_w, const float* cosv, const float* sinv, float eps, int* err, int sms,
+                                  const float* norm_w, const float* cosv, const float* sinv, float eps, void* raw, float* rstd_out, int* err, int sms,
                                   cudaStream_t st);
 }
 

@@ -67,6 +67,9 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
       return 0;
     }
   }
+  // The encoder is a driver entry point and needs a current context; a thread that has made no runtime call yet (an autograd
+  // worker whose first operation is a GEMM) has none. Any runtime call binds the device's primary context to the thread.
+  cudaFree(nullptr);
   cuuint64_t gdim[5];
   cuuint64_t gstr[4];
   cuuint32_t bx[5], estr[5];

@@ -15,6 +15,7 @@ from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
 import torch
+import torch.autograd.forward_ad as fwAD
 import torch.nn.functional as F
 
 from . import native, ref
@@ -38,6 +39,123 @@ class OpSettings:
 
 
 settings = OpSettings()
+
+
+# --------------------------------------------------------------------------------------
+# Forward-mode (tangent) paths. Inside ``native.forward_mode_ad()`` the network runs without autograd on dual tensors; each
+# front-end unpacks (primal, tangent), runs a kernel that produces value and directional derivative together, and packs the
+# result again, so the network JVP of the distillation step stays on this package's kernels.
+# --------------------------------------------------------------------------------------
+def _fm_native(x: torch.Tensor) -> bool:
+    return native.forward_mode() and x.is_cuda and native.available() and settings.gemm == "native"
+
+
+def _unpack(x):
+    """(primal, tangent or None)."""
+    if x is None:
+        return None, None
+    d = fwAD.unpack_dual(x)
+    return d.primal, d.tangent
+
+
+def _pack(p: torch.Tensor, t: Optional[torch.Tensor]) -> torch.Tensor:
+    return p if t is None else fwAD.make_dual(p, t)
+
+
+def _stacked_rows(p2d: torch.Tensor, t2d: torch.Tensor) -> Optional[torch.Tensor]:
+    """[2M, K] view over primal and tangent when the tangent's rows follow the primal's in one allocation (the tangent kernels
+    and the stacked GEMM below lay their results out that way), else None."""
+    if not (p2d.is_contiguous() and t2d.is_contiguous() and p2d.dtype == t2d.dtype):
+        return None
+    if t2d.data_ptr() != p2d.data_ptr() + p2d.numel() * p2d.element_size():
+        return None
+    if p2d.untyped_storage().data_ptr() != t2d.untyped_storage().data_ptr():
+        return None
+    M, K = p2d.shape
+    return torch.as_strided(p2d, (2 * M, K), (K, 1))
+
+
+def _ln_modulate_fm(x, shift, scale, eps):
+    px, tx = _unpack(x)
+    ps, ts = _unpack(shift)
+    pc, tc = _unpack(scale)
+    B, T, L, D = px.shape
+    f32 = lambda v: None if v is None else v.float().expand(B, T, D).contiguous().view(B * T, D)
+    if tx is None:
+        tx = torch.zeros_like(px)
+    if (ts is None) != (tc is None):
+        ts = torch.zeros_like(ps) if ts is None else ts
+        tc = torch.zeros_like(pc) if tc is None else tc
+    y, ty = native.load().ln_modulate_jvp(px.contiguous().view(-1, D), tx.contiguous().view(-1, D), f32(ps), f32(pc), f32(ts), f32(tc),
+                                          L, eps)
+    native.count_launch()
+    return _pack(y.view(B, T, L, D), ty.view(B, T, L, D))
+
+
+def _gate_residual_fm(x, gate, y):
+    ops = native.load()
+    px, tx = _unpack(x)
+    pg, tg = _unpack(gate)
+    py, ty = _unpack(y)
+    B, T, L, D = px.shape
+    g2 = lambda v: v.float().expand(B, T, D).contiguous().view(B * T, D)
+    r2 = lambda v: v.contiguous().view(-1, D)
+    out = ops.gate_residual_fwd(r2(px), g2(pg), r2(py), L)
+    native.count_launch()
+    t = tx
+    if ty is not None:       # t = tx + gate * ty
+        t = ops.gate_residual_fwd(r2(tx if tx is not None else torch.zeros_like(px)), g2(pg), r2(ty), L)
+        native.count_launch()
+    if tg is not None:       # t += tgate * y
+        t = ops.gate_residual_fwd(r2(t if t is not None else torch.zeros_like(px)), g2(tg), r2(py), L)
+        native.count_launch()
+    return _pack(out.view(B, T, L, D), None if t is None else t.view(B, T, L, D))
+
+
+def _rmsnorm_rope_fm(x, weight, rope, eps):
+    px, tx = _unpack(x)
+    cos, sin = rope.cos_sin() if rope is not None else (None, None)
+    if tx is None:
+        y, _ = native.load().rmsnorm_rope_fwd(px.contiguous(), weight, cos, sin, eps)
+        native.count_launch()
+        return y
+    y, ty = native.load().rmsnorm_rope_jvp(px.contiguous(), tx.contiguous(), weight, cos, sin, eps)
+    native.count_launch()
+    return _pack(y, ty)
+
+
+def _linear_fm(x, w, bias, act):
+    """Primal and tangent rows through the tcgen05 GEMM: one call on the stacked [2M, K] rows when they are adjacent in memory
+    (the weight is read once), two calls otherwise. The bias belongs to the primal only; GELU: y = gelu(pre), ty = gelu'(pre) tpre."""
+    ops = native.load()
+    px, tx = _unpack(x)
+    lead, N = px.shape[:-1], w.shape[0]
+    p2 = px.reshape(-1, px.shape[-1])
+    p2 = p2 if p2.is_contiguous() else p2.contiguous()
+    M = p2.shape[0]
+    if tx is None:
+        y = ops.gemm_bf16(p2, w, bias, _ACT_CODE[act], False, False)
+        native.count_launch()
+        return y.view(*lead, N)
+    t2 = tx.reshape(-1, tx.shape[-1])
+    t2 = t2 if t2.is_contiguous() else t2.contiguous()
+    both = _stacked_rows(p2, t2)
+    if both is not None:
+        out = ops.gemm_bf16(both, w, None, 0, False, False)
+        native.count_launch()
+        pre, tpre = out[:M], out[M:]
+    else:
+        pre = ops.gemm_bf16(p2, w, None, 0, False, False)
+        tpre = ops.gemm_bf16(t2, w, None, 0, False, False)
+        native.count_launch(2)
+    if bias is not None:
+        pre += bias
+    if act == "gelu":
+        y, ty = ops.gelu_fwd(pre), ops.gelu_bwd(tpre, pre)
+        native.count_launch(2)
+    else:
+        y, ty = pre, tpre
+    return _pack(y.view(*lead, N), ty.view(*lead, N))
 
 
 # --------------------------------------------------------------------------------------
@@ -73,6 +191,8 @@ class _LnModulate(torch.autograd.Function):
 
 def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     """LayerNorm(x) * (1 + scale) + shift; x [B,T,L,D], shift/scale [B,T,D]."""
+    if _fm_native(x) and x.dtype == torch.bfloat16:
+        return _ln_modulate_fm(x, shift, scale, eps)
     if native.use_native(x):
         return _LnModulate.apply(x, shift, scale, eps)
     return ref.ln_modulate(x, shift, scale, eps)
@@ -108,6 +228,8 @@ class _GateResidual(torch.autograd.Function):
 
 def gate_residual(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """x + gate * y; x,y [B,T,L,D], gate [B,T,D]."""
+    if _fm_native(x) and x.dtype == torch.bfloat16:
+        return _gate_residual_fm(x, gate, y.view_as(x))
     if native.use_native(x):
         return _GateResidual.apply(x, gate, y.view_as(x))
     return ref.gate_residual(x, gate, y.view_as(x))
@@ -154,6 +276,8 @@ class _RmsNormRope(torch.autograd.Function):
 
 def rmsnorm_rope(x: torch.Tensor, weight: torch.Tensor, rope: Optional[RopeTable], eps: float = 1e-6) -> torch.Tensor:
     """Per-head RMSNorm then rotate-half RoPE (if a table is given); x [B,S,H,D]."""
+    if _fm_native(x) and x.dtype == torch.bfloat16 and x.shape[-1] in (64, 128) and _unpack(weight)[1] is None:
+        return _rmsnorm_rope_fm(x, weight, rope, eps)
     if native.use_native(x):
         return _RmsNormRope.apply(x, weight, rope, eps)
     return ref.rmsnorm_rope(x, weight, rope.angles if rope is not None else None, eps)
@@ -400,6 +524,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         if not (x.is_cuda and x.dtype == torch.bfloat16 and not native.forward_mode()):
             raise RuntimeError("a resharded weight can only be used by the bf16 CUDA GEMM (its values live on other ranks)")
         return _LinearGather.apply(x, w, bias, act, info)
+    if _fm_native(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 64 == 0 and w.shape[0] % 8 == 0 \
+            and x.numel() // x.shape[-1] % 8 == 0 and _unpack(w)[1] is None and (bias is None or _unpack(bias)[1] is None):
+        return _linear_fm(x, w, bias, act)
     if x.is_cuda and _native_gemm_ok(x.reshape(-1, x.shape[-1]), w) and x.shape[-1] % 64 == 0 \
             and x.numel() // x.shape[-1] % 8 == 0:
         return _Linear.apply(x, w, bias, act)
@@ -446,8 +573,8 @@ def _ptr_table(weights: Sequence[torch.Tensor]) -> torch.Tensor:
     return t
 
 
-def _skinny_ok(a: torch.Tensor, weights: Sequence[torch.Tensor]) -> bool:
-    if native.forward_mode() or settings.gemm != "native" or not a.is_cuda or not native.available():
+def _skinny_ok(a: torch.Tensor, weights: Sequence[torch.Tensor], ignore_forward_mode: bool = False) -> bool:
+    if (native.forward_mode() and not ignore_forward_mode) or settings.gemm != "native" or not a.is_cuda or not native.available():
         return False
     w0 = weights[0]
     return (w0.dtype in (torch.bfloat16, torch.float32) and all(w.shape == w0.shape and w.dtype == w0.dtype and w.is_contiguous()
@@ -526,6 +653,21 @@ def skinny_linears(a: torch.Tensor, weights: Sequence[torch.Tensor], silu: bool 
     ``add``: [R, <= N] added to the leading columns of every z (the shared AdaLN-LoRA term)."""
     if _skinny_ok(a, weights):
         return _SkinnyLinears.apply(a, add, silu, *weights)
+    if _fm_native(a) and not torch.is_grad_enabled() and _skinny_ok(a, weights, ignore_forward_mode=True) \
+            and all(_unpack(w)[1] is None for w in weights):
+        # value and tangent as stacked rows of one launch; the SiLU runs outside (its derivative scales the tangent)
+        h = F.silu(a.float()) if silu else a.float()
+        ph, th = _unpack(h)
+        padd, tadd = _unpack(add)
+        if th is None and tadd is None:
+            return _SkinnyLinears.apply(ph, padd, False, *weights)
+        R = ph.shape[-2]
+        th = torch.zeros_like(ph) if th is None else th
+        add2 = None
+        if padd is not None:
+            add2 = torch.cat([padd.float(), torch.zeros_like(padd, dtype=torch.float32) if tadd is None else tadd.float()], dim=0)
+        out = _SkinnyLinears.apply(torch.cat([ph, th], dim=-2), add2, False, *weights)
+        return _pack(out[:, :R], out[:, R:])
     h = a.float()
     if silu:
         h = torch.nn.functional.silu(h)

@@ -139,24 +139,32 @@ class PeerAllToAll:
             outs = [o.clone() for o in outs]
         return outs, rstds
 
-    def project_scatter_heads(self, x2d: torch.Tensor, weights, norm_weights, rope, B: int, S: int, eps: float = 1e-6):
+    def project_scatter_heads(self, x2d: torch.Tensor, weights, norm_weights, rope, B: int, S: int, eps: float = 1e-6,
+                              keep_for_backward: bool = False):
         """``x2d [B*S, K] @ w_i^T`` for every projection weight ``w_i [H*128, K]`` with the sequence->head exchange
         as the GEMM epilogue: accumulator rows leave TMEM normalised (``norm_weights[i]``) and rotated (``rope``)
         and are stored straight into the owning rank's staging buffer, so the projected activations never exist
         in sequence layout. One barrier for all projections. The results alias the rotating staging buffers
-        (inference only: consume them before eight more exchanges)."""
+        (consume them before eight more exchanges). ``keep_for_backward`` (training): the results are copied out of the
+        staging buffers, and for every normalised projection the epilogue also stores the raw projection and the reciprocal
+        RMS of every (token, head) locally; returns (heads, raws, rstds) then."""
         P, r = self.ctx.world, self.ctx.rank
         cos, sin = rope.cos_sin() if rope is not None else (None, None)
-        outs = []
+        outs, raws, rstds = [], [], []
         for w, nw in zip(weights, norm_weights):
             H = w.shape[0] // 128
             numel = B * S * w.shape[0]
             slot = self._next(numel)
-            self.ops.gemm_scatter_heads_peer(x2d, w, slot.ptrs, nw, cos if nw is not None else None,
-                                             sin if nw is not None else None, S, r, eps)
+            raw, rstd = self.ops.gemm_scatter_heads_peer(x2d, w, slot.ptrs, nw, cos if nw is not None else None,
+                                                         sin if nw is not None else None, S, r, eps,
+                                                         keep_for_backward and nw is not None)
             native.count_launch()
             outs.append(slot.tensor[:numel].view(B, S * P, H // P, 128))
+            raws.append(raw.view(B, S, H, 128) if raw.numel() else None)
+            rstds.append(rstd.view(B, S, H) if rstd.numel() else None)
         self.ctx.barrier()
+        if keep_for_backward:
+            return [o.clone() for o in outs], raws, rstds
         return outs
 
     def attention_scatter_seq(self, qh: torch.Tensor, kh: torch.Tensor, vh: torch.Tensor, scale: float) -> torch.Tensor:
@@ -172,6 +180,25 @@ class PeerAllToAll:
         native.count_launch()
         self.ctx.barrier()
         return slot.tensor[: qh.numel()].view(B, SP // P, Hl * P, D)
+
+    def head_to_seq_many(self, xs):
+        """``head_to_seq`` of several tensors with one pair of barriers (the three gradients of a q / k / v exchange)."""
+        P, r = self.ctx.world, self.ctx.rank
+        slots = []
+        for x in xs:
+            slot = self._next(x.numel())
+            stage = slot.tensor[: x.numel()].view_as(x)
+            if stage.data_ptr() != x.data_ptr():
+                stage.copy_(x)
+            slots.append(slot)
+        self.ctx.barrier()
+        outs = []
+        for x, slot in zip(xs, slots):
+            B, SP, Hl, D = x.shape
+            outs.append(self.ops.a2a_gather_seq_peer(slot.ptrs, B, SP // P, Hl * P, D, r, x))
+            native.count_launch()
+        self.ctx.barrier()  # peers have finished reading this rank's stages before they are reused
+        return outs
 
     def seq_to_head(self, x: torch.Tensor, copy_out: bool = True) -> torch.Tensor:
         return self.scatter_heads([x], copy_out=copy_out)[0][0]

@@ -128,12 +128,77 @@ class _ScatterHeadsFused(torch.autograd.Function):
         ops_n = native.load()
         q, k, wq, wk, rq, rk = ctx.saved_tensors
         t = ctx.transport
-        dqn, dkn, dv = (t.head_to_seq(g.contiguous()) for g in (dqh, dkh, dvh))
+        dqn, dkn, dv = t.head_to_seq_many([g.contiguous() for g in (dqh, dkh, dvh)])
         cos, sin = ctx.rope.cos_sin() if ctx.rope is not None else (None, None)
         dq, dwq = ops_n.rmsnorm_rope_bwd(dqn, q, wq, rq, cos, sin)
         dk, dwk = ops_n.rmsnorm_rope_bwd(dkn, k, wk, rk, cos, sin)
         native.count_launch(4)
         return dq, dk, dv, dwq.to(wq.dtype), dwk.to(wk.dtype), None, None, None
+
+
+class _ProjectScatterHeads(torch.autograd.Function):
+    """Training form of the GEMM-epilogue exchange: ``x @ Wq^T``, ``x @ Wk^T``, ``x @ Wv^T`` leave their GEMMs normalised,
+    rotated and already in the owners' staging buffers (no projected tensor in sequence layout is read back, no stand-alone
+    exchange kernel); the same epilogue keeps the raw q / k projections and their reciprocal RMS locally for the backward.
+    Backward: head->seq exchange of the three gradients, RMSNorm / RoPE backward kernel, then the input- and weight-gradient
+    GEMMs (a2a_cp.py:120-158 of the reference is the differentiable exchange this replaces)."""
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv, nq, nk, rope, eps, transport):
+        B, S, D = x.shape
+        x2d = x.reshape(B * S, D)
+        x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
+        (qh, kh, vh), (q_raw, k_raw, _), (rq, rk, _) = transport.project_scatter_heads(
+            x2d, [wq, wk, wv], [nq, nk, None], rope, B, S, eps, keep_for_backward=True)
+        ctx.save_for_backward(x2d, wq, wk, wv, nq, nk, q_raw, k_raw, rq, rk)
+        ctx.rope, ctx.transport, ctx.x_shape = rope, transport, x.shape
+        return qh, kh, vh
+
+    @staticmethod
+    def backward(ctx, dqh, dkh, dvh):
+        from ..ops import native
+        from ..ops.functional import gemm_nt
+        ops_n = native.load()
+        x2d, wq, wk, wv, nq, nk, q_raw, k_raw, rq, rk = ctx.saved_tensors
+        t = ctx.transport
+        dqn, dkn, dv = t.head_to_seq_many([g.contiguous() for g in (dqh, dkh, dvh)])
+        cos, sin = ctx.rope.cos_sin() if ctx.rope is not None else (None, None)
+        dq, dnq = ops_n.rmsnorm_rope_bwd(dqn, q_raw, nq, rq, cos, sin)
+        dk, dnk = ops_n.rmsnorm_rope_bwd(dkn, k_raw, nk, rk, cos, sin)
+        native.count_launch(4)
+        M = x2d.shape[0]
+        g2 = [g.reshape(M, -1) for g in (dq, dk, dv)]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_nt(g2[0], wq, None, "none", False, True)
+            dx += gemm_nt(g2[1], wk, None, "none", False, True)
+            dx += gemm_nt(g2[2], wv, None, "none", False, True)
+            dx = dx.view(ctx.x_shape)
+        dws = [gemm_nt(g, x2d, None, "none", True, True) if need else None
+               for g, need in zip(g2, ctx.needs_input_grad[1:4])]
+        return (dx, dws[0], dws[1], dws[2], dnq.to(nq.dtype), dnk.to(nk.dtype), None, None, None)
+
+
+def ulysses_projected_attention_train(x, wq, wk, wv, q_norm_weight, k_norm_weight, rope, group, eps: float = 1e-6,
+                                      scale: Optional[float] = None):
+    """Differentiable self-attention on a sequence shard ``x [B, S_loc, D]`` with the sequence->head exchange in the epilogue of
+    the q / k / v GEMMs; the attention output returns through the head->sequence exchange. Returns [B, S_loc, H, 128]."""
+    t = _peer_transports[id(group)]
+    qh, kh, vh = _ProjectScatterHeads.apply(x, wq, wk, wv, q_norm_weight, k_norm_weight, rope, eps, t)
+    oh = ops.attention(qh, kh, vh, scale)
+    return _HeadToSeq.apply(oh, group)
+
+
+def projected_attention_train_available(x: torch.Tensor, group, head_dim: int) -> bool:
+    """True when the training form of the GEMM-epilogue exchange can run (peer transport attached, bf16 CUDA activations,
+    128-wide heads, native kernels selected, not in forward-mode AD)."""
+    from ..ops import native
+    from ..ops.functional import settings
+    import os
+    return (id(group) in _peer_transports and x.is_cuda and x.dtype == torch.bfloat16 and head_dim == 128
+            and torch.is_grad_enabled() and native.use_native(x) and settings.attention == "native" and settings.gemm == "native"
+            and x.shape[-1] % 64 == 0 and (x.numel() // x.shape[-1]) % 8 == 0
+            and os.environ.get("COSMOS_B200_TRAIN_EXCHANGE", "gemm") == "gemm")
 
 
 def ulysses_attention_fused(q_raw, k_raw, v, q_norm_weight, k_norm_weight, rope, group, eps: float = 1e-6,

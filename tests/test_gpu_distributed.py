@@ -139,20 +139,36 @@ def _projected_scatter_vs_unfused(rank, world):
     ctx.check()
     assert (got_q.float() - want_q.float()).abs().max() < 3e-2
     assert (got_v.float() - want_v.float()).abs().max() < 3e-2
-    # the attention module takes the fused route under no_grad and agrees with its autograd route
+    # the attention module: NCCL exchanges + separate norm kernels (no transport attached) against the GEMM-epilogue exchange in
+    # its training form (outputs and every gradient) and in its inference form
+    from cosmos_predict25_b200.ops import native
     torch.manual_seed(5)
     attn = Attention(K, None, H, D).to(dev).bfloat16()
     attn.init_weights()
     attn.cp_group = g
+    params = [attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight, attn.q_norm.weight, attn.k_norm.weight]
+    xg = x.clone().requires_grad_(True)
+    o_ref = attn(xg, rope=rope)
+    go = torch.randn_like(o_ref)
+    g_ref = torch.autograd.grad(o_ref, [xg] + params, go)
     ulysses.attach_peer_transport(g, t)
-    with torch.enable_grad():
-        o_ref = attn(x.clone().requires_grad_(True), rope=rope).detach()
+    assert ulysses.projected_attention_train_available(xg, g, D)
+    xt = x.clone().requires_grad_(True)
+    o_tr = attn(xt, rope=rope)
+    g_tr = torch.autograd.grad(o_tr, [xt] + params, go)
+    ctx.check()
+    scale_o = max(1.0, o_ref.float().abs().max().item())
+    assert (o_tr.float() - o_ref.float()).abs().max() < 3e-2 * scale_o
+    for name, a, b in zip(("dx", "dWq", "dWk", "dWv", "dnq", "dnk"), g_tr, g_ref):
+        err, ref_max = (a.float() - b.float()).abs().max().item(), b.float().abs().max().item()
+        assert err <= 6e-2 * ref_max + 1e-3, (name, err, ref_max)
     with torch.no_grad():
         assert ulysses.projected_attention_available(x, g, D)
         o = attn(x, rope=rope)
     ulysses.detach_peer_transport(g)
     ctx.check()
-    assert (o.float() - o_ref.float()).abs().max() < 3e-2 * max(1.0, o_ref.float().abs().max().item())
+    assert native_error(rank) == 0
+    assert (o.float() - o_ref.float()).abs().max() < 3e-2 * scale_o
 
 
 def test_projection_gemm_with_exchange_epilogue():

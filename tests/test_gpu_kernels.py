@@ -434,3 +434,69 @@ def test_network_jvp_uses_attention_jvp_kernel(monkeypatch):
     _close(F1, F2, 5e-2, 5e-2, "F")
     _close(dF1, dF2, 8e-2, 8e-2, "dF")
     assert dF2.float().abs().max() > 1e-2
+
+
+@pytest.mark.parametrize("D,L,T", [(256, 12, 3), (2048, 40, 2), (5120, 7, 2)])
+def test_ln_modulate_tangent_kernel(D, L, T):
+    """Value and directional derivative of LayerNorm-modulate in one pass against torch.func.jvp of the fp32 definition."""
+    torch.manual_seed(0)
+    B = 2
+    x, tx = torch.randn(B, T, L, D, device=DEV).bfloat16(), torch.randn(B, T, L, D, device=DEV).bfloat16()
+    sh, sc, tsh, tsc = (0.3 * torch.randn(B, T, D, device=DEV) for _ in range(4))
+    y, ty = _ops().ln_modulate_jvp(x.view(-1, D), tx.view(-1, D), sh.view(-1, D), sc.view(-1, D), tsh.view(-1, D), tsc.view(-1, D), L, 1e-6)
+    assert ty.data_ptr() == y.data_ptr() + y.numel() * 2, "value and tangent must be adjacent for the stacked GEMM"
+    yr, tyr = torch.func.jvp(lambda a, b, c: ref.ln_modulate(a, b, c), (x.float(), sh, sc), (tx.float(), tsh, tsc))
+    _close(y.view(B, T, L, D), yr, 2e-2, 2e-2, "y")
+    _close(ty.view(B, T, L, D), tyr, 3e-2, 3e-2, "ty")
+    y0, ty0 = _ops().ln_modulate_jvp(x.view(-1, D), tx.view(-1, D), sh.view(-1, D), sc.view(-1, D), None, None, L, 1e-6)
+    _, tyr0 = torch.func.jvp(lambda a: ref.ln_modulate(a, sh, sc), (x.float(),), (tx.float(),))
+    _close(ty0.view(B, T, L, D), tyr0, 3e-2, 3e-2, "ty without modulation tangents")
+    _no_kernel_error()
+
+
+@pytest.mark.parametrize("HD,rope", [(128, True), (128, False), (64, True)])
+def test_rmsnorm_rope_tangent_kernel(HD, rope):
+    torch.manual_seed(0)
+    B, S, H = 2, 37, 3
+    x, tx = torch.randn(B, S, H, HD, device=DEV).bfloat16(), torch.randn(B, S, H, HD, device=DEV).bfloat16()
+    w = 1 + 0.1 * torch.randn(HD, device=DEV)
+    half = torch.randn(S, HD // 2, device=DEV)
+    table = F_ops.RopeTable(torch.cat([half, half], -1)) if rope else None
+    cos, sin = table.cos_sin() if rope else (None, None)
+    y, ty = _ops().rmsnorm_rope_jvp(x, tx, w, cos, sin, 1e-6)
+    yr, tyr = torch.func.jvp(lambda a: ref.rmsnorm_rope(a, w, table.angles if rope else None, 1e-6), (x.float(),), (tx.float(),))
+    _close(y, yr, 2e-2, 2e-2, "y")
+    _close(ty, tyr, 3e-2, 3e-2, "ty")
+    _no_kernel_error()
+
+
+def test_network_jvp_runs_on_native_kernels(monkeypatch):
+    """Forward-mode through the DiT with every block op on this package's kernels (tangent kernels, GEMMs on stacked value /
+    tangent rows, JVP attention, few-row GEMM) against the same pass on torch ops (library GEMMs, eager element-wise)."""
+    from cosmos_predict25_b200.models.distill import network_jvp
+    from cosmos_predict25_b200.models.dit import CosmosDiT, dit_mini
+    torch.manual_seed(0)
+    net = CosmosDiT(dit_mini(crossattn_proj_in_channels=256)).to(DEV)
+    net.init_weights()
+    for blk in net.blocks:
+        for m in blk.adaln_mlps():
+            torch.nn.init.normal_(m[-1].weight, std=0.05)
+    torch.nn.init.normal_(net.final_layer.linear.weight, std=0.05)
+    net = net.bfloat16()
+    x = torch.randn(1, 16, 2, 16, 16, device=DEV).bfloat16()
+    t = torch.full((1, 1), 400.0, device=DEV)
+    tx, tt = torch.randn_like(x), torch.full_like(t, 1000.0)
+    kw = dict(crossattn_emb=torch.randn(1, 16, 256, device=DEV).bfloat16(), fps=torch.tensor([16.0], device=DEV),
+              padding_mask=torch.zeros(1, 1, 16, 16, device=DEV))
+    before = native.launches()
+    F1, dF1 = network_jvp(net, x, t, tx, tt, **kw)
+    per_block = 3 + 4 + 2 + 2 + 3 + 2          # LN tangent, GEMMs (stacked q/k/v + out), norm tangent, attention, ... (lower bound)
+    assert native.launches() - before >= len(net.blocks) * per_block, native.launches() - before
+    _no_kernel_error()
+    monkeypatch.setattr(F_ops.settings, "gemm", "cublas")        # switches the forward-mode fast paths off
+    mid = native.launches()
+    F2, dF2 = network_jvp(net, x, t, tx, tt, **kw)
+    assert native.launches() - mid < (native.launches() - before) // 2
+    _close(F1, F2, 5e-2, 5e-2, "F")
+    _close(dF1, dF2, 1e-1, 1e-1, "dF")
+    assert dF2.float().abs().max() > 1e-2
