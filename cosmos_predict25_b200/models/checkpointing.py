@@ -44,10 +44,11 @@ def _attention_ops():
               "_scaled_dot_product_efficient_attention", "_scaled_dot_product_flash_attention_for_cpu"):
         if hasattr(aten, n):
             names.append(getattr(aten, n).default)
-    try:
-        names.append(torch.ops.cosmos_b200.fa_fwd.default)
-    except (AttributeError, RuntimeError):
-        pass
+    for n in ("fa_fwd", "fa_fwd_na"):
+        try:
+            names.append(getattr(torch.ops.cosmos_b200, n).default)
+        except (AttributeError, RuntimeError):
+            pass
     return set(names)
 
 

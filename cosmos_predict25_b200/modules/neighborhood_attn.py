@@ -129,6 +129,7 @@ class TilePlan:
         need = (tile_any[0][:, None, None, :, None, None] & tile_any[1][None, :, None, None, :, None]
                 & tile_any[2][None, None, :, None, None, :]).reshape(nT * nH * nW, nT * nH * nW)
         n_tiles = need.shape[0]
+        need_all = need                                                          # [query tile, key tile], before padding
         if n_tiles % 2:
             need = torch.cat([need, torch.zeros(1, n_tiles, dtype=torch.bool)], 0)
         block_need = need[0::2] | need[1::2]                                    # a CTA serves two consecutive query tiles
@@ -142,6 +143,29 @@ class TilePlan:
         self.kv_cnt = cnt.to(torch.int32).contiguous().to(device)
         self.bt, self.bh, self.bw = (t.contiguous().to(device) for t in tables)
         self.visited_fraction = float(cnt.sum()) / float(block_need.shape[0] * n_tiles)
+        # ---- backward: a CTA owns a key tile and walks the query tiles that see it. Tables: for one key coordinate and one query
+        # tile, the visibility bits of the tile's query coordinates; list entries carry the top bit when the whole pair is visible.
+        tables_b, full_axis = [], []
+        for m, L, t in zip(vis, video_size, TILE):
+            gT = m.t().contiguous().view(L, L // t, t)                          # [key, query tile, query in tile]
+            weights = (1 << torch.arange(t)).view(1, 1, t)
+            tables_b.append((gT.long() * weights).sum(-1).to(torch.uint8))
+            full_axis.append(m.view(L // t, t, L // t, t).permute(0, 2, 1, 3).reshape(L // t, L // t, t * t).all(-1))
+        full = (full_axis[0][:, None, None, :, None, None] & full_axis[1][None, :, None, None, :, None]
+                & full_axis[2][None, None, :, None, None, :]).reshape(n_tiles, n_tiles)
+        need_b, full_b = need_all.t().contiguous(), full.t().contiguous()       # [key tile, query tile]
+        cnt_b = need_b.sum(1)
+        assert int(cnt_b.min()) >= 1                                            # every tile sees itself
+        max_nb = int(cnt_b.max())
+        order_b = torch.argsort((~need_b).to(torch.int8), dim=1, stable=True)[:, :max_nb]
+        last_b = order_b.gather(1, (cnt_b - 1)[:, None])
+        order_b = torch.where(torch.arange(max_nb)[None, :] >= cnt_b[:, None], last_b.expand_as(order_b), order_b)
+        entries = torch.where(full_b.gather(1, order_b), order_b - (1 << 31), order_b)
+        self.q_list = entries.to(torch.int32).contiguous().to(device)
+        self.q_cnt = cnt_b.to(torch.int32).contiguous().to(device)
+        self.bt_b, self.bh_b, self.bw_b = (t.contiguous().to(device) for t in tables_b)
+        L = T * H * W
+        self.perm = self.to_tiles(torch.arange(L).view(1, L, 1, 1)).reshape(L).to(device)   # tile-order position -> natural index
 
     def to_tiles(self, x: torch.Tensor) -> torch.Tensor:
         """[B, T*H*W, heads, D] in (t, h, w) order -> the same tokens tile by tile (the order in which the kernel numbers
@@ -166,13 +190,45 @@ def tile_plan(video_size, window, stride, is_causal, device) -> TilePlan:
     return _plans[key]
 
 
+class _TileNeighborhoodAttention(torch.autograd.Function):
+    """Tile-sparse forward kernel on the natural layout; backward on the tile-sparse single-pass kernel, which wants every
+    128-row tile contiguous: the operands are brought into tile order (one copy each) and the gradients back."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, plan, scale):
+        from ..ops import native
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = native.load().fa_fwd_na(q, k, v, scale, plan.kv_idx, plan.kv_cnt, plan.bt, plan.bh, plan.bw)
+        native.count_launch()
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.plan, ctx.scale = plan, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from ..ops import native
+        q, k, v, o, lse = ctx.saved_tensors
+        plan = ctx.plan
+        qt, kt, vt, ot, dot = (plan.to_tiles(x).contiguous() for x in (q, k, v, o, do))
+        lse_t = lse.index_select(2, plan.perm).contiguous()
+        dq, dk, dv = native.load().fa_bwd_na(dot, qt, kt, vt, ot, lse_t, ctx.scale, plan.q_list, plan.q_cnt,
+                                             plan.bt_b, plan.bh_b, plan.bw_b)
+        native.count_launch(3)
+        return plan.from_tiles(dq), plan.from_tiles(dk), plan.from_tiles(dv), None, None
+
+
 def tile_kernel_supported(q: torch.Tensor, video_size, dilation) -> bool:
     from ..ops import native
     T, H, W = video_size
     return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and native.use_native(q)
-            and not (torch.is_grad_enabled() and q.requires_grad) and all(d == 1 for d in dilation)
+            and all(d == 1 for d in dilation)
             and T % TILE[0] == 0 and H % TILE[1] == 0 and W % TILE[2] == 0
             and native.available() and hasattr(native.load(), "fa_fwd_na"))
+
+
+def _tile_backward_available() -> bool:
+    from ..ops import native
+    return native.available() and hasattr(native.load(), "fa_bwd_na")
 
 
 def _group_starts(L: int, k: int, s: int) -> torch.Tensor:
@@ -234,7 +290,8 @@ def neighborhood_attention(q, k, v, video_size, window, stride=1, dilation=1, is
     """q, k, v: [B, T*H*W, heads, D] -> [B, T*H*W, heads, D]."""
     stride, dilation, is_causal = _triple(stride, int), _triple(dilation, int), _triple(is_causal, bool)
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if not tile_kernel_supported(q, video_size, dilation) or k.requires_grad or v.requires_grad:
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if not tile_kernel_supported(q, video_size, dilation) or (needs_grad and not _tile_backward_available()):
         # training / CPU: gather the shared key box of every stride group when the configuration allows it (cost follows the
         # window), otherwise the dense-masked definition
         if grouped_attention_supported(video_size, window, stride, dilation, is_causal) and q.shape[1] > 4096:
@@ -242,6 +299,8 @@ def neighborhood_attention(q, k, v, video_size, window, stride=1, dilation=1, is
         return neighborhood_attention_reference(q, k, v, video_size, window, stride, dilation, is_causal, scale)
     from ..ops import native
     plan = tile_plan(video_size, window, stride, is_causal, q.device)
+    if needs_grad:
+        return _TileNeighborhoodAttention.apply(q, k, v, plan, scale)
     o, _ = native.load().fa_fwd_na(q.contiguous(), k.contiguous(), v.contiguous(), scale, plan.kv_idx, plan.kv_cnt,
                                    plan.bt, plan.bh, plan.bw)
     native.count_launch()

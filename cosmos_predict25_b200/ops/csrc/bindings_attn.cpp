@@ -88,6 +88,46 @@ std::tuple<Tensor, Tensor> fa_fwd_na(const Tensor& q, const Tensor& k, const Ten
   return {o, lse};
 }
 
+// Gradients of the neighbourhood attention. Every tensor is in TILE order (tile = one 4 x 4 x 8 token box, row dt*32 + dh*8 + dw;
+// ``TilePlan.to_tiles``), lse [B, H, S] in the same order. q_list [S/128, max_n] int32: the query tiles that see each key tile
+// (top bit set: the whole pair is visible), q_cnt [S/128]; bt/bh/bw: uint8 [4 nT, nT], [4 nH, nH], [8 nW, nW] with, for one key
+// coordinate and one query tile, the visibility bits of the tile's query coordinates. Returns (dq, dk, dv) in tile order.
+std::tuple<Tensor, Tensor, Tensor> fa_bwd_na(const Tensor& d_o, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                             const Tensor& lse, double scale, const Tensor& q_list, const Tensor& q_cnt,
+                                             const Tensor& bt, const Tensor& bh, const Tensor& bw) {
+  check_qkv(d_o, "do");
+  check_qkv(q, "q");
+  check_qkv(k, "k");
+  check_qkv(v, "v");
+  check_qkv(o, "o");
+  TORCH_CHECK(q.sizes() == k.sizes() && k.sizes() == v.sizes() && o.sizes() == q.sizes() && d_o.sizes() == q.sizes(),
+              "neighbourhood attention is self-attention: equal shapes");
+  const int B = (int)q.size(0), S = (int)q.size(1), H = (int)q.size(2);
+  TORCH_CHECK(S % 128 == 0, "sequence must be whole 128-token tiles");
+  const int n_tiles = S / 128;
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == (int64_t)B * H * S,
+              "lse must be contiguous fp32 [B,H,S]");
+  for (const Tensor* t : {&q_list, &q_cnt})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous(), "tile lists must be contiguous CUDA int32");
+  for (const Tensor* t : {&bt, &bh, &bw})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kByte && t->is_contiguous() && t->dim() == 2, "visibility tables: CUDA uint8 2-D");
+  TORCH_CHECK(q_list.dim() == 2 && q_list.size(0) == n_tiles && q_list.size(1) >= 1 && q_cnt.numel() == n_tiles,
+              "one query-tile list per key tile");
+  const int nT = (int)bt.size(1), nH = (int)bh.size(1), nW = (int)bw.size(1);
+  TORCH_CHECK((int64_t)nT * nH * nW == n_tiles && bt.size(0) == 4 * nT && bh.size(0) == 4 * nH && bw.size(0) == 8 * nW,
+              "tables do not match the tile grid");
+  c10::cuda::CUDAGuard g(q.device());
+  Tensor dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
+  Tensor scratch = at::empty({(int64_t)cb200_fa_bwd_na_scratch_floats(B, S, H)}, q.options().dtype(at::kFloat));
+  const int rc = cb200_fa_bwd_na(d_o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), scratch.data_ptr<float>(), B, S, H, (float)scale,
+                                 q_list.data_ptr<int>(), q_cnt.data_ptr<int>(), (int)q_list.size(1), bt.data_ptr<uint8_t>(),
+                                 bh.data_ptr<uint8_t>(), bw.data_ptr<uint8_t>(), nT, nH, nW, cb200_error_word(q.get_device()),
+                                 at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "fa_bwd_na launch failed with code ", rc);
+  return {dq, dk, dv};
+}
+
 std::tuple<Tensor, Tensor> fa_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale) {
   return fa_fwd_variant(q, k, v, scale, 0);
 }
@@ -156,7 +196,9 @@ void register_attention_ops(torch::Library& m) {
   // activation checkpointing keeps the attention output by intercepting this op) see the call.
   m.def("fa_fwd(Tensor q, Tensor k, Tensor v, float scale) -> (Tensor, Tensor)");
   m.def("fa_fwd_na(Tensor q, Tensor k, Tensor v, float scale, Tensor kv_idx, Tensor kv_cnt, Tensor bt, Tensor bh, Tensor bw) -> "
-        "(Tensor, Tensor)", &fa_fwd_na);
+        "(Tensor, Tensor)");
+  m.def("fa_bwd_na(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, Tensor q_list, Tensor q_cnt, Tensor bt, "
+        "Tensor bh, Tensor bw) -> (Tensor, Tensor, Tensor)", &fa_bwd_na);
   m.def("fa_fwd_scatter_seq_peer(Tensor q, Tensor k, Tensor v, float scale, int[] out_ptrs, int rank) -> Tensor",
         &fa_fwd_scatter_seq_peer);
   m.def("fa_bwd(Tensor do, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale) -> (Tensor, Tensor, Tensor)");
@@ -168,6 +210,7 @@ void register_attention_ops(torch::Library& m) {
 
 TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
   m.impl("fa_fwd", &fa_fwd);
+  m.impl("fa_fwd_na", &fa_fwd_na);
   m.impl("fa_bwd", &fa_bwd);
   m.impl("fa_fwd_variant", &fa_fwd_variant);
   m.impl("fa_bwd_variant", &fa_bwd_variant);

@@ -642,3 +642,29 @@ extern "C" int cb200_fa_bwd_v(const void* d_o, const void* q, const void* k, con
                                                          scale, err);
   return (int)cudaGetLastError();
 }
+
+// Neighbourhood attention backward on tensors in tile order (see cb200_fa_bwd_tile_na): statistics, tile-sparse single-pass
+// kernel, dQ conversion. scratch: 2 * B * H * S + B * S * H * 128 floats.
+extern "C" int cb200_fa_bwd_tile_na(const void* d_o, const void* q, const void* k, const void* v, const float* lse2, const float* delta,
+                                    float* dq_acc, void* dk, void* dv, int B, int S, int H, float scale, const int* q_list,
+                                    const int* q_cnt, int max_n, const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT, int nH,
+                                    int nW, int* err, cudaStream_t st);
+
+extern "C" long cb200_fa_bwd_na_scratch_floats(int B, int S, int H) { return 2L * B * H * S + (long)B * S * H * 128; }
+
+extern "C" int cb200_fa_bwd_na(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
+                               void* dk, void* dv, float* scratch, int B, int S, int H, float scale, const int* q_list,
+                               const int* q_cnt, int max_n, const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT, int nH,
+                               int nW, int* err, cudaStream_t st) {
+  if (S % 128 != 0) return -41;
+  float* delta = scratch;
+  float* lse2 = scratch + (size_t)B * H * S;
+  float* acc = scratch + 2 * (size_t)B * H * S;
+  const long rows = (long)B * H * S;
+  fa_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const bf16*)o, (const bf16*)d_o, lse, delta, lse2, B, S, H, S, -1.f);
+  const int rc = cb200_fa_bwd_tile_na(d_o, q, k, v, lse2, delta, acc, dk, dv, B, S, H, scale, q_list, q_cnt, max_n, bt, bh, bw, nT, nH, nW,
+                                      err, st);
+  if (rc) return rc;
+  cb200_fa_bwd_dq_convert(acc, dq, B, S, H, scale, st);
+  return (int)cudaGetLastError();
+}

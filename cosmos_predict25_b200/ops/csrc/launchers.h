@@ -64,6 +64,12 @@ int cb200_fa_fwd_scatter_seq(const void* q, const void* k, const void* v, const 
 int cb200_fa_fwd_na(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int H, float scale,
                     const int* kv_idx, const int* kv_cnt, int max_n, const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT,
                     int nH, int nW, int* err, cudaStream_t st);
+// neighbourhood attention backward; every tensor in tile order (128-row tile = one 4 x 4 x 8 token box); q_list [S/128][max_n]
+// (top bit: whole tile pair visible), q_cnt [S/128]; transposed visibility tables bt [4 nT][nT], bh [4 nH][nH], bw [8 nW][nW]
+long cb200_fa_bwd_na_scratch_floats(int B, int S, int H);
+int cb200_fa_bwd_na(const void* d_o, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq, void* dk,
+                    void* dv, float* scratch, int B, int S, int H, float scale, const int* q_list, const int* q_cnt, int max_n,
+                    const uint8_t* bt, const uint8_t* bh, const uint8_t* bw, int nT, int nH, int nW, int* err, cudaStream_t st);
 int cb200_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Skv, int H, float scale,
                  int variant, int* err, cudaStream_t st);
 }

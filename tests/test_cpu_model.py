@@ -296,3 +296,29 @@ def test_batched_adaln_equals_per_mlp_modulation():
         many.square().sum().backward()
         assert all(p.grad is not None and p.grad.abs().sum() > 0 for m in mlps for p in m.parameters())
         assert lora is None or lora.grad is not None
+
+
+def test_neighborhood_backward_plan_matches_dense_mask():
+    """Host plan of the tile-sparse backward kernel (query-tile lists per key tile, transposed per-axis bit tables) rebuilt into a
+    dense mask equals the definition."""
+    from cosmos_predict25_b200.modules.neighborhood_attn import TilePlan, neighborhood_mask
+    vs, win, st, causal = (8, 8, 16), (3, 5, 9), (1, 2, 3), (True, False, False)
+    plan = TilePlan(vs, win, st, causal, torch.device("cpu"))
+    L = vs[0] * vs[1] * vs[2]
+    nT, nH, nW = plan.n
+    want = neighborhood_mask(vs, win, st, 1, causal)[plan.perm][:, plan.perm]          # [query, key] in tile order
+    got = torch.zeros_like(want)
+    row = torch.arange(128)
+    col = torch.arange(128)
+    for kt in range(L // 128):
+        k_t, k_h, k_w = (kt // (nH * nW)) * 4 + (row >> 5), ((kt // nW) % nH) * 4 + ((row >> 3) & 3), (kt % nW) * 8 + (row & 7)
+        for i in range(int(plan.q_cnt[kt])):
+            e = int(plan.q_list[kt, i])
+            qt = e & 0x7FFFFFFF
+            bt = plan.bt_b[k_t, qt // (nH * nW)].long()[:, None]
+            bh = plan.bh_b[k_h, (qt // nW) % nH].long()[:, None]
+            bw = plan.bw_b[k_w, qt % nW].long()[:, None]
+            vis = ((bt >> (col >> 5)[None]) & (bh >> ((col >> 3) & 3)[None]) & (bw >> (col & 7)[None]) & 1).bool()   # [key row, query col]
+            assert not e < 0 or bool(vis.all())
+            got[qt * 128:(qt + 1) * 128, kt * 128:(kt + 1) * 128] = vis.t()
+    assert torch.equal(got, want)

@@ -209,6 +209,35 @@ def test_neighborhood_attention_kernel(vs, window, stride, causal):
     _close(got, want, 2e-2, 2e-2, "neighbourhood attention")
 
 
+@pytest.mark.parametrize("vs,window,stride,causal", [
+    ((8, 8, 16), (4, 4, 8), 1, False),                       # every visited tile pair partly masked
+    ((4, 12, 24), (4, 8, 16), (1, 4, 8), False),             # 9 tiles, stride = tile
+    ((8, 8, 16), (3, 5, 7), (1, 2, 3), (True, False, False)),  # causal in time, odd windows
+    ((4, 4, 8), (4, 4, 8), 1, False),                        # one tile, whole-axis windows = dense attention (fully visible pair)
+    ((8, 16, 32), (8, 12, 24), 1, False),                    # 32 tiles, wide windows: fully visible pairs beside masked ones
+])
+def test_neighborhood_attention_backward_kernel(vs, window, stride, causal):
+    """Gradients of the tile-sparse kernels (forward + single-pass tile-sparse backward) against autograd through the dense-masked
+    fp32 definition."""
+    from cosmos_predict25_b200.modules import neighborhood_attn as na
+    torch.manual_seed(12)
+    L, H = vs[0] * vs[1] * vs[2], 2
+    q, k, v = (torch.randn(1, L, H, 128, device=DEV).bfloat16().requires_grad_(True) for _ in range(3))
+    assert na.tile_kernel_supported(q, vs, (1, 1, 1)) and na._tile_backward_available()
+    before = native.launches()
+    got = na.neighborhood_attention(q, k, v, vs, window, stride, 1, causal)
+    do = torch.randn_like(got)
+    gq, gk, gv = torch.autograd.grad(got, (q, k, v), do)
+    assert native.launches() - before >= 4, "the tile-sparse kernels did not serve forward and backward"
+    _no_kernel_error()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    want = na.neighborhood_attention_reference(qr, kr, vr, vs, window, stride, 1, causal)
+    wq, wk, wv = torch.autograd.grad(want, (qr, kr, vr), do.float())
+    _close(got, want, 2e-2, 2e-2, "o")
+    for name, a, b in (("dq", gq, wq), ("dk", gk, wk), ("dv", gv, wv)):
+        _close(a, b, 3e-2 * b.abs().max().item() + 1e-3, 3e-2, name)
+
+
 # tuning variants of the forward kernel: 1 = all exponentials on the special-function unit, whole-row hand-off; 2-6 = polynomial
 # share 0..3 of 4 pairs with / without the half-row hand-off; 7, 8 = one query tile per CTA (short key sequences);
 # 9-11 = with register re-division between the warpgroups
