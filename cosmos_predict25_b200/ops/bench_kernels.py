@@ -116,6 +116,10 @@ def main():
             b = torch.randn(Nn, K, device=dev).bfloat16()
             fl = 2.0 * M * Nn * K
             add("gemm_tcgen05 nt", f"{M}x{Nn}x{K} {tag}", time_ms(lambda: ops.gemm_bf16(a, b, None, 0, False, False)), fl)
+            prev = ops.gemm_pair_mode(1 - ops.gemm_pair_mode(-1))          # the other tile mode (CTA pairs <-> single CTA)
+            add(f"gemm_tcgen05 nt, {'CTA pairs (256 x 256 per cluster)' if prev == 0 else 'single-CTA tiles'}", f"{M}x{Nn}x{K} {tag}",
+                time_ms(lambda: ops.gemm_bf16(a, b, None, 0, False, False)), fl)
+            ops.gemm_pair_mode(prev)
             add("cublas nt (twin)", f"{M}x{Nn}x{K}", time_ms(lambda: torch.matmul(a, b.T)), fl)
         a = torch.randn(N, D, device=dev).bfloat16()
         b = torch.randn(Fm, D, device=dev).bfloat16()
@@ -125,6 +129,12 @@ def main():
         add("cublas dgrad (twin)", f"{N}x{D}x{Fm}", time_ms(lambda: torch.matmul(dy, b)), 2.0 * N * Fm * D)
         add("gemm_tcgen05 wgrad (both mn-major)", f"{Fm}x{D}x{N}", time_ms(lambda: ops.gemm_bf16(dy, a, None, 0, True, True)), 2.0 * N * Fm * D)
         add("cublas wgrad (twin)", f"{Fm}x{D}x{N}", time_ms(lambda: torch.matmul(dy.T, a)), 2.0 * N * Fm * D)
+        prev = ops.gemm_pair_mode(1 - ops.gemm_pair_mode(-1))
+        tagp = "CTA pairs" if prev == 0 else "single-CTA tiles"
+        add(f"gemm_tcgen05 nt +gelu(+pre), {tagp}", f"{N}x{Fm}x{D}", time_ms(lambda: ops.gemm_bf16_gelu_pre(a, b, None)), 2.0 * N * Fm * D)
+        add(f"gemm_tcgen05 dgrad, {tagp}", f"{N}x{D}x{Fm}", time_ms(lambda: ops.gemm_bf16(dy, b, None, 0, False, True)), 2.0 * N * Fm * D)
+        add(f"gemm_tcgen05 wgrad, {tagp}", f"{Fm}x{D}x{N}", time_ms(lambda: ops.gemm_bf16(dy, a, None, 0, True, True)), 2.0 * N * Fm * D)
+        ops.gemm_pair_mode(prev)
         del a, b, dy
     if want("attention"):
         heads = args.heads or (2 if args.quick else H)

@@ -456,6 +456,9 @@ Tensor skinny_bgemm(const Tensor& a, int64_t a_z, int64_t a_r, int64_t a_k, cons
   return c;
 }
 
+// tile mode of the GEMM: 0 single-CTA 128 x 256 tiles, 1 CTA pairs (256 x 256 per pair), -1 only reads; returns the previous mode
+int64_t gemm_pair_mode(int64_t mode) { return cb200_gemm_pair_mode((int)mode); }
+
 int64_t kernel_error(int64_t device, bool clear) {
   int v = 0;
   int* w = error_word((int)device);
@@ -499,6 +502,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("rmsnorm_rope_jvp(Tensor x, Tensor tx, Tensor w, Tensor? cos, Tensor? sin, float eps) -> (Tensor, Tensor)", &rmsnorm_rope_jvp);
   m.def("skinny_bgemm(Tensor a, int a_z, int a_r, int a_k, Tensor? b_ptrs, Tensor? b, int b_z, int b_n, int b_k, bool b_bf16, "
         "Tensor? add, int add_cols, int Z, int R, int N, int K, bool silu_a, bool silu_b, bool out_bf16, int ksplit) -> Tensor", &skinny_bgemm);
+  m.def("gemm_pair_mode(int mode) -> int", &gemm_pair_mode);
   m.def("kernel_error(int device, bool clear) -> int", &kernel_error);
   register_attention_ops(m);
   register_peer_ops(m);

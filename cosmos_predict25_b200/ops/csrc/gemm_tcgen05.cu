@@ -29,6 +29,9 @@
 #include <math.h>
 
 #include "launchers.h"
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100.cuh"
 #include "tmap.h"
@@ -93,44 +96,61 @@ __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-template <int A_MN, int B_MN, bool GATHER>
+// CTA2: two CTAs of a cluster share one 256 x 256 output tile (tcgen05 cta_group::2). CTA r of the pair loads rows
+// [128 r, 128 r + 128) of the A tile and of the B tile into its own shared memory (half the B bytes per CTA and per MMA), the even
+// CTA issues M = 256 MMAs that read both shared memories, each CTA's TMEM receives its 128 rows and its epilogue warps drain them.
+// Six 32 KB stages instead of four 48 KB ones.
+template <int A_MN, int B_MN, bool GATHER, bool CTA2 = false>
 __global__ void __launch_bounds__(kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, int M, int N, int K,
                  GemmEpilogue ep, GatherB gb, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* full = bars;                    // [kStages]
-  uint64_t* empty = bars + kStages;         // [kStages]
-  uint64_t* acc_full = bars + 2 * kStages;  // [2]
+  static_assert(!(CTA2 && GATHER), "the gather mode runs on single-CTA tiles");
+  constexpr int STG = CTA2 ? 6 : kStages;                                   // pipeline stages
+  constexpr int STG_BYTES = CTA2 ? (kABytes + kBBytes / 2) : kStageBytes;   // bytes per stage in this CTA
+  constexpr int TM = CTA2 ? 2 * BM : BM;                                    // output rows per tile (per pair with CTA2)
+  static_assert(STG * STG_BYTES == kStages * kStageBytes, "both layouts fill the same shared-memory window");
+  const uint32_t pair_rank = CTA2 ? cluster_ctarank() : 0u;
+  const int first_tile = CTA2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, tile_step = CTA2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STG * STG_BYTES);
+  uint64_t* full = bars;                    // [STG]
+  uint64_t* empty = bars + STG;             // [STG]
+  uint64_t* acc_full = bars + 2 * STG;      // [2]
   uint64_t* acc_empty = acc_full + 2;       // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // the shuffle makes the warp index (and every role branch below) provably warp-uniform for the compiler
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int tiles_m = (M + TM - 1) / TM, tiles_n = (N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < STG; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);
+      mbar_init(&acc_empty[a], CTA2 ? 16 : 8);      // the pair leader hears from the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if (CTA2) {
+      tmem_alloc_pair(tmem_slot, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();      // the other CTA's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -156,8 +176,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (g < 128) seen[g >> 6] |= 1ull << (g & 63);
         return true;
       };
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+      for (int t = first_tile; t < n_tiles && ok; t += tile_step) {
+        // with CTA2 this CTA fetches its 128 rows of the pair's A tile and its 128 rows of the B tile
+        const int m0 = (t / tiles_n) * TM + (CTA2 ? (int)pair_rank * BM : 0), n0 = (t % tiles_n) * BN + (CTA2 ? (int)pair_rank * (BN / 2) : 0);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (GATHER) {
             // rows of the weight this stage reads: an N tile of 256 rows (forward) or 64 rows of the contraction dimension (dgrad)
@@ -166,23 +187,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             } else if (!group_ready(kb * BK)) { ok = false; break; }
           }
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sa = smem + s * STG_BYTES;
           uint8_t* sb = sa + kABytes;
-          mbar_arrive_expect_tx(&full[s], kStageBytes);
           const int k0 = kb * BK;
-          if (A_MN == 0) {
-            tma_load_2d(sa, &tma_a, &full[s], k0, m0);
-          } else {
+          if (CTA2) {
+            // all bytes of the pair's stage are counted on the leader's barrier: the leader announces them, both CTAs load
+            if (pair_rank == 0) mbar_arrive_expect_tx(&full[s], 2 * STG_BYTES);
+            const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
+            if (A_MN == 0) {
+              tma_load_2d_pair(sa, &tma_a, bar, k0, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, &full[s], m0 + j * 64, k0);
-          }
-          if (B_MN == 0) {
-            tma_load_2d(sb, &tma_b, &full[s], k0, n0);
-          } else {
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tma_a, bar, m0 + j * 64, k0);
+            }
+            if (B_MN == 0) {
+              tma_load_2d_pair(sb, &tma_b, bar, k0, n0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, &full[s], n0 + j * 64, k0);
+              for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sb + j * 8192, &tma_b, bar, n0 + j * 64, k0);
+            }
+          } else {
+            mbar_arrive_expect_tx(&full[s], kStageBytes);
+            if (A_MN == 0) {
+              tma_load_2d(sa, &tma_a, &full[s], k0, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, &full[s], m0 + j * 64, k0);
+            }
+            if (B_MN == 0) {
+              tma_load_2d(sb, &tma_b, &full[s], k0, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, &full[s], n0 + j * 64, k0);
+            }
           }
-          if (++s == kStages) { s = 0; ph ^= 1; }
+          if (++s == STG) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) { atomicCAS(err, 0, 1); *abort_flag = 1; }
@@ -194,7 +233,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     {
       const uint32_t leader = elect_one() ? 1u : 0u;
       auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)); };
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = umma_idesc_bf16(TM, BN, A_MN, B_MN);
       // stage-0 descriptors; a stage / k-slice is a constant added to the address field (16-byte units)
       const uint64_t da0 = A_MN ? umma_desc_sw128(smem_u32(smem), 8192, 1024) : umma_desc_sw128(smem_u32(smem), 16, 1024);
       const uint64_t db0 = B_MN ? umma_desc_sw128(smem_u32(smem) + kABytes, 8192, 1024) : umma_desc_sw128(smem_u32(smem) + kABytes, 16, 1024);
@@ -203,25 +242,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      for (int t = first_tile; t < n_tiles && ok && pair_rank == 0; t += tile_step) {     // only the pair leader issues
         if (!wait_all(&acc_empty[acc], acc_ph ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!wait_all(&full[s], ph)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t da_s = da0 + (uint64_t)(s * (kStageBytes >> 4)), db_s = db0 + (uint64_t)(s * (kStageBytes >> 4));
+          const uint64_t da_s = da0 + (uint64_t)(s * (STG_BYTES >> 4)), db_s = db0 + (uint64_t)(s * (STG_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
             const uint64_t da = da_s + (uint32_t)((A_MN ? k * (UK * 128) : k * (UK * 2)) >> 4);
             const uint64_t db = db_s + (uint32_t)((B_MN ? k * (UK * 128) : k * (UK * 2)) >> 4);
-            umma_ss_w(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u, leader);
+            if (CTA2) umma_ss_pair_w(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u, leader);
+            else umma_ss_w(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u, leader);
           }
-          umma_commit_w(&empty[s], leader);  // slot reusable once these MMAs have read it
-          if (++s == kStages) { s = 0; ph ^= 1; }
+          // slot reusable once these MMAs have read it (with CTA2: in both CTAs)
+          if (CTA2) umma_commit_pair_w(&empty[s], leader);
+          else umma_commit_w(&empty[s], leader);
+          if (++s == STG) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit_w(&acc_full[acc], leader);
+        if (CTA2) umma_commit_pair_w(&acc_full[acc], leader);
+        else umma_commit_w(&acc_full[acc], leader);
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
       }
       if (!ok && lane == 0) { atomicCAS(err, 0, 2); *abort_flag = 1; }
@@ -273,14 +316,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;      // TMEM lanes [32*quarter, 32*quarter + 32)
     const int part = (warp - 2) >> 2;  // accumulator columns [128*part, 128*part + 128)
-    uint8_t* stage_warp = smem + kStages * kStageBytes + 256 + (warp - 2) * (32 * 128);
+    uint8_t* stage_warp = smem + STG * STG_BYTES + 256 + (warp - 2) * (32 * 128);
     uint8_t* stage_row = stage_warp + lane * 128;
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
     const bool vec_ok = (N % 8) == 0;
-    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-      const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+    const uint32_t acc_empty_leader[2] = {CTA2 ? mapa_shared(smem_u32(&acc_empty[0]), 0) : 0u,
+                                          CTA2 ? mapa_shared(smem_u32(&acc_empty[1]), 0) : 0u};
+    for (int t = first_tile; t < n_tiles && ok; t += tile_step) {
+      const int m0 = (t / tiles_n) * TM + (CTA2 ? (int)pair_rank * BM : 0), n0 = (t % tiles_n) * BN;
       if (!mbar_wait(&acc_full[acc], acc_ph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
@@ -403,7 +448,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (lane == 0) {
+          if (CTA2) mbar_arrive_cluster(acc_empty_leader[acc]);
+          else mbar_arrive(&acc_empty[acc]);
+        }
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         continue;
       }
@@ -507,7 +555,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (lane == 0) {
+          if (CTA2) mbar_arrive_cluster(acc_empty_leader[acc]);
+          else mbar_arrive(&acc_empty[acc]);
+        }
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
         continue;
       }
@@ -583,7 +634,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+          if (CTA2) mbar_arrive_cluster(acc_empty_leader[acc]);
+          else mbar_arrive(&acc_empty[acc]);
+        }
       if (++acc == 2) { acc = 0; acc_ph ^= 1; }
     }
     if (!ok && lane == 0) { atomicCAS(err, 0, 3); *abort_flag = 1; }
@@ -597,9 +651,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();      // neither CTA leaves (or frees TMEM) while the other may still signal it or read its tiles
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (CTA2) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -633,6 +689,66 @@ static int launch_gemm(const void* A, const void* B, int M, int N, int K, const 
   return (int)cudaGetLastError();
 }
 
+// Same contraction on CTA pairs (template flag CTA2): clusters of two CTAs, one 256 x 256 tile per pair.
+template <int A_MN, int B_MN>
+static int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, const GemmEpilogue& ep, int* err, int sms,
+                            cudaStream_t st) {
+  CUtensorMap ta, tb;
+  int rc;
+  if (A_MN == 0) rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM);
+  else rc = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)M * 2, 64, BK);
+  if (rc) return rc;
+  if (B_MN == 0) rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K * 2, BK, BN / 2);   // each CTA loads half the columns
+  else rc = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, BK);
+  if (rc) return rc;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, false, true>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return 100 + (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (sms / 2));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  // A persistent grid must be resident as a whole: the pairs that the GPU can hold at once (a pair lives inside one GPC, so a
+  // GPC with an odd number of free SMs leaves one out) bound the grid, otherwise late pairs would run after the others.
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) return 600;
+    max_pairs = n;
+  }
+  const int pairs = std::min(tiles, std::min(max_pairs, sms / 2));
+  cfg.gridDim = dim3(2 * pairs);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, M, N, K, ep, GatherB{}, err);
+  return e == cudaSuccess ? 0 : 500 + (int)e;
+}
+
+// 0: single-CTA tiles; 1 (default): CTA pairs where the shape allows (measured 8-45 % faster on the 2B shapes: half the B-operand
+// bytes per CTA). COSMOS_B200_GEMM_PAIR=0 selects single-CTA tiles; cb200_gemm_pair_mode switches at run time (the kernel
+// benchmark compares the two).
+static int g_pair_mode = -1;
+extern "C" int cb200_gemm_pair_mode(int mode) {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("COSMOS_B200_GEMM_PAIR");
+    g_pair_mode = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  const int prev = g_pair_mode;
+  if (mode >= 0) g_pair_mode = mode;
+  return prev;
+}
+
 extern "C" int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn,
                                const void* bias, int act, void* pre, const void* resid, const float* gate, int L, int* err,
                                int sms, cudaStream_t st) {
@@ -644,6 +760,12 @@ extern "C" int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int
   ep.gate = gate;
   ep.act = act;
   ep.L = L > 0 ? L : 1;
+  if (cb200_gemm_pair_mode(-1) == 1 && M >= 2 * BM && N % 8 == 0) {
+    if (a_mn == 0 && b_mn == 0) return launch_gemm_pair<0, 0>(A, B, M, N, K, ep, err, sms, st);
+    if (a_mn == 0 && b_mn == 1) return launch_gemm_pair<0, 1>(A, B, M, N, K, ep, err, sms, st);
+    if (a_mn == 1 && b_mn == 0) return launch_gemm_pair<1, 0>(A, B, M, N, K, ep, err, sms, st);
+    return launch_gemm_pair<1, 1>(A, B, M, N, K, ep, err, sms, st);
+  }
   if (a_mn == 0 && b_mn == 0) return launch_gemm<0, 0>(A, B, M, N, K, ep, err, sms, st);
   if (a_mn == 0 && b_mn == 1) return launch_gemm<0, 1>(A, B, M, N, K, ep, err, sms, st);
   if (a_mn == 1 && b_mn == 0) return launch_gemm<1, 0>(A, B, M, N, K, ep, err, sms, st);

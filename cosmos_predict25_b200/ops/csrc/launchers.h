@@ -50,6 +50,7 @@ int cb200_skinny_bgemm(const float* a, long a_z, long a_r, long a_k, const long 
 // gemm_tcgen05.cu
 int cb200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int b_mn, const void* bias,
                     int act, void* pre, const void* resid, const float* gate, int L, int* err, int sms, cudaStream_t st);
+int cb200_gemm_pair_mode(int mode);   // 0 / 1 sets, -1 reads; returns the previous mode (1 = CTA-pair tiles where the shape allows)
 int cb200_gemm_bf16_gather(const void* A, void* ws, void* C, int M, int rows, int ld, int b_mn, const int64_t* shard_ptrs, int P,
                            int chunk_rows, int* counters, const void* bias, int act, void* pre, int* err, int sms, cudaStream_t st);
 int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M, int N, int K, const int64_t* ptrs, int P, int rank, int S,

@@ -139,6 +139,43 @@ def test_gemm_transposed_operands():
     _close(c, want, 2e-2, 2e-2, "gemm trans_a trans_b")
 
 
+@pytest.fixture
+def gemm_pairs():
+    """Run the GEMM on CTA pairs (256 x 256 tile per cluster of two) for the duration of a test."""
+    prev = _ops().gemm_pair_mode(1)
+    yield
+    _ops().gemm_pair_mode(prev)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (1000, 2048, 512), (4096, 64, 2048), (333 * 8, 2048, 72 * 8),
+                                   (8192 + 128, 1024, 1024)])
+def test_gemm_cta_pairs(M, N, K, gemm_pairs):
+    """tcgen05 cta_group::2 tiles: all operand-major combinations, ragged edges (a pair whose second CTA has no rows, a last
+    N tile narrower than 256), many tiles per pair; bitwise equal to the single-CTA kernel (same products, same order)."""
+    torch.manual_seed(4)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    b = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    want = a.float() @ b.float().T
+    got = {}
+    for ta, tb in ((False, False), (False, True), (True, False), (True, True)):
+        aa = a.T.contiguous() if ta else a
+        bb = b.T.contiguous() if tb else b
+        c = _ops().gemm_bf16(aa, bb, None, 0, ta, tb)
+        _no_kernel_error()
+        _close(c, want, 2e-2, 2e-2, f"pair gemm trans_a={ta} trans_b={tb}")
+        got[(ta, tb)] = c
+    _ops().gemm_pair_mode(0)
+    single = _ops().gemm_bf16(a, b, None, 0, False, False)
+    _no_kernel_error()
+    _close(single, want, 2e-2, 2e-2, "single-CTA gemm")
+    assert torch.equal(single, got[(False, False)])
+
+
+@pytest.mark.parametrize("M,N,L", [(640, 1024, 40), (600, 1000, 40)])
+def test_gemm_cta_pairs_epilogues(M, N, L, gemm_pairs):
+    test_gemm_epilogues(M, N, L)
+
+
 @pytest.mark.parametrize("M,N,L", [(640, 1024, 40), (600, 1024, 40), (600, 1000, 40)])   # full, ragged rows, ragged rows + columns
 def test_gemm_epilogues(M, N, L):
     torch.manual_seed(6)
