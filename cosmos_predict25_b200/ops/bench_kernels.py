@@ -233,7 +233,31 @@ def main():
         add("rmsnorm_rope_bwd", f"{T * L}x{H}x{HD}", time_ms(lambda: ops.rmsnorm_rope_bwd(q, q, w, rs, cos, sin)), bytes_=3 * q.numel() * 2)
         h = torch.randn(T * L, Fm, device=dev).bfloat16()
         add("gelu_bwd", f"{T * L}x{Fm}", time_ms(lambda: ops.gelu_bwd(h, h)), bytes_=3 * h.numel() * 2)
+        # forward-mode (value + tangent) variants: two tensors in, two out
+        add("ln_modulate_jvp", f"{T * L}x{D}", time_ms(lambda: ops.ln_modulate_jvp(xf, y.view(-1, D), sh.view(-1, D), sc.view(-1, D),
+                                                                                  sh.view(-1, D), sc.view(-1, D), L, 1e-6)), bytes_=4 * nb)
+        add("rmsnorm_rope_jvp", f"{T * L}x{H}x{HD}", time_ms(lambda: ops.rmsnorm_rope_jvp(q, q, w, cos, sin, 1e-6)), bytes_=4 * q.numel() * 2)
         del x, y, q, h
+    if want("skinny"):
+        # AdaLN-LoRA modulation MLPs of the 2B network: rows = batch x latent frames, D -> 256 -> 3D, bf16 weights, fp32 math
+        R, r = 2 * T, 256
+        emb = torch.randn(R, D, device=dev)
+        lora = torch.randn(R, 3 * D, device=dev)
+        for Z, tag in ((3, "one block"), (84, "all 28 blocks in one launch")):
+            w1 = [(torch.randn(r, D, device=dev) * 0.02).bfloat16() for _ in range(Z)]
+            w2 = [(torch.randn(3 * D, r, device=dev) * 0.02).bfloat16() for _ in range(Z)]
+            wb = Z * (r * D + 3 * D * r) * 2.0
+
+            def two_stage():
+                return F_ops.skinny_linears(F_ops.skinny_linears(emb, w1, silu=True), w2, add=lora)
+
+            def torch_twin():
+                a = torch.nn.functional.silu(emb)
+                return [torch.nn.functional.linear(torch.nn.functional.linear(a, w1[z].float()), w2[z].float()) + lora for z in range(Z)]
+
+            add(f"skinny_bgemm x2 (AdaLN-LoRA, {tag})", f"Z={Z} rows={R} {D}->{r}->{3 * D}", time_ms(two_stage), bytes_=wb)
+            add(f"torch fp32 linears (twin, {tag})", f"Z={Z} rows={R}", time_ms(torch_twin), bytes_=wb)
+            del w1, w2
     if want("optimizer"):
         n = 69_000_000 if not args.quick else 8_000_000
         g16 = torch.randn(n, device=dev).bfloat16()

@@ -794,6 +794,7 @@ extern "C" int cb200_gemm_bf16_scatter_heads(const void* A, const void* W, int M
   ep.hs.raw = (bf16*)raw;
   ep.hs.rstd_out = rstd_out;
   ep.L = 1;
+  if (cb200_gemm_pair_mode(-1) == 1 && M >= 2 * BM) return launch_gemm_pair<0, 0>(A, W, M, N, K, ep, err, sms, st);
   return launch_gemm<0, 0>(A, W, M, N, K, ep, err, sms, st);
 }
 

@@ -68,8 +68,20 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
     }
   }
   // The encoder is a driver entry point and needs a current context; a thread that has made no runtime call yet (an autograd
-  // worker whose first operation is a GEMM) has none. Any runtime call binds the device's primary context to the thread.
-  cudaFree(nullptr);
+  // worker whose first operation is a GEMM) has none. A runtime call binds the device's primary context to the thread; it is
+  // made only when the thread has no context, because cudaFree is not allowed while a stream capture is in progress.
+  {
+    typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+    static CtxGetCurrentFn get_ctx = nullptr;
+    if (get_ctx == nullptr) {
+      void* p = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+        get_ctx = reinterpret_cast<CtxGetCurrentFn>(p);
+    }
+    CUcontext ctx = nullptr;
+    if (get_ctx == nullptr || get_ctx(&ctx) != CUDA_SUCCESS || ctx == nullptr) cudaFree(nullptr);
+  }
   cuuint64_t gdim[5];
   cuuint64_t gstr[4];
   cuuint32_t bx[5], estr[5];
