@@ -258,6 +258,22 @@ def main():
             add(f"skinny_bgemm x2 (AdaLN-LoRA, {tag})", f"Z={Z} rows={R} {D}->{r}->{3 * D}", time_ms(two_stage), bytes_=wb)
             add(f"torch fp32 linears (twin, {tag})", f"Z={Z} rows={R}", time_ms(torch_twin), bytes_=wb)
             del w1, w2
+    if want("conv"):
+        # causal 3 x 3 x 3 convolutions of the Wan2.1 VAE decoder at 720p (channels-last activations, 2 cached + 4 new frames in,
+        # 4 frames out), next to the cuDNN convolution of the same layer on NCTHW tensors
+        from ..models.vae_wan_cl import ConvCL, _causal3_taps
+        div = 2 if (args.quick or args.seq) else 1
+        for C, Hh, Ww, tag in ((384, 176 // div, 320 // div, "stage 1"), (192, 352 // div, 640 // div, "stage 2"), (96, 704 // div, 1280 // div, "stage 3")):
+            wt = torch.randn(C, 27, C, device=dev) * (27 * C) ** -0.5
+            conv = ConvCL(wt, torch.zeros(C, device=dev), _causal3_taps(3, 3, 3), dev)
+            xin = torch.randn(6, Hh, Ww, C, device=dev).bfloat16()
+            fl = 2.0 * 27 * C * C * 4 * Hh * Ww
+            add(f"conv_cl 3x3x3 causal ({tag})", f"C={C} {4}x{Hh}x{Ww}", time_ms(lambda: conv(xin, 4)), fl)
+            if not args.no_twin:
+                w5 = wt.view(C, 3, 3, 3, C).permute(0, 4, 1, 2, 3).contiguous().bfloat16()
+                x5 = xin.permute(3, 0, 1, 2).unsqueeze(0).contiguous()
+                add(f"cudnn conv3d (twin, {tag})", f"C={C}", time_ms(lambda: torch.nn.functional.conv3d(x5, w5, padding=(0, 1, 1))), fl)
+            del wt, conv, xin
     if want("optimizer"):
         n = 69_000_000 if not args.quick else 8_000_000
         g16 = torch.randn(n, device=dev).bfloat16()
