@@ -35,7 +35,8 @@ def _free_port() -> int:
 def pack_state_dict(sd: Dict[str, Any], staging: Optional[Dict[str, torch.Tensor]] = None) -> List[Tuple]:
     """Turn a state dict into picklable entries whose tensors live in shared host memory.
 
-    Entry: ``(key, "dtensor", local, global_shape, shard_dim)`` for a dim-sharded DTensor, ``(key, "tensor", t)`` for a plain
+    Entry: ``(key, "dtensor", local, global_shape, placements, mesh_shape)`` for a DTensor (placements as ``("S", dim)`` /
+    ``("R",)`` per mesh dimension), ``(key, "tensor", t)`` for a plain
     tensor, ``(key, "object", obj)`` for anything else. ``staging`` keeps the shared buffers between saves (same key and
     shape: reused, so a save allocates nothing after the first one)."""
     out: List[Tuple] = []
@@ -43,13 +44,10 @@ def pack_state_dict(sd: Dict[str, Any], staging: Optional[Dict[str, torch.Tensor
     for k, v in sd.items():
         if hasattr(v, "to_local"):
             loc = v.to_local()
-            shard_dim = None
-            for p in v.placements:
-                if getattr(p, "dim", None) is not None:
-                    shard_dim = int(p.dim)
+            spec = tuple(("S", int(p.dim)) if getattr(p, "dim", None) is not None else ("R",) for p in v.placements)
             host = _stage(k, loc, staging)
             copies.append((host, loc))
-            out.append((k, "dtensor", host, tuple(v.shape), shard_dim))
+            out.append((k, "dtensor", host, tuple(v.shape), spec, tuple(v.device_mesh.shape)))
         elif isinstance(v, torch.Tensor):
             host = _stage(k, v, staging)
             copies.append((host, v))
@@ -78,17 +76,28 @@ def _stage(key: str, src: torch.Tensor, staging: Optional[Dict[str, torch.Tensor
     return buf
 
 
-def unpack_state_dict(entries: List[Tuple], mesh) -> Dict[str, Any]:
+_meshes: Dict[Tuple, Any] = {}
+
+
+def _cpu_mesh(shape: Tuple[int, ...]):
+    if shape not in _meshes:
+        from torch.distributed.device_mesh import init_device_mesh
+        names = ("shard",) if len(shape) == 1 else ("replicate", "shard")
+        _meshes[shape] = init_device_mesh("cpu", shape, mesh_dim_names=names)
+    return _meshes[shape]
+
+
+def unpack_state_dict(entries: List[Tuple], distributed: bool) -> Dict[str, Any]:
     sd: Dict[str, Any] = {}
     for e in entries:
         k, kind = e[0], e[1]
-        if kind == "dtensor" and mesh is not None:
+        if kind == "dtensor" and distributed:
             from torch.distributed.tensor import DTensor, Replicate, Shard
-            _, _, local, shape, shard_dim = e
+            _, _, local, shape, spec, mesh_shape = e
             shape = torch.Size(shape)
             stride = torch.empty(shape, device="meta").stride() if len(shape) else ()
-            placements = [Shard(shard_dim)] if shard_dim is not None else [Replicate()]
-            sd[k] = DTensor.from_local(local, mesh, placements, run_check=False, shape=shape, stride=stride)
+            placements = [Shard(p[1]) if p[0] == "S" else Replicate() for p in spec]
+            sd[k] = DTensor.from_local(local, _cpu_mesh(tuple(mesh_shape)), placements, run_check=False, shape=shape, stride=stride)
         else:
             sd[k] = e[2]
     return sd
@@ -116,13 +125,10 @@ def write_state_dicts(sds: Dict[str, Dict[str, Any]], ckpt_dir: str, name: str, 
 
 def _writer_main(rank: int, world: int, addr: str, port: int, jobs, done) -> None:
     """Body of the child: join the writers' gloo group, then serve save jobs until ``None`` arrives."""
-    mesh = None
     try:
         torch.set_num_threads(2)
         if world > 1:
             dist.init_process_group("gloo", init_method=f"tcp://{addr}:{port}", rank=rank, world_size=world)
-            from torch.distributed.device_mesh import init_device_mesh
-            mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("shard",))
         done.put(("ready", None, 0.0))
     except BaseException:
         done.put(("ready", traceback.format_exc(), 0.0))
@@ -134,7 +140,7 @@ def _writer_main(rank: int, world: int, addr: str, port: int, jobs, done) -> Non
         name, ckpt_dir, payload = job
         t0 = time.time()
         try:
-            sds = {key: unpack_state_dict(entries, mesh) for key, entries in payload.items()}
+            sds = {key: unpack_state_dict(entries, world > 1) for key, entries in payload.items()}
             write_state_dicts(sds, ckpt_dir, name, rank, group=None)
             done.put((name, None, time.time() - t0))
         except BaseException:

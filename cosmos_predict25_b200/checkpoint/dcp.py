@@ -40,22 +40,33 @@ def _rank() -> int:
 
 
 def _as_dtensor(local: torch.Tensor, shape, mesh):
-    """Wrap a rank's dim-0 chunk as a ``Shard(0)`` DTensor of global ``shape``."""
-    from torch.distributed.tensor import DTensor, Shard
+    """Wrap a rank's dim-0 chunk as a DTensor of global ``shape``: ``Shard(0)`` on a 1-D mesh, ``[Replicate(), Shard(0)]`` on the
+    (replicate, shard) mesh of hybrid sharding."""
+    from torch.distributed.tensor import DTensor, Replicate, Shard
     shape = torch.Size(shape)
     stride = torch.empty(shape, device="meta").stride() if len(shape) else ()
-    return DTensor.from_local(local, mesh, [Shard(0)], run_check=False, shape=shape, stride=stride)
+    placements = [Shard(0)] if mesh.ndim == 1 else [Replicate(), Shard(0)]
+    return DTensor.from_local(local, mesh, placements, run_check=False, shape=shape, stride=stride)
 
 
 class _Mesh:
     _cache: Dict[Any, Any] = {}
 
     @classmethod
-    def get(cls, device_type: str):
-        key = (device_type, dist.get_world_size())
+    def get(cls, device_type: str, shard_size: Optional[int] = None):
+        """1-D mesh over the world, or - when the state is sharded over ``shard_size`` < world ranks and replicated across the
+        groups (hybrid sharding; rank = replica * shard_size + shard index, as ``parallel.mesh.build_groups`` lays them out) -
+        the 2-D (replicate, shard) mesh."""
+        W = dist.get_world_size()
+        P = W if shard_size in (None, W) else int(shard_size)
+        key = (device_type, W, P)
         if key not in cls._cache:
             from torch.distributed.device_mesh import init_device_mesh
-            cls._cache[key] = init_device_mesh(device_type, (dist.get_world_size(),), mesh_dim_names=("shard",))
+            if P == W:
+                cls._cache[key] = init_device_mesh(device_type, (W,), mesh_dim_names=("shard",))
+            else:
+                assert W % P == 0, (W, P)
+                cls._cache[key] = init_device_mesh(device_type, (W // P, P), mesh_dim_names=("replicate", "shard"))
         return cls._cache[key]
 
 
@@ -79,7 +90,7 @@ class ModelWrapper:
     def state_dict(self) -> Dict[str, Any]:
         sd: Dict[str, Any] = {}
         sharded = _dist_on() and self.model.engine.P > 1
-        mesh = _Mesh.get(self.model.device_.type) if sharded else None
+        mesh = _Mesh.get(self.model.device_.type, self.model.engine.P) if sharded else None
         for key, which, name, local, shape, dtype in self._entries():
             t = local.detach().to(dtype).clone()
             sd[key] = _as_dtensor(t, shape, mesh) if sharded and len(shape) > 0 else t
@@ -117,7 +128,7 @@ class OptimizerWrapper:
     def state_dict(self) -> Dict[str, Any]:
         sd = {}
         sharded = _dist_on() and self.model.engine.P > 1
-        mesh = _Mesh.get(self.model.device_.type) if sharded else None
+        mesh = _Mesh.get(self.model.device_.type, self.model.engine.P) if sharded else None
         shapes = {n: shp for n, (_, shp, _) in self.model.engine.sharded_state("master").items()}
         for k, v in self.optimizer.state_dict().items():
             if isinstance(v, torch.Tensor) and k.startswith("state.") and k != "state.step":
@@ -315,7 +326,7 @@ class DistributedCheckpointer:
                 if loc.is_cuda:
                     host = torch.empty(loc.shape, dtype=loc.dtype, pin_memory=True)
                     host.copy_(loc, non_blocking=True)
-                    mesh = _Mesh.get("cpu")
+                    mesh = _Mesh.get("cpu", v.device_mesh.shape[-1])
                     out[k] = DTensor.from_local(host, mesh, v.placements, run_check=False, shape=v.shape, stride=v.stride())
                 else:
                     out[k] = v

@@ -274,6 +274,52 @@ def test_dcp_async_save_through_writer_processes():
     run_distributed("_dcp_writer_processes", world=2)
 
 
+def _dcp_hybrid_sharding(rank, world, tmp):
+    """DCP save / load of a model whose state is sharded over 2 ranks and replicated over 2 groups (world 4): the tensors are
+    written as [Replicate, Shard(0)] DTensors on the (replicate, shard) mesh, a fresh set of ranks resumes bit-exactly, and the
+    asynchronous writer processes produce the same checkpoint."""
+    from cosmos_predict25_b200.checkpoint.dcp import DistributedCheckpointer
+    from cosmos_predict25_b200.models.dit import dit_tiny
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.parallel.mesh import build_groups
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig, SchedulerConfig
+    job = [tmp]
+    dist.broadcast_object_list(job, src=0)
+    groups = build_groups(world, cp_size=1, shard_size=2)
+    cfg = Video2WorldRFConfig(net=dit_tiny(), precision="float32", state_t=4)
+
+    def make():
+        torch.manual_seed(0)
+        m = Video2WorldModelRectifiedFlow(cfg, device=torch.device("cpu"), fsdp_group=groups.fsdp, replicate_group=groups.replicate)
+        o, s = m.init_optimizer_scheduler(OptimizerConfig(lr=1e-3), SchedulerConfig(kind="constant"))
+        return m, o, s
+
+    torch.manual_seed(3 + rank)
+    batch = {"latents": torch.randn(1, 16, 4, 16, 16), "t5_text_embeddings": torch.randn(1, 32, 256), "fps": torch.tensor([16.0]),
+             "padding_mask": torch.zeros(1, 1, 16, 16)}
+    m, o, s = make()
+    assert m.engine.P == 2 and m.engine.R == 2
+    _, loss = m.training_step(dict(batch), 0)
+    loss.backward()
+    o.step()
+    masters = [u.master.clone() for u in m.engine.units]
+    for sub, cfg_ck in (("sync", {}), ("async", {"dcp_async_mode_enabled": True})):
+        ck = DistributedCheckpointer(cfg_ck, os.path.join(job[0], sub))
+        ck.save(m, o, s, iteration=1)
+        getattr(ck, "close", ck.finalize)()
+        dist.barrier()
+        m2, o2, s2 = make()
+        assert DistributedCheckpointer({}, os.path.join(job[0], sub)).load(m2, o2, s2) == 1
+        for a, u in zip(masters, m2.engine.units):
+            assert torch.equal(a, u.master), (sub, rank)
+        for (n1, p1), (_, p2) in zip(m.net.named_parameters(), m2.net.named_parameters()):
+            assert torch.equal(p1, p2), (sub, n1)
+
+
+def test_dcp_under_hybrid_sharding_four_ranks():
+    run_distributed("_dcp_hybrid_sharding", world=4)
+
+
 def _hsdp(rank, world, tmp, shard_size):
     """Hybrid sharding (shard groups of ``shard_size`` ranks, replicated ``world / shard_size`` times) and plain data
     parallelism (``shard_size`` 1) give the same parameters as one process that sees the whole batch."""
