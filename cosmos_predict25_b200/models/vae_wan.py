@@ -312,12 +312,22 @@ class WanVAE_(nn.Module):
         st = self._enc_state
         t = x.shape[2]
         tw = self.temporal_window
-        outs = [self.encoder(x[:, :, :1], st)]
+        cl = self._kernel_encoder(x)
+        if cl is not None:
+            # channels-last encoder on this package's convolution kernel; it keeps its own stream state
+            if clear_encoder_cache or cl.state is None:
+                cl.reset()
+            run = cl.step
+        else:
+            run = lambda chunk: self.encoder(chunk, st)
+        outs = [run(x[:, :, :1])]
         n_full = (t - 1) // tw
         for i in range(n_full):
-            outs.append(self.encoder(x[:, :, 1 + tw * i: 1 + tw * (i + 1)], st))
+            outs.append(run(x[:, :, 1 + tw * i: 1 + tw * (i + 1)]))
         if (t - 1) % tw:
-            outs.append(self.encoder(x[:, :, 1 + tw * n_full:], st))
+            outs.append(run(x[:, :, 1 + tw * n_full:]))
+        if cl is not None and clear_encoder_cache:
+            cl.state = None
         out = torch.cat(outs, 2)
         mu, _log_var = self.conv1(out).chunk(2, dim=1)
         mean, inv_std = scale
@@ -354,6 +364,18 @@ class WanVAE_(nn.Module):
         if clear_decoder_cache:
             self._dec_state = None
         return torch.cat(outs, 2)
+
+    def _kernel_encoder(self, x):
+        """The channels-last kernel encoder for this input, or None when the torch / cuDNN path has to serve it."""
+        from ..ops import functional as F_ops
+        from . import vae_wan_cl
+        if F_ops.settings.conv != "native" or not vae_wan_cl.encoder_supported(x):
+            return None
+        sig = tuple((p.data_ptr(), p._version) for p in self.encoder.parameters())
+        if getattr(self, "_enc_cl", None) is None or self._enc_cl_sig != sig:
+            self._enc_cl = vae_wan_cl.EncoderCL(self.encoder, x.device)
+            self._enc_cl_sig = sig
+        return self._enc_cl
 
     def _kernel_decoder(self, x):
         """The channels-last kernel decoder for this input, or None when the torch / cuDNN path has to serve it (CPU tensors,

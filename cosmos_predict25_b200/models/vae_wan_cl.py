@@ -265,3 +265,117 @@ def supported(decoder, z: torch.Tensor) -> bool:
     """The kernel path serves bf16 CUDA decodes of one video (whole frames or, under ``vae_parallel.row_sharded``, row bands)."""
     return (z.is_cuda and z.dtype == torch.bfloat16 and z.shape[0] == 1 and native.available()
             and hasattr(native.load(), "conv_cl") and not native.forward_mode())
+
+
+# ------------------------------------------------------------------------------------------------------------------ encoder
+class _DownsampleCL:
+    """``ZeroPad2d((0, 1, 0, 1)) + Conv2d(3 x 3, stride 2)`` and, for the 3-D mode, the causal ``(3, 1, 1)`` convolution with
+    temporal stride 2 (wan2pt1.py:84-137), both restated as stride-1 convolutions the kernel can run:
+
+      * space: the frame is regrouped into 2 x 2 pixel blocks ([T, H/2, W/2, 4C], channel = (row in block, column in block, c));
+        output pixel (y, x) reads input pixels (2y + i, 2x + j), i, j in 0..2, which live in blocks (y, x), (y, x + 1), (y + 1, x),
+        (y + 1, x + 1): a 2 x 2-tap convolution whose weights are the 3 x 3 kernel scattered over the block positions (the rest
+        zero); blocks past the bottom / right edge read the kernel's out-of-range fill, which is the zero padding;
+      * time: [previous last frame | chunk] is regrouped into frame pairs ([T/2 + 1, H, W, 2C]); output frame t reads input frames
+        2t, 2t + 1 (pair t) and 2t + 2 (first half of pair t + 1): two taps."""
+
+    def __init__(self, mod, device):
+        conv = mod.resample[1]
+        w = conv.weight.detach().float()                     # [Cout, C, 3, 3]
+        cout, C = w.shape[:2]
+        taps, mats = [], []
+        for dy in (0, 1):
+            for dx in (0, 1):
+                m = torch.zeros(cout, 2, 2, C)
+                for a in (0, 1):
+                    for b in (0, 1):
+                        if 2 * dy + a < 3 and 2 * dx + b < 3:
+                            m[:, a, b] = w[:, :, 2 * dy + a, 2 * dx + b]
+                mats.append(m.reshape(cout, 4 * C))
+                taps.append((0, dy, dx))
+        self.space = ConvCL(torch.stack(mats, 1), conv.bias, taps, device)
+        self.time = None
+        if mod.mode == "downsample3d":
+            wt = mod.time_conv.weight.detach().float()[:, :, :, 0, 0]     # [C, C, 3]
+            c2 = wt.shape[0]
+            m0 = torch.cat([wt[:, :, 0], wt[:, :, 1]], 1)                   # pair t: frames 2t, 2t + 1
+            m1 = torch.cat([wt[:, :, 2], torch.zeros(c2, c2)], 1)          # pair t + 1: frame 2t + 2
+            self.time = ConvCL(torch.stack([m0, m1], 1), mod.time_conv.bias, [(0, 0, 0), (1, 0, 0)], device)
+        self._key = object()
+
+    def __call__(self, x, state):
+        T, H, W, C = x.shape
+        blocks = x.view(T, H // 2, 2, W // 2, 2, C).permute(0, 1, 3, 2, 4, 5).reshape(T, H // 2, W // 2, 4 * C)
+        y = self.space(blocks, T)
+        if self.time is None:
+            return y
+        prev = state.store.get(id(self._key))
+        state.store[id(self._key)] = y[-1:].clone()
+        if prev is None:                                                 # first chunk: no temporal down-sampling
+            return y
+        full = torch.cat([prev, y], 0)                                   # T + 1 frames
+        if full.shape[0] % 2:
+            full = torch.cat([full, torch.zeros_like(full[:1])], 0)
+        n_p, (_, h, w, c) = full.shape[0] // 2, full.shape
+        pairs = full.view(n_p, 2, h, w, c).permute(0, 2, 3, 1, 4).reshape(n_p, h, w, 2 * c)
+        return self.time(pairs, T // 2)
+
+
+class EncoderCL:
+    """Streaming channels-last encoder built from an ``Encoder3d``: the same chunked semantics (a chunk of one frame first, then
+    chunks of ``temporal_window`` frames; every causal convolution carries the last two input frames; the temporal down-samplers
+    pass the first chunk through), every convolution on the kernel (wan2pt1.py:270-357, 500-533)."""
+
+    def __init__(self, encoder, device):
+        self.device = torch.device(device)
+        dev = self.device
+        from . import vae_wan
+        w = encoder.conv1.weight.detach().float()            # [C0, 3, 3, 3, 3]
+        c0, cin = w.shape[:2]
+        self.in_pad = 16                                     # RGB travels zero-padded to 16 channels
+        wt = torch.zeros(c0, 27, self.in_pad)
+        wt[:, :, :cin] = w.permute(0, 2, 3, 4, 1).reshape(c0, 27, cin)
+        self.cin = cin
+        self.conv1 = ConvCL(wt, encoder.conv1.bias, _causal3_taps(3, 3, 3), dev)
+        self.layers = []
+        for layer in list(encoder.downsamples) + list(encoder.middle):
+            if isinstance(layer, vae_wan.ResidualBlock):
+                self.layers.append(_ResBlockCL(layer, dev))
+            elif isinstance(layer, vae_wan.AttentionBlock):
+                self.layers.append(_AttnCL(layer, dev))
+            elif isinstance(layer, vae_wan.Resample):
+                self.layers.append(_DownsampleCL(layer, dev))
+            else:
+                raise TypeError(type(layer))
+        self.head_gamma = encoder.head[0].gamma.detach().float().reshape(-1).to(dev).contiguous()
+        self.head = _conv3d(encoder.head[2], dev)
+        self.state: Optional[_Stream] = None
+
+    def reset(self):
+        self.state = _Stream()
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor) -> torch.Tensor:
+        """x [1, 3, T, H, W] (one chunk) -> [1, 2 z, T', H / 8, W / 8] (input of the 1 x 1 ``conv1`` of the VAE)."""
+        assert x.shape[0] == 1, "the channels-last encoder runs one video at a time"
+        if self.state is None:
+            self.reset()
+        st = self.state
+        T, H, W = x.shape[2:]
+        xin = torch.zeros(T, H, W, self.in_pad, dtype=torch.bfloat16, device=self.device)
+        xin[..., : self.cin] = x[0].permute(1, 2, 3, 0)
+        y = self.conv1(_with_cache(self.conv1, xin, st), T)
+        for layer in self.layers:
+            y = layer(y, st)
+        y = native.load().rmsnorm_silu_cl(y, self.head_gamma, True)
+        native.count_launch()
+        y = self.head(_with_cache(self.head, y, st), y.shape[0])
+        return y.permute(3, 0, 1, 2).unsqueeze(0)
+
+
+def encoder_supported(x: torch.Tensor) -> bool:
+    """The kernel encoder serves bf16 CUDA videos, one at a time, whole frames (row-sharded encoding stays on the torch path),
+    with frame sizes that survive three halvings as whole 16 x 8 pixel tiles."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] == 1 and x.shape[-2] % 64 == 0 and x.shape[-1] % 128 == 0
+            and vae_parallel.active() is None and native.available() and hasattr(native.load(), "conv_cl")
+            and not native.forward_mode())

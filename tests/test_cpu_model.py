@@ -322,3 +322,67 @@ def test_neighborhood_backward_plan_matches_dense_mask():
             assert not e < 0 or bool(vis.all())
             got[qt * 128:(qt + 1) * 128, kt * 128:(kt + 1) * 128] = vis.t()
     assert torch.equal(got, want)
+
+
+def _conv_cl_on_cpu(self, x, t_out, out=None, out_map=None, resid=None, h_out=None, w_out=None):
+    """What the convolution kernel computes, in plain torch: out[t, y, x] = sum over taps of W_tap x[t + dt, y + dh, x + dw] with
+    zeros outside the tensor (default output mapping only)."""
+    T, H, W, C = x.shape
+    h_out, w_out = h_out or H, w_out or W
+    ntaps = len(self.taps) // 3
+    cpad = self.w.shape[1] // ntaps
+    w = self.w.float().view(-1, ntaps, cpad)[: self.cout, :, :C]
+    xp = torch.nn.functional.pad(x.float(), (0, 0, 2, 2, 2, 2, 0, 2))            # W, H by 2 each side; T by 2 at the end
+    acc = torch.zeros(t_out, h_out, w_out, self.cout)
+    for i in range(ntaps):
+        dt, dh, dw = self.taps[3 * i: 3 * i + 3]
+        acc += xp[dt: dt + t_out, 2 + dh: 2 + dh + h_out, 2 + dw: 2 + dw + w_out] @ w[:, i].t()
+    if self.bias is not None:
+        acc += self.bias
+    return acc.to(torch.bfloat16) if resid is None else (acc + resid.float()).to(torch.bfloat16)
+
+
+def test_kernel_encoder_downsampling_restatements(monkeypatch):
+    """Stride-2 spatial convolution as a 2 x 2-tap convolution on 2 x 2 pixel blocks, and the stride-2 causal time convolution as
+    a 2-tap convolution on frame pairs, against the torch ``Resample`` module chunk by chunk (streaming state included)."""
+    from cosmos_predict25_b200.models import vae_wan, vae_wan_cl
+    monkeypatch.setattr(vae_wan_cl.ConvCL, "__call__", _conv_cl_on_cpu)
+    torch.manual_seed(0)
+    for mode in ("downsample2d", "downsample3d"):
+        mod = vae_wan.Resample(16, mode).float()
+        cl = vae_wan_cl._DownsampleCL(mod, "cpu")
+        st_t, st_c = vae_wan.StreamState(), vae_wan_cl._Stream()
+        for T in (1, 4, 4, 2):
+            x = torch.randn(1, 16, T, 8, 12).bfloat16().float()
+            want = mod(x, st_t)                                                      # [1, C, T', 4, 6]
+            got = cl(x[0].permute(1, 2, 3, 0).contiguous().bfloat16(), st_c)         # [T', 4, 6, C]
+            assert got.shape == (want.shape[2], 4, 6, 16), (mode, T, got.shape, want.shape)
+            err = (got.float().permute(3, 0, 1, 2) - want[0]).abs().max().item()
+            assert err < 3e-2, (mode, T, err)
+
+
+def test_kernel_encoder_matches_torch_encoder_on_cpu(monkeypatch):
+    """The whole channels-last encoder (with the kernel replaced by its torch definition) against ``Encoder3d`` over a 1 + 4 + 4
+    frame video: same chunking, caches and down-sampling skips."""
+    from cosmos_predict25_b200.models import vae_wan, vae_wan_cl
+    from cosmos_predict25_b200.ops import native
+    monkeypatch.setattr(vae_wan_cl.ConvCL, "__call__", _conv_cl_on_cpu)
+
+    class _Ops:
+        @staticmethod
+        def rmsnorm_silu_cl(x, gamma, silu):
+            y = torch.nn.functional.normalize(x.float(), dim=-1) * (x.shape[-1] ** 0.5) * gamma
+            return (torch.nn.functional.silu(y) if silu else y).to(torch.bfloat16)
+
+    monkeypatch.setattr(native, "load", lambda: _Ops)
+    torch.manual_seed(1)
+    enc = vae_wan.Encoder3d(dim=16, z_dim=8, dim_mult=(1, 2, 2), num_res_blocks=1, temperal_downsample=(False, True)).float()
+    cl = vae_wan_cl.EncoderCL(enc, "cpu")
+    st = vae_wan.StreamState()
+    x = torch.randn(1, 3, 9, 16, 32).bfloat16().float()
+    for lo, hi in ((0, 1), (1, 5), (5, 9)):
+        want = enc(x[:, :, lo:hi], st)
+        got = cl.step(x[:, :, lo:hi].bfloat16())
+        assert got.shape == want.shape, (got.shape, want.shape)
+        scale = want.abs().mean().item()
+        assert (got.float() - want).abs().mean().item() < 0.05 * scale + 1e-3, (lo, hi)

@@ -96,3 +96,28 @@ def test_channels_last_decoder_matches_torch_decoder():
     scale = want.abs().mean().item()
     assert err.mean().item() < 0.03 * scale + 1e-3 and err.max().item() < 0.5 * want.abs().max().item() + 0.05, \
         f"mean err {err.mean().item():.4g} (signal {scale:.4g}), max err {err.max().item():.4g}"
+
+
+def test_channels_last_encoder_matches_torch_encoder():
+    """Whole streaming encode (1 + 4 + 4 pixel frames -> 3 latent frames) on the kernel path against the torch modules in fp32."""
+    from cosmos_predict25_b200.models.vae_wan import WanVAE_
+    torch.manual_seed(4)
+    vae = WanVAE_(dim=32, z_dim=16).eval().requires_grad_(False).to(DEV)
+    for p in vae.parameters():
+        p.data = p.data.bfloat16().float()
+    x = torch.randn(1, 3, 9, 128, 256, device=DEV).clamp(-1, 1)
+    F_ops.settings.conv = "cudnn"
+    try:
+        want = vae.encode(x, (0.0, 1.0))
+    finally:
+        F_ops.settings.conv = "native"
+    vae16 = vae.to(torch.bfloat16)
+    before = native.launches()
+    got = vae16.encode(x.bfloat16(), (0.0, 1.0))
+    _no_kernel_error()
+    assert got.shape == want.shape == (1, 16, 3, 16, 32)
+    assert getattr(vae16, "_enc_cl", None) is not None and native.launches() - before > 30, "the kernel encoder did not serve the bf16 encode"
+    err = (got.float() - want).abs()
+    scale = want.abs().mean().item()
+    assert err.mean().item() < 0.03 * scale + 1e-3 and err.max().item() < 0.5 * want.abs().max().item() + 0.05, \
+        f"mean err {err.mean().item():.4g} (signal {scale:.4g}), max err {err.max().item():.4g}"
