@@ -94,11 +94,18 @@ def run_inference(*, model_name="2B", frames=24, height=88, width=160, steps=35,
                                                                          is_negative_prompt=True, num_steps=args.steps))
         launches = native.launches()
         ms_decode, frames = 0.0, None
+        ms_encode, encode_frames = None, None
         if tok is not None:
             model.tokenizer = tok
             model.decode(lat[:, :, :2])                                                                                    # warm-up
             ms_decode, video = timed(lambda: model.decode(lat))   # row bands over the CP group; every rank gets the video
             frames = int(video.shape[2])
+            if world == 1:
+                # the encoder (conditioning clips at inference, every sample of online training): the decoded video back to latents
+                clip = video[:, :, : 1 + 4 * (args.frames - 1)].to(torch.bfloat16).clamp(-1, 1)
+                tok.encode(clip[:, :, :5])                                                                                  # warm-up
+                ms_encode, z = timed(lambda: tok.encode(clip))
+                encode_frames = int(clip.shape[2])
     err = native.load().kernel_error(local_rank, True)
     total = (ms_sample + ms_decode) / 1e3
     return {
@@ -106,7 +113,8 @@ def run_inference(*, model_name="2B", frames=24, height=88, width=160, steps=35,
         "n_gpus": world, "higher_is_better": False, "dtype": "bf16", "data": "synthetic conditioning video + text embeddings, random-init weights",
         "sampling_s": ms_sample / 1e3, "s_per_denoising_step": ms_sample / 1e3 / args.steps, "vae_decode_s": ms_decode / 1e3,
         "s_per_video_35_steps": 35 * ms_sample / 1e3 / args.steps + ms_decode / 1e3,
-        "decoded_frames": frames, "gpu_launches_sampling": launches, "kernel_error": int(err),
+        "decoded_frames": frames, "vae_encode_s": None if ms_encode is None else ms_encode / 1e3, "encoded_frames": encode_frames,
+        "gpu_launches_sampling": launches, "kernel_error": int(err),
         "config": {"model": f"cosmos-predict2.5-{args.model}-video2world", "steps": args.steps, "guidance": args.guidance,
                    "cfg": "batched cond/uncond (one batch-2 forward per step)", "latent_shape": [1, 16, args.frames, args.height, args.width],
                    "parallelism": f"cp{world}" + (" (ring)" if world > 1 and args.cp_comm == "p2p" else ""),
