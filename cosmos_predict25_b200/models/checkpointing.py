@@ -55,7 +55,7 @@ def _attention_ops():
 def _mm_ops():
     aten = torch.ops.aten
     s = {aten.mm.default, aten.addmm.default, aten.bmm.default}
-    for name in ("gemm_bf16", "gemm_bf16_gelu_pre", "gemm_bf16_gate_residual", "gemm_bf16_gather"):
+    for name in ("gemm_bf16", "gemm_bf16_gelu_pre", "gemm_bf16_gate_residual", "gemm_bf16_gate_residual_pre", "gemm_bf16_gather"):
         try:
             s.add(getattr(torch.ops.cosmos_b200, name).default)
         except (AttributeError, RuntimeError):

@@ -303,6 +303,15 @@ std::tuple<Tensor, Tensor> gemm_bf16_gelu_pre(const Tensor& a, const Tensor& b, 
   return {c, pre};
 }
 
+// resid + gate * (a @ b^T) and, as a second output, the product itself (training keeps it for the gate gradient)
+std::tuple<Tensor, Tensor> gemm_bf16_gate_residual_pre(const Tensor& a, const Tensor& b, const Tensor& resid, const Tensor& gate,
+                                                       int64_t L) {
+  TORCH_CHECK(b.size(0) % 256 == 0, "the two-output gated-residual epilogue needs whole 256-column tiles");
+  Tensor pre;
+  Tensor c = gemm_impl(a, b, c10::nullopt, 0, false, false, &pre, &resid, &gate, L);
+  return {c, pre};
+}
+
 Tensor gemm_bf16_gate_residual(const Tensor& a, const Tensor& b, const Tensor& resid, const Tensor& gate, int64_t L) {
   return gemm_impl(a, b, c10::nullopt, 0, false, false, nullptr, &resid, &gate, L);
 }
@@ -495,6 +504,7 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor? bias, int act, bool trans_a, bool trans_b) -> Tensor");
   m.def("gemm_bf16_gelu_pre(Tensor a, Tensor b, Tensor? bias) -> (Tensor, Tensor)");
   m.def("gemm_bf16_gate_residual(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> Tensor");
+  m.def("gemm_bf16_gate_residual_pre(Tensor a, Tensor b, Tensor resid, Tensor gate, int L) -> (Tensor, Tensor)");
   m.def("gemm_scatter_heads_peer(Tensor x, Tensor w, int[] out_ptrs, Tensor? norm_w, Tensor? cos, Tensor? sin, int S, int rank, "
         "float eps, bool keep_raw) -> (Tensor, Tensor)", &gemm_scatter_heads_peer);
   m.def("ln_modulate_jvp(Tensor x, Tensor tx, Tensor shift, Tensor scale, Tensor? tshift, Tensor? tscale, int L, float eps) -> "
@@ -513,4 +523,5 @@ TORCH_LIBRARY_IMPL(cosmos_b200, CUDA, m) {
   m.impl("gemm_bf16", &gemm_bf16);
   m.impl("gemm_bf16_gelu_pre", &gemm_bf16_gelu_pre);
   m.impl("gemm_bf16_gate_residual", &gemm_bf16_gate_residual);
+  m.impl("gemm_bf16_gate_residual_pre", &gemm_bf16_gate_residual_pre);
 }

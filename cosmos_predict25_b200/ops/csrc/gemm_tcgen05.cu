@@ -65,7 +65,8 @@ struct HeadScatter {
 struct GemmEpilogue {
   HeadScatter hs;     // hs.P == 0: disabled
   bf16* C;
-  bf16* pre;          // optional pre-activation output (only with act == 1)
+  bf16* pre;          // optional second output: the pre-activation (act == 1) or the product before the gated residual
+                      // (full 256-column tiles only)
   const bf16* bias;   // optional [N]
   const bf16* resid;  // optional [M, N] (gated residual)
   const float* gate;  // optional [M / L, N]
@@ -486,17 +487,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         for (int pass = 0; pass < 2; ++pass) {
           const int coff = part * 128 + pass * 64;              // column offset inside the tile
           const int colbase = n0 + coff;
-          if (ep.gate != nullptr) {                             // residual rows in, coalesced
-#pragma unroll 4
-            for (int it = 0; it < 8; ++it) {
-              const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
-              uint4 v4 = make_uint4(0, 0, 0, 0);
-              if (row0 + r_src < M) v4 = *reinterpret_cast<const uint4*>(ep.resid + (size_t)(row0 + r_src) * N + colbase + chunk * 8);
-              *reinterpret_cast<uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4)) = v4;
-            }
-            __syncwarp();
-          }
-          if (ep.act == 1 && ep.pre != nullptr) {               // pre-activation output first (TMEM is read again below)
+          if (ep.pre != nullptr && (ep.act == 1 || ep.gate != nullptr)) {
+            // second output first (TMEM is read again below): the pre-activation of a GELU, or the plain product of a
+            // gated-residual GEMM (training keeps it for the gate gradient)
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
               uint32_t r[32];
@@ -512,6 +505,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               stage_chunk(c, v);
             }
             write_out(ep.pre, colbase);
+          }
+          if (ep.gate != nullptr) {                             // residual rows in, coalesced
+#pragma unroll 4
+            for (int it = 0; it < 8; ++it) {
+              const int r_src = it * 4 + (lane >> 3), chunk = lane & 7;
+              uint4 v4 = make_uint4(0, 0, 0, 0);
+              if (row0 + r_src < M) v4 = *reinterpret_cast<const uint4*>(ep.resid + (size_t)(row0 + r_src) * N + colbase + chunk * 8);
+              *reinterpret_cast<uint4*>(stage_warp + r_src * 128 + ((chunk ^ (r_src & 7)) << 4)) = v4;
+            }
+            __syncwarp();
           }
 #pragma unroll 1
           for (int c = 0; c < 2; ++c) {

@@ -536,6 +536,39 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return y
 
 
+class _LinearGateResidual(torch.autograd.Function):
+    """``resid + gate * (h @ w^T)`` as ONE GEMM whose epilogue also stores the product (the gate gradient needs it): replaces the
+    GEMM + gated-residual kernel pair of the training path. Backward: gate / product gradients by the gated-residual backward
+    kernel, then the input- and weight-gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, h, w, resid, gate):
+        B, T, L, D = resid.shape
+        h2d = h.reshape(-1, h.shape[-1])
+        h2d = h2d if h2d.is_contiguous() else h2d.contiguous()
+        gate_c = gate.float().contiguous().view(B * T, D)
+        out, y = native.load().gemm_bf16_gate_residual_pre(h2d, w, resid.contiguous().view(-1, D), gate_c, L)
+        native.count_launch()
+        ctx.save_for_backward(h2d, w, gate_c, y)
+        ctx.dims, ctx.h_shape, ctx.gate_dtype = (B, T, L, D), h.shape, gate.dtype
+        return out.view(B, T, L, D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ops = native.load()
+        h2d, w, gate_c, y = ctx.saved_tensors
+        B, T, L, D = ctx.dims
+        dout = dout.contiguous()
+        dy, dgate = ops.gate_residual_bwd(dout.view(-1, D), gate_c, y, L)
+        native.count_launch(2)
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            dh = gemm_nt(dy, w, None, "none", False, True).view(ctx.h_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm_nt(dy, h2d, None, "none", True, True)
+        return dh, dw, dout, dgate.view(B, T, D).to(ctx.gate_dtype)
+
+
 def linear_gate_residual(h: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     """resid + gate * (h @ w.T); resid [B,T,L,D], gate [B,T,D], h [B,T*L,K]. Without autograd the gated
     residual is the GEMM epilogue (the product never goes to memory); with autograd the product is kept
@@ -549,6 +582,10 @@ def linear_gate_residual(h: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, 
                                                     gate.float().contiguous().view(B * T, D), L)
         native.count_launch()
         return out.view(B, T, L, D)
+    if (resid.is_cuda and needs_grad and _native_gemm_ok(h2d, w) and h2d.shape[0] % 8 == 0 and w.shape[0] % 256 == 0
+            and resid.dtype == torch.bfloat16 and getattr(w, "_cb200_gather", None) is None
+            and hasattr(native.load(), "gemm_bf16_gate_residual_pre")):
+        return _LinearGateResidual.apply(h, w, resid, gate)
     return gate_residual(resid, gate, linear(h, w).view(B, T, L, D))
 
 

@@ -566,3 +566,26 @@ def test_network_jvp_runs_on_native_kernels(monkeypatch):
     _close(F1, F2, 5e-2, 5e-2, "F")
     _close(dF1, dF2, 1e-1, 1e-1, "dF")
     assert dF2.float().abs().max() > 1e-2
+
+
+def test_linear_gate_residual_training_path():
+    """One GEMM with the gated residual in its epilogue and the product as second output: forward and all four gradients against
+    the fp32 composition; the unfused pair (GEMM + gated-residual kernel) must give the same result."""
+    torch.manual_seed(8)
+    B, T, L, D, K = 1, 3, 88, 512, 256
+    h = torch.randn(B, T * L, K, device=DEV).bfloat16().requires_grad_(True)
+    w = (torch.randn(D, K, device=DEV) / math.sqrt(K)).bfloat16().requires_grad_(True)
+    resid = torch.randn(B, T, L, D, device=DEV).bfloat16().requires_grad_(True)
+    gate = torch.randn(B, T, D, device=DEV).requires_grad_(True)
+    before = native.launches()
+    out = F_ops.linear_gate_residual(h, w, resid, gate)
+    assert native.launches() == before + 1, "the fused two-output GEMM did not serve the training path"
+    do = torch.randn_like(out)
+    got = torch.autograd.grad(out, (h, w, resid, gate), do)
+    hr, wr, rr, gr = (t.detach().float().requires_grad_(True) for t in (h, w, resid, gate))
+    want_out = rr + gr.unsqueeze(2) * (hr @ wr.t()).view(B, T, L, D)
+    want = torch.autograd.grad(want_out, (hr, wr, rr, gr), do.float())
+    _close(out, want_out, 3e-2, 2e-2, "out")
+    for name, a, b in zip(("dh", "dw", "dresid", "dgate"), got, want):
+        _close(a, b, 3e-2 * b.abs().max().item() + 1e-3, 3e-2, name)
+    _no_kernel_error()
