@@ -281,7 +281,7 @@ class _DownsampleCL:
 
     def __init__(self, mod, device):
         conv = mod.resample[1]
-        w = conv.weight.detach().float()                     # [Cout, C, 3, 3]
+        w = conv.weight.detach().float().cpu()               # [Cout, C, 3, 3]
         cout, C = w.shape[:2]
         taps, mats = [], []
         for dy in (0, 1):
@@ -296,7 +296,7 @@ class _DownsampleCL:
         self.space = ConvCL(torch.stack(mats, 1), conv.bias, taps, device)
         self.time = None
         if mod.mode == "downsample3d":
-            wt = mod.time_conv.weight.detach().float()[:, :, :, 0, 0]     # [C, C, 3]
+            wt = mod.time_conv.weight.detach().float().cpu()[:, :, :, 0, 0]     # [C, C, 3]
             c2 = wt.shape[0]
             m0 = torch.cat([wt[:, :, 0], wt[:, :, 1]], 1)                   # pair t: frames 2t, 2t + 1
             m1 = torch.cat([wt[:, :, 2], torch.zeros(c2, c2)], 1)          # pair t + 1: frame 2t + 2
@@ -330,7 +330,7 @@ class EncoderCL:
         self.device = torch.device(device)
         dev = self.device
         from . import vae_wan
-        w = encoder.conv1.weight.detach().float()            # [C0, 3, 3, 3, 3]
+        w = encoder.conv1.weight.detach().float().cpu()      # [C0, 3, 3, 3, 3]
         c0, cin = w.shape[:2]
         self.in_pad = 16                                     # RGB travels zero-padded to 16 channels
         wt = torch.zeros(c0, 27, self.in_pad)
