@@ -22,7 +22,7 @@ import json
 import math
 import os
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Tuple, Dict, List, Optional, Sequence
 
 import torch
 import torch.nn as nn
@@ -159,16 +159,19 @@ class QwenLanguageModel(nn.Module):
         return emb.cos()[None, None].to(dtype), emb.sin()[None, None].to(dtype)
 
     @torch.no_grad()
-    def forward(self, input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor] = None, cp_group=None) -> List[torch.Tensor]:
+    def forward(self, input_ids: Optional[torch.Tensor], attention_mask: Optional[torch.Tensor] = None, cp_group=None,
+                inputs_embeds: Optional[torch.Tensor] = None, rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> List[torch.Tensor]:
         """Every hidden state [B, S, hidden]. With ``cp_group`` (every rank passes the same ``input_ids``) the sequence is
         split into contiguous ranges over the group: embeddings, RoPE rows and causal-mask rows are sliced, each attention
         all-gathers keys / values (the reference's all-gather-KV context parallelism of the VLM tower,
         cosmos_reason1 qwen2_5_vl.py:1032-1034,1267-1281), and the hidden states are gathered back at the end."""
         import torch.distributed as dist
         cp = dist.get_world_size(cp_group) if cp_group is not None and dist.is_initialized() else 1
-        x = self.embed_tokens(input_ids)
+        # ``inputs_embeds`` (token embeddings with vision features scattered in) and ``rope`` (cos, sin [B, 1, S, head_dim] from
+        # 3-D multimodal positions) are supplied by the vision-language wrapper (models/qwen_vl.py)
+        x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
         B, S, _ = x.shape
-        cos, sin = self.rope(S, x.device, x.dtype)
+        cos, sin = self.rope(S, x.device, x.dtype) if rope is None else rope
         mask = None
         if attention_mask is not None or cp > 1:
             causal = torch.ones(S, S, dtype=torch.bool, device=x.device).tril()
@@ -208,7 +211,7 @@ class QwenLanguageModel(nn.Module):
         for k, v in sd.items():
             if k.endswith("._extra_state"):
                 continue
-            for prefix in ("model.language_model.", "language_model.model.", "model.", ""):
+            for prefix in ("model.language_model.", "language_model.model.", "language_model.", "model.", ""):
                 kk = k[len(prefix):] if k.startswith(prefix) else None
                 if kk is not None and kk in own:
                     mapped[kk] = v
