@@ -194,3 +194,5 @@ cs.store(group="experiment", package="_global_", name="error-free_fsdp_mock-data
                                                                            text_len=64, length=64), batch_size=1, num_workers=0),
     trainer=dict(max_iter=4, logging_iter=2),
 ))
+
+from . import sparse as _sparse_experiments  # noqa: E402,F401  (registers the sparse-attention experiments; needs the names above)

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass, field
-from typing import Sequence, List, Optional, Tuple
+from typing import Any, Sequence, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -61,6 +61,10 @@ class DiTConfig:
     timestep_scale: float = 0.001
     extra_image_context_dim: Optional[int] = None
     checkpoint_mode: str = "none"  # none | block_wise | save_attention
+    # sparse self-attention (minimal_v4_dit.py:1279-1290, 1435-1436 of the reference): -1 = every block dense; otherwise see
+    # ``replace_selfattn_op_with_sparse_attn_op``. ``natten_parameters``: one dict, or a list with one entry (or None) per block.
+    n_dense_blocks: int = -1
+    natten_parameters: Any = None
 
     @property
     def head_dim(self) -> int:
@@ -531,6 +535,8 @@ class CosmosDiT(nn.Module):
             self.register_buffer(name, torch.zeros(1, dtype=torch.float32), persistent=True)
         self.cp_group = None
         self._fsdp = None
+        if cfg.n_dense_blocks != -1:
+            replace_selfattn_op_with_sparse_attn_op(self, cfg.n_dense_blocks, cfg.natten_parameters)
 
     # ---- initialisation ---------------------------------------------------------------
     def init_weights(self):

@@ -378,7 +378,7 @@ class Text2WorldModelRectifiedFlow(nn.Module):
         latents = noise
         ones = torch.ones(n_sample, 1, **self.tensor_kwargs_fp32)
         for t in sched.timesteps.tolist():
-            v = velocity_fn(noise, latents.to(**self.tensor_kwargs), ones * float(t))
+            v = velocity_fn(noise, latents, ones * float(t))      # the fp32 state: denoise casts where it replaces the frames
             latents = sched.step(v, t, latents)
         if self.net.is_context_parallel_enabled and cp_size > 1:
             latents = cp.cat_outputs_cp(latents, 2, self.cp_group)
@@ -490,9 +490,10 @@ class Video2WorldModelRectifiedFlow(Text2WorldModelRectifiedFlow):
         mask = None
         if is_video:
             B, C = xt_B_C_T_H_W.shape[:2]
-            gt = condition.gt_frames.type_as(xt_B_C_T_H_W) * self._use_flags(condition, B, xt_B_C_T_H_W)
             mask = condition.condition_video_input_mask_B_C_T_H_W.type_as(xt_B_C_T_H_W)
-            xt_B_C_T_H_W = gt * mask + xt_B_C_T_H_W * (1 - mask)
+            # conditioning frames replace the noisy ones; on a GPU one kernel that writes the network's input dtype directly
+            xt_B_C_T_H_W = ops.frame_blend(xt_B_C_T_H_W, condition.gt_frames.type_as(xt_B_C_T_H_W), None, mask,
+                                           self._use_flags(condition, B, xt_B_C_T_H_W), out_dtype=self.tensor_kwargs.get("dtype"))
             if cfg.conditional_frame_timestep >= 0:
                 m_B_T = mask.mean(dim=[1, 3, 4]).float()
                 timesteps_B_T = cfg.conditional_frame_timestep * m_B_T + timesteps_B_T.float().view(B, -1) * (1 - m_B_T)
@@ -500,9 +501,7 @@ class Video2WorldModelRectifiedFlow(Text2WorldModelRectifiedFlow):
                        condition_video_input_mask_B_C_T_H_W=mask, context_cache=context_cache,
                        **self._net_kwargs(condition)).float()
         if is_video and cfg.denoise_replace_gt_frames:
-            gt_v = noise - condition.gt_frames.type_as(out)
-            m = mask.type_as(out)
-            out = gt_v * m + out * (1 - m)
+            out = ops.frame_blend(out, condition.gt_frames.type_as(out), noise.type_as(out), mask)
         return out
 
     def get_velocity_fn_from_batch(self, data_batch: Dict, guidance: float = 1.5, is_negative_prompt: bool = False):

@@ -21,6 +21,8 @@ from typing import Callable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..ops import functional as ops
+
 
 class RectifiedFlowSchedule:
     def __init__(self, shift: float = 5.0, num_train_timesteps: int = 1000,
@@ -120,7 +122,7 @@ class FlowEulerSolver(_FlowSolverBase):
         i = self.step_index
         dt = float(self.sigmas[i + 1]) - float(self.sigmas[i])
         self.step_index += 1
-        return sample + dt * model_output.to(sample.dtype)
+        return ops.lincomb([sample, model_output.to(sample.dtype)], [1.0, dt])
 
 
 class FlowUniPCSolver(_FlowSolverBase):
@@ -195,28 +197,32 @@ class FlowUniPCSolver(_FlowSolverBase):
         return float(c_x), float(c_m0), float(alpha_t * B_h), rks, rhos
 
     # ---- tensor updates -------------------------------------------------------------------
+    def _combine(self, base: torch.Tensor, c_x: float, c_m0: float, terms) -> torch.Tensor:
+        """``c_x * base + c_m0 * m0 - sum_k a_k * (t_k - m0)`` for ``terms = [(a_k, t_k)]``. fp32 state on a GPU: the coefficients of
+        m0 are folded on the host and the update is ONE pass over memory (``ops.lincomb``); elsewhere term by term."""
+        m0 = self.model_outputs[-1]
+        ts = [t for _, t in terms]
+        if base.is_cuda and base.dtype == torch.float32 and all(t.dtype == torch.float32 and t.shape == base.shape for t in [m0] + ts):
+            return ops.lincomb([base, m0] + ts, [c_x, c_m0 + sum(a for a, _ in terms)] + [-a for a, _ in terms])
+        x = c_x * base + c_m0 * m0
+        for a, t in terms:
+            x = x - a * (t - m0)
+        return x.to(base.dtype)
+
     def _predict(self, sample: torch.Tensor, order: int) -> torch.Tensor:
         i = self.step_index
         prev = [self.sigmas[i - k] for k in range(1, order)]
         c_x, c_m0, aB, rks, rhos = self._coeffs(self.sigmas[i + 1], self.sigmas[i], prev, order, corrector=False)
-        m0 = self.model_outputs[-1]
-        x = c_x * sample + c_m0 * m0
-        for k in range(order - 1):
-            mk = self.model_outputs[-(k + 2)]
-            x = x - (aB * float(rhos[k]) / float(rks[k])) * (mk - m0)
-        return x.to(sample.dtype)
+        terms = [(aB * float(rhos[k]) / float(rks[k]), self.model_outputs[-(k + 2)]) for k in range(order - 1)]
+        return self._combine(sample, c_x, c_m0, terms)
 
     def _correct(self, this_x0: torch.Tensor, order: int) -> torch.Tensor:
         i = self.step_index
         prev = [self.sigmas[i - (k + 1)] for k in range(1, order)]
         c_x, c_m0, aB, rks, rhos = self._coeffs(self.sigmas[i], self.sigmas[i - 1], prev, order, corrector=True)
-        m0 = self.model_outputs[-1]
-        x = c_x * self.last_sample + c_m0 * m0
-        for k in range(order - 1):
-            mk = self.model_outputs[-(k + 2)]
-            x = x - (aB * float(rhos[k]) / float(rks[k])) * (mk - m0)
-        x = x - (aB * float(rhos[-1])) * (this_x0 - m0)
-        return x.to(self.last_sample.dtype)
+        terms = [(aB * float(rhos[k]) / float(rks[k]), self.model_outputs[-(k + 2)]) for k in range(order - 1)]
+        terms.append((aB * float(rhos[-1]), this_x0))
+        return self._combine(self.last_sample, c_x, c_m0, terms)
 
     def step(self, model_output: torch.Tensor, timestep, sample: torch.Tensor) -> torch.Tensor:
         """One solver step: optional corrector on ``sample`` with the new evaluation, then predictor."""
@@ -225,7 +231,7 @@ class FlowUniPCSolver(_FlowSolverBase):
         if self.step_index is None:
             self.step_index = 0
         i = self.step_index
-        x0 = sample - float(self.sigmas[i]) * model_output.to(sample.dtype)
+        x0 = ops.lincomb([sample, model_output.to(sample.dtype)], [1.0, -float(self.sigmas[i])])
         use_corrector = i > 0 and (i - 1) not in self.disable_corrector and self.last_sample is not None
         if use_corrector:
             sample = self._correct(x0, self.this_order)

@@ -190,6 +190,53 @@ Tensor cfg_combine(const Tensor& c, const Tensor& u, double gval) {
   return o;
 }
 
+// out = sum_k coeffs[k] * xs[k]; fp32 tensors of one shape, at most 6
+Tensor lincomb(at::TensorList xs, at::ArrayRef<double> coeffs) {
+  TORCH_CHECK(!xs.empty() && xs.size() <= 6 && xs.size() == coeffs.size(), "lincomb takes 1 to 6 tensors and as many coefficients");
+  const float* ptrs[6];
+  float cs[6];
+  for (size_t k = 0; k < xs.size(); ++k) {
+    check_f32(xs[k], "operand");
+    TORCH_CHECK(xs[k].sizes() == xs[0].sizes() && xs[k].device() == xs[0].device(), "lincomb operands differ in shape or device");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(xs[k].data_ptr()) % 16 == 0, "lincomb operand is not 16-byte aligned");
+    ptrs[k] = xs[k].data_ptr<float>();
+    cs[k] = (float)coeffs[k];
+  }
+  c10::cuda::CUDAGuard g(xs[0].device());
+  Tensor o = at::empty_like(xs[0]);
+  TORCH_CHECK(cb200_lincomb(ptrs, cs, (int)xs.size(), o.data_ptr<float>(), o.numel(), stream()) == 0, "lincomb: bad operand count");
+  return o;
+}
+
+// out = keep * mask + x * (1 - mask); keep = gt * flag[b] (noise absent) or noise - gt. x, gt, noise [B, C, ...] fp32, mask
+// [B, 1, ...] fp32, flag [B] fp32.
+Tensor frame_blend(const Tensor& x, const Tensor& gt, const c10::optional<Tensor>& noise, const Tensor& mask,
+                   const c10::optional<Tensor>& flag, bool out_bf16) {
+  check_f32(x, "x");
+  check_f32(gt, "gt");
+  check_f32(mask, "mask");
+  TORCH_CHECK(x.dim() >= 3 && gt.sizes() == x.sizes(), "frame_blend: x and gt are [B, C, ...] of one shape");
+  const long B = x.size(0), C = x.size(1), S = x.numel() / (B * C);
+  TORCH_CHECK(mask.numel() == B * S, "frame_blend: the mask has one value per (sample, position)");
+  if (noise.has_value()) {
+    check_f32(*noise, "noise");
+    TORCH_CHECK(noise->sizes() == x.sizes(), "frame_blend: noise and x differ in shape");
+  }
+  if (flag.has_value()) {
+    check_f32(*flag, "flag");
+    TORCH_CHECK(flag->numel() == B, "frame_blend: one flag per sample");
+  }
+  for (const Tensor* t : {&x, &gt, &mask, noise.has_value() ? &*noise : &x})
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "frame_blend operand is not 16-byte aligned");
+  c10::cuda::CUDAGuard g(x.device());
+  Tensor o = at::empty(x.sizes(), x.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  TORCH_CHECK(cb200_frame_blend(x.data_ptr<float>(), gt.data_ptr<float>(), noise.has_value() ? noise->data_ptr<float>() : nullptr,
+                                mask.data_ptr<float>(), flag.has_value() ? flag->data_ptr<float>() : nullptr, o.data_ptr(),
+                                out_bf16 ? 1 : 0, B, C, S, stream()) == 0,
+              "frame_blend: positions per channel must be a multiple of 4");
+  return o;
+}
+
 void grad_cast_norm(const Tensor& g16, Tensor g32, Tensor sumsq, double scale) {
   check_bf16(g16, "grad");
   check_f32(g32, "grad_shard");
@@ -495,6 +542,8 @@ TORCH_LIBRARY(cosmos_b200, m) {
   m.def("gelu_fwd(Tensor x) -> Tensor", &gelu_fwd);
   m.def("gelu_bwd(Tensor dy, Tensor x) -> Tensor", &gelu_bwd);
   m.def("cfg_combine(Tensor cond, Tensor uncond, float guidance) -> Tensor", &cfg_combine);
+  m.def("lincomb(Tensor[] xs, float[] coeffs) -> Tensor", &lincomb);
+  m.def("frame_blend(Tensor x, Tensor gt, Tensor? noise, Tensor mask, Tensor? flag, bool out_bf16) -> Tensor", &frame_blend);
   m.def("grad_cast_norm(Tensor g16, Tensor(a!) g32, Tensor(b!) sumsq, float scale) -> ()", &grad_cast_norm);
   m.def("adamw_ema_shard(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? ema, Tensor(e!)? out16, "
         "Tensor clip, float lr, float beta1, float beta2, float eps, float wd, int step, float ema_beta) -> ()",

@@ -28,6 +28,10 @@ void cb200_rmsnorm_rope_bwd(const void* dy, const void* x, const float* w, const
 void cb200_gelu_fwd(const void* x, void* y, long n, cudaStream_t st);
 void cb200_gelu_bwd(const void* dy, const void* x, void* dx, long n, cudaStream_t st);
 void cb200_cfg_combine(const float* c, const float* u, float* o, float g, long n, cudaStream_t st);
+// sampler_ops.cu (return 0, or 1 when the shape is not served: the caller falls back)
+int cb200_lincomb(const float* const* xs, const float* cs, int count, float* out, long n, cudaStream_t st);
+int cb200_frame_blend(const float* x, const float* gt, const float* noise, const float* mask, const float* flag, void* out,
+                      int out_bf16, long B, long C, long S, cudaStream_t st);
 int cb200_grad_cast_norm_blocks(long n);
 void cb200_grad_cast_norm(const void* g16, float* g32, float* sumsq, float* partials, float scale, long n, cudaStream_t st);
 void cb200_adamw_ema_shard(float* master, const float* grad, float* m, float* v, float* ema, void* out16,

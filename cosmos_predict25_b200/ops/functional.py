@@ -722,3 +722,37 @@ def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, guidance: float) -> to
         native.count_launch()
         return native.load().cfg_combine(cond.contiguous(), uncond.contiguous(), float(guidance))
     return ref.cfg_combine(cond, uncond, guidance)
+
+
+def _sampler_native(*ts) -> bool:
+    # contiguous already (a .contiguous() copy would cost the pass the kernel saves) and aligned for 16-byte accesses
+    return (all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.data_ptr() % 16 == 0 for t in ts)
+            and native.available() and not any(t.requires_grad for t in ts if torch.is_grad_enabled()))
+
+
+def lincomb(xs, coeffs) -> torch.Tensor:
+    """``sum_k coeffs[k] * xs[k]``: one pass over memory for a state update of the multistep sampler (fp32 on a GPU; anything
+    else goes through torch)."""
+    xs = list(xs)
+    coeffs = [float(c) for c in coeffs]
+    if 1 <= len(xs) <= 6 and _sampler_native(*xs) and all(x.shape == xs[0].shape for x in xs) and xs[0].numel() > 0:
+        native.count_launch()
+        return native.load().lincomb([x.contiguous() for x in xs], coeffs)
+    return ref.lincomb(xs, coeffs)
+
+
+def frame_blend(x, gt, noise, mask, flag=None, out_dtype=None) -> torch.Tensor:
+    """Put conditioning frames back: ``keep * mask + x * (1 - mask)`` with ``keep = gt * flag`` or ``noise - gt`` (see
+    ``ref.frame_blend``); on a GPU one kernel that can also write the network's bf16 input directly."""
+    ts = [t for t in (x, gt, noise) if t is not None]
+    B, C = x.shape[0], x.shape[1]
+    S = x.numel() // max(B * C, 1)
+    if (x.dim() >= 3 and _sampler_native(*ts) and all(t.shape == x.shape for t in ts) and mask.is_cuda and mask.numel() == B * S
+            and mask.is_contiguous() and mask.data_ptr() % 16 == 0
+            and S % 4 == 0 and out_dtype in (None, torch.float32, torch.bfloat16) and x.numel() > 0):
+        native.count_launch()
+        f = None if flag is None else flag.reshape(-1).float().contiguous()
+        return native.load().frame_blend(x.contiguous(), gt.contiguous(), None if noise is None else noise.contiguous(),
+                                         mask.float().contiguous(), f, out_dtype == torch.bfloat16)
+    return ref.frame_blend(x, gt, noise, mask, flag, out_dtype)
+

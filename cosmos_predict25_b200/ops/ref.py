@@ -141,6 +141,26 @@ def cfg_combine(cond: torch.Tensor, uncond: torch.Tensor, guidance: float) -> to
     return cond + guidance * (cond - uncond)
 
 
+def lincomb(xs, coeffs) -> torch.Tensor:
+    """``sum_k coeffs[k] * xs[k]`` in the dtype of ``xs[0]``."""
+    out = coeffs[0] * xs[0]
+    for c, x in zip(coeffs[1:], xs[1:]):
+        out = out + c * x.to(out.dtype)
+    return out
+
+
+def frame_blend(x, gt, noise, mask, flag=None, out_dtype=None) -> torch.Tensor:
+    """``keep * mask + x * (1 - mask)``; ``keep = gt * flag`` (``noise`` is None) or ``noise - gt``. ``mask`` broadcasts over the
+    channels, ``flag`` ([B]) over everything but the batch."""
+    if noise is not None:
+        keep = noise - gt
+    else:
+        keep = gt if flag is None else gt * flag.view(-1, *([1] * (gt.dim() - 1))).to(gt.dtype)
+    m = mask.to(x.dtype)
+    out = keep.to(x.dtype) * m + x * (1 - m)
+    return out if out_dtype is None else out.to(out_dtype)
+
+
 def causal_conv3d(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], cache: Optional[torch.Tensor] = None):
     """3-D conv that pads (or prepends ``cache`` frames) on the past side of time only.
 

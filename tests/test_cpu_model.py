@@ -386,3 +386,21 @@ def test_kernel_encoder_matches_torch_encoder_on_cpu(monkeypatch):
         assert got.shape == want.shape, (got.shape, want.shape)
         scale = want.abs().mean().item()
         assert (got.float() - want).abs().mean().item() < 0.05 * scale + 1e-3, (lo, hi)
+
+
+def test_sampler_state_update_definitions():
+    """The torch definitions behind the sampling-loop kernels: a linear combination equals the term-by-term arithmetic, the frame
+    replacement keeps conditioning frames (scaled by the per-sample flag) or their velocity and everything else untouched."""
+    from cosmos_predict25_b200.ops import functional as F
+    torch.manual_seed(0)
+    xs = [torch.randn(2, 3, 4, 5, 8) for _ in range(3)]
+    out = F.lincomb(xs, [1.0, -0.25, 2.0])
+    assert torch.allclose(out, xs[0] - 0.25 * xs[1] + 2.0 * xs[2], atol=1e-6)
+    x, gt, noise = xs
+    mask = torch.zeros(2, 1, 4, 5, 8)
+    mask[:, :, 0] = 1
+    flag = torch.tensor([1.0, 0.0]).view(2, 1, 1, 1, 1)
+    a = F.frame_blend(x, gt, None, mask, flag)
+    assert torch.equal(a[0, :, 0], gt[0, :, 0]) and torch.equal(a[1, :, 0], torch.zeros_like(gt[1, :, 0])) and torch.equal(a[:, :, 1:], x[:, :, 1:])
+    b = F.frame_blend(x, gt, noise, mask, out_dtype=torch.bfloat16)
+    assert b.dtype == torch.bfloat16 and torch.equal(b[:, :, 0], (noise - gt)[:, :, 0].bfloat16()) and torch.equal(b[:, :, 1:], x[:, :, 1:].bfloat16())

@@ -164,3 +164,22 @@ def test_folder_monitor_and_text2image(tmp_path):
     mon.run()                                                        # returns at once
     img = Text2ImageInference("tiny_video2world_cpu", None, pipe=pipe).generate_image("a dog", resolution="32,32", num_steps=2, guidance=2.0)
     assert img.shape[0] == 1 and img.shape[2] == 1 and torch.isfinite(img).all()
+
+
+def test_sparse_attention_experiments_resolve_and_build():
+    """The sparse experiments: schedules have one entry per block of their network, the chosen 2B schedule resolves through the
+    config system into the network's two sparse fields, and the tiny sparse experiment builds a model whose first block attends
+    through the neighbourhood operator (second block dense) and still trains a step."""
+    from cosmos_predict25_b200.configs import sparse
+    for name, sched in sparse.SCHEDULES.items():
+        assert len(sched) == (28 if name.startswith("2B") else 36) and set(sched) <= set(sparse.LAYER_KINDS) | {"-"}
+    assert 0.5 < sparse.skipped_fraction("2B_comb02") < 0.9
+    cfg = override(v2w_cfg.make_config(), ["--", f"experiment={sparse.SPARSE_2B}"])
+    net = cfg["model"]["config"]["net"]
+    assert net["n_dense_blocks"] == 0 and len(net["natten_parameters"]) == 28
+    assert tuple(net["natten_parameters"][0]["dilation"]) == (1, 11, 5) and cfg["optimizer"]["weight_decay"] == 0.1
+    cfg = override(v2w_cfg.make_config(), ["--", "experiment=tiny_video2world_sparse_cpu"])
+    model = instantiate(cfg["model"])
+    assert model.net.blocks[0].self_attn.sparse_op is not None and model.net.blocks[1].self_attn.sparse_op is None
+    out = model.net(torch.randn(1, 16, 4, 16, 16), torch.full((1, 1), 500.0), crossattn_emb=torch.randn(1, 32, 256))
+    assert out.shape == (1, 16, 4, 16, 16) and bool(out.isfinite().all())

@@ -589,3 +589,48 @@ def test_linear_gate_residual_training_path():
     for name, a, b in zip(("dh", "dw", "dresid", "dgate"), got, want):
         _close(a, b, 3e-2 * b.abs().max().item() + 1e-3, 3e-2, name)
     _no_kernel_error()
+
+
+@pytest.mark.gpu
+def test_sampler_state_update_and_frame_replacement_kernels():
+    """One-pass kernels of the sampling loop against their torch definitions: linear combination of up to 6 fp32 tensors (ragged
+    tail included) and the replacement of conditioning frames (both forms, fp32 and bf16 output)."""
+    from cosmos_predict25_b200.ops import functional as F, ref
+    torch.manual_seed(0)
+    for n_ops, shape in ((1, (1027,)), (2, (2, 16, 3, 10, 12)), (4, (1, 16, 24, 88, 160)), (6, (3, 5, 7))):
+        xs = [torch.randn(shape, device="cuda") for _ in range(n_ops)]
+        cs = [0.37 * (k + 1) * (-1) ** k for k in range(n_ops)]
+        out = F.lincomb(xs, cs)
+        want = sum(c * x.double() for c, x in zip(cs, xs))
+        assert out.dtype == torch.float32 and (out.double() - want).abs().max().item() < 1e-5
+    B, C, T, H, W = 2, 16, 6, 10, 12
+    x, gt, noise = (torch.randn(B, C, T, H, W, device="cuda") for _ in range(3))
+    mask = torch.zeros(B, 1, T, H, W, device="cuda")
+    mask[:, :, :2] = 1
+    flag = torch.tensor([1.0, 0.0], device="cuda").view(B, 1, 1, 1, 1)
+    before = F.native.launches()
+    a = F.frame_blend(x, gt, None, mask, flag)
+    assert torch.equal(a, ref.frame_blend(x, gt, None, mask, flag))
+    a16 = F.frame_blend(x, gt, None, mask, flag, out_dtype=torch.bfloat16)
+    assert a16.dtype == torch.bfloat16 and torch.equal(a16, ref.frame_blend(x, gt, None, mask, flag).bfloat16())
+    b = F.frame_blend(x, gt, noise, mask)
+    assert torch.equal(b, ref.frame_blend(x, gt, noise, mask))
+    soft = torch.rand(B, 1, T, H, W, device="cuda")                # a fractional mask: fused multiply-add rounding only
+    assert (F.frame_blend(x, gt, noise, soft) - ref.frame_blend(x, gt, noise, soft)).abs().max().item() < 1e-5
+    assert F.native.launches() >= before + 5, "the sampler kernels did not run"
+
+
+@pytest.mark.gpu
+def test_unipc_on_the_state_update_kernel_matches_the_host_arithmetic():
+    from cosmos_predict25_b200.models.schedulers import FlowUniPCSolver
+    torch.manual_seed(1)
+    x_dev = torch.randn(1, 16, 4, 8, 12, device="cuda")
+    x_cpu = x_dev.cpu()
+    s_dev, s_cpu = FlowUniPCSolver(1000), FlowUniPCSolver(1000)
+    for s in (s_dev, s_cpu):
+        s.set_timesteps(6, device="cpu", shift=5.0)
+    for t in s_dev.timesteps.tolist():
+        v = torch.randn_like(x_cpu)
+        x_cpu = s_cpu.step(v, t, x_cpu)
+        x_dev = s_dev.step(v.cuda(), t, x_dev)
+    assert (x_dev.cpu() - x_cpu).abs().max().item() < 1e-4 * x_cpu.abs().max().item()
