@@ -25,9 +25,9 @@ def apply_tp(model: nn.Module, tp_mesh, sequence_parallel: bool = False, loss_pa
     from torch.distributed.tensor import Replicate, Shard
     from torch.distributed.tensor.parallel import (ColwiseParallel, PrepareModuleInput, RowwiseParallel, SequenceParallel,
                                                    parallelize_module)
-    if enable_float8:
-        raise NotImplementedError("float8 tensor-parallel plans need torchao, which is not available here")
     if enable_async_tp:
+        # the reference's asynchronous tensor parallelism is a torch.compile pass over symmetric memory; this framework's
+        # counterpart for weights that arrive over NVLink is the all-gather fused into the GEMM kernel of the video model
         log.warning("async tensor parallelism relies on torch.compile; running the synchronous plan")
     cfg = model.config
     tp = tp_mesh.size()
@@ -86,6 +86,16 @@ def apply_ac(model: nn.Module, mode: str = "full", selective_option: str = "2") 
     return model
 
 
+def apply_float8(model: nn.Module, keep_high_precision=("lm_head", "embed_tokens")) -> int:
+    """Run the linear layers of the tower on 8-bit GEMM operands (dynamic tensor-wise scaling, e4m3 forward / e5m2 gradients:
+    ``modules/float8.py``). Applied BEFORE the tensor-parallel plan: the converted layers are still ``nn.Linear`` modules, so the
+    column- / row-wise plans shard them as usual and the 8-bit products run on the local shards."""
+    from ..modules.float8 import convert_to_float8
+    n = convert_to_float8(model, lambda name, m: not any(k in name for k in keep_high_precision))
+    log.info(f"float8: {n} linear layers converted")
+    return n
+
+
 def apply_compile(model: nn.Module, enabled: bool = False) -> nn.Module:
     if enabled:
         raise NotImplementedError("torch.compile is not used by this framework: hot operators are hand-written kernels")
@@ -114,7 +124,9 @@ def apply_ddp(model: nn.Module, dp_mesh) -> nn.Module:
 def parallelize_qwen(model: nn.Module, world_mesh, parallel_dims: ParallelDims, ac_mode: str = "none", sequence_parallel: bool = False,
                      enable_float8: bool = False, enable_async_tp: bool = False, compile: bool = False, data_parallel: str = "fsdp",
                      param_dtype=torch.bfloat16, reduce_dtype=torch.float32) -> nn.Module:
-    """TP -> activation checkpointing -> (compile) -> FSDP / DDP, in that order."""
+    """(float8 conversion) -> TP -> activation checkpointing -> (compile) -> FSDP / DDP, in that order."""
+    if enable_float8:
+        apply_float8(model)
     if parallel_dims.tp_enabled:
         apply_tp(model, world_mesh["tp"], sequence_parallel, parallel_dims.loss_parallel_enabled, enable_float8, enable_async_tp)
     apply_ac(model, ac_mode)

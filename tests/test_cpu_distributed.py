@@ -439,6 +439,48 @@ def _tp_qwen(rank, world, tmp, sequence_parallel):
     assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
 
 
+def _tp_qwen_float8(rank, world, tmp):
+    """Float8 linears under the tensor-parallel plan: logits and every gradient stay within the 8-bit error of the fp32 model."""
+    from cosmos_predict25_b200.models.text_encoder import QwenConfig
+    from cosmos_predict25_b200.models.vlm_train import QwenForCausalLM
+    from cosmos_predict25_b200.modules.float8 import Float8Linear
+    from cosmos_predict25_b200.parallel.parallel_dims import ParallelDims
+    from cosmos_predict25_b200.parallel.parallelize_qwen import parallelize_qwen
+    from torch.distributed.tensor import DTensor
+    torch.manual_seed(0)
+    cfg = QwenConfig(vocab_size=64, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2)
+    ref = QwenForCausalLM(cfg)
+    tp_model = QwenForCausalLM(cfg)
+    tp_model.load_state_dict(ref.state_dict())
+    dims = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, world_size=world)
+    parallelize_qwen(tp_model.model, dims.build_mesh("cpu"), dims, enable_float8=True)
+    q = tp_model.model.layers[0].self_attn.q_proj
+    assert isinstance(q, Float8Linear) and isinstance(q.weight, DTensor) and q.weight.to_local().shape[0] == 64 // world
+    assert type(tp_model.lm_head) is torch.nn.Linear
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(1))
+    want = ref(ids)
+    got = tp_model(ids)
+    got = got.full_tensor() if isinstance(got, DTensor) else got
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()
+    assert rel(got, want) < 0.1, rel(got, want)
+    g = torch.randn(want.shape, generator=torch.Generator().manual_seed(2))
+    (want * g).sum().backward()
+    (got * g).sum().backward()
+    checked = 0
+    for (n, p), (_, pr) in zip(tp_model.named_parameters(), ref.named_parameters()):
+        if pr.grad is None:
+            continue
+        assert p.grad is not None, n
+        grad = p.grad.full_tensor() if isinstance(p.grad, DTensor) else p.grad
+        assert rel(grad, pr.grad) < 0.25, (n, rel(grad, pr.grad))
+        checked += 1
+    assert checked >= 20
+
+
+def test_tensor_parallel_float8_qwen():
+    run_distributed("_tp_qwen_float8", 2)
+
+
 @pytest.mark.parametrize("sequence_parallel", [False])
 def test_tensor_parallel_qwen_matches_single_rank(sequence_parallel):
     run_distributed("_tp_qwen", 2, sequence_parallel=sequence_parallel)
