@@ -68,7 +68,8 @@ class _Float8Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = scaled_mm(g8, sg, w8.t().contiguous(), sw, ctx.x_dtype).reshape(ctx.x_shape)           # [M, N] x [K, N]^T
         if ctx.needs_input_grad[1]:
-            dw = scaled_mm(g8.t().contiguous(), sg, x8.t().contiguous(), sx, torch.float32).to(ctx.w_dtype)   # [N, M] x [K, M]^T
+            acc = torch.float32 if not g.is_cuda or ctx.w_dtype == torch.float32 else ctx.w_dtype
+            dw = scaled_mm(g8.t().contiguous(), sg, x8.t().contiguous(), sx, acc).to(ctx.w_dtype)      # [N, M] x [K, M]^T
         return dx, dw
 
 

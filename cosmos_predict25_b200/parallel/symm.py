@@ -35,34 +35,76 @@ class SymmetricTensor:
     ptrs: List[int]
 
 
-class SymmetricArena:
-    """One symmetric allocation per rank, bump-allocated into tensors (256-byte aligned)."""
+CANARY_BYTES = 256
+CANARY_VALUE = 0xA5
+CANARY_SLOTS = 4096           # head-room (in allocations) that a guarded arena adds to the size its owner asked for
 
-    def __init__(self, nbytes: int, group, device: torch.device):
-        import torch.distributed._symmetric_memory as symm_mem
 
-        self.group = group
-        self.device = device
-        self.nbytes = (nbytes + 255) // 256 * 256
-        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
-        self.handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
-        self.rank = self.handle.rank
-        self.world = self.handle.world_size
-        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        assert self.base_ptrs[self.rank] == self.buf.data_ptr(), "symmetric arena: local pointer mismatch"
+class BumpArena:
+    """Bump allocator over one uint8 buffer whose address on every peer is known (256-byte aligned tensors).
+
+    With ``canary`` every allocation is followed by a 256-byte guard filled with 0xA5; ``check_canaries()`` reads the guards back
+    and raises if a kernel (this rank's or a peer's: peers store into this memory) wrote past the end of a buffer. The guards
+    cost one small device-to-host copy per check and nothing inside the kernels."""
+
+    def __init__(self, buf: torch.Tensor, base_ptrs: List[int], canary: bool = False):
+        self.buf = buf
+        self.nbytes = buf.numel()
+        self.base_ptrs = base_ptrs
+        self.canary = canary
         self.offset = 0
+        self._guards: List[Tuple[int, int, str]] = []      # (offset of the guard, bytes of the allocation before it, dtype)
 
     def alloc(self, numel: int, dtype: torch.dtype, zero: bool = True) -> SymmetricTensor:
         esize = torch.empty((), dtype=dtype).element_size()
         nbytes = (numel * esize + 255) // 256 * 256
-        if self.offset + nbytes > self.nbytes:
-            raise MemoryError(f"symmetric arena exhausted: need {nbytes} more bytes, {self.nbytes - self.offset} left")
+        need = nbytes + (CANARY_BYTES if self.canary else 0)
+        if self.offset + need > self.nbytes:
+            raise MemoryError(f"symmetric arena exhausted: need {need} more bytes, {self.nbytes - self.offset} left")
         t = self.buf[self.offset: self.offset + numel * esize].view(dtype)
         if zero:
             t.zero_()
         st = SymmetricTensor(t, [p + self.offset for p in self.base_ptrs])
         self.offset += nbytes
+        if self.canary:
+            # the guard starts at the 256-byte boundary after the data: the alignment slack before it is not watched
+            self.buf[self.offset: self.offset + CANARY_BYTES].fill_(CANARY_VALUE)
+            self._guards.append((self.offset, numel * esize, str(dtype)))
+            self.offset += CANARY_BYTES
         return st
+
+    def check_canaries(self) -> None:
+        if not self._guards:
+            return
+        idx = torch.tensor([g[0] for g in self._guards], device=self.buf.device)
+        words = self.buf[(idx[:, None] + torch.arange(CANARY_BYTES, device=self.buf.device)[None, :])].cpu()
+        bad = (words != CANARY_VALUE).any(dim=1).nonzero().flatten().tolist()
+        if bad:
+            i = bad[0]
+            off, nbytes, dtype = self._guards[i]
+            first = int((words[i] != CANARY_VALUE).nonzero()[0])
+            raise RuntimeError(f"symmetric arena: allocation #{i} ({nbytes} bytes of {dtype}, guard at offset {off}) was overrun: "
+                               f"guard byte {first} holds {int(words[i][first]):#x}; {len(bad)} guard(s) damaged in total")
+
+
+class SymmetricArena(BumpArena):
+    """One symmetric allocation per rank, bump-allocated into tensors (256-byte aligned). ``canary`` (default: the environment
+    variable ``COSMOS_B200_CANARY=1``) adds guard words behind every tensor, see ``BumpArena``."""
+
+    def __init__(self, nbytes: int, group, device: torch.device, canary: Optional[bool] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if canary is None:
+            canary = os.environ.get("COSMOS_B200_CANARY", "0") == "1"
+        self.group = group
+        self.device = device
+        nbytes = (nbytes + 255) // 256 * 256 + (CANARY_BYTES * CANARY_SLOTS if canary else 0)
+        buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        super().__init__(buf, [int(p) for p in self.handle.buffer_ptrs], canary)
+        assert self.base_ptrs[self.rank] == self.buf.data_ptr(), "symmetric arena: local pointer mismatch"
 
 
 class PeerContext:
@@ -89,6 +131,7 @@ class PeerContext:
     def check(self) -> None:
         """Host-side check of the device error word (synchronises the device)."""
         code = int(self.ops.kernel_error(self.device.index, True))
+        self.arena.check_canaries()
         if code != 0:
             raise RuntimeError(f"a peer-memory kernel gave up waiting (error code {code}): rank {code - 100} did not arrive"
                                if code >= 100 else f"kernel error code {code}")

@@ -134,3 +134,26 @@ def test_kernel_error_word_stops_the_run_before_a_checkpoint(tmp_path):
     with pytest.raises(RuntimeError, match="gave up waiting"):
         t.train(list(_batches(6)))
     assert ck.saved == [2]                        # iteration 4's save was refused
+
+
+def test_arena_guard_words_catch_an_overrun():
+    """Guard words behind every allocation of the peer arena: untouched guards pass, a write one byte past the end of a buffer
+    (what a kernel with a wrong bound would do to this rank's or a peer's memory) is reported with the allocation it follows."""
+    import pytest
+    import torch
+    from cosmos_predict25_b200.parallel.symm import CANARY_BYTES, BumpArena
+    arena = BumpArena(torch.zeros(1 << 16, dtype=torch.uint8), [0, 1 << 20], canary=True)
+    a = arena.alloc(100, torch.float32)
+    b = arena.alloc(64, torch.bfloat16, zero=False)
+    assert a.ptrs == [0, 1 << 20] and b.ptrs[0] == 512 + CANARY_BYTES and b.tensor.numel() == 64
+    a.tensor.fill_(1.0)
+    b.tensor.fill_(2.0)
+    arena.check_canaries()
+    arena.buf[512 + 3] = 0                          # first guard = bytes [512, 768): a's 400 bytes round up to 512
+    with pytest.raises(RuntimeError, match=r"allocation #0 \(400 bytes of torch.float32, guard at offset 512\).*guard byte 3"):
+        arena.check_canaries()
+    plain = BumpArena(torch.zeros(1024, dtype=torch.uint8), [0])
+    assert plain.alloc(64, torch.float32).tensor.numel() == 64 and plain.offset == 256
+    plain.check_canaries()
+    with pytest.raises(MemoryError):
+        plain.alloc(1024, torch.float32)

@@ -73,12 +73,13 @@ def _run(fn_name, world=2):
 def _a2a_peer_vs_nccl(rank, world):
     from cosmos_predict25_b200.ops import functional as F_ops
     from cosmos_predict25_b200.parallel import ulysses
-    from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext
+    from cosmos_predict25_b200.parallel.symm import PeerAllToAll, PeerContext, SymmetricArena
     dev = torch.device("cuda", rank)
     g = dist.group.WORLD
     torch.manual_seed(7 + rank)
     B, S, H, D = 1, 96, 4, 128
-    ctx = PeerContext(g, dev, arena_bytes=64 << 20)
+    # guard words behind every buffer of the arena: ctx.check() also verifies that no kernel of either rank wrote past a buffer
+    ctx = PeerContext(g, dev, arena=SymmetricArena(64 << 20, g, dev, canary=True))
     t = PeerAllToAll(ctx, max_elems=B * S * H * D)
     x = torch.randn(B, S, H, D, device=dev).bfloat16()
     want = ulysses.seq_to_head(x, g)            # NCCL all_to_all_single
