@@ -121,6 +121,27 @@ class Video2WorldCondition(Text2WorldCondition):
         return replace(base, gt_frames=gt, condition_video_input_mask_B_C_T_H_W=mask)
 
 
+class Video2WorldConditionV2(Video2WorldCondition):
+    """Variant whose samples WITHOUT the video-condition flag get no conditioning frames at all (the mask is zero for them), where
+    the first version keeps the frames and lets the model multiply them by the flag; at inference both guidance branches see the
+    requested number of frames (configs/video2world/defaults/conditioner.py:172-209 of the reference)."""
+
+    def set_video_condition(self, gt_frames, random_min_num_conditional_frames, random_max_num_conditional_frames,
+                            num_conditional_frames=None, conditional_frames_probs=None) -> "Video2WorldConditionV2":
+        c = super().set_video_condition(gt_frames, random_min_num_conditional_frames, random_max_num_conditional_frames,
+                                        num_conditional_frames, conditional_frames_probs)
+        uvc = self.use_video_condition
+        if isinstance(uvc, torch.Tensor):
+            keep = uvc.to(c.condition_video_input_mask_B_C_T_H_W.device).bool().view(-1, 1, 1, 1, 1)
+            mask = c.condition_video_input_mask_B_C_T_H_W * keep.to(c.condition_video_input_mask_B_C_T_H_W.dtype)
+        else:
+            mask = c.condition_video_input_mask_B_C_T_H_W if uvc else torch.zeros_like(c.condition_video_input_mask_B_C_T_H_W)
+        return replace(c, condition_video_input_mask_B_C_T_H_W=mask)
+
+    def edit_for_inference(self, is_cfg_conditional: bool = True, num_conditional_frames: int = 1) -> "Video2WorldConditionV2":
+        return Video2WorldCondition.set_video_condition(self, self.gt_frames, 0, 0, num_conditional_frames=num_conditional_frames)
+
+
 # --------------------------------------------------------------------------------------------
 # embedders
 # --------------------------------------------------------------------------------------------
@@ -255,6 +276,10 @@ class VideoConditioner(GeneralConditioner):
 
 class Video2WorldConditioner(GeneralConditioner):
     condition_cls = Video2WorldCondition
+
+
+class Video2WorldConditionerV2(GeneralConditioner):
+    condition_cls = Video2WorldConditionV2
 
 
 def default_video2world_conditioner(text_dropout: float = 0.2) -> Video2WorldConditioner:

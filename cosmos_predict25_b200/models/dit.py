@@ -151,6 +151,23 @@ class Timesteps(nn.Module):
         return torch.cat([ang.cos(), ang.sin()], dim=-1)
 
 
+class FourierFeatures(nn.Module):
+    """[B] -> [B, D] random Fourier features cos(2 pi (bandwidth f x + p)) with f ~ N(0, 1), p ~ U(0, 1) drawn once from a fixed seed
+    (so every rank and every restart holds the same table); ``normalize`` scales by sqrt(2) for unit variance. An alternative
+    noise-level embedding of the EDM-era networks (minimal_v4_dit.py:786-838 of the reference)."""
+
+    def __init__(self, num_channels: int, bandwidth: float = 1.0, normalize: bool = False):
+        super().__init__()
+        g = torch.Generator().manual_seed(0)
+        self.register_buffer("freqs", 2 * math.pi * bandwidth * torch.randn(num_channels, generator=g), persistent=True)
+        self.register_buffer("phases", 2 * math.pi * torch.rand(num_channels, generator=g), persistent=True)
+        self.gain = math.sqrt(2.0) if normalize else 1.0
+
+    def forward(self, x: torch.Tensor, gain: float = 1.0) -> torch.Tensor:
+        y = torch.outer(x.float(), self.freqs.float()) + self.phases.float()
+        return (y.cos() * (self.gain * gain)).to(x.dtype)
+
+
 class TimestepEmbedding(nn.Module):
     """Linear -> SiLU -> Linear(3D). With AdaLN-LoRA the *raw sinusoid* is the embedding that is
     passed on and the MLP output is the shared LoRA term (minimal_v4_dit.py:776-783)."""

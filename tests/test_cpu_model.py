@@ -404,3 +404,23 @@ def test_sampler_state_update_definitions():
     assert torch.equal(a[0, :, 0], gt[0, :, 0]) and torch.equal(a[1, :, 0], torch.zeros_like(gt[1, :, 0])) and torch.equal(a[:, :, 1:], x[:, :, 1:])
     b = F.frame_blend(x, gt, noise, mask, out_dtype=torch.bfloat16)
     assert b.dtype == torch.bfloat16 and torch.equal(b[:, :, 0], (noise - gt)[:, :, 0].bfloat16()) and torch.equal(b[:, :, 1:], x[:, :, 1:].bfloat16())
+
+
+def test_condition_v2_and_fourier_features():
+    from dataclasses import replace
+    from cosmos_predict25_b200.models.conditioner import Video2WorldCondition, Video2WorldConditionV2
+    from cosmos_predict25_b200.models.dit import FourierFeatures
+    gt = torch.randn(2, 4, 5, 6, 6)
+    base = dict(crossattn_emb=torch.zeros(2, 3, 8))
+    flags = torch.tensor([True, False])
+    v1 = Video2WorldCondition(**base, use_video_condition=flags).set_video_condition(gt, 0, 0, num_conditional_frames=2)
+    v2 = Video2WorldConditionV2(**base, use_video_condition=flags).set_video_condition(gt, 0, 0, num_conditional_frames=2)
+    m1, m2 = v1.condition_video_input_mask_B_C_T_H_W, v2.condition_video_input_mask_B_C_T_H_W
+    assert m1[:, 0, :, 0, 0].sum(1).tolist() == [2, 2] and m2[:, 0, :, 0, 0].sum(1).tolist() == [2, 0]
+    inf = replace(v2, use_video_condition=False).edit_for_inference(is_cfg_conditional=False, num_conditional_frames=1)
+    assert inf.condition_video_input_mask_B_C_T_H_W[:, 0, :, 0, 0].sum(1).tolist() == [1, 1]
+    f1, f2 = FourierFeatures(16, bandwidth=0.5, normalize=True), FourierFeatures(16, bandwidth=0.5, normalize=True)
+    x = torch.tensor([0.0, 0.3, -1.2])
+    y = f1(x)
+    assert y.shape == (3, 16) and torch.equal(y, f2(x)) and torch.allclose(y[0], math.sqrt(2) * f1.phases.cos(), atol=1e-6)
+    assert set(f1.state_dict()) == {"freqs", "phases"}
