@@ -548,8 +548,9 @@ class CosmosDiT(nn.Module):
         self.blocks = nn.ModuleList([Block(cfg) for _ in range(cfg.num_blocks)])
         self.final_layer = FinalLayer(cfg)
         # training statistics buffers kept for checkpoint parity (model_weights_stats.py:41-51)
-        for name in ("accum_video_sample_counter", "accum_image_sample_counter", "accum_iteration", "accum_train_in_hours"):
-            self.register_buffer(name, torch.zeros(1, dtype=torch.float32), persistent=True)
+        for name in ("accum_video_sample_counter", "accum_image_sample_counter", "accum_iteration"):
+            self.register_buffer(name, torch.tensor(0, dtype=torch.int64), persistent=True)
+        self.register_buffer("accum_train_in_hours", torch.tensor(0.0, dtype=torch.float32), persistent=True)
         self.cp_group = None
         self._fsdp = None
         if cfg.n_dense_blocks != -1:

@@ -1,0 +1,102 @@
+"""Import modules of the reference implementation as test oracles.
+
+The reference tree is looked up in ``$COSMOS_REFERENCE_DIR`` and then in ``baseline/_ref`` under the repository root; tests that
+need it are skipped when neither exists. Packages that the reference imports at module level but that the compared code paths
+never touch (object-store clients, video writers) are replaced by inert stand-ins, so that its unmodified files load in an image
+without them. Nothing here is used by the framework itself.
+"""
+
+import importlib
+import os
+import sys
+import types
+from unittest.mock import MagicMock
+
+import pytest
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class _Inert(types.ModuleType):
+    __path__ = []
+
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return MagicMock(name=f"{self.__name__}.{name}")
+
+
+def reference_dir():
+    for cand in (os.environ.get("COSMOS_REFERENCE_DIR"), os.path.join(_ROOT, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "cosmos_predict2")):
+            return cand
+    return None
+
+
+def import_reference(module: str, max_stubs: int = 24):
+    """Import ``module`` (dotted name under ``cosmos_predict2``) from the reference tree; skip the test if that is impossible."""
+    root = reference_dir()
+    if root is None:
+        pytest.skip("no copy of the reference implementation here")
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    for _ in range(max_stubs):
+        try:
+            return importlib.import_module(module)
+        except ModuleNotFoundError as e:
+            if e.name is None or e.name.startswith("cosmos_predict2"):
+                pytest.skip(f"the reference module {module} does not import here: {e}")
+            sys.modules[e.name] = _Inert(e.name)
+            for k in [k for k in sys.modules if k.startswith("cosmos_predict2")]:
+                del sys.modules[k]
+        except Exception as e:          # anything else (a missing compiled extension, a version clash): no oracle
+            pytest.skip(f"the reference module {module} does not import here: {type(e).__name__}: {e}")
+    pytest.skip(f"the reference module {module} needs more than {max_stubs} absent packages")
+
+
+def install_transformer_engine_standins() -> None:
+    """The two TransformerEngine entry points that the reference network calls, restated in plain torch from their documented
+    semantics, so that the reference's network file imports and runs without the package: ``pytorch.RMSNorm`` (fp32 statistics,
+    learnable weight) and ``pytorch.attention.apply_rotary_pos_emb`` (non-interleaved rotation by the given angles)."""
+    import torch
+    import torch.nn as nn
+    if "transformer_engine" in sys.modules:
+        return
+
+    class RMSNorm(nn.Module):
+        def __init__(self, dim, eps=1e-6):
+            super().__init__()
+            self.weight, self.eps = nn.Parameter(torch.ones(dim)), eps
+
+        def reset_parameters(self):
+            nn.init.ones_(self.weight)
+
+        def forward(self, x):
+            h = x.float()
+            return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()).to(x.dtype)
+
+    def apply_rotary_pos_emb(t, freqs, tensor_format="sbhd", fused=False, **_):
+        f = freqs.transpose(0, 1) if tensor_format == "bshd" else freqs
+        a, b = t[..., : t.shape[-1] // 2], t[..., t.shape[-1] // 2:]
+        return t * f.cos().to(t.dtype) + torch.cat([-b, a], -1) * f.sin().to(t.dtype)
+
+    te, tep, tea = (types.ModuleType(n) for n in ("transformer_engine", "transformer_engine.pytorch", "transformer_engine.pytorch.attention"))
+    te.__path__, tep.__path__ = [], []
+    tep.RMSNorm, tea.apply_rotary_pos_emb = RMSNorm, apply_rotary_pos_emb
+    te.pytorch, tep.attention = tep, tea
+    sys.modules.update({"transformer_engine": te, "transformer_engine.pytorch": tep, "transformer_engine.pytorch.attention": tea})
+
+
+def reference_network_modules():
+    """(lvg network module, attention module) of the reference, prepared for a CPU run in fp32: its attention dispatcher only
+    enables GPU back ends and casts to bf16, so here the math back end is added and the compute dtype is fp32. Nothing else of
+    the reference is touched."""
+    import torch
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    install_transformer_engine_standins()
+    lvg = import_reference("cosmos_predict2._src.predict2.networks.minimal_v1_lvg_dit")
+    att = import_reference("cosmos_predict2._src.predict2.networks.attention")
+    a2a = import_reference("cosmos_predict2._src.predict2.networks.a2a_cp")
+    att.sdpa_kernel = lambda backends, **kw: sdpa_kernel(list(backends) + [SDPBackend.MATH])
+    a2a.attention = lambda q, k, v, **kw: att.attention(q, k, v, **{**kw, "dtype": torch.float32})
+    return lvg, att
