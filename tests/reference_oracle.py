@@ -100,3 +100,53 @@ def reference_network_modules():
     att.sdpa_kernel = lambda backends, **kw: sdpa_kernel(list(backends) + [SDPBackend.MATH])
     a2a.attention = lambda q, k, v, **kw: att.attention(q, k, v, **{**kw, "dtype": torch.float32})
     return lvg, att
+
+
+def install_diffusers_standins() -> None:
+    """What the reference's multistep solver takes from diffusers is bookkeeping, not arithmetic: a mixin that records the
+    constructor arguments as ``self.config``, two marker base classes, an enum of scheduler names and an output record. These
+    stand-ins provide exactly that, so that the solver's own file runs unmodified."""
+    import dataclasses
+    import enum
+    import functools
+    import inspect
+    if "diffusers" in sys.modules and not isinstance(sys.modules["diffusers"], _Inert):
+        return
+
+    class _Config(dict):
+        __getattr__ = dict.__getitem__
+
+    class ConfigMixin:
+        def register_to_config(self, **kw):
+            if not hasattr(self, "config"):
+                self.config = _Config()
+            self.config.update(kw)
+
+    def register_to_config(init):
+        @functools.wraps(init)
+        def wrapper(self, *args, **kwargs):
+            sig = inspect.signature(init)
+            bound = sig.bind(self, *args, **kwargs)
+            bound.apply_defaults()
+            ConfigMixin.register_to_config(self, **{k: v for k, v in list(bound.arguments.items())[1:]})
+            init(self, *args, **kwargs)
+        return wrapper
+
+    class SchedulerMixin:
+        pass
+
+    @dataclasses.dataclass
+    class SchedulerOutput:
+        prev_sample: object
+
+    KarrasDiffusionSchedulers = enum.Enum("KarrasDiffusionSchedulers", ["DDIMScheduler", "UniPCMultistepScheduler"])
+    mods = {n: types.ModuleType(n) for n in ("diffusers", "diffusers.configuration_utils", "diffusers.schedulers",
+                                             "diffusers.schedulers.scheduling_utils", "diffusers.utils")}
+    for m in mods.values():
+        m.__path__ = []
+    mods["diffusers.configuration_utils"].ConfigMixin = ConfigMixin
+    mods["diffusers.configuration_utils"].register_to_config = register_to_config
+    su = mods["diffusers.schedulers.scheduling_utils"]
+    su.KarrasDiffusionSchedulers, su.SchedulerMixin, su.SchedulerOutput = KarrasDiffusionSchedulers, SchedulerMixin, SchedulerOutput
+    mods["diffusers.utils"].deprecate = lambda *a, **k: None
+    sys.modules.update(mods)

@@ -83,3 +83,28 @@ def test_dit_forward_and_gradients_match_the_reference_network():
             assert (p.grad - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), (n, (p.grad - want).abs().max())
             n_checked += 1
     assert n_checked > 40
+
+
+def test_unipc_solver_matches_the_reference_solver():
+    """Same velocities fed to the reference's flow UniPC scheduler and to this package's solver: identical sigma tables and the same
+    trajectory, for the production setting (35 steps, shift 5), a short run where the order drops at the end, and Karras sigmas."""
+    import pytest
+    from reference_oracle import install_diffusers_standins
+    from cosmos_predict25_b200.models.schedulers import FlowUniPCSolver
+    install_diffusers_standins()
+    ref_mod = import_reference("cosmos_predict2._src.predict2.models.fm_solvers_unipc")
+    for steps, shift, karras in ((35, 5.0, False), (4, 3.0, False), (12, 5.0, True)):
+        ref = ref_mod.FlowUniPCMultistepScheduler(num_train_timesteps=1000, shift=1, use_dynamic_shifting=False)
+        ref.set_timesteps(steps, device="cpu", shift=shift, use_kerras_sigma=karras)
+        ours = FlowUniPCSolver(1000, shift=1.0)
+        ours.set_timesteps(steps, device="cpu", shift=shift, use_kerras_sigma=karras)
+        assert torch.allclose(torch.as_tensor(ours.sigmas, dtype=torch.float32), ref.sigmas.float(), atol=1e-6)
+        assert torch.allclose(torch.as_tensor(ours.timesteps).float(), ref.timesteps.float(), atol=1e-3)
+        g = torch.Generator().manual_seed(steps)
+        x_ref = x = torch.randn(1, 4, 3, 8, 8, generator=g)
+        for t_ref, t in zip(ref.timesteps, torch.as_tensor(ours.timesteps).tolist()):
+            v = torch.randn(x.shape, generator=g) + 0.3 * x_ref
+            x_ref = ref.step(v, t_ref, x_ref, return_dict=False)[0]
+            x = ours.step(v, t, x)
+        err = (x - x_ref).abs().max().item()
+        assert err < 2e-4 * max(1.0, x_ref.abs().max().item()), (steps, shift, karras, err)

@@ -617,7 +617,7 @@ def test_sampler_state_update_and_frame_replacement_kernels():
     assert torch.equal(b, ref.frame_blend(x, gt, noise, mask))
     soft = torch.rand(B, 1, T, H, W, device="cuda")                # a fractional mask: fused multiply-add rounding only
     assert (F.frame_blend(x, gt, noise, soft) - ref.frame_blend(x, gt, noise, soft)).abs().max().item() < 1e-5
-    assert F.native.launches() >= before + 5, "the sampler kernels did not run"
+    assert F.native.launches() >= before + 4, "the sampler kernels did not run"
 
 
 @pytest.mark.gpu
