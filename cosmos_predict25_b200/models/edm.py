@@ -44,6 +44,13 @@ class RectifiedFlowScaling:
         assert abs(sigma_data - 1.0) < 1e-6, "sigma_data must be 1.0 for rectified-flow scaling"
         self.t_scaling_factor = t_scaling_factor
         self.loss_weight_uniform = loss_weight_uniform
+        if not loss_weight_uniform:
+            # a bell over t in [0, 1] centred on 0.5, shifted to zero at the ends and scaled to mean 1: the middle of the
+            # trajectory weighs most (denoiser_scaling.py:38-45 of the reference)
+            self.num_steps = 1000
+            bell = torch.exp(-2 * (torch.linspace(0, 1, self.num_steps) - 0.5) ** 2)
+            bell = bell - bell.min()
+            self.weights = bell * (self.num_steps / bell.sum())
 
     def __call__(self, sigma: torch.Tensor):
         t = sigma / (sigma + 1)
@@ -52,7 +59,8 @@ class RectifiedFlowScaling:
     def sigma_loss_weights(self, sigma: torch.Tensor) -> torch.Tensor:
         if self.loss_weight_uniform:
             return (1.0 + sigma) ** 2 / sigma ** 2
-        return ((1.0 + sigma) ** 2 / sigma ** 2) * (1 + sigma)  # emphasises low noise
+        index = (sigma / (sigma + 1) * self.num_steps).round().long().clamp_(0, self.num_steps - 1)
+        return self.weights.to(sigma.device)[index].type_as(sigma)
 
 
 class EDMSDE:

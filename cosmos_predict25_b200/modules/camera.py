@@ -191,7 +191,7 @@ class Quaternion:
     @staticmethod
     @supports_numpy(["R"])
     def from_rotation_matrix(R, eps: float = 1e-8):
-        """Numerically stable: pick, per matrix, the branch whose pivot (trace or largest diagonal entry) is largest."""
+        """Numerically stable: per matrix, the branch whose pivot is the trace (when positive) or the largest diagonal entry."""
         m = R.float()
         m00, m11, m22 = m[..., 0, 0], m[..., 1, 1], m[..., 2, 2]
         cand = torch.stack([
@@ -200,12 +200,11 @@ class Quaternion:
             torch.stack([m[..., 0, 1] + m[..., 1, 0], 1 - m00 + m11 - m22, m[..., 1, 2] + m[..., 2, 1], m[..., 0, 2] - m[..., 2, 0]], -1),
             torch.stack([m[..., 0, 2] + m[..., 2, 0], m[..., 1, 2] + m[..., 2, 1], 1 - m00 - m11 + m22, m[..., 1, 0] - m[..., 0, 1]], -1),
         ], -2)                                                     # [...,4 branches,4]; branch b has pivot cand[b, pivot_idx[b]]
-        pivots = torch.stack([cand[..., 0, 3], cand[..., 1, 0], cand[..., 2, 1], cand[..., 3, 2]], -1)
-        best = pivots.argmax(dim=-1)
+        # branch rule and sign of the reference (camera.py:556-617 there), so that serialised poses agree number by number: the
+        # trace branch when the trace is positive, else the branch of the largest diagonal entry; the pivot component is positive
+        best = torch.where(m00 + m11 + m22 > 0, 0, torch.where((m00 > m11) & (m00 > m22), 1, torch.where(m11 > m22, 2, 3)))
         q = torch.gather(cand, -2, best[..., None, None].expand(*best.shape, 1, 4))[..., 0, :]
-        q = Quaternion.normalize(q, eps)
-        q = torch.where(q[..., 3:] < 0, -q, q)                     # canonical sign: w >= 0
-        return q.to(R.dtype)
+        return Quaternion.normalize(q, eps).to(R.dtype)
 
     @staticmethod
     @supports_numpy(["q"])

@@ -108,3 +108,98 @@ def test_unipc_solver_matches_the_reference_solver():
             x = ours.step(v, t, x)
         err = (x - x_ref).abs().max().item()
         assert err < 2e-4 * max(1.0, x_ref.abs().max().item()), (steps, shift, karras, err)
+
+
+def test_edm_scaling_sde_and_samplers_match_the_reference():
+    """EDM-era pieces against the reference's files: preconditioning coefficients, noise marginal, the Karras grid, and whole
+    sampling trajectories of the multistep ("2ab") and Runge-Kutta ("1euler", "2mid") solvers on a closed-form denoiser."""
+    from cosmos_predict25_b200.models import edm
+    ref_scale = import_reference("cosmos_predict2._src.common.modules.denoiser_scaling")
+    ref_sde = import_reference("cosmos_predict2._src.common.modules.edm_sde")
+    ref_samp = import_reference("cosmos_predict2._src.common.modules.res_sampler")
+    sigma = torch.tensor([0.002, 0.3, 1.0, 7.5, 80.0])
+    for a, b in zip(edm.EDMScaling(0.5)(sigma), ref_scale.EDMScaling(0.5)(sigma)):
+        assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)
+    for kw in (dict(sigma_data=1.0, t_scaling_factor=1.0, loss_weight_uniform=True), dict(sigma_data=1.0, t_scaling_factor=1000.0,
+                                                                                        loss_weight_uniform=False)):
+        ours, ref = edm.RectifiedFlowScaling(**kw), ref_scale.RectifiedFlowScaling(**kw)
+        for a, b in zip(ours(sigma), ref(sigma)):
+            assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)
+        assert torch.allclose(ours.sigma_loss_weights(sigma), ref.sigma_loss_weights(sigma), rtol=1e-6)
+    x0 = torch.randn(5, 2, 3)
+    for a, b in zip(edm.EDMSDE(-1.2, 1.2, 80.0, 0.002).marginal_prob(x0, sigma), ref_sde.EDMSDE(-1.2, 1.2, 80.0, 0.002).marginal_prob(x0, sigma)):
+        assert torch.allclose(torch.as_tensor(a), torch.as_tensor(b))
+    assert torch.allclose(torch.as_tensor(edm.get_rev_ts(0.002, 80.0, 9, 7.0)), ref_samp.get_rev_ts(0.002, 80.0, 9, 7.0).double(), rtol=1e-6)
+
+    target = torch.randn(2, 4, 3, 3)
+
+    def x0_fn(x, s):                                      # the exact denoiser of a Gaussian around ``target`` with unit prior variance
+        w = 1.0 / (1.0 + s.view(-1, 1, 1, 1).to(x.dtype) ** 2)
+        return w * x + (1 - w) * target.to(x.dtype)
+    noise = torch.randn(2, 4, 3, 3) * 80.0
+    for solver, steps in (("2ab", 12), ("1euler", 9), ("2mid", 10)):
+        want = ref_samp.Sampler()(x0_fn, noise, num_steps=steps, sigma_max=80.0, sigma_min=0.002, solver_option=solver)
+        got = edm.RESSampler()(x0_fn, noise, num_steps=steps, sigma_max=80.0, sigma_min=0.002, solver_option=solver)
+        assert torch.allclose(got, want, atol=1e-5), (solver, (got - want).abs().max())
+
+
+def test_lr_schedules_guidance_and_camera_math_match_the_reference():
+    from cosmos_predict25_b200.models.multiview import MomentumBuffer, adaptive_projected_guidance
+    from cosmos_predict25_b200.modules import camera as cam
+    from cosmos_predict25_b200.modules import volume_render as vr
+    from cosmos_predict25_b200.trainer import optim
+    ref_lr = import_reference("cosmos_predict2._src.common.functional.lr_scheduler")
+    args = dict(warm_up_steps=[10, 5], f_min=[0.1, 0.2], f_max=[1.0, 0.8], f_start=[0.01, 0.3], cycle_lengths=[50, 40])
+    for name in ("LambdaLinearScheduler", "LambdaWarmUpCosineScheduler"):
+        ours, ref = getattr(optim, name)(**args), getattr(ref_lr, name)(**args)
+        for n in range(0, 90):
+            assert abs(ours(n) - ref(n)) < 1e-9, (name, n, ours(n), ref(n))
+
+    ref_cfg = import_reference("cosmos_predict2._src.predict2_multiview.models.cfg")
+    torch.manual_seed(0)
+    buf, ref_buf = MomentumBuffer(-0.5), ref_cfg.MomentumBuffer(-0.5)
+    for _ in range(3):
+        c, u = torch.randn(2, 4, 3, 5, 5), torch.randn(2, 4, 3, 5, 5)
+        got = adaptive_projected_guidance(c, u, 4.0, buf, eta=0.3, norm_threshold=2.5)
+        want = ref_cfg.adaptive_projected_guidance(c, u, 4.0, ref_buf, eta=0.3, norm_threshold=2.5)
+        assert torch.allclose(got, want, atol=1e-6)
+
+    ref_cam = import_reference("cosmos_predict2._src.imaginaire.modules.camera")
+    q = ref_cam.Quaternion.normalize(torch.randn(6, 4))
+    assert torch.allclose(cam.Quaternion.normalize(q * 3), q, atol=1e-6)
+    R = ref_cam.Quaternion.to_rotation_matrix(q)
+    assert torch.allclose(cam.Quaternion.to_rotation_matrix(q), R, atol=1e-6)
+    assert torch.allclose(cam.Quaternion.from_rotation_matrix(R), ref_cam.Quaternion.from_rotation_matrix(R), atol=1e-5)
+    assert torch.allclose(cam.Quaternion.multiply(q, q.flip(0)), ref_cam.Quaternion.multiply(q, q.flip(0)), atol=1e-6)
+    pose = torch.cat([R, torch.randn(6, 3, 1)], -1)
+    intr = torch.tensor([[[50.0, 0, 16], [0, 55.0, 12], [0, 0, 1]]]).repeat(6, 1, 1)
+    assert torch.allclose(cam.Camera.invert_pose(pose), ref_cam.Camera.invert_pose(pose), atol=1e-5)
+    assert torch.allclose(cam.Camera.compose_poses([pose, pose.flip(0)]), ref_cam.Camera.compose_poses([pose, pose.flip(0)]), atol=1e-5)
+    for a, b in zip(cam.Camera.get_camera_rays(pose, intr, (24, 32)), ref_cam.Camera.get_camera_rays(pose, intr, (24, 32))):
+        assert torch.allclose(a, b, atol=1e-5)
+    assert torch.allclose(cam.Camera.get_plucker_rays(pose, intr, (24, 32)), ref_cam.Camera.get_plucker_rays(pose, intr, (24, 32)), atol=1e-5)
+    assert torch.allclose(cam.Camera.get_relative_poses_wrt_frame0(pose), ref_cam.Camera.get_relative_poses_wrt_frame0(pose), atol=1e-5)
+    params = ref_cam.Camera.extrinsic_matrices_to_params(pose)
+    assert torch.allclose(cam.Camera.extrinsic_matrices_to_params(pose), params, atol=1e-5)
+    assert torch.allclose(cam.Camera.extrinsic_params_to_matrices(params), ref_cam.Camera.extrinsic_params_to_matrices(params), atol=1e-5)
+    assert torch.allclose(cam.Camera.intrinsic_matrices_to_params(intr), ref_cam.Camera.intrinsic_matrices_to_params(intr))
+
+    ref_vr = import_reference("cosmos_predict2._src.imaginaire.modules.volume_render")
+    near, far = torch.full((2, 7, 1), 0.5), torch.full((2, 7, 1), 4.0)
+    dists = ref_vr.sample_dists(near, far, 9)
+    assert torch.allclose(vr.sample_dists(near, far, 9), dists, atol=1e-6)
+    dens = torch.rand(2, 7, 9, 1) * 3
+    for dist_far in (None, torch.full((2, 7, 1, 1), 4.0)):
+        alphas = ref_vr.volume_rendering_alphas(dens, dists[..., None], dist_far)
+        assert torch.allclose(vr.volume_rendering_alphas(dens, dists[..., None], dist_far), alphas, atol=1e-6)
+    w = ref_vr.alpha_compositing_weights(alphas)
+    assert torch.allclose(vr.alpha_compositing_weights(alphas), w, atol=1e-6)
+    rgb = torch.rand(2, 7, 9, 3)
+    assert torch.allclose(vr.composite(rgb, w), ref_vr.composite(rgb, w), atol=1e-6)
+
+    class _Field(torch.nn.Module):                        # a radiance field in closed form
+        def forward(self, points, ray_unit):
+            return torch.sigmoid(points), points.norm(dim=-1, keepdim=True)
+    center, ray = torch.randn(2, 7, 3), torch.nn.functional.normalize(torch.randn(2, 7, 3), dim=-1)
+    for a, b in zip(vr.volume_render_rays(_Field(), center, ray, near, far, 9), ref_vr.volume_render_rays(_Field(), center, ray, near, far, 9)):
+        assert torch.allclose(a, b, atol=1e-5)
