@@ -78,6 +78,18 @@ class MultiViewDiT(CosmosDiT):
             self.x_embedder = PatchEmbed(cfg.patch_spatial, cfg.patch_temporal, in_ch, D)
             self.view_embeddings = nn.Embedding(cfg.n_cameras_emb, cfg.view_condition_dim)
         self.blocks = nn.ModuleList([MultiViewBlock(cfg) for _ in range(cfg.num_blocks)])
+        # the released multi-camera checkpoints hold one rotary-position module per camera count (``pos_embedder_options.
+        # n_cameras_K.*``, multiview_dit.py:397-403 of the reference); their tables are identical - a view's positions do not
+        # depend on the number of views - so the first one serves every count and the rest only keep the state dict's names
+        import copy
+        one = self._modules.pop("pos_embedder")
+        self.pos_embedder_options = nn.ModuleDict({f"n_cameras_{k}": (one if k == 1 else copy.deepcopy(one))
+                                                   for k in range(1, cfg.n_cameras_emb + 1)})
+
+    def __getattr__(self, name):
+        if name == "pos_embedder":
+            return self._modules["pos_embedder_options"]["n_cameras_1"]
+        return super().__getattr__(name)
 
     # ---- embedding ---------------------------------------------------------------------------------------------
     def n_views_of(self, local_T: int) -> int:

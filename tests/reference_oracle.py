@@ -55,12 +55,13 @@ def import_reference(module: str, max_stubs: int = 24):
 
 
 def install_transformer_engine_standins() -> None:
-    """The two TransformerEngine entry points that the reference network calls, restated in plain torch from their documented
+    """The three TransformerEngine entry points that the reference network calls, restated in plain torch from their documented
     semantics, so that the reference's network file imports and runs without the package: ``pytorch.RMSNorm`` (fp32 statistics,
-    learnable weight) and ``pytorch.attention.apply_rotary_pos_emb`` (non-interleaved rotation by the given angles)."""
+    learnable weight), ``pytorch.attention.apply_rotary_pos_emb`` (non-interleaved rotation by the given angles) and
+    ``pytorch.attention.DotProductAttention`` (plain softmax attention, used by the multi-camera cross-attention)."""
     import torch
     import torch.nn as nn
-    if "transformer_engine" in sys.modules:
+    if "transformer_engine" in sys.modules and not isinstance(sys.modules["transformer_engine"], _Inert):
         return
 
     class RMSNorm(nn.Module):
@@ -80,9 +81,23 @@ def install_transformer_engine_standins() -> None:
         a, b = t[..., : t.shape[-1] // 2], t[..., t.shape[-1] // 2:]
         return t * f.cos().to(t.dtype) + torch.cat([-b, a], -1) * f.sin().to(t.dtype)
 
+    class DotProductAttention(nn.Module):
+        """softmax(q k^T / sqrt(d)) v for [batch, sequence, heads, d] operands, heads folded into the last output dimension."""
+
+        def __init__(self, num_heads, head_dim, qkv_format="sbhd", **_):
+            super().__init__()
+            assert qkv_format == "bshd"
+
+        def forward(self, q, k, v, **_):
+            o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+            return o.transpose(1, 2).flatten(2)
+
+        def set_context_parallel_group(self, *a, **k):
+            pass
+
     te, tep, tea = (types.ModuleType(n) for n in ("transformer_engine", "transformer_engine.pytorch", "transformer_engine.pytorch.attention"))
     te.__path__, tep.__path__ = [], []
-    tep.RMSNorm, tea.apply_rotary_pos_emb = RMSNorm, apply_rotary_pos_emb
+    tep.RMSNorm, tea.apply_rotary_pos_emb, tea.DotProductAttention = RMSNorm, apply_rotary_pos_emb, DotProductAttention
     te.pytorch, tep.attention = tep, tea
     sys.modules.update({"transformer_engine": te, "transformer_engine.pytorch": tep, "transformer_engine.pytorch.attention": tea})
 

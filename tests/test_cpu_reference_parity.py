@@ -203,3 +203,71 @@ def test_lr_schedules_guidance_and_camera_math_match_the_reference():
     center, ray = torch.randn(2, 7, 3), torch.nn.functional.normalize(torch.randn(2, 7, 3), dim=-1)
     for a, b in zip(vr.volume_render_rays(_Field(), center, ray, near, far, 9), ref_vr.volume_render_rays(_Field(), center, ray, near, far, 9)):
         assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_wan22_vae_matches_the_reference():
+    ref_mod = import_reference("cosmos_predict2._src.predict2.tokenizers.wan2pt2")
+    from cosmos_predict25_b200.models.vae_wan22 import Wan22VAE_
+    torch.manual_seed(0)
+    kw = dict(dim=16, dec_dim=16, z_dim=8, dim_mult=[1, 2, 4, 4], num_res_blocks=1, attn_scales=[], temperal_downsample=[False, True, True])
+    ref = ref_mod.WanVAE_(**kw).eval()
+    ours = Wan22VAE_(**kw).eval()
+    res = ours.load_state_dict(ref.state_dict(), strict=True)
+    assert not res.missing_keys and not res.unexpected_keys
+    scale = [torch.linspace(-0.3, 0.3, 8), 1.0 / torch.linspace(0.5, 2.0, 8)]
+    with torch.no_grad():
+        for T in (5, 1):
+            x = torch.randn(1, 3, T, 32, 32)
+            mu_ref = ref.encode(x, scale)
+            mu = ours.encode(x, scale)
+            assert mu.shape == mu_ref.shape and torch.allclose(mu, mu_ref, atol=1e-4), (mu - mu_ref).abs().max()
+            rec_ref = ref.decode(mu_ref, scale)
+            rec = ours.decode(mu_ref, scale)
+            assert rec.shape == rec_ref.shape == x.shape and torch.allclose(rec, rec_ref, atol=1e-4), (rec - rec_ref).abs().max()
+
+
+def test_multiview_dit_matches_the_reference_network():
+    """The multi-camera network: views stacked along time, per-view cross-attention over each view's own caption, camera embedding
+    channels, per-camera rotary positions. Same state dict, same output and gradients as the reference's file."""
+    from reference_oracle import install_transformer_engine_standins, reference_network_modules
+    from cosmos_predict25_b200.models.multiview_dit import MultiViewDiT, MultiViewDiTConfig
+    install_transformer_engine_standins()
+    mv = import_reference("cosmos_predict2._src.predict2_multiview.networks.multiview_dit")
+    reference_network_modules()                               # after the import above: stand-ins installed on the way reload modules
+    mv.parallel_state.is_initialized = lambda: False          # the absent process-group registry: no model parallelism here
+    torch.manual_seed(0)
+    V, state_t = 3, 2
+    ref = mv.MultiViewDiT(max_img_h=32, max_img_w=32, max_frames=16, in_channels=16, out_channels=16, patch_spatial=2, patch_temporal=1,
+                          concat_padding_mask=True, model_channels=128, num_blocks=2, num_heads=2, atten_backend="minimal_a2a",
+                          crossattn_emb_channels=64, use_crossattn_projection=False, pos_emb_cls="rope3d", use_adaln_lora=True,
+                          adaln_lora_dim=32, rope_h_extrapolation_ratio=3.0, rope_w_extrapolation_ratio=3.0, rope_t_extrapolation_ratio=1.0,
+                          rope_enable_fps_modulation=False, use_wan_fp32_strategy=True, timestep_scale=0.001, state_t=state_t,
+                          n_cameras_emb=4, view_condition_dim=4, concat_view_embedding=True)
+    ours = MultiViewDiT(MultiViewDiTConfig(max_img_h=32, max_img_w=32, max_frames=16, model_channels=128, num_blocks=2, num_heads=2,
+                                           crossattn_emb_channels=64, use_crossattn_projection=False, adaln_lora_dim=32, state_t=state_t,
+                                           n_cameras_emb=4, view_condition_dim=4, concat_view_embedding=True))
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.abs().max() == 0:
+                p.normal_(0, 0.02)
+    res = ours.load_state_dict(ref.state_dict(), strict=True)
+    assert not res.missing_keys and not res.unexpected_keys
+    x = torch.randn(1, 16, V * state_t, 16, 12)
+    t = torch.full((1, 1), 420.0)
+    ctx = torch.randn(1, V * 512, 64)                                      # 512 caption tokens per view
+    mask = torch.zeros(1, 1, V * state_t, 16, 12)
+    mask[:, :, ::state_t] = 1                                              # first frame of every view is given
+    views = torch.tensor([[0, 0, 2, 2, 1, 1]])
+    pad = torch.zeros(1, 1, 16, 12)
+    y = ref(x, t, ctx, condition_video_input_mask_B_C_T_H_W=mask, fps=None, padding_mask=pad, view_indices_B_T=views)
+    z = ours(x, t, crossattn_emb=ctx, condition_video_input_mask_B_C_T_H_W=mask, padding_mask=pad, view_indices_B_T=views)
+    assert (y - z).abs().max().item() < 2e-5 * max(1.0, y.abs().max().item()), (y - z).abs().max()
+    g = torch.randn_like(y)
+    (y * g).sum().backward()
+    (z * g).sum().backward()
+    ref_grads = {n.replace("_checkpoint_wrapped_module.", ""): p.grad for n, p in ref.named_parameters()}
+    for n, p in ours.named_parameters():
+        want = ref_grads[n]
+        assert (p.grad is None) == (want is None), n
+        if want is not None:
+            assert (p.grad - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), n
