@@ -369,6 +369,36 @@ class Attention(nn.Module):
         return o if return_pre_proj else self.output_proj(o)
 
 
+class I2VCrossAttention(Attention):
+    """Cross-attention over a text context AND an image context: ``context = (text, image)``; the two attention results are added
+    before the output projection; the image keys have their own projection and per-head norm (minimal_v4_dit.py:451-492)."""
+
+    def __init__(self, query_dim: int, context_dim: int, n_heads: int, head_dim: int, img_latent_dim: int):
+        super().__init__(query_dim, context_dim, n_heads, head_dim)
+        inner = n_heads * head_dim
+        self.k_img = FusedLinear(img_latent_dim, inner)
+        self.v_img = FusedLinear(img_latent_dim, inner)
+        self.k_img_norm = RMSNorm(head_dim)
+
+    def init_weights(self):
+        super().init_weights()
+        inner = self.n_heads * self.head_dim
+        nn.init.trunc_normal_(self.k_img.weight, std=1.0 / math.sqrt(inner))
+        nn.init.trunc_normal_(self.v_img.weight, std=1.0 / math.sqrt(inner))
+        self.k_img_norm.reset_parameters()
+
+    def forward(self, x, context=None, rope=None, kv=None, return_pre_proj: bool = False):
+        text, img = context
+        B, S, _ = x.shape
+        Si = img.shape[1]
+        q = ops.rmsnorm_rope(self.q_proj(x).view(B, S, self.n_heads, self.head_dim), self.q_norm.weight, None, self.q_norm.eps)
+        k, v = kv if kv is not None else self.project_kv(text)
+        k_img = ops.rmsnorm_rope(self.k_img(img).view(B, Si, self.n_heads, self.head_dim), self.k_img_norm.weight, None, self.k_img_norm.eps)
+        v_img = self.v_img(img).view(B, Si, self.n_heads, self.head_dim)
+        o = (ops.attention(q, k, v) + ops.attention(q, k_img, v_img)).reshape(B, S, self.n_heads * self.head_dim)
+        return o if return_pre_proj else self.output_proj(o)
+
+
 class GPT2FeedForward(nn.Module):
     def __init__(self, d_model: int, d_ff: int):
         super().__init__()
@@ -432,7 +462,10 @@ class Block(nn.Module):
         D = cfg.model_channels
         self.cfg = cfg
         self.self_attn = Attention(D, None, cfg.num_heads, cfg.head_dim)
-        self.cross_attn = Attention(D, cfg.crossattn_emb_channels, cfg.num_heads, cfg.head_dim)
+        if cfg.extra_image_context_dim is None:
+            self.cross_attn = Attention(D, cfg.crossattn_emb_channels, cfg.num_heads, cfg.head_dim)
+        else:       # the image context arrives already projected to the model width
+            self.cross_attn = I2VCrossAttention(D, cfg.crossattn_emb_channels, cfg.num_heads, cfg.head_dim, img_latent_dim=D)
         self.mlp = GPT2FeedForward(D, int(D * cfg.mlp_ratio))
         self.adaln_modulation_self_attn = _adaln_mlp(D, cfg.adaln_lora_dim, 3, cfg.use_adaln_lora)
         self.adaln_modulation_cross_attn = _adaln_mlp(D, cfg.adaln_lora_dim, 3, cfg.use_adaln_lora)
@@ -633,8 +666,10 @@ class CosmosDiT(nn.Module):
     def forward(self, x_B_C_T_H_W: torch.Tensor, timesteps_B_T: torch.Tensor, crossattn_emb: Optional[torch.Tensor],
                 condition_video_input_mask_B_C_T_H_W: Optional[torch.Tensor] = None,
                 fps: Optional[torch.Tensor] = None, padding_mask: Optional[torch.Tensor] = None,
-                context_cache: Optional[ContextCache] = None, **_unused) -> torch.Tensor:
-        """Velocity prediction. Under context parallelism every input is the local T-slice."""
+                context_cache: Optional[ContextCache] = None, img_context_emb: Optional[torch.Tensor] = None,
+                **_unused) -> torch.Tensor:
+        """Velocity prediction. Under context parallelism every input is the local T-slice. ``img_context_emb`` [B, N, extra_image_
+        context_dim]: tokens of a reference image for networks built with ``extra_image_context_dim``."""
         cfg = self.cfg
         x = self._embed(x_B_C_T_H_W, condition_video_input_mask_B_C_T_H_W, padding_mask)  # [B,T,H,W,D]
         B, T, H, W, D = x.shape
@@ -649,6 +684,10 @@ class CosmosDiT(nn.Module):
             context, cross_kv = context_cache.context, context_cache.cross_kv
         else:
             context, cross_kv = self.project_context(crossattn_emb), None
+        if cfg.extra_image_context_dim is not None:
+            assert img_context_emb is not None, "this network was built with extra_image_context_dim: pass img_context_emb"
+            lin = self.img_context_proj[0]
+            context = (context, ops.linear(img_context_emb.to(lin.weight.dtype), lin.weight, lin.bias, "gelu"))
 
         if timesteps_B_T.ndim == 1:
             timesteps_B_T = timesteps_B_T.unsqueeze(1)

@@ -36,14 +36,14 @@ def _net_pair(**extra):
     from cosmos_predict25_b200.models.dit import CosmosDiT, DiTConfig
     lvg, _ = reference_network_modules()
     torch.manual_seed(0)
-    ref = lvg.MinimalV1LVGDiT(max_img_h=32, max_img_w=32, max_frames=16, in_channels=16, out_channels=16, patch_spatial=2, patch_temporal=1,
-                              concat_padding_mask=True, model_channels=128, num_blocks=2, num_heads=2, atten_backend="minimal_a2a",
-                              crossattn_emb_channels=64, use_crossattn_projection=True, crossattn_proj_in_channels=96, pos_emb_cls="rope3d",
-                              use_adaln_lora=True, adaln_lora_dim=32, rope_h_extrapolation_ratio=3.0, rope_w_extrapolation_ratio=3.0,
-                              rope_t_extrapolation_ratio=1.0, rope_enable_fps_modulation=False, use_wan_fp32_strategy=True,
-                              timestep_scale=0.001, **extra)
-    ours = CosmosDiT(DiTConfig(max_img_h=32, max_img_w=32, max_frames=16, model_channels=128, num_blocks=2, num_heads=2,
-                               crossattn_emb_channels=64, crossattn_proj_in_channels=96, adaln_lora_dim=32, **extra))
+    kw = dict(max_img_h=32, max_img_w=32, max_frames=16, in_channels=16, out_channels=16, patch_spatial=2, patch_temporal=1,
+              concat_padding_mask=True, model_channels=128, num_blocks=2, num_heads=2, crossattn_emb_channels=64,
+              use_crossattn_projection=True, crossattn_proj_in_channels=96, pos_emb_cls="rope3d", use_adaln_lora=True, adaln_lora_dim=32,
+              rope_h_extrapolation_ratio=3.0, rope_w_extrapolation_ratio=3.0, rope_t_extrapolation_ratio=1.0,
+              rope_enable_fps_modulation=False, use_wan_fp32_strategy=True, timestep_scale=0.001)
+    kw.update(extra)
+    ref = lvg.MinimalV1LVGDiT(atten_backend="minimal_a2a", **kw)
+    ours = CosmosDiT(DiTConfig(**kw))
     with torch.no_grad():
         for p in ref.parameters():                       # the reference zero-initialises its output layers: make every weight count
             if p.abs().max() == 0:
@@ -271,3 +271,39 @@ def test_multiview_dit_matches_the_reference_network():
         assert (p.grad is None) == (want is None), n
         if want is not None:
             assert (p.grad - want).abs().max().item() < 1e-4 * max(1.0, want.abs().max().item()), n
+
+
+def test_dit_variants_match_the_reference_network():
+    """Options of the network beyond the released 2B / 14B setting: learnable per-block position embedding, frame-rate modulated
+    rotary positions, an extra image context for the cross-attention, plain AdaLN without the low-rank branch, no text projection,
+    temporal patches of 2."""
+    import pytest
+    cases = [
+        dict(extra_per_block_abs_pos_emb=True),
+        dict(rope_enable_fps_modulation=True),
+        dict(extra_image_context_dim=48),
+        dict(use_adaln_lora=False),
+        dict(use_crossattn_projection=False, crossattn_emb_channels=96),
+        dict(patch_temporal=2, rope_t_extrapolation_ratio=2.0),
+        dict(use_wan_fp32_strategy=False),
+    ]
+    for extra in cases:
+        try:
+            ref, ours = _net_pair(**extra)
+        except TypeError as e:                      # an option this package does not have would show up here, not pass silently
+            pytest.fail(f"{extra}: {e}")
+        torch.manual_seed(2)
+        x = torch.randn(1, 16, 4, 16, 12)
+        t = torch.tensor([[250.0]])
+        ctx = torch.randn(1, 8, 96)
+        mask = torch.zeros(1, 1, 4, 16, 12)
+        mask[:, :, :1] = 1
+        kw = dict(condition_video_input_mask_B_C_T_H_W=mask, padding_mask=torch.zeros(1, 1, 16, 12))
+        if extra.get("rope_enable_fps_modulation"):
+            kw["fps"] = torch.tensor([24.0])
+        if "extra_image_context_dim" in extra:
+            kw["img_context_emb"] = torch.randn(1, 6, 48)
+        with torch.no_grad():
+            y = ref(x, t, ctx, **kw)
+            z = ours(x, t, crossattn_emb=ctx, **kw)
+        assert (y - z).abs().max().item() < 2e-5 * max(1.0, y.abs().max().item()), (extra, (y - z).abs().max())
