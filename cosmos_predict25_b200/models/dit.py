@@ -552,6 +552,14 @@ class ContextCache:
     cross_kv: List[Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=list)
 
 
+def register_training_stats(module: nn.Module) -> None:
+    """Scalar buffers that travel with the weights of every released network: samples seen, iterations, training hours
+    (model_weights_stats.py:41-51 of the reference)."""
+    for name in ("accum_video_sample_counter", "accum_image_sample_counter", "accum_iteration"):
+        module.register_buffer(name, torch.tensor(0, dtype=torch.int64), persistent=True)
+    module.register_buffer("accum_train_in_hours", torch.tensor(0.0, dtype=torch.float32), persistent=True)
+
+
 class CosmosDiT(nn.Module):
     """The Predict2.5 network: text2world / image2world / video2world share it; the conditioning
     mask enters as an extra input channel and timesteps arrive in scheduler units (0..1000)."""
@@ -581,9 +589,7 @@ class CosmosDiT(nn.Module):
         self.blocks = nn.ModuleList([Block(cfg) for _ in range(cfg.num_blocks)])
         self.final_layer = FinalLayer(cfg)
         # training statistics buffers kept for checkpoint parity (model_weights_stats.py:41-51)
-        for name in ("accum_video_sample_counter", "accum_image_sample_counter", "accum_iteration"):
-            self.register_buffer(name, torch.tensor(0, dtype=torch.int64), persistent=True)
-        self.register_buffer("accum_train_in_hours", torch.tensor(0.0, dtype=torch.float32), persistent=True)
+        register_training_stats(self)
         self.cp_group = None
         self._fsdp = None
         if cfg.n_dense_blocks != -1:

@@ -23,6 +23,7 @@ import torch.nn.functional as F
 from ..ops import functional as ops
 from ..parallel import ulysses
 from .conditioner import DataType
+from .dit import register_training_stats
 from .rectified_flow import Text2WorldModelRectifiedFlow, Text2WorldRFConfig
 
 T5_CONTEXT_TOKEN_NUMBER = 512
@@ -281,6 +282,7 @@ class WanModel(nn.Module):
         self.time_projection = nn.Sequential(nn.SiLU(), nn.Linear(cfg.dim, cfg.dim * 6))
         self.blocks = nn.ModuleList([WanAttentionBlock(cfg) for _ in range(cfg.num_layers)])
         self.head = WanHead(cfg.dim, cfg.out_dim, cfg.patch_size, cfg.eps)
+        register_training_stats(self)
         self.rope_position_embedding = WanRope3D(cfg.head_dim)
         if cfg.model_type in ("i2v", "flf2v"):
             self.img_emb = MLPProj(1280, cfg.dim, flf_pos_emb=cfg.model_type == "flf2v")

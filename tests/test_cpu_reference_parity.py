@@ -233,7 +233,7 @@ def test_multiview_dit_matches_the_reference_network():
     from cosmos_predict25_b200.models.multiview_dit import MultiViewDiT, MultiViewDiTConfig
     install_transformer_engine_standins()
     mv = import_reference("cosmos_predict2._src.predict2_multiview.networks.multiview_dit")
-    reference_network_modules()                               # after the import above: stand-ins installed on the way reload modules
+    reference_network_modules()
     mv.parallel_state.is_initialized = lambda: False          # the absent process-group registry: no model parallelism here
     torch.manual_seed(0)
     V, state_t = 3, 2
@@ -307,3 +307,46 @@ def test_dit_variants_match_the_reference_network():
             y = ref(x, t, ctx, **kw)
             z = ours(x, t, crossattn_emb=ctx, **kw)
         assert (y - z).abs().max().item() < 2e-5 * max(1.0, y.abs().max().item()), (extra, (y - z).abs().max())
+
+
+def test_wan21_network_matches_the_reference(monkeypatch):
+    """Wan2.1 text-to-video and image-to-video networks against the reference's file (same state dict): interleaved rotary
+    positions, cross-attention over text (+ CLIP image tokens), 6-way modulation."""
+    from reference_oracle import install_transformer_engine_standins, reference_network_modules
+    from cosmos_predict25_b200.models.wan2pt1 import WanConfig, WanModel
+    install_transformer_engine_standins()
+    wan = import_reference("cosmos_predict2._src.predict2.networks.wan2pt1")
+    reference_network_modules()
+
+    def rotary_interleaved(x, cos, sin, interleaved=True, inplace=False):
+        # documented semantics of the fused rotary kernel the reference calls: pairs (x[2i], x[2i+1]) turn by angle i
+        a, b = x[..., 0::2], x[..., 1::2]
+        c, s = cos[None, :, None, :], sin[None, :, None, :]
+        return torch.stack([a * c - b * s, a * s + b * c], -1).flatten(-2)
+    wan.flash_apply_rotary_emb = rotary_interleaved
+    a2a = import_reference("cosmos_predict2._src.predict2.networks.a2a_cp")
+    wan.attention = a2a.attention                           # the fp32 / math-back-end form prepared by reference_network_modules
+    monkeypatch.setattr(torch.Tensor, "cuda", lambda self, *a, **k: self)       # its position tables are placed with .cuda()
+    for model_type in ("t2v", "i2v"):
+        torch.manual_seed(0)
+        kw = dict(model_type=model_type, patch_size=(1, 2, 2), text_len=512, in_dim=16 if model_type == "t2v" else 36, dim=128, ffn_dim=256,
+                  freq_dim=64, text_dim=96, out_dim=16, num_heads=2, num_layers=2, qk_norm=True, cross_attn_norm=True, eps=1e-6)
+        ref = wan.WanModel(**kw, attention_backend="minimal_a2a", cp_comm_type="a2a")
+        ours = WanModel(WanConfig(**kw))
+        with torch.no_grad():
+            for p in ref.parameters():
+                if p.abs().max() == 0:
+                    p.normal_(0, 0.02)
+        res = ours.load_state_dict(ref.state_dict(), strict=True)
+        assert not res.missing_keys and not res.unexpected_keys
+        x = torch.randn(2, 16, 3, 16, 12)
+        t = torch.tensor([[700.0], [20.0]])
+        ctx = torch.randn(2, 512, 96)
+        extra = {}
+        if model_type == "i2v":
+            extra = dict(frame_cond_crossattn_emb_B_L_D=torch.randn(2, 257, 1280), y_B_C_T_H_W=torch.randn(2, 20, 3, 16, 12))
+        with torch.no_grad():
+            y = ref(x, t, ctx, **extra)
+            z = ours(x, t, ctx, **extra)
+        assert y.shape == z.shape == x.shape
+        assert (y - z).abs().max().item() < 3e-5 * max(1.0, y.abs().max().item()), (model_type, (y - z).abs().max())
