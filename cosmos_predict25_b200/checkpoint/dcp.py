@@ -120,27 +120,43 @@ class ModelWrapper:
 
 
 class OptimizerWrapper:
-    """Flattened optimizer state of the local shards (``state.<param>.<exp_avg|exp_avg_sq|master>``)."""
+    """Flattened optimizer state of the local shards under the names torch's flattened optimizer state dict gives them when the
+    optimizer is looked at from the model object (``state.net.<param>.<exp_avg|exp_avg_sq>``: what the reference writes,
+    checkpointer/dcp.py:283-307 there), plus this engine's fp32 masters (``state.net.<param>.master``) and its single step count.
+    ``prefix=""`` reads checkpoints of this package written before the names carried the ``net.`` part."""
 
-    def __init__(self, model, optimizer):
-        self.model, self.optimizer = model, optimizer
+    def __init__(self, model, optimizer, prefix: str = "net."):
+        self.model, self.optimizer, self.prefix = model, optimizer, prefix
 
-    def state_dict(self) -> Dict[str, Any]:
+    def _ckpt_key(self, k: str) -> str:
+        return "state." + self.prefix + k[len("state."):] if k.startswith("state.") and k != "state.step" else k
+
+    def state_dict(self, for_load: bool = False) -> Dict[str, Any]:
         sd = {}
         sharded = _dist_on() and self.model.engine.P > 1
         mesh = _Mesh.get(self.model.device_.type, self.model.engine.P) if sharded else None
         shapes = {n: shp for n, (_, shp, _) in self.model.engine.sharded_state("master").items()}
+        if for_load and shapes:
+            # torch's flattened optimizer state (what the reference writes) keeps the step count per parameter; this engine has
+            # one count, stored as ``state.step``. When reading, ask for one parameter's count too, so either layout resumes.
+            sd[f"state.{self.prefix}{next(iter(shapes))}.step"] = torch.tensor(-1.0)
         for k, v in self.optimizer.state_dict().items():
             if isinstance(v, torch.Tensor) and k.startswith("state.") and k != "state.step":
                 name = k[len("state."):].rsplit(".", 1)[0]
                 t = v.detach().clone()
-                sd[k] = _as_dtensor(t, shapes[name], mesh) if sharded and len(shapes[name]) > 0 else t
+                sd[self._ckpt_key(k)] = _as_dtensor(t, shapes[name], mesh) if sharded and len(shapes[name]) > 0 else t
             else:
                 sd[k] = v
         return sd
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
         flat = {k: (v.to_local() if hasattr(v, "to_local") else v) for k, v in sd.items()}
+        per_param = [k for k in flat if k.startswith("state.") and k.endswith(".step") and k != "state.step"]
+        steps = [float(flat.pop(k)) for k in per_param]
+        if steps and max(steps) > float(flat.get("state.step", 0)):
+            flat["state.step"] = torch.tensor(int(max(steps)), dtype=torch.int64)
+        strip = len("state." + self.prefix)
+        flat = {("state." + k[strip:] if k.startswith("state." + self.prefix) else k): v for k, v in flat.items()}
         self.optimizer.load_state_dict(flat)
 
 
@@ -278,8 +294,10 @@ class DistributedCheckpointer:
                 dcp.load(sd, storage_reader=reader, planner=_TolerantLoadPlanner(self.allow_mismatched or not self.strict_resume))
                 w.load_state_dict(sd)
             elif key == "optim" and optimizer is not None:
-                w = OptimizerWrapper(model, optimizer)
-                sd = w.state_dict()
+                stored = reader.read_metadata().state_dict_metadata
+                legacy = not any(k.startswith("state.net.") for k in stored)
+                w = OptimizerWrapper(model, optimizer, prefix="" if legacy else "net.")
+                sd = w.state_dict(for_load=True)
                 dcp.load(sd, storage_reader=reader, planner=_TolerantLoadPlanner(self.allow_mismatched))
                 w.load_state_dict(sd)
             elif key == "scheduler" and scheduler is not None:

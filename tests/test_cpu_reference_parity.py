@@ -350,3 +350,60 @@ def test_wan21_network_matches_the_reference(monkeypatch):
             z = ours(x, t, ctx, **extra)
         assert y.shape == z.shape == x.shape
         assert (y - z).abs().max().item() < 3e-5 * max(1.0, y.abs().max().item()), (model_type, (y - z).abs().max())
+
+
+def test_checkpoint_written_in_the_reference_layout_resumes_here(tmp_path):
+    """A checkpoint written with the reference's own state-dict wrappers (torch's flattened optimizer state, its scheduler and
+    trainer records, ``iter_%09d/{model,optim,scheduler,trainer}``) is read by this package's checkpointer: weights, EMA, Adam
+    moments, step count, schedule position and iteration all arrive."""
+    import copy
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint import FileSystemWriter
+    ref_ck = import_reference("cosmos_predict2._src.predict2.checkpointer.dcp")
+    from cosmos_predict25_b200.checkpoint.dcp import DistributedCheckpointer
+    from cosmos_predict25_b200.models.dit import CosmosDiT, dit_tiny
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.trainer.optim import OptimizerConfig, SchedulerConfig
+    torch.manual_seed(0)
+
+    class RefStyleModel(torch.nn.Module):                       # what the reference's model object looks like to its checkpointer
+        def __init__(self):
+            super().__init__()
+            self.net = CosmosDiT(dit_tiny())
+            self.net_ema = copy.deepcopy(self.net).requires_grad_(False)
+            self.config = type("C", (), {"use_lora": False})()
+    src = RefStyleModel()
+    with torch.no_grad():
+        for p in src.net_ema.parameters():
+            p.add_(0.01 * torch.randn_like(p))
+    opt = torch.optim.AdamW([p for p in src.net.parameters()], lr=1e-3, betas=(0.9, 0.999), weight_decay=0.01)
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda n: 1.0)
+    x = torch.randn(1, 16, 4, 16, 16)
+    for _ in range(3):
+        src.net(x, torch.full((1, 1), 500.0), crossattn_emb=torch.randn(1, 32, 256)).pow(2).mean().backward()
+        opt.step()
+        sched.step()
+        opt.zero_grad()
+    parts = {"model": ref_ck.ModelWrapper(src).state_dict(), "optim": ref_ck.OptimizerWrapper(src, opt).state_dict(),
+             "scheduler": sched.state_dict(), "trainer": {"grad_scaler": torch.amp.GradScaler("cpu", enabled=False).state_dict(), "iteration": 3}}
+    root = tmp_path / "checkpoints" / "iter_000000003"
+    for k, sd in parts.items():
+        dcp.save(sd, storage_writer=FileSystemWriter(str(root / k)))
+    (tmp_path / "checkpoints" / "latest_checkpoint.txt").write_text("iter_000000003\n")
+
+    m = Video2WorldModelRectifiedFlow(Video2WorldRFConfig(net=dit_tiny(), precision="float32", state_t=4), device=torch.device("cpu"))
+    o, s = m.init_optimizer_scheduler(OptimizerConfig(lr=1e-3), SchedulerConfig(kind="constant"))
+    it = DistributedCheckpointer({}, str(tmp_path)).load(m, o, s)
+    assert it == 3 and s.last_epoch == 3 and o.engine.step_count == 3
+    for (n, a), (_, b) in zip(src.net.named_parameters(), m.net.named_parameters()):
+        assert torch.equal(a, b), n
+    names = [n for n, _ in src.net.named_parameters()]
+    ema = {n: t for n, (t, _, _) in m.engine.sharded_state("ema").items()}
+    exp_avg = {n: t for n, (t, _, _) in m.engine.sharded_state("exp_avg").items()}
+    exp_avg_sq = {n: t for n, (t, _, _) in m.engine.sharded_state("exp_avg_sq").items()}
+    ref_state = opt.state_dict()["state"]
+    for i, (n, p) in enumerate(src.net.named_parameters()):
+        assert torch.equal(ema[n].view(-1), dict(src.net_ema.named_parameters())[n].view(-1)), n
+        assert torch.equal(exp_avg[n].view(-1), ref_state[i]["exp_avg"].view(-1)), n
+        assert torch.equal(exp_avg_sq[n].view(-1), ref_state[i]["exp_avg_sq"].view(-1)), n
+    assert len(names) == len(exp_avg)
