@@ -160,10 +160,12 @@ class AbstractEmbModel(nn.Module):
         if x is None:
             return None
         rate = self.dropout_rate if dropout_rate is None else dropout_rate
+        # one host-side draw per sample for EVERY embedder, also at rate 0: the same seed then drops the same samples as in the
+        # reference (conditioner.py:215-223 there), whose generator advances the same way
+        keep = torch.bernoulli((1.0 - rate) * torch.ones(x.shape[0]))
         if rate <= 0.0:
             return x
-        keep = torch.bernoulli((1.0 - rate) * torch.ones(x.shape[0], device=x.device)).type_as(x)
-        return x * keep.view(-1, *([1] * (x.ndim - 1)))
+        return x * keep.to(x.device).type_as(x).view(-1, *([1] * (x.ndim - 1)))
 
     def details(self) -> str:
         return f"{type(self).__name__}(in={self.input_key}, out={self.output_key}, dropout={self.dropout_rate})"
@@ -202,7 +204,7 @@ class BooleanFlag(AbstractEmbModel):
 
     def random_dropout_input(self, x, dropout_rate=None, key=None):
         rate = self.dropout_rate if dropout_rate is None else dropout_rate
-        return torch.rand(1).item() >= rate if rate > 0 else True
+        return bool(torch.bernoulli((1.0 - rate) * torch.ones(1)).item())
 
     def forward(self, flag):
         return {self.output_key: torch.tensor(bool(flag))}

@@ -163,3 +163,28 @@ def install_diffusers_standins() -> None:
     su.KarrasDiffusionSchedulers, su.SchedulerMixin, su.SchedulerOutput = KarrasDiffusionSchedulers, SchedulerMixin, SchedulerOutput
     mods["diffusers.utils"].deprecate = lambda *a, **k: None
     sys.modules.update(mods)
+
+
+def install_omegaconf_standins() -> None:
+    """``omegaconf`` as two empty container classes: the compared code only asks ``isinstance(x, DictConfig / ListConfig)`` of
+    objects that are neither."""
+    if "omegaconf" in sys.modules and not isinstance(sys.modules["omegaconf"], _Inert):
+        return
+
+    class DictConfig(dict):
+        pass
+
+    class ListConfig(list):
+        pass
+
+    class _OmegaConf(_Inert):
+        pass
+    om = _OmegaConf("omegaconf")
+    om.DictConfig, om.ListConfig = DictConfig, ListConfig
+    for sub, cls in (("dictconfig", DictConfig), ("listconfig", ListConfig), ("base", None)):
+        m = _OmegaConf(f"omegaconf.{sub}")
+        if cls is not None:
+            setattr(m, cls.__name__, cls)
+        setattr(om, sub, m)
+        sys.modules[f"omegaconf.{sub}"] = m
+    sys.modules["omegaconf"] = om

@@ -407,3 +407,35 @@ def test_checkpoint_written_in_the_reference_layout_resumes_here(tmp_path):
         assert torch.equal(exp_avg[n].view(-1), ref_state[i]["exp_avg"].view(-1)), n
         assert torch.equal(exp_avg_sq[n].view(-1), ref_state[i]["exp_avg_sq"].view(-1)), n
     assert len(names) == len(exp_avg)
+
+
+def test_conditioner_matches_the_reference():
+    """Embedder registry of the reference's conditioner against this package's: conditioned / unconditioned pair, the
+    negative-prompt pair, and random dropout drawn from the same generator state."""
+    from reference_oracle import install_omegaconf_standins
+    install_omegaconf_standins()
+    rc = import_reference("cosmos_predict2._src.predict2.conditioner")
+    from cosmos_predict25_b200.models import conditioner as oc
+    ref = rc.VideoConditioner(fps=rc.ReMapkey(input_key="fps", output_key="fps", dropout_rate=0.0),
+                              padding_mask=rc.ReMapkey(input_key="padding_mask", output_key="padding_mask", dropout_rate=0.0),
+                              text=rc.TextAttr(input_key=["t5_text_embeddings"], dropout_rate=0.2))
+    ours = oc.VideoConditioner(fps=oc.ReMapkey("fps", "fps", 0.0), padding_mask=oc.ReMapkey("padding_mask", "padding_mask", 0.0),
+                               text=oc.TextAttr("t5_text_embeddings", 0.2))
+    torch.manual_seed(0)
+    batch = {"fps": torch.tensor([16.0, 24.0, 30.0, 10.0]), "padding_mask": torch.zeros(4, 1, 8, 8), "t5_text_embeddings": torch.randn(4, 6, 16),
+             "neg_t5_text_embeddings": torch.randn(4, 6, 16)}
+
+    def same(a, b):
+        for k in ("crossattn_emb", "fps", "padding_mask"):
+            assert torch.equal(getattr(a, k), getattr(b, k)), k
+    for fn in ("get_condition_uncondition", "get_condition_with_negative_prompt"):
+        (c_ref, u_ref), (c, u) = getattr(ref, fn)(batch), getattr(ours, fn)(batch)
+        same(c, c_ref)
+        same(u, u_ref)
+    assert u.crossattn_emb.abs().max() > 0 and torch.equal(u.crossattn_emb, batch["neg_t5_text_embeddings"])
+    for seed in range(4):                                      # training-time dropout: same draws, same rows dropped
+        torch.manual_seed(seed)
+        a = ref(batch)
+        torch.manual_seed(seed)
+        b = ours(batch)
+        same(b, a)
