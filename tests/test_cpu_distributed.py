@@ -44,6 +44,54 @@ def run_distributed(fn_name: str, world: int = 2, **kwargs):
 
 
 # ------------------------------------------------------------------------------------------------
+def _cp_utils_vs_reference(rank, world, tmp):
+    """The sequence split / gather helpers and the Ulysses exchange against the reference's own files, on gloo ranks."""
+    from reference_oracle import import_reference, reference_network_modules
+    from cosmos_predict25_b200.parallel import context_parallel as cp, ulysses
+    ref = import_reference("cosmos_predict2._src.predict2.utils.context_parallel")
+    g = dist.group.WORLD
+    torch.manual_seed(3)
+    y = torch.randn(2, 8, 3, 5)
+    for dim in (1, 2) if world == 3 else (1,):
+        if y.shape[dim] % world:
+            continue
+        loc, loc_ref = cp.split_inputs_cp(y, dim, g), ref.split_inputs_cp(y, dim, g)
+        assert torch.equal(loc, loc_ref)
+        assert torch.equal(cp.cat_outputs_cp(loc, dim, g), ref.cat_outputs_cp(loc_ref, dim, g))
+        z, z_ref = loc.clone().requires_grad_(True), loc_ref.clone().requires_grad_(True)
+        w = torch.randn(y.shape, generator=torch.Generator().manual_seed(9))
+        (cp.cat_outputs_cp_with_grad(z, dim, g) * w).sum().backward()
+        (ref.cat_outputs_cp_with_grad(z_ref, dim, g) * w).sum().backward()
+        assert torch.equal(z.grad, z_ref.grad)
+    # Ulysses exchange: [B, S/P, H, D] -> [B, S, H/P, D] and back, forward and backward, against the reference's autograd functions
+    reference_network_modules()
+    a2a = import_reference("cosmos_predict2._src.predict2.networks.a2a_cp")
+
+    class _Dist:                                                 # torch.distributed with an all-to-all that gloo can run
+        def __getattr__(self, name):
+            return getattr(dist, name)
+
+        @staticmethod
+        def all_to_all_single(output, input, group=None, async_op=False):
+            output.copy_(ulysses._a2a(input, group))
+    a2a.dist = _Dist()
+    x = torch.randn(2, 6, 4, 8, generator=torch.Generator().manual_seed(20 + rank))
+    x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    h = ulysses._SeqToHead.apply(x1, g)
+    h_ref = a2a._SeqAllToAll.apply(g, x2, True)                  # local sequence -> local heads
+    assert torch.equal(h, h_ref)
+    back, back_ref = ulysses._HeadToSeq.apply(h, g), a2a._SeqAllToAll.apply(g, h_ref, False)
+    assert torch.equal(back, back_ref) and torch.equal(back, x)
+    wgt = torch.randn(back.shape, generator=torch.Generator().manual_seed(40 + rank))
+    (back * wgt).sum().backward()
+    (back_ref * wgt).sum().backward()
+    assert torch.equal(x1.grad, x2.grad)
+
+
+def test_context_parallel_helpers_match_the_reference():
+    run_distributed("_cp_utils_vs_reference", 2)
+
+
 def _cp_utils(rank, world, tmp):
     from cosmos_predict25_b200.parallel import context_parallel as cp
     g = dist.group.WORLD
