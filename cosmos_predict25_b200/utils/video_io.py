@@ -28,7 +28,8 @@ def resize_input(video: torch.Tensor, resolution: Tuple[int, int]) -> torch.Tens
     lead = video.shape[:-2]
     x = video.reshape(-1, 1, H, W).float()
     x = F.interpolate(x, size=(nh, nw), mode="bilinear", align_corners=False, antialias=True)
-    top, left = (nh - th) // 2, (nw - tw) // 2
+    # offsets rounded half-to-even like torchvision's center_crop, which the reference calls (an odd margin puts the extra pixel first)
+    top, left = int(round((nh - th) / 2.0)), int(round((nw - tw) / 2.0))
     x = x[..., top:top + th, left:left + tw]
     x = x.reshape(*lead, th, tw)
     return x.round().clamp(0, 255).to(torch.uint8) if video.dtype == torch.uint8 else x

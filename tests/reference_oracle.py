@@ -33,7 +33,7 @@ def reference_dir():
     return None
 
 
-def import_reference(module: str, max_stubs: int = 24):
+def import_reference(module: str, max_stubs: int = 64):
     """Import ``module`` (dotted name under ``cosmos_predict2``) from the reference tree; skip the test if that is impossible."""
     root = reference_dir()
     if root is None:

@@ -439,3 +439,27 @@ def test_conditioner_matches_the_reference():
         torch.manual_seed(seed)
         b = ours(batch)
         same(b, a)
+
+
+def test_input_preprocessing_and_resolution_tables_match_the_reference(tmp_path):
+    """What reaches the tokenizer from an input image: same resize (antialiased, ceil of the scaled size), centre crop, zero frames
+    after the first, uint8 layout [1, C, T, H, W]; and the resolution tables of datasets and pipelines."""
+    import numpy as np
+    from PIL import Image
+    from reference_oracle import install_diffusers_standins, install_omegaconf_standins, install_transformer_engine_standins
+    install_diffusers_standins(), install_omegaconf_standins(), install_transformer_engine_standins()
+    ref = import_reference("cosmos_predict2._src.predict2.inference.video2world")
+    ref_du = import_reference("cosmos_predict2._src.predict2.datasets.utils")
+    from cosmos_predict25_b200.data import utils as du
+    from cosmos_predict25_b200.utils import video_io
+    assert du.IMAGE_RES_SIZE_INFO == ref_du.IMAGE_RES_SIZE_INFO and du.VIDEO_RES_SIZE_INFO == ref_du.VIDEO_RES_SIZE_INFO
+    rng = np.random.RandomState(0)
+    for (h, w), res in (((90, 200), (64, 96)), ((333, 127), (48, 80)), ((64, 96), (64, 96))):
+        path = str(tmp_path / f"in_{h}x{w}.png")
+        Image.fromarray((rng.rand(h, w, 3) * 255).astype(np.uint8)).save(path)
+        want = ref.read_and_process_image(path, list(res), 5)
+        got = video_io.read_and_process_image(path, res, 5)
+        assert got.dtype == want.dtype == torch.uint8 and got.shape == want.shape == (1, 3, 5, *res)
+        assert torch.equal(got, want), (h, w, res, (got.int() - want.int()).abs().max())
+        vid = torch.from_numpy((rng.rand(4, 3, h, w) * 255).astype(np.uint8))
+        assert torch.equal(video_io.resize_input(vid, res), ref.resize_input(vid, list(res)))
