@@ -88,7 +88,9 @@ class Video2WorldInference:
                  "num_conditional_frames": num_latent_conditional_frames, "ai_caption": [prompt] * B}
         batch["t5_text_embeddings"] = self.text_encoder.encode_prompts([prompt] * B).to(self.device, self.model.precision)
         if use_neg_prompt:
-            neg = negative_prompt or ""
+            if negative_prompt is None:          # the library call without a negative prompt uses the default one, like the CLI
+                from ..config import DEFAULT_NEGATIVE_PROMPT as negative_prompt
+            neg = negative_prompt
             batch["neg_t5_text_embeddings"] = self.text_encoder.encode_prompts([neg] * B).to(self.device, self.model.precision)
         return batch
 
