@@ -125,9 +125,13 @@ class Camera:
         ys, xs = torch.meshgrid(torch.arange(H, dtype=torch.float32, device=dev) + 0.5,
                                 torch.arange(W, dtype=torch.float32, device=dev) + 0.5, indexing="ij")
         xy = torch.stack([xs, ys], dim=-1).view(-1, 2).repeat(*cam_pose.shape[:-2], 1, 1)
+        Camera._check_valid_pose(cam_pose)                    # with the tolerance of the pose's own dtype; the math below is fp32
         grid_cam = Camera.image2camera(Camera.to_homogeneous(xy), cam_intr.float())
-        grid_world = Camera.camera2world(grid_cam, cam_pose.float())
-        center = Camera.get_camera_center(cam_pose.float()).unsqueeze(-2)
+        R, t = cam_pose[..., :3].float(), cam_pose[..., 3:].float()
+        Rt = R.transpose(-1, -2)
+        inv = torch.cat([Rt, -Rt @ t], dim=-1)                # cam2world
+        grid_world = Camera.to_homogeneous(grid_cam) @ inv.transpose(-1, -2)
+        center = (-Rt @ t)[..., 0].unsqueeze(-2)
         return torch.nn.functional.normalize(grid_world - center, dim=-1).to(cam_pose.dtype)
 
     @staticmethod

@@ -1,0 +1,52 @@
+"""The reference's own unit-test files, run unmodified against this package (module names mapped by
+``reference_alias_plugin``). Each entry: test file inside the reference tree, the mapping, and the tests of that file that are
+expected to pass (all of them unless a reason is given)."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from reference_oracle import reference_dir
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+P = "cosmos_predict25_b200"
+def _offline_checkpoint_cache(tmp_path):
+    """No network here: the two checkpoints those tests resolve are placed in the local cache directory."""
+    root = tmp_path / "cache"
+    (root / "7219c6c7-f878-4137-bbdb-76842ea85e70").mkdir(parents=True)
+    (root / "685afcaa-4de2-42fe-b7b9-69f7a2dee4d8").write_bytes(b"0")
+    return {"COSMOS_CHECKPOINT_DIR": str(root)}
+
+
+PREPARE = {"checkpoint_db_test.py": _offline_checkpoint_cache}
+SUITES = [
+    ("cosmos_predict2/_src/imaginaire/modules/camera_test.py", {"cosmos_predict2._src.imaginaire.modules.camera": f"{P}.modules.camera"}, ""),
+    ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
+    ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
+    ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
+     {"cosmos_predict2._src.imaginaire.utils.checkpoint_db": f"{P}.utils.checkpoint_db"}, "not hf_ and not all_checkpoints"),     # the L1 tests download from the hub
+]
+
+
+@pytest.mark.parametrize("path,aliases,select", SUITES, ids=[s[0].split("/")[-1] for s in SUITES])
+def test_reference_test_file_passes_against_this_package(path, aliases, select, tmp_path):
+    root = reference_dir()
+    if root is None:
+        pytest.skip("no copy of the reference implementation here")
+    src = os.path.join(root, path)
+    # a copy outside the reference tree: its pyproject / conftest must not configure the run, its packages must not be importable
+    dst = tmp_path / os.path.basename(path)
+    dst.write_text(open(src).read())
+    (tmp_path / "pytest.ini").write_text("[pytest]\n")
+    extra = PREPARE.get(os.path.basename(path), lambda _: {})(tmp_path)
+    env = dict(os.environ, **extra, COSMOS_ALIAS_JSON=json.dumps(aliases), PYTHONPATH=os.pathsep.join([_HERE, os.path.dirname(_HERE)]))
+    cmd = [sys.executable, "-m", "pytest", str(dst), "-q", "-x", "-p", "reference_alias_plugin", "-p", "no:cacheprovider", "--rootdir", str(tmp_path)]
+    if select:
+        cmd += ["-k", select]
+    out = subprocess.run(cmd, env=env, cwd=str(tmp_path), capture_output=True, text=True, timeout=600)
+    tail = (out.stdout + out.stderr)[-3000:]
+    assert out.returncode == 0, tail
+    assert " passed" in out.stdout, tail
