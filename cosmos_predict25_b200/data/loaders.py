@@ -76,14 +76,115 @@ class OperationWatchdog:
         self._t.join(timeout=1.0)
 
 
+# ---- batch-level augmentations for the cached loader (cached_replay_dataloader.py:28-258 of the reference) -----------------------
+def _grid_starts(full: int, out: int, n: int) -> List[int]:
+    """Start offsets of ``n`` crops of length ``out`` spread over ``full``: centred for one crop, else on a regular grid with a
+    random shift inside each cell."""
+    if out > full:
+        raise ValueError("Output dimensions cannot be larger than original dimensions")
+    if n == 1:
+        return [(full - out) // 2]
+    step = max(1, (full - out) // (n - 1))
+    return [min(full - out, i * step + random.randrange(max(1, step))) for i in range(n)]
+
+
+def generate_multiple_image_batches(data_batch: Dict, nh: int, nw: int, output_height: int, output_width: int) -> List[Dict]:
+    """``nh * nw`` copies of the batch whose ``images`` [B, C, H, W] are crops spread over the original."""
+    import copy
+    img = data_batch["images"]
+    out = []
+    for h0 in _grid_starts(img.shape[-2], output_height, nh):
+        for w0 in _grid_starts(img.shape[-1], output_width, nw):
+            b = copy.deepcopy(data_batch)
+            b["images"] = img[..., h0:h0 + output_height, w0:w0 + output_width]
+            out.append(b)
+    return out
+
+
+def generate_multiple_video_batches(data_batch: Dict, nt: int, nh: int, nw: int, output_length: int, output_height: int,
+                                    output_width: int) -> List[Dict]:
+    """``nt * nh * nw`` copies whose ``video`` [B, C, T, H, W] are space-time crops spread over the original."""
+    import copy
+    vid = data_batch["video"]
+    out = []
+    for t0 in _grid_starts(vid.shape[2], output_length, nt):
+        for h0 in _grid_starts(vid.shape[3], output_height, nh):
+            for w0 in _grid_starts(vid.shape[4], output_width, nw):
+                b = copy.deepcopy(data_batch)
+                b["video"] = vid[:, :, t0:t0 + output_length, h0:h0 + output_height, w0:w0 + output_width]
+                out.append(b)
+    return out
+
+
+def duplicate_batches(data_batch: Dict, n: int) -> List[Dict]:
+    import copy
+    return [copy.deepcopy(data_batch) for _ in range(n)]
+
+
+_DUP_RNG = random.Random(123)
+
+
+def duplicate_batches_random(data_batch: Dict, n: float) -> List[Dict]:
+    """``floor(n)`` or ``ceil(n)`` copies, so that the expected number of copies is ``n``."""
+    import copy
+    import math
+    lo, hi = int(math.floor(n)), int(math.ceil(n))
+    k = lo if _DUP_RNG.uniform(lo, hi) > n else hi
+    return [copy.deepcopy(data_batch) for _ in range(k)]
+
+
+def concatenate_batches(n: int, data_batches: List[Dict]) -> List[Dict]:
+    """Merge ``n`` batches into one, for all ``len / n`` groups (group i takes batches i, i + m, i + 2m ...): tensors are
+    concatenated along the batch axis, lists are joined, a string keeps the first value, anything else becomes a list."""
+    import torch
+    if n <= 0:
+        raise ValueError("n must be a positive integer")
+    if len(data_batches) % n != 0:
+        raise ValueError(f"Length of data_batches ({len(data_batches)}) must be divisible by n ({n})")
+    m = len(data_batches) // n
+    out = []
+    for i in range(m):
+        group = [data_batches[j * m + i] for j in range(n)]
+        merged: Dict = {}
+        for key in {k for b in group for k in b}:
+            vals = [b[key] for b in group if key in b]
+            first = next((v for v in vals if v is not None), None)
+            if first is None:
+                merged[key] = None
+            elif isinstance(first, torch.Tensor):
+                merged[key] = torch.cat(vals, dim=0)
+            elif isinstance(first, str):
+                merged[key] = vals[0]
+            elif isinstance(first, list):
+                merged[key] = [x for v in vals for x in v]
+            else:
+                merged[key] = vals
+        out.append(merged)
+    return out
+
+
+def get_cached_replay_dataloader(use_cache: bool = False, cache_size: int = 32, concat_size: int = 1,
+                                 cache_augment_fn: Optional[Callable] = None, cache_replay_name: str = "cached_replay_dataloader",
+                                 webdataset: bool = False, **kwargs):
+    """A torch ``DataLoader(**kwargs)``, wrapped in the cached loader when ``use_cache``."""
+    from torch.utils.data import DataLoader
+    loader = DataLoader(**kwargs)
+    if not use_cache:
+        return loader
+    return CachedReplayDataLoader(loader, cache_size=cache_size, cache_augmentation_fn=cache_augment_fn, concat_size=concat_size,
+                                  name=cache_replay_name)
+
+
 class CachedReplayDataLoader:
     """Prefetches batches from a base loader on a background thread into a bounded cache; each fetched batch is
     passed through ``cache_augmentation_fn`` (which may return several batches: crops, duplicates) and can be
     replayed ``cache_replay_n`` times, trading data diversity for loader throughput."""
 
     def __init__(self, dataloader: Iterable, cache_size: int = 8, cache_replay_n: int = 1,
-                 cache_augmentation_fn: Optional[Callable] = None, shuffle_cache: bool = False, watchdog_threshold: float = 120.0):
+                 cache_augmentation_fn: Optional[Callable] = None, shuffle_cache: bool = False, watchdog_threshold: float = 120.0,
+                 concat_size: int = 1, name: str = "cached_replay_dataloader"):
         self.base = dataloader
+        self.concat_size, self.name = max(1, concat_size), name
         self.cache_size = cache_size
         self.replay_n = max(1, cache_replay_n)
         self.aug = cache_augmentation_fn
@@ -116,6 +217,17 @@ class CachedReplayDataLoader:
             self._q.put(StopIteration)
 
     def __iter__(self):
+        if self.concat_size == 1:
+            yield from self._iter_single()
+            return
+        group: List = []
+        for item in self._iter_single():                # ``concat_size`` cached batches become one (batch axis)
+            group.append(item)
+            if len(group) == self.concat_size:
+                yield concatenate_batches(self.concat_size, group)[0]
+                group = []
+
+    def _iter_single(self):
         self.close()
         self._stop.clear()
         self._q = queue.Queue(maxsize=self.cache_size)

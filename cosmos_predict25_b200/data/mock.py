@@ -68,6 +68,50 @@ class MockImageDataset(Dataset):
                 "padding_mask": torch.zeros(1, self.h, self.w), "ai_caption": f"synthetic image {i}", "dataset_name": "mock_image"}
 
 
+MAX_LENGTH = 1 << 15
+
+
+class LambdaDataset(Dataset):
+    """Items are whatever ``fn()`` returns (imaginaire/datasets/mock_dataset.py:29-84 of the reference)."""
+
+    def __init__(self, fn, length: int = MAX_LENGTH):
+        self.fn, self.length = fn, length
+
+    def __len__(self):
+        return self.length
+
+    def __getitem__(self, index):
+        return self.fn()
+
+
+class RepeatDataset(Dataset):
+    """Cycles over the first ``num_item`` items of ``dataset`` (one fixed sample by default) for ``length`` indices."""
+
+    def __init__(self, dataset, length: int = MAX_LENGTH, num_item: int = 1):
+        self.length = length
+        self.items = [dataset[i] for i in range(num_item)]
+
+    def __len__(self):
+        return self.length
+
+    def __getitem__(self, index):
+        return self.items[index % len(self.items)]
+
+
+class CombinedDictDataset(Dataset):
+    """{key: dataset} -> items {key: dataset[i]}; the length is the shortest member's."""
+
+    def __init__(self, **datasets):
+        self.datasets = datasets
+        self.length = min(len(d) for d in datasets.values())
+
+    def __len__(self):
+        return self.length
+
+    def __getitem__(self, index):
+        return {k: d[index] for k, d in self.datasets.items()}
+
+
 def get_sampler(dataset, dp_size: int = 1, dp_rank: int = 0, shuffle: bool = True, seed: int = 0):
     """Shard by data-parallel rank (all ranks of a context-parallel group share ``dp_rank``)."""
     return DistributedSampler(dataset, num_replicas=dp_size, rank=dp_rank, shuffle=shuffle, seed=seed)

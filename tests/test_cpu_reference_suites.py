@@ -24,6 +24,13 @@ def _offline_checkpoint_cache(tmp_path):
 PREPARE = {"checkpoint_db_test.py": _offline_checkpoint_cache}
 SUITES = [
     ("cosmos_predict2/_src/imaginaire/modules/camera_test.py", {"cosmos_predict2._src.imaginaire.modules.camera": f"{P}.modules.camera"}, ""),
+    ("cosmos_predict2/_src/imaginaire/utils/validator_test.py",
+     {"cosmos_predict2._src.imaginaire.utils.validator": f"{P}.utils.validator",
+      "cosmos_predict2._src.imaginaire.utils.validator_params": f"{P}.utils.validator_params"}, ""),
+    ("cosmos_predict2/_src/imaginaire/datasets/mock_dataset_test.py",
+     {"cosmos_predict2._src.imaginaire.datasets.mock_dataset": f"{P}.data.mock", "cosmos_predict2._src.imaginaire.lazy_config": f"{P}.utils.lazy_config"}, ""),
+    ("cosmos_predict2/_src/predict2/datasets/cached_replay_dataloader_test.py",
+     {"cosmos_predict2._src.predict2.datasets.cached_replay_dataloader": f"{P}.data.loaders"}, ""),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
