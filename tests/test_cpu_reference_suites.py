@@ -31,6 +31,8 @@ SUITES = [
      {"cosmos_predict2._src.imaginaire.datasets.mock_dataset": f"{P}.data.mock", "cosmos_predict2._src.imaginaire.lazy_config": f"{P}.utils.lazy_config"}, ""),
     ("cosmos_predict2/_src/predict2/datasets/cached_replay_dataloader_test.py",
      {"cosmos_predict2._src.predict2.datasets.cached_replay_dataloader": f"{P}.data.loaders"}, ""),
+    ("cosmos_predict2/_src/predict2/datasets/decoders/video_decoder_test.py",
+     {"cosmos_predict2._src.predict2.datasets.decoders.video_decoder": f"{P}.data.video_decoder"}, ""),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
