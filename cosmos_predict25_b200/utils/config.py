@@ -275,6 +275,10 @@ def _apply_defaults(cfg: Config, node: Mapping, cs: ConfigStore, seen: Tuple[str
 
 def _select_group(cfg: Config, group: str, name: str, cs: ConfigStore) -> None:
     node = copy.deepcopy(cs.get(group, name))
+    if cs.repo[group][name].get("package") == "_global_":
+        # a whole-tree node (e.g. the ``model`` group of the Text2World project sets ``trainer`` and ``model`` together)
+        deep_merge(cfg, node)
+        return
     path = GROUP_PATHS.get(group)
     if path is None:
         raise KeyError(f"unknown config group {group!r}")

@@ -33,6 +33,9 @@ SUITES = [
      {"cosmos_predict2._src.predict2.datasets.cached_replay_dataloader": f"{P}.data.loaders"}, ""),
     ("cosmos_predict2/_src/predict2/datasets/decoders/video_decoder_test.py",
      {"cosmos_predict2._src.predict2.datasets.decoders.video_decoder": f"{P}.data.video_decoder"}, ""),
+    ("cosmos_predict2/_src/predict2/configs/text2world/config_test.py",
+     {"cosmos_predict2._src.imaginaire.utils.config_helper": f"{P}.utils.config",
+      "cosmos_predict2._src.predict2.configs.text2world.config": f"{P}.configs.text2world"}, ""),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
