@@ -258,6 +258,27 @@ def main():
             add(f"skinny_bgemm x2 (AdaLN-LoRA, {tag})", f"Z={Z} rows={R} {D}->{r}->{3 * D}", time_ms(two_stage), bytes_=wb)
             add(f"torch fp32 linears (twin, {tag})", f"Z={Z} rows={R}", time_ms(torch_twin), bytes_=wb)
             del w1, w2
+    if want("sampler"):
+        # state updates of the sampling loop on the batched cond / uncond latent [2, 16, 24, 88, 160] fp32 (21.6 MB per tensor,
+        # smaller than L2: the flush between iterations makes every operand come from HBM)
+        from . import ref as ref_ops
+        shape = (2, 16, 24, 88, 160)
+        xs = [torch.randn(shape, device=dev) for _ in range(4)]
+        cs = [0.9, -0.3, 0.2, 0.05]
+        nbt = xs[0].numel() * 4.0
+        add("lincomb (4 operands: corrector update)", "2x16x24x88x160 fp32", time_ms(lambda: F_ops.lincomb(xs, cs)), bytes_=5 * nbt)
+        add("torch term by term (twin)", "4 operands", time_ms(lambda: ref_ops.lincomb(xs, cs)), bytes_=5 * nbt)
+        mask = torch.zeros(2, 1, 24, 88, 160, device=dev)
+        mask[:, :, :2] = 1
+        flag = torch.ones(2, 1, 1, 1, 1, device=dev)
+        add("frame_blend -> bf16 (conditioning frames in)", "2x16x24x88x160", time_ms(
+            lambda: F_ops.frame_blend(xs[0], xs[1], None, mask, flag, out_dtype=torch.bfloat16)), bytes_=2.5 * nbt + mask.numel() * 4.0)
+        add("torch blend + cast (twin)", "", time_ms(
+            lambda: ref_ops.frame_blend(xs[0], xs[1], None, mask, flag, out_dtype=torch.bfloat16)), bytes_=2.5 * nbt + mask.numel() * 4.0)
+        add("frame_blend (velocity of conditioning frames)", "2x16x24x88x160", time_ms(
+            lambda: F_ops.frame_blend(xs[0], xs[1], xs[2], mask)), bytes_=4 * nbt + mask.numel() * 4.0)
+        add("torch blend (twin)", "", time_ms(lambda: ref_ops.frame_blend(xs[0], xs[1], xs[2], mask)), bytes_=4 * nbt + mask.numel() * 4.0)
+        del xs
     if want("conv"):
         # causal 3 x 3 x 3 convolutions of the Wan2.1 VAE decoder at 720p (channels-last activations, 2 cached + 4 new frames in,
         # 4 frames out), next to the cuDNN convolution of the same layer on NCTHW tensors

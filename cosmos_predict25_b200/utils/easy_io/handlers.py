@@ -114,13 +114,18 @@ class ByteHandler(BaseFileHandler):
 
 
 class CsvHandler(BaseFileHandler):
-    def load_from_fileobj(self, file, **kw): return list(csv.DictReader(file, **kw))
+    """Rows as lists of strings, header row included (the reference's convention: csv_handler.py:22-42 there); rows given as
+    dicts are written as a header plus values."""
+
+    def load_from_fileobj(self, file, **kw): return list(csv.reader(file))
 
     def dump_to_fileobj(self, obj, file, **kw):
         rows = list(obj)
-        w = csv.DictWriter(file, fieldnames=list(rows[0].keys()) if rows else [], **kw)
-        w.writeheader()
-        w.writerows(rows)
+        if rows and all(isinstance(r, dict) for r in rows):
+            rows = [list(rows[0].keys())] + [list(r.values()) for r in rows]
+        if not all(isinstance(r, (list, tuple)) for r in rows):
+            raise ValueError("Each row must be a list")
+        csv.writer(file).writerows(rows)
 
     def dump_to_str(self, obj, **kw):
         s = io.StringIO()

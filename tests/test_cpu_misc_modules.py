@@ -24,7 +24,8 @@ def test_quaternion_roundtrip_and_product():
     R = Quaternion.to_rotation_matrix(q)
     assert torch.allclose(R @ R.transpose(-1, -2), torch.eye(3).expand(64, 3, 3), atol=1e-5)
     assert torch.allclose(torch.linalg.det(R), torch.ones(64), atol=1e-5)
-    assert torch.allclose(Quaternion.from_rotation_matrix(R), q, atol=1e-5)
+    back = Quaternion.from_rotation_matrix(R)                     # q and -q are the same rotation; the sign rule is the reference's
+    assert torch.allclose(back * torch.sign((back * q).sum(-1, keepdim=True)), q, atol=1e-5)
     # 180-degree rotations exercise the non-trace branches
     for axis in range(3):
         qq = torch.zeros(4); qq[axis] = 1.0

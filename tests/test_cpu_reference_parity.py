@@ -463,3 +463,25 @@ def test_input_preprocessing_and_resolution_tables_match_the_reference(tmp_path)
         assert torch.equal(got, want), (h, w, res, (got.int() - want.int()).abs().max())
         vid = torch.from_numpy((rng.rand(4, 3, h, w) * 255).astype(np.uint8))
         assert torch.equal(video_io.resize_input(vid, res), ref.resize_input(vid, list(res)))
+
+
+def test_easy_io_files_interoperate_with_the_reference(tmp_path):
+    """Every local file format written by one side is read back identically by the other."""
+    import numpy as np
+    ref = import_reference("cosmos_predict2._src.imaginaire.utils.easy_io.easy_io")
+    from cosmos_predict25_b200.utils.easy_io import easy_io as own
+    objs = {"a.json": {"x": [1, 2, {"y": "z"}], "f": 1.5}, "b.yaml": {"k": [1, 2], "n": {"m": True}}, "c.pkl": {"t": (1, 2)},
+            "d.txt": "hello\nworld\n", "e.npy": np.arange(6).reshape(2, 3), "f.pt": {"w": torch.arange(4.0)}, "g.jsonl": [{"a": 1}, {"b": 2}],
+            "h.csv": [["a", "b"], ["1", "2"]]}
+    for name, obj in objs.items():
+        for writer, reader, tag in ((own, ref, "own_ref"), (ref, own, "ref_own")):
+            path = str(tmp_path / f"{tag}_{name}")
+            writer.dump(obj, path)
+            back = reader.load(path)
+            if isinstance(obj, np.ndarray):
+                assert np.array_equal(back, obj), (name, tag)
+            elif name.endswith(".pt"):
+                assert torch.equal(back["w"], obj["w"]), (name, tag)
+            else:
+                assert back == obj, (name, tag, back)
+    assert own.exists(str(tmp_path / "own_ref_a.json")) and ref.exists(str(tmp_path / "own_ref_a.json"))
