@@ -36,6 +36,9 @@ SUITES = [
     ("cosmos_predict2/_src/predict2/configs/text2world/config_test.py",
      {"cosmos_predict2._src.imaginaire.utils.config_helper": f"{P}.utils.config",
       "cosmos_predict2._src.predict2.configs.text2world.config": f"{P}.configs.text2world"}, ""),
+    ("cosmos_predict2/_src/imaginaire/utils/ema_test.py",
+     {"cosmos_predict2._src.imaginaire.model": f"{P}.trainer.model", "cosmos_predict2._src.imaginaire.utils.ema": f"{P}.utils.ema"},
+     ""),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
