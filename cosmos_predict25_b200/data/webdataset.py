@@ -65,8 +65,9 @@ class TarSample:
     root: str
     path: str                      # relative shard path, with ``{key}`` replaced per data key
     keys: Sequence[str]
-    dset_id: int = 0
+    dset_id: Any = 0
     sample_keys_full_list: Optional[str] = None
+    meta: Any = None               # the DatasetInfo this shard came from (its ``opts`` carry e.g. the aspect ratio)
 
 
 def _aspect_of(path: str) -> str:
@@ -135,6 +136,92 @@ class ShardlistMultiAspectRatioParallelSync(ShardlistMultiAspectRatio):
     def reader_id(self):
         rank, world = super().reader_id()
         return rank // self.model_parallel_size, max(1, world // self.model_parallel_size)
+
+
+class ShardlistMultiAspectRatioInfinite(IterableDataset):
+    """Endless shard stream in which every reader (rank x loader worker) stays inside ONE aspect-ratio group, so that a batch never
+    mixes frame shapes. Readers are dealt to the groups in proportion to the groups' shard counts (at least one each); inside a
+    group the readers take interleaved slices. The group of a shard is ``shard.meta.opts["aspect_ratio"]``. Reader identity comes
+    from RANK / WORLD_SIZE / WORKER / NUM_WORKERS when set (tests, external launchers), else from torch.distributed and the loader's
+    worker info. Yields ``{"url": shard}`` (imaginaire/datasets/webdataset/distributors/multi_aspect_ratio_v2.py:30-252 of the
+    reference)."""
+
+    def __init__(self, shuffle: bool = True, split_by_node: bool = True, split_by_worker: bool = True, chunk_size: int = 1,
+                 resume_flag: bool = True, verbose: bool = False, is_infinite_loader: bool = True, seed: int = 0):
+        super().__init__()
+        assert is_infinite_loader, "this distributor only runs as an endless stream"
+        self.shuffle, self.split_by_node, self.split_by_worker, self.verbose, self.seed = shuffle, split_by_node, split_by_worker, verbose, seed
+        self.chunk_size, self.resume_flag = chunk_size, resume_flag            # accepted for compatibility, unused
+        self.groups: Dict[str, List[TarSample]] = {}
+
+    def set_urls(self, urls: List[TarSample]):
+        groups: Dict[str, List[TarSample]] = {}
+        for u in urls:
+            opts = getattr(u.meta, "opts", None) or {}
+            if "aspect_ratio" not in opts:
+                raise ValueError("aspect_ratio should be specified in dataset_info when using multi aspect distributor")
+            groups.setdefault(opts["aspect_ratio"], []).append(u)
+        self.groups = {k: sorted(v, key=lambda t: (t.path, t.root)) for k, v in sorted(groups.items())}
+
+    def set_chunk_size(self, chunk_size: int):
+        self.chunk_size = chunk_size
+
+    def set_epoch(self, epoch: int, start_index: int = 0):
+        self.epoch, self.start_index = epoch, start_index
+
+    def _reader(self):
+        env = os.environ
+        if self.split_by_node:
+            rank = int(env["RANK"]) if "RANK" in env else (dist.get_rank() if dist.is_available() and dist.is_initialized() else 0)
+            world = int(env["WORLD_SIZE"]) if "WORLD_SIZE" in env else (dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1)
+        else:
+            rank, world = 0, 1
+        wi = get_worker_info()
+        if not self.split_by_worker:
+            wid, nw = 0, 1
+        elif "WORKER" in env and "NUM_WORKERS" in env:
+            wid, nw = int(env["WORKER"]), int(env["NUM_WORKERS"])
+        else:
+            wid, nw = (wi.id, wi.num_workers) if wi is not None else (0, 1)
+        return rank * nw + wid, world * nw
+
+    def allocate_readers(self, n_readers: int) -> List[str]:
+        """Group name of every reader: one reader per group first, the rest by largest remainder of the shard shares."""
+        names = list(self.groups)
+        if n_readers < len(names):
+            return [names[r % len(names)] for r in range(n_readers)]          # fewer readers than groups: each reader rotates
+        total = sum(len(v) for v in self.groups.values())
+        extra = n_readers - len(names)
+        share = {k: extra * len(self.groups[k]) / total for k in names}
+        counts = {k: 1 + int(share[k]) for k in names}
+        for k in sorted(names, key=lambda k: share[k] - int(share[k]), reverse=True)[: n_readers - sum(counts.values())]:
+            counts[k] += 1
+        return [k for k in names for _ in range(counts[k])]
+
+    def __iter__(self):
+        rid, n = self._reader()
+        alloc = self.allocate_readers(n)
+        names = list(self.groups)
+        rotate = n < len(names)
+        group = alloc[rid]
+        peers = [r for r in range(n) if alloc[r] == group]
+        j, k = peers.index(rid), len(peers)
+        if self.verbose:
+            log.info(f"reader {rid}/{n}: aspect ratio {group}, slice {j} of {k}, {len(self.groups[group])} shards")
+        rng = random.Random(self.seed + 7919 * rid)
+        epoch = 0
+        while True:
+            if rotate:
+                group = names[(rid + epoch * n) % len(names)]
+                j, k = 0, 1
+            urls = self.groups[group]
+            mine = urls[j::k] if len(urls) >= k else [urls[j % len(urls)]]
+            if self.shuffle:
+                mine = list(mine)
+                rng.shuffle(mine)
+            for u in mine:
+                yield {"url": u}
+            epoch += 1
 
 
 # ---- decoders -----------------------------------------------------------------------------------------------------------

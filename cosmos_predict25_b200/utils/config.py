@@ -10,6 +10,7 @@ the tree is made of ``LazyDict`` nodes; ``${a.b}`` interpolations are resolved o
 
 from __future__ import annotations
 
+import dataclasses
 import copy
 import os
 import re
@@ -22,6 +23,14 @@ import yaml
 from .lazy_config import LazyConfig, LazyDict, instantiate, is_lazy
 
 # where each config group lands in the tree
+@dataclasses.dataclass
+class ObjectStoreConfig:
+    """Where a dataset or a checkpoint lives when it is not on the local disk (imaginaire/config.py:170-176 of the reference)."""
+    enabled: bool = False
+    credentials: str = ""
+    bucket: str = ""
+
+
 GROUP_PATHS = {
     "model": "model", "net": "model.config.net", "conditioner": "model.config.conditioner",
     "tokenizer": "model.config.tokenizer", "ema": "model.config.ema", "optimizer": "optimizer", "scheduler": "scheduler",

@@ -187,3 +187,28 @@ def test_video_decoders_sample_windows_from_an_encoded_clip(tmp_path):
     assert construct_video_decoder("chunked_video_decoder", sequence_length=8, min_fps_thres=30, max_fps_thres=60)("clip.mp4", data) is None
     assert dec("a/clip.txt", b"caption") is None
     assert construct_video_decoder("video_naive_bytes")("clip.mp4", data) is data
+
+
+def test_infinite_multi_aspect_distributor_deals_readers_by_shard_share(monkeypatch):
+    from cosmos_predict25_b200.data.webdataset import DatasetInfo, ShardlistMultiAspectRatioInfinite, TarSample
+    urls = []
+    for aspect, count in (("16:9", 60), ("1:1", 30), ("9:16", 10)):
+        info = DatasetInfo(wdinfo=[], opts={"aspect_ratio": aspect})
+        urls += [TarSample(root="r/", path=f"{aspect}/part_{i:04d}.tar", keys=[], meta=info) for i in range(count)]
+    d = ShardlistMultiAspectRatioInfinite(shuffle=False)
+    d.set_urls(urls)
+    alloc = d.allocate_readers(10)
+    assert len(alloc) == 10 and {a: alloc.count(a) for a in set(alloc)} == {"16:9": 5, "1:1": 3, "9:16": 2}
+    assert sorted(set(d.allocate_readers(2))) == ["16:9", "1:1"] or len(set(d.allocate_readers(2))) == 2      # fewer readers than groups
+    seen = {}
+    for worker in range(10):                                    # every reader stays in its group and the slices of a group are disjoint
+        for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("WORKER", str(worker)), ("NUM_WORKERS", "10")):
+            monkeypatch.setenv(k, v)
+        it = iter(d)
+        got = [next(it)["url"] for _ in range(4)]
+        assert len({u.meta.opts["aspect_ratio"] for u in got}) == 1
+        seen.setdefault(got[0].meta.opts["aspect_ratio"], []).append({u.path for u in got})
+    for group in seen.values():
+        assert all(a.isdisjoint(b) for i, a in enumerate(group) for b in group[i + 1:])
+    with pytest.raises(ValueError):
+        d.set_urls([TarSample(root="r/", path="x.tar", keys=[], meta=DatasetInfo(wdinfo=[]))])

@@ -39,6 +39,10 @@ SUITES = [
     ("cosmos_predict2/_src/imaginaire/utils/ema_test.py",
      {"cosmos_predict2._src.imaginaire.model": f"{P}.trainer.model", "cosmos_predict2._src.imaginaire.utils.ema": f"{P}.utils.ema"},
      ""),
+    ("cosmos_predict2/_src/imaginaire/datasets/webdataset/distributors/multi_aspect_ratio_v2_test.py",
+     {"cosmos_predict2._src.imaginaire.config": f"{P}.utils.config", "cosmos_predict2._src.imaginaire.utils": f"{P}.utils",
+      "cosmos_predict2._src.imaginaire.datasets.webdataset.config.schema": f"{P}.data.webdataset",
+      "cosmos_predict2._src.imaginaire.datasets.webdataset.distributors.multi_aspect_ratio_v2": f"{P}.data.webdataset"}, ""),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
