@@ -162,6 +162,20 @@ def install_diffusers_standins() -> None:
     su = mods["diffusers.schedulers.scheduling_utils"]
     su.KarrasDiffusionSchedulers, su.SchedulerMixin, su.SchedulerOutput = KarrasDiffusionSchedulers, SchedulerMixin, SchedulerOutput
     mods["diffusers.utils"].deprecate = lambda *a, **k: None
+
+    class FlowMatchEulerDiscreteScheduler:
+        """Only what the reference's training schedule reads from this diffusers class: the table of the 1000 training noise
+        levels sigma = shift * s / (1 + (shift - 1) s), s = 1 ... 1/1000, and the matching timesteps 1000 sigma."""
+
+        def __init__(self, num_train_timesteps=1000, shift=1.0, use_dynamic_shifting=False, **_):
+            import numpy as np
+            import torch
+            self.config = _Config(num_train_timesteps=num_train_timesteps, shift=shift, use_dynamic_shifting=use_dynamic_shifting)
+            s = torch.from_numpy(np.linspace(1, num_train_timesteps, num_train_timesteps, dtype=np.float32)[::-1].copy()) / num_train_timesteps
+            if not use_dynamic_shifting:
+                s = shift * s / (1 + (shift - 1) * s)
+            self.sigmas, self.timesteps = s, s * num_train_timesteps
+    mods["diffusers"].FlowMatchEulerDiscreteScheduler = FlowMatchEulerDiscreteScheduler
     sys.modules.update(mods)
 
 
@@ -188,3 +202,18 @@ def install_omegaconf_standins() -> None:
         setattr(om, sub, m)
         sys.modules[f"omegaconf.{sub}"] = m
     sys.modules["omegaconf"] = om
+
+
+def install_import_time_patches() -> None:
+    """Things some reference modules evaluate while they are being imported, and that only exist on a GPU box or with an older
+    transformers: a default argument ``torch.cuda.current_device()``, ``is_flash_attn_2_available()``, a cache class name."""
+    import torch
+    import transformers.cache_utils as cache_utils
+    import transformers.utils
+    if not hasattr(cache_utils, "SlidingWindowCache"):
+        cache_utils.SlidingWindowCache = type("SlidingWindowCache", (), {})
+    transformers.utils.is_flash_attn_2_available = lambda: True
+    if not torch.cuda.is_available():
+        torch.cuda.current_device = lambda: 0
+    if "diffusers" in sys.modules and not hasattr(sys.modules["diffusers"], "FlowMatchEulerDiscreteScheduler"):
+        sys.modules["diffusers"].FlowMatchEulerDiscreteScheduler = type("FlowMatchEulerDiscreteScheduler", (), {})

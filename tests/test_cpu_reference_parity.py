@@ -485,3 +485,165 @@ def test_easy_io_files_interoperate_with_the_reference(tmp_path):
             else:
                 assert back == obj, (name, tag, back)
     assert own.exists(str(tmp_path / "own_ref_a.json")) and ref.exists(str(tmp_path / "own_ref_a.json"))
+
+
+def test_video_condition_matches_the_reference():
+    """Conditioning-frame masks of the Video2World condition: fixed count, per-batch categorical draw and uniform draw from the same
+    generator states, image batches, the inference edit of both guidance branches, and the second version of the condition."""
+    import random
+    from reference_oracle import (install_diffusers_standins, install_import_time_patches, install_omegaconf_standins,
+                                  install_transformer_engine_standins)
+    install_omegaconf_standins(), install_diffusers_standins(), install_transformer_engine_standins(), install_import_time_patches()
+    ref = import_reference("cosmos_predict2._src.predict2.configs.video2world.defaults.conditioner")
+    from cosmos_predict25_b200.models import conditioner as oc
+    gt = torch.randn(4, 16, 6, 4, 4)
+    flags = torch.tensor([True, True, False, True])
+    for ref_cls, own_cls in ((ref.Video2WorldCondition, oc.Video2WorldCondition), (ref.Video2WorldConditionV2, oc.Video2WorldConditionV2)):
+        def pair(**kw):
+            a = ref_cls(crossattn_emb=torch.zeros(4, 2, 8), use_video_condition=flags.clone())
+            b = own_cls(crossattn_emb=torch.zeros(4, 2, 8), use_video_condition=flags.clone())
+            random.seed(5), torch.manual_seed(5)
+            a = a.set_video_condition(gt, **kw)
+            random.seed(5), torch.manual_seed(5)
+            b = b.set_video_condition(gt, **kw)
+            return a, b
+        v2 = ref_cls is ref.Video2WorldConditionV2
+        cases = [dict(random_min_num_conditional_frames=0, random_max_num_conditional_frames=2, num_conditional_frames=2)]
+        if not v2:          # the second version overrides the count by its (scalar) flag: only the fixed-count form applies to a batch of flags
+            cases += [dict(random_min_num_conditional_frames=0, random_max_num_conditional_frames=2, conditional_frames_probs={0: 0.5, 1: 0.25, 2: 0.25}),
+                      dict(random_min_num_conditional_frames=1, random_max_num_conditional_frames=3)]
+        for kw in cases:
+            if v2:
+                continue
+            a, b = pair(**kw)
+            assert torch.equal(a.condition_video_input_mask_B_C_T_H_W, b.condition_video_input_mask_B_C_T_H_W), kw
+            assert torch.equal(a.gt_frames, b.gt_frames)
+        if not v2:
+            a, b = pair(random_min_num_conditional_frames=0, random_max_num_conditional_frames=2, num_conditional_frames=1)
+            for cond_branch in (True, False):
+                ea, eb = a.edit_for_inference(cond_branch, 2), b.edit_for_inference(cond_branch, 2)
+                assert torch.equal(ea.condition_video_input_mask_B_C_T_H_W, eb.condition_video_input_mask_B_C_T_H_W)
+                assert torch.equal(torch.as_tensor(ea.use_video_condition), torch.as_tensor(eb.use_video_condition))
+            img = torch.randn(4, 16, 1, 4, 4)
+            ia = ref_cls(crossattn_emb=torch.zeros(4, 2, 8), use_video_condition=flags.clone()).set_video_condition(img, 0, 2, num_conditional_frames=2)
+            ib = own_cls(crossattn_emb=torch.zeros(4, 2, 8), use_video_condition=flags.clone()).set_video_condition(img, 0, 2, num_conditional_frames=2)
+            assert ia.condition_video_input_mask_B_C_T_H_W.sum() == ib.condition_video_input_mask_B_C_T_H_W.sum() == 0
+        else:               # scalar flag, as the second version expects
+            for flag in (True, False):
+                a = ref_cls(crossattn_emb=torch.zeros(4, 2, 8), use_video_condition=flag).set_video_condition(gt, 0, 2, num_conditional_frames=2)
+                b = own_cls(crossattn_emb=torch.zeros(4, 2, 8), use_video_condition=flag).set_video_condition(gt, 0, 2, num_conditional_frames=2)
+                assert torch.equal(a.condition_video_input_mask_B_C_T_H_W, b.condition_video_input_mask_B_C_T_H_W), flag
+                ea, eb = a.edit_for_inference(False, 1), b.edit_for_inference(False, 1)
+                assert torch.equal(ea.condition_video_input_mask_B_C_T_H_W, eb.condition_video_input_mask_B_C_T_H_W)
+
+
+def _reference_v2w_model(net_kw, conditional_frame_timestep=-1.0, high_sigma=False):
+    """The reference's Video2World rectified-flow model object with its own network, conditioner, training schedule and sampler,
+    assembled without its constructor (which needs the lazy-config / sharding stack): every method that runs below is the
+    reference's, unmodified."""
+    import types
+    from reference_oracle import (install_diffusers_standins, install_import_time_patches, install_omegaconf_standins,
+                                  reference_network_modules)
+    from cosmos_predict25_b200.models.vae_wan import DummyTokenizer
+    install_omegaconf_standins(), install_diffusers_standins(), install_import_time_patches()
+    lvg, _ = reference_network_modules()
+    ref_v2w = import_reference("cosmos_predict2._src.predict2.models.video2world_model_rectified_flow")
+    ref_t2w = import_reference("cosmos_predict2._src.predict2.models.text2world_model_rectified_flow")
+    ref_rf = import_reference("cosmos_predict2._src.predict2.schedulers.rectified_flow")
+    ref_unipc = import_reference("cosmos_predict2._src.predict2.models.fm_solvers_unipc")
+    ref_cond = import_reference("cosmos_predict2._src.predict2.configs.video2world.defaults.conditioner")
+    rc = import_reference("cosmos_predict2._src.predict2.conditioner")
+    for mod in (ref_v2w, ref_t2w):
+        mod.parallel_state.is_initialized = lambda: False          # the absent process-group registry: no model parallelism
+    m = ref_v2w.Video2WorldModelRectifiedFlow.__new__(ref_v2w.Video2WorldModelRectifiedFlow)
+    torch.nn.Module.__init__(m)
+    m.config = types.SimpleNamespace(
+        text_encoder_config=None, use_high_sigma_strategy=high_sigma, high_sigma_ratio=0.5, high_sigma_timesteps_min=850,
+        high_sigma_timesteps_max=1000, min_num_conditional_frames=0, max_num_conditional_frames=2,
+        conditional_frames_probs={0: 0.5, 1: 0.25, 2: 0.25}, conditional_frame_timestep=conditional_frame_timestep,
+        denoise_replace_gt_frames=True, state_ch=16, use_kerras_sigma_at_inference=False)
+    torch.manual_seed(0)
+    m.net = lvg.MinimalV1LVGDiT(atten_backend="minimal_a2a", **net_kw)
+    with torch.no_grad():
+        for p in m.net.parameters():
+            if p.abs().max() == 0:
+                p.normal_(0, 0.02)
+    m.net.disable_context_parallel = lambda: None                 # it would create a CUDA stream
+    m.conditioner = ref_cond.Video2WorldConditioner(
+        fps=rc.ReMapkey(input_key="fps", output_key="fps", dropout_rate=0.0),
+        padding_mask=rc.ReMapkey(input_key="padding_mask", output_key="padding_mask", dropout_rate=0.0),
+        text=rc.TextAttr(input_key=["t5_text_embeddings"], dropout_rate=0.2),
+        use_video_condition=rc.BooleanFlag(input_key="fps", output_key="use_video_condition", dropout_rate=0.0))
+    m.rectified_flow = ref_rf.RectifiedFlow(velocity_field=m.net, train_time_distribution="logitnormal", use_dynamic_shift=False, shift=5,
+                                            device=torch.device("cpu"), dtype=torch.float32)
+    m.sample_scheduler = ref_unipc.FlowUniPCMultistepScheduler(num_train_timesteps=1000, shift=1, use_dynamic_shifting=False)
+    m.tokenizer = DummyTokenizer()
+    m.tensor_kwargs = m.tensor_kwargs_fp32 = {"device": "cpu", "dtype": torch.float32}
+    m.input_data_key, m.input_image_key, m.input_caption_key, m.data_parallel_size = "video", "images", "ai_caption", 1
+    m.text_encoder = None
+    return m
+
+
+def _own_v2w_model(ref, net_kw, conditional_frame_timestep=-1.0, high_sigma=False):
+    from cosmos_predict25_b200.models.conditioner import default_video2world_conditioner
+    from cosmos_predict25_b200.models.dit import DiTConfig
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    from cosmos_predict25_b200.models.vae_wan import DummyTokenizer
+    cfg = Video2WorldRFConfig(net=DiTConfig(**net_kw), tokenizer=DummyTokenizer(), conditioner=default_video2world_conditioner(0.2),
+                              precision="float32", state_t=4, shift=5.0, train_time_distribution="logitnormal",
+                              min_num_conditional_frames=0, max_num_conditional_frames=2, conditional_frames_probs={0: 0.5, 1: 0.25, 2: 0.25},
+                              conditional_frame_timestep=conditional_frame_timestep, use_high_sigma_strategy=high_sigma, high_sigma_ratio=0.5,
+                              high_sigma_timesteps_min=850, high_sigma_timesteps_max=1000)
+    m = Video2WorldModelRectifiedFlow(cfg, device=torch.device("cpu"))
+    m.net.load_state_dict(ref.net.state_dict(), strict=True)
+    return m
+
+
+_NET_KW = dict(max_img_h=32, max_img_w=32, max_frames=16, in_channels=16, out_channels=16, patch_spatial=2, patch_temporal=1,
+               concat_padding_mask=True, model_channels=128, num_blocks=2, num_heads=2, crossattn_emb_channels=64,
+               use_crossattn_projection=True, crossattn_proj_in_channels=96, pos_emb_cls="rope3d", use_adaln_lora=True, adaln_lora_dim=32,
+               rope_h_extrapolation_ratio=3.0, rope_w_extrapolation_ratio=3.0, rope_t_extrapolation_ratio=1.0,
+               rope_enable_fps_modulation=False, use_wan_fp32_strategy=True, timestep_scale=0.001)
+
+
+def _batch(seed, B=2):
+    g = torch.Generator().manual_seed(seed)
+    return {"video": torch.randint(0, 256, (B, 3, 13, 32, 32), generator=g, dtype=torch.uint8), "fps": torch.full((B,), 16.0),
+            "t5_text_embeddings": torch.randn(B, 8, 96, generator=g), "neg_t5_text_embeddings": torch.randn(B, 8, 96, generator=g),
+            "padding_mask": torch.zeros(B, 1, 32, 32)}
+
+
+def test_training_step_matches_the_reference_model():
+    """Whole training step (pixels -> tokenizer -> conditioner with dropout -> conditioning frames -> noise / time sampling ->
+    interpolation -> network with frame replacement -> loss) of the reference's Video2World model object and this package's, with
+    the same weights and the same seeds: the same loss, for the plain setting, with a noise level given to conditioning frames, and
+    with the high-noise re-sampling strategy."""
+    import random
+    for kw in (dict(), dict(conditional_frame_timestep=0.1), dict(high_sigma=True)):
+        ref = _reference_v2w_model(_NET_KW, **kw)
+        own = _own_v2w_model(ref, _NET_KW, **kw)
+        for seed in (0, 1, 2):
+            B = 1 if "conditional_frame_timestep" in kw else 2      # the reference's per-frame timestep broadcast holds for one sample
+            random.seed(seed), torch.manual_seed(seed)
+            out_ref, loss_ref = ref.training_step(_batch(10 + seed, B), seed)
+            random.seed(seed), torch.manual_seed(seed)
+            out, loss = own.training_step(_batch(10 + seed, B), seed)
+            assert torch.allclose(out["xt"], out_ref["xt"], atol=1e-5), (kw, seed)
+            assert torch.allclose(out["sigma"].view(-1), out_ref["sigma"].view(-1)), (kw, seed)
+            assert abs(loss.item() - loss_ref.item()) < 2e-5 * max(1.0, abs(loss_ref.item())), (kw, seed, loss.item(), loss_ref.item())
+
+
+def test_sampling_matches_the_reference_model():
+    """Latents sampled by the reference's model object and by this package's from the same conditioning clip, prompt embeddings,
+    weights and seed (UniPC, classifier-free guidance with and without a negative prompt, one and two conditioning frames). The
+    reference evaluates the two guidance branches one after the other, this package in one batch of two."""
+    ref = _reference_v2w_model(_NET_KW)
+    own = _own_v2w_model(ref, _NET_KW)
+    for n_cond, neg, guidance in ((1, True, 3.0), (2, False, 1.5)):
+        b1, b2 = _batch(21, 1), _batch(21, 1)
+        b1["num_conditional_frames"] = b2["num_conditional_frames"] = n_cond
+        with torch.no_grad():
+            want = ref.generate_samples_from_batch(b1, guidance=guidance, seed=7, is_negative_prompt=neg, num_steps=5, shift=5.0)
+            got = own.generate_samples_from_batch(b2, guidance=guidance, seed=7, is_negative_prompt=neg, num_steps=5, shift=5.0)
+        assert got.shape == want.shape == (1, 16, 4, 4, 4)
+        assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), (n_cond, neg, (got - want).abs().max())
