@@ -20,7 +20,8 @@ import numpy as np
 import torch
 
 from .conditioner import DataType
-from .rectified_flow import Text2WorldModelRectifiedFlow, Text2WorldRFConfig, NUM_CONDITIONAL_FRAMES_KEY
+from .rectified_flow import (NUM_CONDITIONAL_FRAMES_KEY, Text2WorldModelRectifiedFlow, Text2WorldRFConfig,
+                             Video2WorldModelRectifiedFlow)
 
 
 # ---- preconditioning ----------------------------------------------------------------------------------------------
@@ -70,7 +71,14 @@ class EDMSDE:
         self.p_mean, self.p_std, self.sigma_max, self.sigma_min = p_mean, p_std, sigma_max, sigma_min
 
     def sample_t(self, batch_size: int, generator: Optional[torch.Generator] = None) -> torch.Tensor:
-        return torch.exp(torch.randn(batch_size, generator=generator) * self.p_std + self.p_mean)
+        """With a torch generator: exp(p_mean + p_std N(0,1)) from it. Without: uniform draws from NumPy's global generator
+        pushed through the inverse normal CDF, like the reference (edm_sde.py:34-39 there), so ``np.random.seed`` reproduces its
+        noise levels."""
+        if generator is not None:
+            return torch.exp(torch.randn(batch_size, generator=generator) * self.p_std + self.p_mean)
+        from statistics import NormalDist
+        dist = NormalDist(mu=self.p_mean, sigma=self.p_std)
+        return torch.exp(torch.tensor([dist.inv_cdf(float(u)) for u in np.random.uniform(size=(batch_size))]))
 
     def marginal_prob(self, x0: torch.Tensor, sigma: torch.Tensor):
         return x0, sigma
@@ -208,7 +216,7 @@ class EDMEulerSampler:
 class HighSigmaStrategy:
     NONE = "none"
     UNIFORM80_2000 = "uniform80_2000"
-    LOGUNIFORM200_100000 = "loguniform200_100000"
+    LOGUNIFORM200_100000 = "LOGUNIFORM200_100000"      # spelled like the reference's value; compared without regard to case
     SHIFT24 = "shift24"
     BALANCED_TWO_HEADS_V1 = "balanced_two_heads_v1"
     HARDCODED_20steps = "hardcoded_20steps"
@@ -216,8 +224,11 @@ class HighSigmaStrategy:
 
 @dataclass
 class EDMConfig(Text2WorldRFConfig):
-    sigma_data: float = 1.0
-    scaling: str = "rectified_flow"          # "edm" | "rectified_flow"
+    sigma_data: float = 0.5                  # 1.0 with the rectified-flow scaling
+    scaling: str = "edm"                     # "edm" | "rectified_flow"
+    denoise_replace_gt_frames: bool = True   # Video2World: the prediction on conditioning frames is their clean latent
+    adjust_video_noise: bool = True          # video batches: noise levels x sqrt(state_t) (more frames share one level)
+    loss_reduce: str = "mean"                # "mean" | "sum" (sum over channels, mean over the rest)
     p_mean: float = 0.0
     p_std: float = 1.0
     sigma_max: float = 80.0
@@ -244,29 +255,30 @@ class DiffusionModel(Text2WorldModelRectifiedFlow):
         self.scaling = (RectifiedFlowScaling(c.sigma_data, c.rectified_flow_t_scaling_factor, c.rectified_flow_loss_weight_uniform)
                         if c.scaling == "rectified_flow" else EDMScaling(c.sigma_data))
         self.sampler = RESSampler()
+        self.sigma_data = c.sigma_data
+        self.video_noise_multiplier = math.sqrt(c.state_t) if c.adjust_video_noise else 1.0
+        assert c.loss_reduce in ("mean", "sum")
+
+    @torch.no_grad()
+    def encode(self, state: torch.Tensor) -> torch.Tensor:
+        return super().encode(state) * self.sigma_data            # latents are kept at the data scale the preconditioning assumes
+
+    @torch.no_grad()
+    def decode(self, latent: torch.Tensor) -> torch.Tensor:
+        return super().decode(latent / self.sigma_data)
+
+    def get_data_and_condition(self, batch: Dict):
+        raw, latent, condition = super().get_data_and_condition(batch)
+        if raw is None:                                            # pre-computed tokenizer latents: same scale as ``encode`` gives
+            latent = latent * self.sigma_data
+        return raw, latent, condition
 
     def draw_training_sigma(self, B: int, is_video: bool) -> torch.Tensor:
+        """[B] noise levels: log-normal, times sqrt(state_t) for video; Video2World models then apply the high-noise strategy
+        (``_high_sigma``)."""
         sigma = self.sde.sample_t(B)
-        c = self.config
-        if is_video and c.high_sigma_strategy != HighSigmaStrategy.NONE:
-            pick = torch.rand(B) < c.high_sigma_ratio
-            if c.high_sigma_strategy == HighSigmaStrategy.UNIFORM80_2000:
-                new = torch.rand(B) * (2000 - 80) + 80
-            elif c.high_sigma_strategy == HighSigmaStrategy.LOGUNIFORM200_100000:
-                new = torch.exp(torch.rand(B) * (math.log(100000) - math.log(200)) + math.log(200))
-            elif c.high_sigma_strategy in (HighSigmaStrategy.SHIFT24, HighSigmaStrategy.BALANCED_TWO_HEADS_V1):
-                t = torch.rand(B).double()
-                t = 24 * t / (1 + 23 * t)
-                new = (t / (1 - t + 1e-12)).float().clamp(max=1e6)
-            elif c.high_sigma_strategy == HighSigmaStrategy.HARDCODED_20steps:
-                grid = torch.tensor(get_rev_ts(0.002, 80.0, 20, 7.0)[:-1], dtype=torch.float32)
-                new = grid[torch.randint(0, len(grid), (B,))]
-            else:
-                raise ValueError(c.high_sigma_strategy)
-            sigma = torch.where(pick, new, sigma)
-            if c.high_sigma_strategy == HighSigmaStrategy.BALANCED_TWO_HEADS_V1:
-                low = torch.rand(B) < c.low_sigma_ratio
-                sigma = torch.where(low & ~pick, torch.rand(B) * (2 - 1e-5) + 1e-5, sigma)
+        if is_video:
+            sigma = sigma * self.video_noise_multiplier
         return sigma
 
     def sigma_loss_weights(self, sigma: torch.Tensor) -> torch.Tensor:
@@ -288,14 +300,17 @@ class DiffusionModel(Text2WorldModelRectifiedFlow):
         _, x0, condition = self.get_data_and_condition(data_batch)
         B = x0.shape[0]
         is_video = condition.data_type == DataType.VIDEO
+        eps = torch.randn(x0.shape, **self.tensor_kwargs_fp32)          # noise first, then the levels: the reference's draw order
         sigma = self.draw_training_sigma(B, is_video).to(**self.tensor_kwargs_fp32)
-        eps = torch.randn_like(x0)
         x0, condition, eps, sigma = self.broadcast_split_for_model_parallelsim(x0, condition, eps, sigma)
         xt = x0 + eps * sigma.view(B, 1, 1, 1, 1)
         x0_pred = self.denoise_edm(xt, sigma, condition)
         w = self.sigma_loss_weights(sigma).view(B, 1, 1, 1, 1)
-        per = (w * (x0_pred - x0) ** 2).mean(dim=list(range(1, x0.ndim)))
-        loss = per.mean() * self.config.loss_scale
+        weighted = w * (x0_pred - x0) ** 2
+        if self.config.loss_reduce == "mean":
+            loss = weighted.mean() * self.config.loss_scale
+        else:
+            loss = weighted.sum(dim=1).mean() * self.config.loss_scale
         return {"x0": x0, "xt": xt, "sigma": sigma, "model_pred": x0_pred, "edm_loss": loss / self.config.loss_scale}, loss
 
     @torch.no_grad()
@@ -339,26 +354,70 @@ class Video2WorldModel(DiffusionModel):
                                                   c.conditional_frames_probs)
         return raw, latent, condition
 
+    def draw_training_sigma(self, B: int, is_video: bool) -> torch.Tensor:
+        """Base levels, then for video batches the high-noise strategy (video2world_model.py:89-146 of the reference; draws in
+        its order): ``uniform80_2000`` / ``loguniform200_100000``: a share ``high_sigma_ratio`` of the samples is re-drawn from
+        that range; ``shift24``: every sample is re-drawn as t / (1 - t) with t = 24 u / (1 + 23 u), then the uniform re-draw;
+        ``balanced_two_heads_v1``: the log-uniform re-draw, then a share ``low_sigma_ratio`` re-drawn uniformly in (1e-5, 2);
+        ``hardcoded_20steps``: every sample from the 20-step sampling grid plus 100000."""
+        sigma = super().draw_training_sigma(B, is_video)
+        c = self.config
+        strat = str(c.high_sigma_strategy).lower()
+        if not is_video or strat == HighSigmaStrategy.NONE:
+            return sigma
+        rand = lambda: torch.rand(sigma.shape)
+        log_lo, log_hi = math.log(200.0), math.log(100000.0)
+        if strat == HighSigmaStrategy.UNIFORM80_2000.lower():
+            pick = rand() < c.high_sigma_ratio
+            sigma = torch.where(pick, rand().type_as(sigma) * 1920 + 80, sigma)
+        elif strat == HighSigmaStrategy.LOGUNIFORM200_100000.lower():
+            pick = rand() < c.high_sigma_ratio
+            sigma = torch.where(pick, (rand().type_as(sigma) * (log_hi - log_lo) + log_lo).exp(), sigma)
+        elif strat == HighSigmaStrategy.SHIFT24.lower():
+            t = rand().double()
+            t = 24 * t / (24 * t + 1 - t)
+            sigma = (t / (1.0 - t)).float()
+            pick = rand() < c.high_sigma_ratio
+            sigma = torch.where(pick, rand().type_as(sigma) * 1920 + 80, sigma)
+        elif strat == HighSigmaStrategy.BALANCED_TWO_HEADS_V1.lower():
+            pick = rand() < c.high_sigma_ratio
+            sigma = torch.where(pick, (rand().type_as(sigma) * (log_hi - log_lo) + log_lo).exp(), sigma)
+            low = rand() < c.low_sigma_ratio
+            sigma = torch.where(low, rand().type_as(sigma) * 2.0 + 0.00001, sigma)
+        elif strat == HighSigmaStrategy.HARDCODED_20steps.lower():
+            grid = torch.cat([torch.tensor([100000.0]), torch.as_tensor(get_rev_ts(self.sde.sigma_min, self.sde.sigma_max, 20, 7.0)).float()])
+            sigma = grid[torch.randint(0, len(grid), sigma.shape)].type_as(sigma)
+        else:
+            raise ValueError(f"High sigma strategy {strat} is not supported")
+        return sigma
+
     def denoise_edm(self, xt, sigma, condition):
+        """x0 prediction with conditioning frames (video2world_model.py:168-247 of the reference): their clean latents, divided by
+        sigma_data (and zeroed when the sample's video-condition flag is off), replace the scaled noisy input; their noise
+        conditioning is c_noise(sigma_conditional); with ``denoise_replace_gt_frames`` their prediction is the clean latent."""
         if condition.data_type != DataType.VIDEO or getattr(condition, "gt_frames", None) is None:
             return super().denoise_edm(xt, sigma, condition)
         B, C, T = xt.shape[:3]
+        xt = xt.float()
+        sig = sigma.view(B, 1, -1, 1, 1).float() if sigma.ndim == 2 else sigma.view(B, 1, 1, 1, 1).float()
+        c_skip, c_out, c_in, c_noise = self.scaling(sig)
         mask = condition.condition_video_input_mask_B_C_T_H_W.type_as(xt)
         gt = condition.gt_frames.type_as(xt)
-        m_B_T = mask.mean(dim=[1, 3, 4])
-        sig_B_T = self.config.sigma_conditional * m_B_T + sigma.view(B, 1).float() * (1 - m_B_T)
-        # conditioning frames enter at their own (tiny) noise level: x = gt / c_in-normalisation handled by per-frame sigma
-        xt = gt * mask + xt * (1 - mask)
-        sig = sig_B_T.view(B, 1, T, 1, 1)
-        c_skip, c_out, c_in, c_noise = self.scaling(sig)
-        net_out = self.net((xt.float() * c_in).to(**self.tensor_kwargs), c_noise.view(B, T),
+        keep = gt / self.config.sigma_data * Video2WorldModelRectifiedFlow._use_flags(condition, B, xt)
+        net_in = keep * mask + xt * c_in * (1 - mask)
+        c_noise_cond = self.scaling(torch.ones_like(sig) * self.config.sigma_conditional)[3]
+        m_T = mask.mean(dim=[1, 3, 4], keepdim=True)
+        c_noise = c_noise_cond * m_T + c_noise * (1 - m_T)
+        net_out = self.net(net_in.to(**self.tensor_kwargs), c_noise.expand(B, 1, T, 1, 1).reshape(B, T),
                            condition_video_input_mask_B_C_T_H_W=mask, **self._net_kwargs(condition)).float()
-        x0 = c_skip * xt.float() + c_out * net_out
-        return gt.float() * mask + x0 * (1 - mask)
+        x0 = c_skip * xt + c_out * net_out
+        if self.config.denoise_replace_gt_frames:
+            x0 = gt * mask + x0 * (1 - mask)
+        return x0
 
     def _prepare_sampling_conditions(self, data_batch, cond, uncond):
         n = data_batch.get(NUM_CONDITIONAL_FRAMES_KEY, 1)
-        _, x0, _ = Text2WorldModelRectifiedFlow.get_data_and_condition(self, data_batch)
+        _, x0, _ = DiffusionModel.get_data_and_condition(self, data_batch)
         x0 = x0.to(**self.tensor_kwargs)
         cond = cond.set_video_condition(x0, 0, 0, num_conditional_frames=n).edit_for_inference(True, n)
         uncond = uncond.set_video_condition(x0, 0, 0, num_conditional_frames=n).edit_for_inference(False, n)

@@ -93,12 +93,12 @@ def test_edm_training_step_and_sampling():
     x = m.generate_samples_from_batch(b, guidance=2.0, num_steps=4)
     assert x.shape == (1, 16, 3, 8, 8) and torch.isfinite(x).all()
     # conditioning frame comes back unchanged
-    assert torch.allclose(x[:, :, 0], b["latents"][:, :, 0], atol=1e-4)
+    assert torch.allclose(x[:, :, 0], b["latents"][:, :, 0] * m.sigma_data, atol=1e-4)      # samples live at the model's data scale
 
 
 def test_high_sigma_strategies():
     for strat in ("uniform80_2000", "loguniform200_100000", "shift24", "balanced_two_heads_v1", "hardcoded_20steps"):
-        m = edm.DiffusionModel(_edm_cfg(high_sigma_strategy=strat, high_sigma_ratio=1.0), device=torch.device("cpu"))
+        m = edm.Video2WorldModel(_edm_cfg(high_sigma_strategy=strat, high_sigma_ratio=1.0), device=torch.device("cpu"))
         s = m.draw_training_sigma(64, True)
         assert torch.isfinite(s).all() and (s > 0).all()
         if strat == "uniform80_2000":

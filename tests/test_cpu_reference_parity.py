@@ -647,3 +647,82 @@ def test_sampling_matches_the_reference_model():
             got = own.generate_samples_from_batch(b2, guidance=guidance, seed=7, is_negative_prompt=neg, num_steps=5, shift=5.0)
         assert got.shape == want.shape == (1, 16, 4, 4, 4)
         assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), (n_cond, neg, (got - want).abs().max())
+
+
+def test_edm_training_step_matches_the_reference_model(monkeypatch):
+    """Noise-level (EDM) parameterised Video2World model of the reference against this package's: same loss for the same seeds with
+    EDM and with rectified-flow preconditioning, the video noise multiplier, latents scaled by sigma_data, conditioning frames
+    with their own noise conditioning, and each high-noise strategy. The reference places its draws with ``device="cuda"``; here
+    those land on the CPU."""
+    import random
+    import types
+    import numpy as np
+    from reference_oracle import (install_diffusers_standins, install_import_time_patches, install_omegaconf_standins,
+                                  reference_network_modules)
+    from cosmos_predict25_b200.models import edm
+    from cosmos_predict25_b200.models.conditioner import default_video2world_conditioner
+    from cosmos_predict25_b200.models.dit import DiTConfig
+    from cosmos_predict25_b200.models.vae_wan import DummyTokenizer
+    install_omegaconf_standins(), install_diffusers_standins(), install_import_time_patches()
+    lvg, _ = reference_network_modules()
+    ref_mod = import_reference("cosmos_predict2._src.predict2.models.video2world_model")
+    ref_t2w = import_reference("cosmos_predict2._src.predict2.models.text2world_model")
+    ref_cond = import_reference("cosmos_predict2._src.predict2.configs.video2world.defaults.conditioner")
+    ref_scale = import_reference("cosmos_predict2._src.common.modules.denoiser_scaling")
+    ref_sde = import_reference("cosmos_predict2._src.common.modules.edm_sde")
+    rc = import_reference("cosmos_predict2._src.predict2.conditioner")
+    for mod in (ref_mod, ref_t2w):
+        mod.parallel_state.is_initialized = lambda: False
+    # device="cuda" in the reference's draws -> the CPU
+    for name in ("randn", "rand", "tensor"):
+        orig = getattr(torch, name)
+        monkeypatch.setattr(torch, name, (lambda f: lambda *a, **k: f(*a, **{**k, "device": "cpu"} if k.get("device") == "cuda" else k))(orig))
+    orig_to = torch.Tensor.to
+    monkeypatch.setattr(torch.Tensor, "to", lambda self, *a, **k: orig_to(self, *a, **({**k, "device": "cpu"} if k.get("device") == "cuda" else k)))
+
+    net_kw = dict(_NET_KW, timestep_scale=1.0)
+    cases = [dict(scaling="edm", sigma_data=0.5, strat="none"), dict(scaling="rectified_flow", sigma_data=1.0, strat="none"),
+             dict(scaling="edm", sigma_data=0.5, strat="uniform80_2000"), dict(scaling="edm", sigma_data=0.5, strat="LOGUNIFORM200_100000"),
+             dict(scaling="rectified_flow", sigma_data=1.0, strat="shift24"), dict(scaling="edm", sigma_data=0.5, strat="balanced_two_heads_v1"),
+             dict(scaling="edm", sigma_data=0.5, strat="hardcoded_20steps")]
+    for case in cases:
+        m = ref_mod.Video2WorldModel.__new__(ref_mod.Video2WorldModel)
+        torch.nn.Module.__init__(m)
+        m.config = types.SimpleNamespace(
+            text_encoder_config=None, scaling=case["scaling"], sigma_data=case["sigma_data"], use_wan_fp32_strategy=False,
+            min_num_conditional_frames=1, max_num_conditional_frames=2, conditional_frames_probs=None, sigma_conditional=0.0001,
+            denoise_replace_gt_frames=True, high_sigma_strategy=case["strat"], high_sigma_ratio=0.5, low_sigma_ratio=0.3, state_t=4)
+        torch.manual_seed(0)
+        m.net = lvg.MinimalV1LVGDiT(atten_backend="minimal_a2a", **net_kw)
+        with torch.no_grad():
+            for p in m.net.parameters():
+                if p.abs().max() == 0:
+                    p.normal_(0, 0.02)
+        m.net.disable_context_parallel = lambda: None
+        m.conditioner = ref_cond.Video2WorldConditioner(
+            fps=rc.ReMapkey(input_key="fps", output_key="fps", dropout_rate=0.0),
+            padding_mask=rc.ReMapkey(input_key="padding_mask", output_key="padding_mask", dropout_rate=0.0),
+            text=rc.TextAttr(input_key=["t5_text_embeddings"], dropout_rate=0.2),
+            use_video_condition=rc.BooleanFlag(input_key="fps", output_key="use_video_condition", dropout_rate=0.0))
+        m.sde = ref_sde.EDMSDE(p_mean=0.0, p_std=1.0, sigma_max=80, sigma_min=0.0002)
+        m.sigma_data = case["sigma_data"]
+        m.scaling = ref_scale.EDMScaling(0.5) if case["scaling"] == "edm" else ref_scale.RectifiedFlowScaling(1.0, 1.0, True)
+        m.tokenizer = DummyTokenizer()
+        m.tensor_kwargs = m.tensor_kwargs_fp32 = {"device": "cpu", "dtype": torch.float32}
+        m.input_data_key, m.input_image_key, m.input_caption_key, m.data_parallel_size = "video", "images", "ai_caption", 1
+        m.loss_reduce, m.loss_scale, m.video_noise_multiplier, m.text_encoder = "mean", 10.0, 2.0, None
+
+        own = edm.Video2WorldModel(edm.EDMConfig(
+            net=DiTConfig(**net_kw), tokenizer=DummyTokenizer(), conditioner=default_video2world_conditioner(0.2), precision="float32",
+            state_t=4, scaling=case["scaling"], sigma_data=case["sigma_data"], p_mean=0.0, p_std=1.0, sigma_max=80.0, sigma_min=0.0002,
+            loss_scale=10.0, adjust_video_noise=True, min_num_conditional_frames=1, max_num_conditional_frames=2, sigma_conditional=0.0001,
+            high_sigma_strategy=case["strat"], high_sigma_ratio=0.5, low_sigma_ratio=0.3), device=torch.device("cpu"))
+        own.net.load_state_dict(m.net.state_dict(), strict=True)
+        for seed in (0, 1):
+            random.seed(seed), np.random.seed(seed), torch.manual_seed(seed)
+            out_ref, loss_ref = m.training_step(_batch(30 + seed), seed)
+            random.seed(seed), np.random.seed(seed), torch.manual_seed(seed)
+            out, loss = own.training_step(_batch(30 + seed), seed)
+            assert torch.allclose(out["sigma"].view(-1), out_ref["sigma"].view(-1), rtol=1e-5), (case, seed, out["sigma"], out_ref["sigma"])
+            assert torch.allclose(out["xt"], out_ref["xt"], rtol=1e-4, atol=1e-4), (case, seed)
+            assert abs(loss.item() - loss_ref.item()) < 1e-4 * max(1.0, abs(loss_ref.item())), (case, seed, loss.item(), loss_ref.item())
