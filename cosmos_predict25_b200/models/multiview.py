@@ -95,9 +95,12 @@ class MultiViewCondition(Video2WorldCondition):
             droppable.remove(pos)
         elif ConditionLocation.ANY_CAM in locs:
             if condition_cam_idx is None:
-                # one camera for the whole batch, drawn from the view-index table
-                t_sel = int(torch.randint(0, state_t, (1,)))
-                condition_cam_idx = int(self.view_indices_B_T[0, t_sel]) if self.view_indices_B_T is not None else 0
+                # a latent frame per sample picks the camera from the view-index table (draws like the reference: one value per
+                # sample; the samples of a batch must agree, their first frames belong to the same view)
+                t_sel = torch.randint(0, state_t, size=(B,))
+                cams = self.view_indices_B_T[torch.arange(B), t_sel]
+                assert (cams == cams[0]).all(), f"the conditioning camera must be the same for all samples, got {cams}"
+                condition_cam_idx = int(cams[0])
             mask[:, :, condition_cam_idx] = 1
             droppable.remove(condition_cam_idx)
         if ConditionLocation.FIRST_RANDOM_N in locs:

@@ -726,3 +726,47 @@ def test_edm_training_step_matches_the_reference_model(monkeypatch):
             assert torch.allclose(out["sigma"].view(-1), out_ref["sigma"].view(-1), rtol=1e-5), (case, seed, out["sigma"], out_ref["sigma"])
             assert torch.allclose(out["xt"], out_ref["xt"], rtol=1e-4, atol=1e-4), (case, seed)
             assert abs(loss.item() - loss_ref.item()) < 1e-4 * max(1.0, abs(loss_ref.item())), (case, seed, loss.item(), loss_ref.item())
+
+
+def test_multiview_condition_matches_the_reference():
+    """Conditioning masks of the multi-camera condition for every location rule (reference camera, any camera, first n frames of
+    every view, their combinations, view dropout), from the same generator states."""
+    import random
+    from reference_oracle import (install_diffusers_standins, install_import_time_patches, install_omegaconf_standins,
+                                  install_transformer_engine_standins)
+    install_omegaconf_standins(), install_diffusers_standins(), install_transformer_engine_standins(), install_import_time_patches()
+    ref = import_reference("cosmos_predict2._src.predict2_multiview.configs.vid2vid.defaults.conditioner")
+    from cosmos_predict25_b200.models import multiview as om
+    B, V, state_t = 2, 3, 4
+    gt = torch.randn(B, 16, V * state_t, 4, 4)
+    views = torch.tensor([[2] * state_t + [0] * state_t + [1] * state_t] * B)
+    base = dict(crossattn_emb=torch.zeros(B, 2, 8), use_video_condition=torch.tensor([True, True]), view_indices_B_T=views,
+                ref_cam_view_idx_sample_position=torch.tensor([1, 1]))
+    L = ref.ConditionLocation
+    cases = [
+        ([L.FIRST_RANDOM_N], ["first_random_n"], dict(num_conditional_frames_per_view=2)),
+        ([L.FIRST_RANDOM_N], ["first_random_n"], dict(random_min_num_conditional_frames_per_view=0, random_max_num_conditional_frames_per_view=3)),
+        ([L.FIRST_RANDOM_N], ["first_random_n"], dict(conditional_frames_probs={0: 0.3, 1: 0.3, 2: 0.4}, random_min_num_conditional_frames_per_view=0,
+                                                      random_max_num_conditional_frames_per_view=2)),
+        ([L.REF_CAM], ["ref_cam"], dict()),
+        ([L.REF_CAM, L.FIRST_RANDOM_N], ["ref_cam", "first_random_n"], dict(num_conditional_frames_per_view=1, view_condition_dropout_max=2)),
+        ([L.ANY_CAM], ["any_cam"], dict(condition_cam_idx=2)),
+        ([L.ANY_CAM], ["any_cam"], dict()),
+        ([L.ANY_CAM, L.FIRST_RANDOM_N], ["any_cam", "first_random_n"], dict(random_min_num_conditional_frames_per_view=1,
+                                                                            random_max_num_conditional_frames_per_view=2, view_condition_dropout_max=1)),
+    ]
+    for ref_locs, own_locs, kw in cases:
+        for seed in (0, 1, 2):
+            random.seed(seed), torch.manual_seed(seed)
+            a = ref.MultiViewCondition(**base).set_video_condition(state_t=state_t, gt_frames=gt, condition_locations=ref.ConditionLocationList(ref_locs), **kw)
+            random.seed(seed), torch.manual_seed(seed)
+            b = om.MultiViewCondition(**base).set_video_condition(state_t=state_t, gt_frames=gt, condition_locations=own_locs, **kw)
+            assert torch.equal(a.condition_video_input_mask_B_C_T_H_W, b.condition_video_input_mask_B_C_T_H_W), (own_locs, kw, seed)
+    a = ref.MultiViewCondition(**base).set_video_condition(state_t=state_t, gt_frames=gt, condition_locations=ref.ConditionLocationList([L.FIRST_RANDOM_N]),
+                                                           num_conditional_frames_per_view=1)
+    b = om.MultiViewCondition(**base).set_video_condition(state_t=state_t, gt_frames=gt, condition_locations=["first_random_n"], num_conditional_frames_per_view=1)
+    for cond_branch in (True, False):
+        ea = a.edit_for_inference(ref.ConditionLocationList([L.FIRST_RANDOM_N]), cond_branch, 2)
+        eb = b.edit_for_inference(["first_random_n"], cond_branch, 2)
+        assert torch.equal(ea.condition_video_input_mask_B_C_T_H_W, eb.condition_video_input_mask_B_C_T_H_W)
+        assert torch.equal(torch.as_tensor(ea.use_video_condition), torch.as_tensor(eb.use_video_condition))
