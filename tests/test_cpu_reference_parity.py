@@ -770,3 +770,86 @@ def test_multiview_condition_matches_the_reference():
         eb = b.edit_for_inference(["first_random_n"], cond_branch, 2)
         assert torch.equal(ea.condition_video_input_mask_B_C_T_H_W, eb.condition_video_input_mask_B_C_T_H_W)
         assert torch.equal(torch.as_tensor(ea.use_video_condition), torch.as_tensor(eb.use_video_condition))
+
+
+def test_multiview_training_step_matches_the_reference_model():
+    """Multi-camera model object of the reference (its network, conditioner, per-view tokenisation, latent view indices) against
+    this package's: the same loss for the same seeds and weights."""
+    import random
+    import types
+    from reference_oracle import (install_diffusers_standins, install_import_time_patches, install_omegaconf_standins,
+                                  install_transformer_engine_standins, reference_network_modules)
+    from cosmos_predict25_b200.models import multiview as om
+    from cosmos_predict25_b200.models.multiview_dit import MultiViewDiTConfig
+    from cosmos_predict25_b200.models.vae_wan import DummyTokenizer
+    install_omegaconf_standins(), install_diffusers_standins(), install_transformer_engine_standins(), install_import_time_patches()
+    mvnet = import_reference("cosmos_predict2._src.predict2_multiview.networks.multiview_dit")
+    reference_network_modules()
+    ref_mod = import_reference("cosmos_predict2._src.predict2_multiview.models.multiview_vid2vid_model_rectified_flow")
+    ref_t2w = import_reference("cosmos_predict2._src.predict2.models.text2world_model_rectified_flow")
+    ref_v2w = import_reference("cosmos_predict2._src.predict2.models.video2world_model_rectified_flow")
+    ref_rf = import_reference("cosmos_predict2._src.predict2.schedulers.rectified_flow")
+    ref_cond = import_reference("cosmos_predict2._src.predict2_multiview.configs.vid2vid.defaults.conditioner")
+    rc = import_reference("cosmos_predict2._src.predict2.conditioner")
+    for mod in (ref_mod, ref_t2w, ref_v2w, mvnet):
+        mod.parallel_state.is_initialized = lambda: False
+    ref_mod.parallel_state.get_context_parallel_group = lambda: None
+    ref_mod.get_process_group_ranks = lambda g: [0]                  # one rank: views are tokenised one after the other
+    V, state_t = 3, 2
+    net_kw = dict(max_img_h=32, max_img_w=32, max_frames=16, in_channels=16, out_channels=16, patch_spatial=2, patch_temporal=1,
+                  concat_padding_mask=True, model_channels=128, num_blocks=2, num_heads=2, crossattn_emb_channels=64,
+                  use_crossattn_projection=False, pos_emb_cls="rope3d", use_adaln_lora=True, adaln_lora_dim=32, rope_h_extrapolation_ratio=3.0,
+                  rope_w_extrapolation_ratio=3.0, rope_t_extrapolation_ratio=1.0, rope_enable_fps_modulation=False, use_wan_fp32_strategy=True,
+                  timestep_scale=0.001, state_t=state_t, n_cameras_emb=4, view_condition_dim=4, concat_view_embedding=True)
+    m = ref_mod.MultiviewVid2VidModelRectifiedFlow.__new__(ref_mod.MultiviewVid2VidModelRectifiedFlow)
+    torch.nn.Module.__init__(m)
+    L = ref_cond.ConditionLocation
+    m.config = types.SimpleNamespace(
+        text_encoder_config=None, use_high_sigma_strategy=False, state_t=state_t, train_sample_views_range=None,
+        condition_locations=ref_cond.ConditionLocationList([L.FIRST_RANDOM_N]), min_num_conditional_frames_per_view=0,
+        max_num_conditional_frames_per_view=1, view_condition_dropout_max=0, conditional_frames_probs=None,
+        conditional_frame_timestep=-1.0, denoise_replace_gt_frames=True)
+    m.state_t = state_t
+    torch.manual_seed(0)
+    m.net = mvnet.MultiViewDiT(atten_backend="minimal_a2a", **net_kw)
+    with torch.no_grad():
+        for p in m.net.parameters():
+            if p.abs().max() == 0:
+                p.normal_(0, 0.02)
+    m.net.disable_context_parallel = lambda: None
+    m.conditioner = ref_cond.MultiViewConditioner(
+        fps=rc.ReMapkey(input_key="fps", output_key="fps", dropout_rate=0.0),
+        padding_mask=rc.ReMapkey(input_key="padding_mask", output_key="padding_mask", dropout_rate=0.0),
+        text=rc.TextAttr(input_key=["t5_text_embeddings"], dropout_rate=0.2),
+        use_video_condition=rc.BooleanFlag(input_key="fps", output_key="use_video_condition", dropout_rate=0.0),
+        view_indices_B_T=rc.ReMapkey(input_key="latent_view_indices_B_T", output_key="view_indices_B_T", dropout_rate=0.0),
+        ref_cam_view_idx_sample_position=rc.ReMapkey(input_key="ref_cam_view_idx_sample_position",
+                                                     output_key="ref_cam_view_idx_sample_position", dropout_rate=0.0))
+    m.rectified_flow = ref_rf.RectifiedFlow(velocity_field=m.net, train_time_distribution="logitnormal", use_dynamic_shift=False, shift=5,
+                                            device=torch.device("cpu"), dtype=torch.float32)
+    m.tokenizer = DummyTokenizer()
+    m.tensor_kwargs = m.tensor_kwargs_fp32 = {"device": "cpu", "dtype": torch.float32}
+    m.input_data_key, m.input_image_key, m.input_caption_key, m.data_parallel_size, m.text_encoder = "video", "images", "ai_caption", 1, None
+
+    own_net_kw = {k: v for k, v in net_kw.items() if k not in ("in_channels", "out_channels", "patch_spatial", "patch_temporal", "concat_padding_mask",
+                                                                "pos_emb_cls", "use_adaln_lora")}
+    own = om.MultiviewVid2VidModelRectifiedFlow(om.MultiviewRFConfig(
+        net=MultiViewDiTConfig(**own_net_kw), tokenizer=DummyTokenizer(), precision="float32", state_t=state_t, shift=5.0,
+        train_time_distribution="logitnormal", condition_locations=["first_random_n"], min_num_conditional_frames_per_view=0,
+        max_num_conditional_frames_per_view=1, text_dropout=0.2), device=torch.device("cpu"))
+    own.net.load_state_dict(m.net.state_dict(), strict=True)
+    fpv = DummyTokenizer().get_pixel_num_frames(state_t)
+
+    def batch(seed):
+        g = torch.Generator().manual_seed(seed)
+        return {"video": torch.randint(0, 256, (1, 3, V * fpv, 32, 32), generator=g, dtype=torch.uint8), "fps": torch.full((1,), 16.0),
+                "t5_text_embeddings": torch.randn(1, V * 512, 64, generator=g), "padding_mask": torch.zeros(1, 1, 32, 32),
+                "view_indices": torch.tensor([2, 0, 1]).repeat_interleave(fpv)[None], "num_video_frames_per_view": torch.tensor(fpv),
+                "sample_n_views": torch.tensor(V), "ref_cam_view_idx_sample_position": torch.tensor([-1])}
+    for seed in (0, 1, 2):
+        random.seed(seed), torch.manual_seed(seed)
+        out_ref, loss_ref = m.training_step(batch(40 + seed), seed)
+        random.seed(seed), torch.manual_seed(seed)
+        out, loss = own.training_step(batch(40 + seed), seed)
+        assert torch.allclose(out["xt"], out_ref["xt"], atol=1e-5), seed
+        assert abs(loss.item() - loss_ref.item()) < 2e-5 * max(1.0, abs(loss_ref.item())), (seed, loss.item(), loss_ref.item())
