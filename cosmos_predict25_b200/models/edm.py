@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from .conditioner import DataType
+from .schedulers import FlowUniPCSolver
 from .rectified_flow import (NUM_CONDITIONAL_FRAMES_KEY, Text2WorldModelRectifiedFlow, Text2WorldRFConfig,
                              Video2WorldModelRectifiedFlow)
 
@@ -227,6 +228,7 @@ class EDMConfig(Text2WorldRFConfig):
     sigma_data: float = 0.5                  # 1.0 with the rectified-flow scaling
     scaling: str = "edm"                     # "edm" | "rectified_flow"
     denoise_replace_gt_frames: bool = True   # Video2World: the prediction on conditioning frames is their clean latent
+    use_flowunipc_scheduler: bool = False    # sample with the flow UniPC solver instead of the noise-level samplers
     adjust_video_noise: bool = True          # video batches: noise levels x sqrt(state_t) (more frames share one level)
     loss_reduce: str = "mean"                # "mean" | "sum" (sum over channels, mean over the rest)
     p_mean: float = 0.0
@@ -316,25 +318,52 @@ class DiffusionModel(Text2WorldModelRectifiedFlow):
     @torch.no_grad()
     def generate_samples_from_batch(self, data_batch: Dict, guidance: float = 1.5, seed: int = 1, state_shape=None,
                                     n_sample=None, is_negative_prompt: bool = False, num_steps: int = 35,
-                                    solver_option: str = "2ab", **kw) -> torch.Tensor:
+                                    solver_option: str = "2ab", x_sigma_max: Optional[torch.Tensor] = None,
+                                    sigma_max: Optional[float] = None, **kw) -> torch.Tensor:
+        """Latents (at the model's data scale) from noise: the multistep / Runge-Kutta sampler over Karras noise levels, or - with
+        ``config.use_flowunipc_scheduler`` - the flow UniPC solver driven through ``denoise_with_velocity`` (text2world_model.py:
+        519-640 of the reference). ``guided_image`` / ``guided_mask`` in the batch pin parts of every prediction."""
         from ..utils.misc import arch_invariant_rand
         self._normalize_video_databatch_inplace(data_batch)
         self._augment_image_dim_inplace(data_batch)
+        is_image = self.is_image_batch(data_batch)
         cond, uncond = self._conditions_for_sampling(data_batch, is_negative_prompt)
-        key = self.config.input_latent_key if self.config.input_latent_key in data_batch else self.config.input_data_key
+        cfg = self.config
+        key = cfg.input_image_key if is_image else (cfg.input_data_key if cfg.input_data_key in data_batch else cfg.input_latent_key)
         n_sample = n_sample or data_batch[key].shape[0]
         if state_shape is None:
-            state_shape = tuple(data_batch[key].shape[1:])
+            if key == cfg.input_latent_key:
+                state_shape = tuple(data_batch[key].shape[1:])
+            else:
+                _T, _H, _W = data_batch[key].shape[-3:]
+                tk = self.tokenizer
+                state_shape = (cfg.state_ch, tk.get_latent_num_frames(_T), _H // tk.spatial_compression_factor, _W // tk.spatial_compression_factor)
         cond, uncond = self._prepare_sampling_conditions(data_batch, cond, uncond)
+        noise = arch_invariant_rand((n_sample,) + tuple(state_shape), torch.float32, self.device_, seed)
+
+        if getattr(cfg, "use_flowunipc_scheduler", False):
+            solver = FlowUniPCSolver(1000, shift=1.0)
+            solver.set_timesteps(num_steps, device="cpu", shift=5.0)
+            x = noise
+            for t in solver.timesteps.tolist():
+                tt = torch.full((n_sample, 1), float(t) / 1000.0, device=x.device)
+                c, u = self.denoise_with_velocity(x, tt, cond), self.denoise_with_velocity(x, tt, uncond)
+                x = solver.step(u + guidance * (c - u), t, x)
+            return x
 
         def x0_fn(x, sigma):
             c = self.denoise_edm(x, sigma, cond)
             u = self.denoise_edm(x, sigma, uncond)
-            return c + guidance * (c - u)
+            x0 = c + guidance * (c - u)
+            if "guided_image" in data_batch:
+                assert "guided_mask" in data_batch, "guided_mask should be in data_batch if guided_image is present"
+                x0 = data_batch["guided_mask"] * data_batch["guided_image"] + (1 - data_batch["guided_mask"]) * x0
+            return x0
 
-        noise = arch_invariant_rand((n_sample,) + tuple(state_shape), torch.float32, self.device_, seed) * self.sde.sigma_max
-        return self.sampler(x0_fn, noise, num_steps=num_steps, sigma_max=self.sde.sigma_max, sigma_min=self.sde.sigma_min,
-                            solver_option=solver_option)
+        if x_sigma_max is None:
+            x_sigma_max = noise * self.sde.sigma_max
+        return self.sampler(x0_fn, x_sigma_max, num_steps=num_steps, sigma_max=self.sde.sigma_max if sigma_max is None else sigma_max,
+                            sigma_min=self.sde.sigma_min, solver_option=solver_option)
 
     def _prepare_sampling_conditions(self, data_batch, cond, uncond):
         return cond, uncond

@@ -649,7 +649,7 @@ def test_sampling_matches_the_reference_model():
         assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), (n_cond, neg, (got - want).abs().max())
 
 
-def test_edm_training_step_matches_the_reference_model(monkeypatch):
+def test_edm_training_step_and_sampling_match_the_reference_model(monkeypatch):
     """Noise-level (EDM) parameterised Video2World model of the reference against this package's: same loss for the same seeds with
     EDM and with rectified-flow preconditioning, the video noise multiplier, latents scaled by sigma_data, conditioning frames
     with their own noise conditioning, and each high-noise strategy. The reference places its draws with ``device="cuda"``; here
@@ -726,6 +726,21 @@ def test_edm_training_step_matches_the_reference_model(monkeypatch):
             assert torch.allclose(out["sigma"].view(-1), out_ref["sigma"].view(-1), rtol=1e-5), (case, seed, out["sigma"], out_ref["sigma"])
             assert torch.allclose(out["xt"], out_ref["xt"], rtol=1e-4, atol=1e-4), (case, seed)
             assert abs(loss.item() - loss_ref.item()) < 1e-4 * max(1.0, abs(loss_ref.item())), (case, seed, loss.item(), loss_ref.item())
+        if case["strat"] != "none":
+            continue
+        # sampling: noise-level sampler ("2ab", "2mid") and the flow UniPC route, guidance with a negative prompt
+        ref_samp = import_reference("cosmos_predict2._src.common.modules.res_sampler")
+        m.sampler = ref_samp.Sampler()
+        m.config.state_ch = 16
+        for flow, solver in ((False, "2ab"), (False, "2mid"), (True, "2ab")):
+            m.config.use_flowunipc_scheduler = own.config.use_flowunipc_scheduler = flow
+            b1, b2 = _batch(50, 1), _batch(50, 1)
+            b1["num_conditional_frames"] = b2["num_conditional_frames"] = 1
+            with torch.no_grad():
+                want = m.generate_samples_from_batch(b1, guidance=2.0, seed=3, is_negative_prompt=True, num_steps=6, solver_option=solver)
+                got = own.generate_samples_from_batch(b2, guidance=2.0, seed=3, is_negative_prompt=True, num_steps=6, solver_option=solver)
+            assert got.shape == want.shape == (1, 16, 4, 4, 4)
+            assert (got - want).abs().max().item() < 5e-4 * max(1.0, want.abs().max().item()), (case, flow, solver, (got - want).abs().max())
 
 
 def test_multiview_condition_matches_the_reference():
