@@ -159,7 +159,8 @@ def test_item_datasets_with_media_and_rank_split(tmp_path):
 
 
 def test_video_decoders_sample_windows_from_an_encoded_clip(tmp_path):
-    """Both shard decoders on a real encoded clip whose frame k has brightness 8 (k mod 30), with one caption chunk per 30 frames:
+    """Both shard decoders on a real encoded clip whose frame k has brightness 40 + 6 (k mod 30) (inside the
+    codec's video range, so no level is clipped), with one caption chunk per 30 frames:
     consecutive window inside one chunk, strided window with the lowered frame rate, clips outside the frame-rate bounds dropped,
     non-video members ignored."""
     cv2 = pytest.importorskip("cv2")
@@ -168,7 +169,7 @@ def test_video_decoders_sample_windows_from_an_encoded_clip(tmp_path):
     path = str(tmp_path / "clip.mp4")
     w = cv2.VideoWriter(path, cv2.VideoWriter_fourcc(*"mp4v"), 24.0, (32, 32))
     for k in range(60):
-        w.write(np.full((32, 32, 3), 8 * (k % 30), np.uint8))
+        w.write(np.full((32, 32, 3), 40 + 6 * (k % 30), np.uint8))
     w.release()
     data = open(path, "rb").read()
     dec = construct_video_decoder("chunked_video_decoder", chunk_size=30, sequence_length=8, min_fps_thres=10, max_fps_thres=60)
@@ -176,14 +177,14 @@ def test_video_decoders_sample_windows_from_an_encoded_clip(tmp_path):
         out = dec("a/clip.mp4", data)
         assert out["video"].shape == (3, 8, 32, 32) and out["video"].dtype == torch.uint8 and out["fps"] == 24 and out["n_orig_video_frames"] == 60
         level = out["video"].float().mean((0, 2, 3))
-        assert torch.allclose(level[1:] - level[:-1], torch.full((7,), 8.0), atol=3.0)              # consecutive frames, one chunk
-        assert abs(level[0].item() - 8 * (out["frame_start"] % 30)) < 4 and out["frame_start"] // 30 == out["chunk_index"]
+        assert torch.allclose(level[1:] - level[:-1], torch.full((7,), 6.0), atol=2.5)              # consecutive frames, one chunk
+        assert abs(level[0].item() - 40 - 6 * (out["frame_start"] % 30)) < 4 and out["frame_start"] // 30 == out["chunk_index"]
     low = construct_video_decoder("chunked_video_decoder_w_lower_fps", chunk_size=30, sequence_length=5, min_fps_thres=4,
                                   max_fps_thres=12)("clip.mp4", data)
     stride = low["frame_indices"][1] - low["frame_indices"][0]
     assert stride in (5, 6) and low["fps"] == 24 / stride and low["frame_indices"][0] // 30 == low["frame_indices"][-1] // 30
     lv = low["video"].float().mean((0, 2, 3))
-    assert torch.allclose(lv[1:] - lv[:-1], torch.full((4,), 8.0 * stride), atol=4.0)
+    assert torch.allclose(lv[1:] - lv[:-1], torch.full((4,), 6.0 * stride), atol=4.0)
     assert construct_video_decoder("chunked_video_decoder", sequence_length=8, min_fps_thres=30, max_fps_thres=60)("clip.mp4", data) is None
     assert dec("a/clip.txt", b"caption") is None
     assert construct_video_decoder("video_naive_bytes")("clip.mp4", data) is data
