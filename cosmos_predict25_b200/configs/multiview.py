@@ -2,8 +2,10 @@
 
 Registers the multiview network / conditioner groups and the experiment names of the reference
 (cosmos_predict2/_src/predict2_multiview/configs/vid2vid/config.py,
-.../experiment/buttercup/buttercup2p5_rectified_flow.py:29-580, .../buttercup2p5_rectified_flow_14b.py) so that the
-checkpoint registry's ``experiment`` strings resolve. The training data groups of the reference (joint Alpamayo / MADS
+.../experiment/buttercup/buttercup2p5_rectified_flow.py:29-580, .../buttercup2p5_rectified_flow_14b.py, and the noise-level
+(predict2.1-era) ones of .../buttercup_predict2_frombase2p1.py:29-225) so that the checkpoint registry's ``experiment`` strings
+resolve, plus the model groups ``ddp_multiview`` / ``fsdp_multiview`` / ``fsdp_rectified_flow_multiview``
+(.../defaults/model.py:29-67). The training data groups of the reference (joint Alpamayo / MADS
 webdataset shards) are replaced by the mock multiview dataset; point ``dataloader_train`` at your own data.
 """
 
@@ -14,7 +16,8 @@ import copy
 from ..data.mock import build_dataloader
 from ..data.multiview_dataset import MockMultiviewLatentDataset
 from ..models.conditioner import BooleanFlag, ReMapkey, TextAttr
-from ..models.multiview import MultiViewConditioner, MultiviewRFConfig, MultiviewVid2VidModelRectifiedFlow
+from ..models.multiview import (MultiViewConditioner, MultiviewRFConfig, MultiviewVid2VidModel, MultiviewVid2VidModelConfig,
+                                MultiviewVid2VidModelRectifiedFlow)
 from ..models.multiview_dit import MultiViewDiTConfig
 from ..models.rectified_flow import EMAConfig
 from ..utils.config import Config, ConfigStore
@@ -57,6 +60,31 @@ def _mv_model(net="cosmos_v1_2B_multiview", tokenizer="wan2pt1_tokenizer", **cfg
               text_dropout=0.2, sharding_transport="peer")
     kw.update(cfg_kw)
     return L(MultiviewVid2VidModelRectifiedFlow)(config=L(MultiviewRFConfig)(**kw))
+
+
+def _mv_edm_model(net="cosmos_v1_2B_multiview", tokenizer="wan2pt1_tokenizer", **cfg_kw):
+    """The noise-level twin with the settings of the base run those experiments start from: rectified-flow preconditioning at
+    sigma_data 1, non-uniform loss weights, noise levels in (0.01, 200), 5 % of the video samples re-drawn log-uniformly in
+    (200, 100000)."""
+    kw = dict(net=copy.deepcopy(cs.get("net", net)),
+              conditioner=copy.deepcopy(cs.get("conditioner", "video_prediction_multiview_conditioner")),
+              tokenizer=copy.deepcopy(cs.get("tokenizer", tokenizer)), ema=L(EMAConfig)(enabled=True, rate=0.1),
+              precision="bfloat16", state_ch=16, state_t=8, resolution="720p", scaling="rectified_flow", sigma_data=1.0,
+              rectified_flow_loss_weight_uniform=False, sigma_max=200.0, sigma_min=0.01, high_sigma_strategy="LOGUNIFORM200_100000",
+              high_sigma_ratio=0.05, min_num_conditional_frames_per_view=0, max_num_conditional_frames_per_view=2,
+              condition_locations=["first_random_n"], conditional_frames_probs={0: 0.5, 1: 0.25, 2: 0.25},
+              online_text_embeddings_as_dict=False, text_dropout=0.2, sharding_transport="peer")
+    kw.update(cfg_kw)
+    kw["net"].update(timestep_scale=1.0)                       # the noise conditioning is c_noise(sigma), not a 0..1000 time
+    return L(MultiviewVid2VidModel)(config=L(MultiviewVid2VidModelConfig)(**kw))
+
+
+cs.store(group="model", package="_global_", name="ddp_multiview",
+         node=dict(trainer=dict(distributed_parallelism="ddp"), model=_mv_edm_model()))
+cs.store(group="model", package="_global_", name="fsdp_multiview",
+         node=dict(trainer=dict(distributed_parallelism="fsdp"), model=_mv_edm_model(fsdp_shard_size=8)))
+cs.store(group="model", package="_global_", name="fsdp_rectified_flow_multiview",
+         node=dict(trainer=dict(distributed_parallelism="fsdp"), model=_mv_model()))
 
 
 def make_config() -> Config:
@@ -112,6 +140,40 @@ _exp("multicamera_video2video_rectified_flow_2b_res_720_fps16_s3_multicam_syncam
      condition_locations=["ref_cam", "first_random_n"])
 _exp("multicamera_video2video_rectified_flow_2b_res_720_fps16_s3_agibot", state_t=24, resolution="720", fps_mod=False,
      condition_locations=["ref_cam", "first_random_n"])
+
+
+
+def _exp_edm(name, lr=2 ** -14.5, **model_kw):
+    node = dict(
+        defaults=[{"override /optimizer": "adamw"}, {"override /scheduler": "lambdalinear"}, {"override /callbacks": "basic"}, "_self_"],
+        job=dict(project="cosmos_predict2_multiview", group="cosmos2_mv", name=name),
+        model=_mv_edm_model(**model_kw),
+        model_parallel=dict(context_parallel_size=8),
+        optimizer=dict(lr=lr, weight_decay=1e-3, betas=(0.9, 0.999)),
+        checkpoint=dict(save_iter=500),
+    )
+    cs.store(group="experiment", package="_global_", name=name, node=node)
+
+
+_R = "buttercup_predict2p1_2b_mv_7views_res720p_fps10_t8_"
+_exp_edm(_R + "frombase2p1iter45k_alpamayo85to29res720p")
+_exp_edm(_R + "frombase2p1iter45k_mads720p")
+_exp_edm(_R + "frombase2p1iter45k_jointalpamayov2mads720p")
+_exp_edm(_R + "from23klr1x_jointalpamayov2mads720p_lr2x", lr=2 ** -13.5)
+_exp_edm(_R + "from42p5k_jointalpamayov2mads720p_multiwindow_multicaptions")
+
+cs.store(group="experiment", package="_global_", name="tiny_multiview_edm_cpu", node=dict(
+    defaults=["_self_"],
+    job=dict(group="tests", name="tiny_multiview_edm_cpu"),
+    model=_mv_edm_model("tiny_multiview", tokenizer="dummy_tokenizer", precision="float32", state_t=2, tokens_per_view=8,
+                        resolution="tiny", sharding_transport="nccl"),
+    dataloader_train=L(build_dataloader)(dataset=L(MockMultiviewLatentDataset)(n_views=3, state_t=2, height=8, width=8, text_dim=256,
+                                                                               text_len=8, length=16), batch_size=1, num_workers=0),
+    optimizer=dict(lr=1e-3),
+    scheduler=dict(warm_up_steps=(0,), f_start=(1.0,)),
+    trainer=dict(max_iter=2, logging_iter=1, callbacks=dict()),
+    checkpoint=dict(save_iter=0),
+))
 
 cs.store(group="experiment", package="_global_", name="tiny_multiview_cpu", node=dict(
     defaults=["_self_"],

@@ -172,14 +172,60 @@ class AbstractEmbModel(nn.Module):
 
 
 class TextAttr(AbstractEmbModel):
-    """Text embedding [B, L, C] -> ``crossattn_emb``; dropped samples become zeros."""
+    """Text embedding [B, L, C] -> ``crossattn_emb``. A dropped sample becomes zeros or, with ``use_empty_string``, the embedding
+    of the empty prompt (a tensor file read once through easy_io, or ``set_empty_string_embeddings``); ``*mask*`` entries are
+    never dropped (conditioner.py:238-289 of the reference)."""
 
-    def __init__(self, input_key="t5_text_embeddings", dropout_rate: float = 0.0, use_empty_string: bool = False):
+    def __init__(self, input_key="t5_text_embeddings", dropout_rate: float = 0.0, use_empty_string: bool = False,
+                 empty_string_embeddings_path: Optional[str] = None, credential_path: Optional[str] = None):
         super().__init__(input_key, "crossattn_emb", dropout_rate)
         self.use_empty_string = use_empty_string
+        self.empty_string_embeddings_path = empty_string_embeddings_path
+        self.credential_path = credential_path
+        self._empty = None
+
+    def set_empty_string_embeddings(self, emb: torch.Tensor) -> None:
+        self._empty = emb
+
+    def _empty_string_embeddings(self) -> torch.Tensor:
+        if self._empty is None:
+            if not self.empty_string_embeddings_path:
+                raise ValueError("use_empty_string needs the empty prompt's embedding: give empty_string_embeddings_path or call "
+                                 "set_empty_string_embeddings")
+            from ..utils.easy_io import easy_io
+            kw = {}
+            if str(self.empty_string_embeddings_path).startswith("s3://"):
+                kw["backend_args"] = {"backend": "s3", "s3_credential_path": self.credential_path}
+            self._empty = easy_io.load(self.empty_string_embeddings_path, **kw)
+        return self._empty
+
+    def random_dropout_input(self, x, dropout_rate=None, key=None):
+        if key is not None and "mask" in key:
+            return x
+        if not self.use_empty_string or x is None:
+            return super().random_dropout_input(x, dropout_rate, key)
+        rate = self.dropout_rate if dropout_rate is None else dropout_rate
+        keep = torch.bernoulli((1.0 - rate) * torch.ones(x.shape[0])).to(x.device).type_as(x).view(-1, *([1] * (x.ndim - 1)))
+        empty = self._empty_string_embeddings().to(dtype=x.dtype, device=x.device).expand(x.shape)
+        return keep * x + (1.0 - keep) * empty
 
     def forward(self, emb: torch.Tensor) -> Dict[str, torch.Tensor]:
         return {"crossattn_emb": emb}
+
+
+class TextAttrEmptyStringDrop(TextAttr):
+    """``TextAttr`` that always replaces a dropped prompt by the empty prompt's embedding (conditioner.py:291-335 of the reference,
+    which reads that embedding from a fixed bucket path; here the path is an argument)."""
+
+    def __init__(self, input_key="t5_text_embeddings", dropout_rate: float = 0.0, empty_string_embeddings_path: Optional[str] = None,
+                 credential_path: Optional[str] = None):
+        super().__init__(input_key, dropout_rate, True, empty_string_embeddings_path, credential_path)
+
+    def _empty_string_embeddings(self) -> torch.Tensor:
+        e = super()._empty_string_embeddings()
+        if isinstance(e, (list, tuple)):
+            e = e[0]
+        return e if e.ndim == 3 else e.unsqueeze(0)
 
 
 class ReMapkey(AbstractEmbModel):

@@ -351,10 +351,10 @@ class DiffusionModel(Text2WorldModelRectifiedFlow):
                 x = solver.step(u + guidance * (c - u), t, x)
             return x
 
+        combine = self._guidance_combiner(data_batch, guidance)
+
         def x0_fn(x, sigma):
-            c = self.denoise_edm(x, sigma, cond)
-            u = self.denoise_edm(x, sigma, uncond)
-            x0 = c + guidance * (c - u)
+            x0 = combine(self.denoise_edm(x, sigma, cond), self.denoise_edm(x, sigma, uncond))
             if "guided_image" in data_batch:
                 assert "guided_mask" in data_batch, "guided_mask should be in data_batch if guided_image is present"
                 x0 = data_batch["guided_mask"] * data_batch["guided_image"] + (1 - data_batch["guided_mask"]) * x0
@@ -367,6 +367,10 @@ class DiffusionModel(Text2WorldModelRectifiedFlow):
 
     def _prepare_sampling_conditions(self, data_batch, cond, uncond):
         return cond, uncond
+
+    def _guidance_combiner(self, data_batch: Dict, guidance: float) -> Callable:
+        """(conditional, unconditional) clean-latent predictions -> the guided one."""
+        return lambda c, u: c + guidance * (c - u)
 
 
 class Video2WorldModel(DiffusionModel):

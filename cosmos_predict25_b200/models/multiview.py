@@ -4,7 +4,9 @@ Parity targets: ``MultiViewCondition`` / ``ConditionLocation`` / ``MultiViewCond
 (cosmos_predict2/_src/predict2_multiview/configs/vid2vid/defaults/conditioner.py:40-420),
 ``MultiviewVid2VidModelRectifiedFlow`` (cosmos_predict2/_src/predict2_multiview/models/multiview_vid2vid_model_rectified_flow.py:59-400:
 per-view VAE encode/decode, view-distributed ``encode_cp``/``decode_cp``, per-view context-parallel split, latent view
-indices, training-time view sub-sampling) and adaptive projected guidance (cosmos_predict2/_src/predict2_multiview/models/cfg.py:17-80).
+indices, training-time view sub-sampling, prompt embeddings computed online per view), its noise-level (EDM-era) twin
+``MultiviewVid2VidModel`` (cosmos_predict2/_src/predict2_multiview/models/multiview_vid2vid_model.py:64-430) and adaptive projected
+guidance (cosmos_predict2/_src/predict2_multiview/models/cfg.py:17-80).
 
 Layout convention everywhere: the V views of a sample are concatenated on the time axis, ``[B, C, V*T, H, W]``.
 """
@@ -20,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..parallel import context_parallel as cp
+from . import edm
 from .conditioner import (BooleanFlag, DataType, GeneralConditioner, ReMapkey, Text2WorldCondition, TextAttr,
                           Video2WorldCondition)
 from .multiview_dit import MultiViewDiT
@@ -211,12 +214,16 @@ class MultiviewRFConfig(Video2WorldRFConfig):
     apg_norm_threshold: float = 7.5
 
 
-class MultiviewVid2VidModelRectifiedFlow(Video2WorldModelRectifiedFlow):
-    def __init__(self, config: MultiviewRFConfig, **kw):
-        if config.conditioner is None:
-            config.conditioner = default_multiview_conditioner(config.text_dropout)
-        super().__init__(config, **kw)
-        self.state_t = config.state_t
+class _MultiviewMixin:
+    """What the rectified-flow model and the noise-level model share: one tokenizer call per view (or one view per rank), view
+    sub-sampling, latent view indices, the per-view context-parallel split and prompt embeddings computed online per view."""
+
+    _plain_model = Text2WorldModelRectifiedFlow      # whose ``get_data_and_condition`` gives (raw, latent, condition) without frames
+    empty_string_text_embeddings: Optional[torch.Tensor] = None
+    neg_text_embeddings: Optional[torch.Tensor] = None
+
+    def _latent_scale(self) -> float:
+        return 1.0
 
     def build_net(self):
         net = MultiViewDiT(self.config.net).to(self.device_)
@@ -246,14 +253,16 @@ class MultiviewVid2VidModelRectifiedFlow(Video2WorldModelRectifiedFlow):
     def encode(self, state: torch.Tensor) -> torch.Tensor:
         V = state.shape[2] // self._pixel_frames_per_view()
         size, _ = cp._size_rank(self.cp_group)
+        k = self._latent_scale()
         if 4 < V <= size:
-            return self._distribute_views(state, V, self.tokenizer.encode)
-        return batch_to_views(self.tokenizer.encode(views_to_batch(state, V)), V)
+            return self._distribute_views(state, V, self.tokenizer.encode) * k
+        return batch_to_views(self.tokenizer.encode(views_to_batch(state, V)), V) * k
 
     @torch.no_grad()
     def decode(self, latent: torch.Tensor) -> torch.Tensor:
         V = latent.shape[2] // self.state_t
         size, _ = cp._size_rank(self.cp_group)
+        latent = latent / self._latent_scale()
         if 4 < V <= size:
             return self._distribute_views(latent, V, self.tokenizer.decode)
         return batch_to_views(self.tokenizer.decode(views_to_batch(latent, V)), V)
@@ -320,7 +329,7 @@ class MultiviewVid2VidModelRectifiedFlow(Video2WorldModelRectifiedFlow):
 
     def get_data_and_condition(self, batch: Dict):
         b = self.with_latent_view_indices(batch)
-        raw, latent, condition = Text2WorldModelRectifiedFlow.get_data_and_condition(self, b)
+        raw, latent, condition = self._plain_model.get_data_and_condition(self, b)
         c = self.config
         condition = condition.set_video_condition(
             state_t=c.state_t, gt_frames=latent.to(**self.tensor_kwargs), condition_locations=c.condition_locations,
@@ -354,18 +363,102 @@ class MultiviewVid2VidModelRectifiedFlow(Video2WorldModelRectifiedFlow):
             t = t.view(t.shape[0] // V, -1)
         return x0, condition, eps, t
 
+    # ---- prompt embeddings computed online -------------------------------------------------------------------------------
+    def compute_empty_and_negative_text_embeddings(self) -> None:
+        """Embeddings of the blank prompt (the filler of views without a caption, and what a dropped prompt becomes) and of the
+        default negative prompt, computed once."""
+        from ..config import DEFAULT_NEGATIVE_PROMPT
+        key = self.config.input_caption_key
+        if self.empty_string_text_embeddings is None:
+            self.empty_string_text_embeddings = self.text_encoder.compute_text_embeddings_online({key: [" "]}, key)
+        if self.neg_text_embeddings is None:
+            self.neg_text_embeddings = self.text_encoder.compute_text_embeddings_online({key: [DEFAULT_NEGATIVE_PROMPT]}, key)
+
+    def compute_text_embeddings_online_multiview(self, batch: Dict) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(prompt, negative prompt, dropped prompt) embeddings ``[B, V L, D]``. One caption per sample: it describes the front
+        camera (``front_cam_view_idx_sample_position``) and every other view gets the blank prompt's embedding. ``V`` captions
+        joined by `` -- `` (batch size 1): one per view, and the negative prompt is repeated for every view."""
+        self.compute_empty_and_negative_text_embeddings()
+        key, cap_key = self.config.input_data_key, self.config.input_caption_key
+        fpv = self._pixel_frames_per_view() if batch.get(IS_PREPROCESSED_KEY) is True else int(batch["num_video_frames_per_view"])
+        B, V = batch[key].shape[0], batch[key].shape[2] // fpv
+        captions = batch[cap_key][0].split(" -- ")
+        assert len(captions) in (1, V), f"Expected 1 or {V} captions, got {len(captions)}"
+        empty, enc = self.empty_string_text_embeddings, self.text_encoder
+        L = empty.shape[1]
+        if len(captions) == 1:
+            front = enc.compute_text_embeddings_online(batch, cap_key)                      # [B, L, D]
+            assert front.shape[1] == L, f"the prompt embedding should have {L} tokens, got {tuple(front.shape)}"
+            pos = empty.clone().repeat(B, V, 1).view(B, V, L, -1)
+            neg = pos.clone()
+            for b in range(B):
+                v = int(batch["front_cam_view_idx_sample_position"][b])
+                pos[b, v] = front[b]
+                neg[b, v] = self.neg_text_embeddings[0]
+            pos, neg = pos.flatten(1, 2), neg.flatten(1, 2)
+        else:
+            if len(batch[cap_key]) != 1:
+                raise NotImplementedError(f"Expected batch size of 1, got {len(batch[cap_key])}")
+            pos = torch.cat([enc.compute_text_embeddings_online({cap_key: [c]}, cap_key) for c in captions], dim=1)
+            neg = self.neg_text_embeddings[:1].repeat(B, V, 1)
+        dropped = empty.clone().repeat(B, V, 1)
+        embedders = getattr(self.conditioner, "embedders", None)
+        text = embedders["text"] if embedders is not None and "text" in embedders else None
+        if not getattr(text, "use_empty_string", False):
+            dropped = dropped * 0.0
+        return pos, neg, dropped
+
+    def inplace_compute_text_embeddings_online(self, batch: Dict) -> None:
+        pos, neg, dropped = self.compute_text_embeddings_online_multiview(batch)
+        if getattr(self.config, "online_text_embeddings_as_dict", False):
+            batch["t5_text_embeddings"] = {"text_embeddings": pos, "dropout_text_embeddings": dropped}
+            batch["neg_t5_text_embeddings"] = {"text_embeddings": neg, "dropout_text_embeddings": dropped}
+        else:
+            batch["t5_text_embeddings"], batch["neg_t5_text_embeddings"] = pos, neg
+        batch["t5_text_mask"] = torch.ones(pos.shape[0], pos.shape[1], device=pos.device)
+
     # ---- sampling -----------------------------------------------------------------------------------------------------
-    def get_velocity_fn_from_batch(self, data_batch: Dict, guidance: float = 1.5, is_negative_prompt: bool = False):
-        b = self.with_latent_view_indices(data_batch)
+    def _multiview_sampling_conditions(self, b: Dict, cond, uncond):
+        """Conditions of the two guidance branches for a batch that carries latent view indices: the clean frames of every view,
+        the inference-time mask, split for context parallelism."""
         n = b.get(NUM_CONDITIONAL_FRAMES_KEY, 1)
-        cond, uncond = self._conditions_for_sampling(b, is_negative_prompt)
-        _, x0, _ = Text2WorldModelRectifiedFlow.get_data_and_condition(self, b)
+        _, x0, _ = self._plain_model.get_data_and_condition(self, b)
         x0 = x0.to(**self.tensor_kwargs)
         locs = self.config.condition_locations
         cond = replace(cond, state_t=self.state_t, gt_frames=x0).edit_for_inference(locs, True, n)
         uncond = replace(uncond, state_t=self.state_t, gt_frames=x0).edit_for_inference(locs, False, n)
         _, cond, _, _ = self.broadcast_split_for_model_parallelsim(x0, cond, None, None)
         _, uncond, _, _ = self.broadcast_split_for_model_parallelsim(x0, uncond, None, None)
+        return cond, uncond
+
+    def _regroup_gathered_views(self, out: torch.Tensor) -> torch.Tensor:
+        size = cp._size_rank(self.cp_group)[0]
+        if size > 1 and self.net.is_context_parallel_enabled:
+            # the gather concatenated rank-major: (rank, view, t) -> (view, rank, t)
+            B, C, T, H, W = out.shape
+            V = T // self.state_t
+            out = out.view(B, C, size, V, self.state_t // size, H, W).transpose(2, 3).reshape(B, C, T, H, W)
+        return out
+
+
+class MultiviewVid2VidModelRectifiedFlow(_MultiviewMixin, Video2WorldModelRectifiedFlow):
+    def __init__(self, config: MultiviewRFConfig, **kw):
+        if config.conditioner is None:
+            config.conditioner = default_multiview_conditioner(config.text_dropout)
+        super().__init__(config, **kw)
+        self.state_t = config.state_t
+        if self.text_encoder is not None and getattr(config, "compute_text_embeddings_online", True):
+            self.compute_empty_and_negative_text_embeddings()
+
+    def training_step(self, data_batch: Dict, iteration: int):
+        if self.text_encoder is not None and "t5_text_embeddings" not in data_batch:
+            self.inplace_compute_text_embeddings_online(data_batch)
+        return super().training_step(data_batch, iteration)
+
+    def get_velocity_fn_from_batch(self, data_batch: Dict, guidance: float = 1.5, is_negative_prompt: bool = False):
+        b = self.with_latent_view_indices(data_batch)
+        cond, uncond = self._conditions_for_sampling(b, is_negative_prompt)
+        cond, uncond = self._multiview_sampling_conditions(b, cond, uncond)
         if not self.config.use_apg:
             return self._batched_cfg_fn(cond, uncond, guidance, t2w_formula=False)
         buf = MomentumBuffer(self.config.apg_momentum)
@@ -379,11 +472,60 @@ class MultiviewVid2VidModelRectifiedFlow(Video2WorldModelRectifiedFlow):
 
     @torch.no_grad()
     def generate_samples_from_batch(self, data_batch: Dict, *args, **kw) -> torch.Tensor:
-        out = super().generate_samples_from_batch(self.with_latent_view_indices(data_batch), *args, **kw)
-        size = cp._size_rank(self.cp_group)[0]
-        if size > 1 and self.net.is_context_parallel_enabled:
-            # the gather concatenated rank-major: (rank, view, t) -> (view, rank, t)
-            B, C, T, H, W = out.shape
-            V = T // self.state_t
-            out = out.view(B, C, size, V, self.state_t // size, H, W).transpose(2, 3).reshape(B, C, T, H, W)
-        return out
+        return self._regroup_gathered_views(super().generate_samples_from_batch(self.with_latent_view_indices(data_batch), *args, **kw))
+
+
+# ---- noise-level (EDM-era) twin ---------------------------------------------------------------------------------------------
+USE_APG_KEY = "use_apg"
+
+
+@dataclass
+class MultiviewVid2VidModelConfig(edm.EDMConfig):
+    min_num_conditional_frames_per_view: int = 1
+    max_num_conditional_frames_per_view: int = 2
+    train_sample_views_range: Optional[Tuple[int, int]] = None
+    condition_locations: List[str] = field(default_factory=list)
+    state_t: int = 8
+    view_condition_dropout_max: int = 0
+    tokens_per_view: int = 512
+    apg_momentum: float = -0.75
+    apg_eta: float = 0.0
+    apg_norm_threshold: float = 7.5
+    online_text_embeddings_as_dict: bool = True
+
+class MultiviewVid2VidModel(_MultiviewMixin, edm.Video2WorldModel):
+    """Multi-camera model on the noise-level (EDM) preconditioning. Sampling guides the clean-latent predictions; a batch with
+    ``use_apg: True`` switches classifier-free guidance for adaptive projected guidance with the configured momentum, eta
+    and norm threshold (the guidance scale is passed to it as given)."""
+
+    _plain_model = edm.DiffusionModel
+
+    def __init__(self, config, **kw):
+        if config.conditioner is None:
+            config.conditioner = default_multiview_conditioner(config.text_dropout)
+        super().__init__(config, **kw)
+        self.state_t = config.state_t
+        if self.text_encoder is not None:
+            self.compute_empty_and_negative_text_embeddings()
+
+    def _latent_scale(self) -> float:
+        return self.sigma_data
+
+    def training_step(self, data_batch: Dict, iteration: int):
+        if self.text_encoder is not None and "t5_text_embeddings" not in data_batch:
+            self.inplace_compute_text_embeddings_online(data_batch)
+        return super().training_step(data_batch, iteration)
+
+    def _prepare_sampling_conditions(self, data_batch, cond, uncond):
+        return self._multiview_sampling_conditions(data_batch, cond, uncond)
+
+    def _guidance_combiner(self, data_batch: Dict, guidance: float) -> Callable:
+        if data_batch.get(USE_APG_KEY) is not True:
+            return super()._guidance_combiner(data_batch, guidance)
+        buf, c = MomentumBuffer(self.config.apg_momentum), self.config
+        return lambda cond_x0, uncond_x0: adaptive_projected_guidance(cond_x0, uncond_x0, guidance, buf, c.apg_eta, c.apg_norm_threshold)
+
+    @torch.no_grad()
+    def generate_samples_from_batch(self, data_batch: Dict, *args, **kw) -> torch.Tensor:
+        return self._regroup_gathered_views(super().generate_samples_from_batch(self.with_latent_view_indices(data_batch), *args, **kw))
+

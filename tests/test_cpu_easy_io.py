@@ -11,7 +11,7 @@ from cosmos_predict25_b200.utils.object_store import ObjectStore
 
 def test_roundtrip_formats(tmp_path):
     objs = {"a.json": {"x": [1, 2], "y": np.float32(1.5)}, "b.yaml": {"k": "v"}, "c.pkl": {"t": (1, 2)}, "d.txt": "hello",
-            "e.jsonl": [{"i": 1}, {"i": 2}], "f.csv": [{"a": "1", "b": "2"}]}
+            "e.jsonl": [{"i": 1}, {"i": 2}], "f.csv": [["a", "b"], ["1", "2"]]}
     for name, obj in objs.items():
         p = str(tmp_path / "sub" / name)
         easy_io.dump(obj, p)

@@ -868,3 +868,126 @@ def test_multiview_training_step_matches_the_reference_model():
         out, loss = own.training_step(batch(40 + seed), seed)
         assert torch.allclose(out["xt"], out_ref["xt"], atol=1e-5), seed
         assert abs(loss.item() - loss_ref.item()) < 2e-5 * max(1.0, abs(loss_ref.item())), (seed, loss.item(), loss_ref.item())
+
+    # sampling: every view's first latent frame given, classifier-free guidance on the other frames (the reference runs the two
+    # guidance branches one after the other and draws the conditioning mask before it overwrites it for inference)
+    ref_unipc = import_reference("cosmos_predict2._src.predict2.models.fm_solvers_unipc")
+    m.sample_scheduler = ref_unipc.FlowUniPCMultistepScheduler(num_train_timesteps=1000, shift=1, use_dynamic_shifting=False)
+    m.config.state_ch, m.config.use_kerras_sigma_at_inference = 16, False
+    shape = (16, V * state_t, 4, 4)                                  # callers pass the shape of the tokenised views
+    for n_cond, guidance in ((1, 2.0), (0, 0.5)):
+        b1, b2 = batch(50), batch(50)
+        b1["num_conditional_frames"] = b2["num_conditional_frames"] = n_cond
+        with torch.no_grad():
+            random.seed(3), torch.manual_seed(3)
+            want = m.generate_samples_from_batch(b1, guidance=guidance, seed=11, state_shape=shape, num_steps=4, shift=5.0)
+            random.seed(3), torch.manual_seed(3)
+            got = own.generate_samples_from_batch(b2, guidance=guidance, seed=11, state_shape=shape, num_steps=4, shift=5.0)
+        assert got.shape == want.shape == (1, 16, V * state_t, 4, 4)
+        assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item()), (n_cond, (got - want).abs().max())
+
+
+def test_noise_level_multiview_model_matches_the_reference_model(monkeypatch):
+    """The reference's EDM-era multi-camera model object against this package's: training loss, and sampling with classifier-free
+    and with adaptive projected guidance (requested through the batch)."""
+    import random
+    import types
+    import numpy as np
+    from reference_oracle import (install_diffusers_standins, install_import_time_patches, install_omegaconf_standins,
+                                  install_transformer_engine_standins, reference_network_modules)
+    from cosmos_predict25_b200.models import multiview as om
+    from cosmos_predict25_b200.models.multiview_dit import MultiViewDiTConfig
+    from cosmos_predict25_b200.models.vae_wan import DummyTokenizer
+    install_omegaconf_standins(), install_diffusers_standins(), install_transformer_engine_standins(), install_import_time_patches()
+    mvnet = import_reference("cosmos_predict2._src.predict2_multiview.networks.multiview_dit")
+    reference_network_modules()
+    ref_mod = import_reference("cosmos_predict2._src.predict2_multiview.models.multiview_vid2vid_model")
+    ref_v2w = import_reference("cosmos_predict2._src.predict2.models.video2world_model")
+    ref_t2w = import_reference("cosmos_predict2._src.predict2.models.text2world_model")
+    ref_cond = import_reference("cosmos_predict2._src.predict2_multiview.configs.vid2vid.defaults.conditioner")
+    ref_scale = import_reference("cosmos_predict2._src.common.modules.denoiser_scaling")
+    ref_sde = import_reference("cosmos_predict2._src.common.modules.edm_sde")
+    ref_samp = import_reference("cosmos_predict2._src.common.modules.res_sampler")
+    rc = import_reference("cosmos_predict2._src.predict2.conditioner")
+    for mod in (ref_mod, ref_v2w, ref_t2w, mvnet):
+        mod.parallel_state.is_initialized = lambda: False
+    for name in ("randn", "rand", "tensor"):                         # device="cuda" in the reference's draws -> the CPU
+        orig = getattr(torch, name)
+        monkeypatch.setattr(torch, name, (lambda f: lambda *a, **k: f(*a, **{**k, "device": "cpu"} if k.get("device") == "cuda" else k))(orig))
+    orig_to = torch.Tensor.to
+    monkeypatch.setattr(torch.Tensor, "to", lambda self, *a, **k: orig_to(self, *a, **({**k, "device": "cpu"} if k.get("device") == "cuda" else k)))
+    V, state_t = 3, 2
+    net_kw = dict(max_img_h=32, max_img_w=32, max_frames=16, in_channels=16, out_channels=16, patch_spatial=2, patch_temporal=1,
+                  concat_padding_mask=True, model_channels=128, num_blocks=2, num_heads=2, crossattn_emb_channels=64,
+                  use_crossattn_projection=False, pos_emb_cls="rope3d", use_adaln_lora=True, adaln_lora_dim=32, rope_h_extrapolation_ratio=3.0,
+                  rope_w_extrapolation_ratio=3.0, rope_t_extrapolation_ratio=1.0, rope_enable_fps_modulation=False, use_wan_fp32_strategy=False,
+                  timestep_scale=1.0, state_t=state_t, n_cameras_emb=4, view_condition_dim=4, concat_view_embedding=True)
+    m = ref_mod.MultiviewVid2VidModel.__new__(ref_mod.MultiviewVid2VidModel)
+    torch.nn.Module.__init__(m)
+    L = ref_cond.ConditionLocation
+    m.config = types.SimpleNamespace(
+        text_encoder_config=None, scaling="edm", sigma_data=0.5, use_wan_fp32_strategy=False, state_t=state_t, state_ch=16,
+        train_sample_views_range=None, condition_locations=ref_cond.ConditionLocationList([L.FIRST_RANDOM_N]),
+        min_num_conditional_frames_per_view=0, max_num_conditional_frames_per_view=1, view_condition_dropout_max=0,
+        conditional_frames_probs=None, sigma_conditional=0.0001, denoise_replace_gt_frames=True, high_sigma_strategy="none",
+        high_sigma_ratio=0.05, low_sigma_ratio=0.05, apg_momentum=-0.75, apg_eta=0.0, apg_norm_threshold=7.5, use_flowunipc_scheduler=False)
+    m.state_t = state_t
+    torch.manual_seed(0)
+    m.net = mvnet.MultiViewDiT(atten_backend="minimal_a2a", **net_kw)
+    with torch.no_grad():
+        for p in m.net.parameters():
+            if p.abs().max() == 0:
+                p.normal_(0, 0.02)
+    m.net.disable_context_parallel = lambda: None
+    m.conditioner = ref_cond.MultiViewConditioner(
+        fps=rc.ReMapkey(input_key="fps", output_key="fps", dropout_rate=0.0),
+        padding_mask=rc.ReMapkey(input_key="padding_mask", output_key="padding_mask", dropout_rate=0.0),
+        text=rc.TextAttr(input_key=["t5_text_embeddings"], dropout_rate=0.2),
+        use_video_condition=rc.BooleanFlag(input_key="fps", output_key="use_video_condition", dropout_rate=0.0),
+        view_indices_B_T=rc.ReMapkey(input_key="latent_view_indices_B_T", output_key="view_indices_B_T", dropout_rate=0.0),
+        ref_cam_view_idx_sample_position=rc.ReMapkey(input_key="ref_cam_view_idx_sample_position",
+                                                     output_key="ref_cam_view_idx_sample_position", dropout_rate=0.0))
+    m.sde = ref_sde.EDMSDE(p_mean=0.0, p_std=1.0, sigma_max=80, sigma_min=0.0002)
+    m.sigma_data, m.scaling, m.sampler = 0.5, ref_scale.EDMScaling(0.5), ref_samp.Sampler()
+    m.tokenizer = DummyTokenizer()
+    m.tensor_kwargs = m.tensor_kwargs_fp32 = {"device": "cpu", "dtype": torch.float32}
+    m.input_data_key, m.input_image_key, m.input_caption_key, m.data_parallel_size = "video", "images", "ai_caption", 1
+    m.loss_reduce, m.loss_scale, m.video_noise_multiplier, m.text_encoder = "mean", 10.0, state_t ** 0.5, None
+
+    own_net_kw = {k: v for k, v in net_kw.items() if k not in ("in_channels", "out_channels", "patch_spatial", "patch_temporal", "concat_padding_mask",
+                                                                "pos_emb_cls", "use_adaln_lora")}
+    own = om.MultiviewVid2VidModel(om.MultiviewVid2VidModelConfig(
+        net=MultiViewDiTConfig(**own_net_kw), tokenizer=DummyTokenizer(), precision="float32", state_t=state_t, scaling="edm", sigma_data=0.5,
+        p_mean=0.0, p_std=1.0, sigma_max=80.0, sigma_min=0.0002, loss_scale=10.0, adjust_video_noise=True, sigma_conditional=0.0001,
+        condition_locations=["first_random_n"], min_num_conditional_frames_per_view=0, max_num_conditional_frames_per_view=1,
+        text_dropout=0.2), device=torch.device("cpu"))
+    own.net.load_state_dict(m.net.state_dict(), strict=True)
+    fpv = DummyTokenizer().get_pixel_num_frames(state_t)
+
+    def batch(seed):
+        g = torch.Generator().manual_seed(seed)
+        return {"video": torch.randint(0, 256, (1, 3, V * fpv, 32, 32), generator=g, dtype=torch.uint8), "fps": torch.full((1,), 16.0),
+                "t5_text_embeddings": torch.randn(1, V * 512, 64, generator=g), "padding_mask": torch.zeros(1, 1, 32, 32),
+                "view_indices": torch.tensor([2, 0, 1]).repeat_interleave(fpv)[None], "num_video_frames_per_view": torch.tensor(fpv),
+                "sample_n_views": torch.tensor(V), "ref_cam_view_idx_sample_position": torch.tensor([-1])}
+    for seed in (0, 1):
+        random.seed(seed), np.random.seed(seed), torch.manual_seed(seed)
+        out_ref, loss_ref = m.training_step(batch(60 + seed), seed)
+        random.seed(seed), np.random.seed(seed), torch.manual_seed(seed)
+        out, loss = own.training_step(batch(60 + seed), seed)
+        assert torch.allclose(out["xt"], out_ref["xt"], rtol=1e-4, atol=1e-4), seed
+        assert abs(loss.item() - loss_ref.item()) < 1e-4 * max(1.0, abs(loss_ref.item())), (seed, loss.item(), loss_ref.item())
+    shape = (16, V * state_t, 4, 4)
+    for apg in (False, True):
+        b1, b2 = batch(70), batch(70)
+        for b in (b1, b2):
+            b["num_conditional_frames"] = 1
+            if apg:
+                b["use_apg"] = True
+        with torch.no_grad():
+            random.seed(3), torch.manual_seed(3)
+            want = m.generate_samples_from_batch(b1, guidance=2.5, seed=4, state_shape=shape, num_steps=5)
+            random.seed(3), torch.manual_seed(3)
+            got = own.generate_samples_from_batch(b2, guidance=2.5, seed=4, state_shape=shape, num_steps=5)
+        assert got.shape == want.shape == (1,) + shape
+        assert (got - want).abs().max().item() < 5e-4 * max(1.0, want.abs().max().item()), (apg, (got - want).abs().max())
