@@ -313,7 +313,10 @@ class DiffusionModel(Text2WorldModelRectifiedFlow):
             loss = weighted.mean() * self.config.loss_scale
         else:
             loss = weighted.sum(dim=1).mean() * self.config.loss_scale
-        return {"x0": x0, "xt": xt, "sigma": sigma, "model_pred": x0_pred, "edm_loss": loss / self.config.loss_scale}, loss
+        out = {"x0": x0, "xt": xt, "sigma": sigma, "weights_per_sigma": w.view(B, -1), "condition": condition, "model_pred": x0_pred,
+               "mse_loss": ((x0_pred - x0) ** 2).mean().detach(), "edm_loss": weighted.mean().detach(),
+               "edm_loss_per_frame": weighted.detach().mean(dim=[1, 3, 4])}        # [B, T]: what the per-frame analysis reads
+        return out, loss
 
     @torch.no_grad()
     def generate_samples_from_batch(self, data_batch: Dict, guidance: float = 1.5, seed: int = 1, state_shape=None,

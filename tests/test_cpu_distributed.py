@@ -733,3 +733,36 @@ def _network_jvp_under_cp(rank, world, tmp):
 
 def test_network_jvp_under_context_parallel():
     run_distributed("_network_jvp_under_cp", world=2)
+
+
+# ------------------------------------------------------------------------------------------------
+def _sigma_loss_analysis(rank, world, tmp):
+    """Ranks hold different numbers of rows (rank 1 has image rows only on some steps): rank 0's record covers all of them."""
+    import json
+    import types
+    from cosmos_predict25_b200.trainer.analysis_callbacks import SigmaLossAnalysisPerFrame
+    out_dir = os.path.join(tmp, "run")
+    cb = SigmaLossAnalysisPerFrame(logging_iter_multipler=1, logging_viz_iter_multipler=2, save_dir=os.path.join(tmp, "dump"))
+    cb.config = types.SimpleNamespace(trainer=types.SimpleNamespace(logging_iter=2), output_dir=out_dir)
+    model = types.SimpleNamespace(is_image_batch=lambda b: b["image"])
+    g = torch.Generator().manual_seed(rank)
+    rows = {0: 2, 1: 3}[rank]
+    for it in (1, 2, 3, 4):
+        image = rank == 1 and it == 3                      # only rank 1 ever sees an image batch
+        T = 1 if image else 4
+        out = {"sigma": torch.rand(rows, 1, generator=g) + 0.1, "edm_loss_per_frame": torch.rand(rows, T, generator=g)}
+        cb.on_training_step_end(model, {"image": image}, out, None, it)
+    if rank == 0:
+        recs = [json.loads(l) for l in open(os.path.join(out_dir, "sigma_loss_analysis.jsonl"))]
+        assert [r["iteration"] for r in recs] == [2, 4]
+        assert recs[0]["sigma_loss_video/total_samples"] == 2 * (2 + 3)          # two steps x both ranks' rows
+        assert recs[1]["sigma_loss_video/total_samples"] == 2 * 2 + 3 and recs[1]["sigma_loss_image/total_samples"] == 3
+        assert "sigma_loss_video/frame_3/loss_q3" in recs[0] and "sigma_loss_video/frame_0/loss_by_sigma_bin" not in recs[0]
+        bins = recs[1]["sigma_loss_video/frame_0/loss_by_sigma_bin"]
+        assert sum(b["count"] for b in bins) == 7 and "sigma_loss_image/loss_mean" in recs[1]
+        assert sorted(os.listdir(os.path.join(tmp, "dump"))) == ["sigma_loss_image_Iter000000004.pkl", "sigma_loss_video_Iter000000002.pkl",
+                                                                 "sigma_loss_video_Iter000000004.pkl"]
+
+
+def test_sigma_loss_analysis_gathers_uneven_ranks():
+    run_distributed("_sigma_loss_analysis", world=2)

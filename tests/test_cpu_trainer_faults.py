@@ -157,3 +157,34 @@ def test_arena_guard_words_catch_an_overrun():
     plain.check_canaries()
     with pytest.raises(MemoryError):
         plain.alloc(1024, torch.float32)
+
+
+def test_sigma_loss_analysis_on_the_noise_level_model(tmp_path):
+    """One process: the EDM-era model's training output feeds the per-frame analysis; statistics match a direct computation; the
+    placeholder callbacks accept the real ones' arguments and do nothing."""
+    import json
+    import types
+    from cosmos_predict25_b200.models import edm
+    from cosmos_predict25_b200.models.dit import NET_PRESETS
+    from cosmos_predict25_b200.trainer.analysis_callbacks import (DummyFrameLossLog, DummySigmaLossAnalysisPerFrame,
+                                                                  SigmaLossAnalysisPerFrame, normal_quantile_bins)
+    torch.manual_seed(0)
+    m = edm.Video2WorldModel(edm.EDMConfig(net=NET_PRESETS["tiny"](), precision="float32"), device=torch.device("cpu"))
+    net = NET_PRESETS["tiny"]()
+    d = net.crossattn_proj_in_channels if net.use_crossattn_projection else net.crossattn_emb_channels
+    batch = {"latents": torch.randn(2, 16, 3, 8, 8), "t5_text_embeddings": torch.randn(2, 8, d), "fps": torch.full((2,), 16.0),
+             "padding_mask": torch.zeros(2, 1, 8, 8)}
+    cb = SigmaLossAnalysisPerFrame()
+    cb.config = types.SimpleNamespace(trainer=types.SimpleNamespace(logging_iter=1), output_dir=str(tmp_path))
+    out, loss = m.training_step(batch, 1)
+    assert out["edm_loss_per_frame"].shape == (2, 3) and out["weights_per_sigma"].shape == (2, 1)
+    cb.on_training_step_end(m, batch, out, loss, 1)
+    rec = json.loads(open(tmp_path / "sigma_loss_analysis.jsonl").read())
+    lf = out["edm_loss_per_frame"].to(torch.bfloat16).float()
+    assert rec["sigma_loss_video/total_samples"] == 2
+    assert abs(rec["sigma_loss_video/frame_1/loss_mean"] - lf[:, 1].mean().item()) < 1e-6
+    assert abs(rec["sigma_loss_video/frame_2/sigma_log_mean"] - out["sigma"].to(torch.bfloat16).float().log().mean().item()) < 1e-6
+    edges = normal_quantile_bins()
+    assert len(edges) == 11 and bool((edges[1:] > edges[:-1]).all()) and abs(edges[5].item() - 1.0) < 1e-6
+    for dummy in (DummyFrameLossLog(2, 4, True), DummySigmaLossAnalysisPerFrame(2, 4, True)):
+        assert dummy.on_training_step_end(m, batch, out, loss, 1) is None
