@@ -68,7 +68,7 @@ class PtCheckpointer:
         cpu = lambda sd: {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in sd.items()}
         parts = {"model": cpu(model.state_dict()), "optim": cpu(_optim_state(optimizer)),
                  "scheduler": scheduler.state_dict() if scheduler is not None else {}}
-        trainer_state = {"iteration": iteration, "grad_scaler": {}}
+        trainer_state = {"iteration": iteration, "grad_scaler": grad_scaler.state_dict() if grad_scaler is not None else {}}
 
         def work():
             if _rank() == 0:
@@ -103,7 +103,10 @@ class PtCheckpointer:
         if "optim" in resume and optimizer is not None and os.path.exists(base + "_optim.pt"):
             optimizer.load_state_dict(torch.load(base + "_optim.pt", map_location="cpu", weights_only=False))
         if "trainer" in resume and os.path.exists(base + ".pt") and os.path.exists(base + "_model.pt"):
-            iteration = int(torch.load(base + ".pt", map_location="cpu", weights_only=False)["iteration"])
+            trainer_state = torch.load(base + ".pt", map_location="cpu", weights_only=False)
+            iteration = int(trainer_state["iteration"])
+            if grad_scaler is not None and trainer_state.get("grad_scaler"):
+                grad_scaler.load_state_dict(trainer_state["grad_scaler"])
         if "scheduler" in resume and scheduler is not None and os.path.exists(base + "_scheduler.pt"):
             scheduler.load_state_dict(torch.load(base + "_scheduler.pt", map_location="cpu", weights_only=False))
             if iteration:

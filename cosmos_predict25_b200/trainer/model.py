@@ -12,6 +12,12 @@ import torch
 class ImaginaireModel(torch.nn.Module):
     def init_optimizer_scheduler(self, optimizer_config, scheduler_config):
         """(optimizer, scheduler) for this model's trainable parameters."""
+        from ..utils.lazy_config import instantiate, is_lazy
+        if is_lazy(optimizer_config):
+            # the reference's form: lazy calls whose ``params`` / ``optimizer`` arguments are filled in here
+            # (imaginaire/model.py:40-56 there)
+            optimizer = instantiate(optimizer_config, params=[p for p in self.parameters() if p.requires_grad])
+            return optimizer, instantiate(scheduler_config, optimizer=optimizer)
         from .optim import build_scheduler
         opt = torch.optim.AdamW([p for p in self.parameters() if p.requires_grad], lr=optimizer_config.lr, betas=tuple(optimizer_config.betas),
                                 eps=optimizer_config.eps, weight_decay=optimizer_config.weight_decay)

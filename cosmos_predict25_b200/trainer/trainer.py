@@ -97,7 +97,9 @@ class Trainer:
         batch = self.to_device(batch)
         self.callbacks.on_training_step_start(model, batch, iteration=self.iteration)
         last_micro = (self.grad_accum_count + 1) == cfg.grad_accum_iter
-        model.engine.set_requires_gradient_sync(last_micro)
+        engine = getattr(model, "engine", None)        # the sharded engine of the video models; a plain module has none
+        if engine is not None:
+            engine.set_requires_gradient_sync(last_micro)
         with self.timer("forward"):
             out, loss = model.training_step(batch, self.iteration)
         with self.timer("backward"):
@@ -106,11 +108,14 @@ class Trainer:
         if last_micro:
             with self.timer("optimizer_step"):
                 self.callbacks.on_before_optimizer_step(model, self.optimizer, self.scheduler, iteration=self.iteration)
-                self.optimizer.ema_beta = model.ema_beta(self.iteration + 1) if model.config.ema.enabled else None
+                if engine is not None:
+                    self.optimizer.ema_beta = model.ema_beta(self.iteration + 1) if model.config.ema.enabled else None
                 self.optimizer.step()
                 self.scheduler.step()
                 self.callbacks.on_before_zero_grad(model, self.optimizer, self.scheduler, iteration=self.iteration)
                 model.on_before_zero_grad(self.optimizer, self.scheduler, iteration=self.iteration)
+                if engine is None:
+                    self.optimizer.zero_grad(set_to_none=True)   # the engine's optimizer kernel clears its gradients itself
             self.grad_accum_count = 0
             self.iteration += 1
         if last_micro and cfg.logging_iter and self.iteration % cfg.logging_iter == 0:
@@ -201,3 +206,53 @@ class Trainer:
 def _timeout_handler(signum, frame):
     """Watchdog: the alarm is re-armed after every successful iteration; firing means a hung step."""
     raise TimeoutError("training step exceeded trainer.timeout_period seconds")
+
+
+class ImaginaireTrainer:
+    """The reference's entry object: built from the WHOLE config, then ``train(model, dataloader_train, dataloader_val)``
+    (cosmos_predict2/_src/imaginaire/trainer.py:58-150). Construction joins the process group (NCCL on GPUs, gloo without),
+    seeds every generator per rank, creates the job's output directory, the callback bus from ``config.trainer.callbacks`` and the
+    checkpointer from ``config.checkpoint.type`` (the legacy ``.pt`` checkpointer when none is named). ``train`` hands over to
+    ``Trainer``, the loop of this package; a model that lacks the video models' device attribute gets it from its parameters."""
+
+    def __init__(self, config):
+        from ..utils import distributed
+        from ..utils.lazy_config import _locate, instantiate
+        self.config = config
+        distributed.init()
+        t = config["trainer"]
+        misc.set_random_seed(t.get("seed", 0), by_rank=True)
+        self.output_dir = config.job_path_local
+        os.makedirs(self.output_dir, exist_ok=True)
+        cbs = [instantiate(v) for v in (t.get("callbacks") or {}).values() if v is not None]
+        self.callbacks = CallBackGroup(cbs, trainer=self, config=config)
+        kind = config["checkpoint"].get("type")
+        if kind:
+            cls = _locate(kind) if isinstance(kind, str) else kind
+            self.checkpointer = cls() if cls.__name__ == "DummyCheckpointer" else cls(config["checkpoint"], self.output_dir, self.callbacks)
+        else:
+            from ..checkpoint.ddp import Checkpointer
+            self.checkpointer = Checkpointer(config["checkpoint"], self.output_dir, self.callbacks)
+        self.training_timer = misc.TrainingTimer()
+
+    def _trainer_config(self) -> TrainerConfig:
+        t, c = self.config["trainer"], self.config["checkpoint"]
+        timeout = t.get("timeout_period", 0)
+        return TrainerConfig(max_iter=t["max_iter"], grad_accum_iter=t.get("grad_accum_iter", 1), logging_iter=t["logging_iter"],
+                             validation_iter=t.get("validation_iter", 0), max_val_iter=t.get("max_val_iter"),
+                             save_iter=c.get("save_iter", 0), seed=t.get("seed", 0), timeout_period=timeout if timeout < 10 ** 8 else 0,
+                             run_validation=t.get("run_validation", False), distributed_parallelism=t.get("distributed_parallelism", "ddp"),
+                             cudnn_deterministic=(t.get("cudnn") or {}).get("deterministic", False), output_dir=self.output_dir)
+
+    def train(self, model, dataloader_train, dataloader_val=None) -> None:
+        from ..utils.lazy_config import is_lazy, instantiate
+        if not hasattr(model, "device_"):
+            p = next(model.parameters(), None)
+            model.device_ = p.device if p is not None else torch.device("cpu")
+        opt, sch = self.config.get("optimizer"), self.config.get("scheduler")
+        opt = opt if is_lazy(opt) else instantiate(opt)
+        sch = sch if is_lazy(sch) else instantiate(sch)
+        inner = Trainer(self._trainer_config(), model, opt, sch, list(self.callbacks._callbacks), self.checkpointer)
+        self.inner = inner
+        model.train()
+        inner.train(dataloader_train, dataloader_val)

@@ -31,6 +31,34 @@ class ObjectStoreConfig:
     bucket: str = ""
 
 
+class JobConfig(LazyDict):
+    """Where a run writes: ``<project>/<group>/<name>`` under the output root (imaginaire/config.py:104-166 of the reference)."""
+
+    def __init__(self, project: str = "", group: str = "", name: str = "", wandb_mode: str = "offline", **extra):
+        super().__init__(project=project, group=group, name=name, wandb_mode=wandb_mode, **extra)
+
+    @property
+    def path(self) -> str:
+        return os.path.join(self["project"], self["group"], self["name"])
+
+    @property
+    def path_local(self) -> str:
+        return os.path.join(os.environ.get("IMAGINAIRE_OUTPUT_ROOT", "/tmp/imaginaire4-output"), self.path)
+
+
+class CheckpointConfig(LazyDict):
+    """Settings of the trainer's checkpointer (imaginaire/config.py:284-330 of the reference); the registry of released
+    checkpoints has its own ``CheckpointConfig`` in ``utils/checkpoint_db.py``."""
+
+    def __init__(self, **kw):
+        base = dict(type=None, dcp_async_mode_enabled=False, save_to_object_store=ObjectStoreConfig(),
+                    load_from_object_store=ObjectStoreConfig(), save_iter=999999999, load_path="", load_training_state=False,
+                    only_load_scheduler_state=False, strict_resume=True, keys_not_to_resume=[], load_ema_to_reg=False,
+                    dcp_allow_mismatched_size=False, broadcast_via_filesystem=False, verbose=True)
+        base.update(kw)
+        super().__init__(**base)
+
+
 GROUP_PATHS = {
     "model": "model", "net": "model.config.net", "conditioner": "model.config.conditioner",
     "tokenizer": "model.config.tokenizer", "ema": "model.config.ema", "optimizer": "optimizer", "scheduler": "scheduler",
@@ -147,6 +175,15 @@ class Config(LazyDict):
     model_parallel / checkpoint (+ ``defaults``)."""
 
     _frozen = False
+
+    def __init__(self, *args, **kw):
+        """``Config()`` is an empty tree (``Config.default()`` fills it); ``Config(model=..., optimizer=..., ...)`` - the
+        reference's constructor call - is the default tree with those entries set."""
+        super().__init__(*args)
+        if kw:
+            self.update(Config.default())
+            for k, v in kw.items():
+                self[k] = _wrap(v)
 
     @staticmethod
     def default() -> "Config":

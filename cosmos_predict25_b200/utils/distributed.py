@@ -107,3 +107,30 @@ def sync_model_states(model: torch.nn.Module, group=None, src: int = 0, params: 
 def destroy() -> None:
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
+
+
+class DistributedDataParallel(torch.nn.parallel.DistributedDataParallel):
+    """Data-parallel wrapper whose ``training_step`` runs the wrapped model's ``training_step`` THROUGH the wrapper's forward, so
+    that the gradient hooks see it (imaginaire/utils/distributed.py:205-232 of the reference): ``forward`` is swapped for the
+    step for the duration of one call and restored inside it."""
+
+    def training_step(self, *args, **kwargs):
+        original_forward = self.module.forward
+
+        def step(*a, **k):
+            self.module.forward = original_forward
+            return self.module.training_step(*a, **k)
+
+        self.module.forward = step
+        return self(*args, **kwargs)
+
+
+def parallel_model_wrapper(config_ddp, model: torch.nn.Module) -> torch.nn.Module:
+    """Wrap for data parallelism when a process group exists; the model itself otherwise."""
+    if dist.is_available() and dist.is_initialized():
+        kw = dict(find_unused_parameters=getattr(config_ddp, "find_unused_parameters", False),
+                  static_graph=getattr(config_ddp, "static_graph", False), broadcast_buffers=getattr(config_ddp, "broadcast_buffers", True))
+        if torch.cuda.is_available():
+            kw.update(device_ids=[torch.cuda.current_device()], output_device=torch.cuda.current_device())
+        return DistributedDataParallel(model, **kw)
+    return model

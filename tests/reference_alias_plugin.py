@@ -24,7 +24,18 @@ def _install():
         setattr(sys.modules[".".join(parts[:-1])], parts[-1], mod)
 
 
+def _cuda_calls_stay_on_the_host():
+    """Some of those files place tensors with ``.cuda()``; without a GPU (``COSMOS_ALIAS_NO_CUDA=1``) that call is the identity
+    and the process group is gloo."""
+    import torch
+    if os.environ.get("COSMOS_ALIAS_NO_CUDA") != "1" or torch.cuda.is_available():
+        return
+    torch.Tensor.cuda = lambda self, *a, **k: self
+    torch.nn.Module.cuda = lambda self, *a, **k: self
+
+
 _install()
+_cuda_calls_stay_on_the_host()
 
 
 def pytest_configure(config):

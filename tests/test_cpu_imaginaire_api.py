@@ -1,0 +1,117 @@
+"""The reference's entry objects on this package's loop: whole-config trainer, user model class, lazy optimizer / scheduler
+configs, the ``.pt`` checkpointer's calling convention and the global parallel-state accessors (CPU, one rank)."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from cosmos_predict25_b200.checkpoint.ddp import Checkpointer
+from cosmos_predict25_b200.parallel import parallel_state
+from cosmos_predict25_b200.trainer.callbacks import Callback
+from cosmos_predict25_b200.trainer.model import ImaginaireModel
+from cosmos_predict25_b200.trainer.trainer import ImaginaireTrainer
+from cosmos_predict25_b200.utils.config import CheckpointConfig, Config, JobConfig, ObjectStoreConfig
+from cosmos_predict25_b200.utils.lazy_config import L
+
+
+class Regressor(ImaginaireModel):
+    def __init__(self):
+        super().__init__()
+        self.fc = torch.nn.Linear(10, 5)
+
+    def forward(self, x):
+        return self.fc(x)
+
+    def training_step(self, data_batch, iteration):
+        pred = self(data_batch["x"])
+        loss = torch.nn.functional.mse_loss(pred, data_batch["y"])
+        return {"pred": pred}, loss
+
+
+class Count(Callback):
+    steps = saves = 0
+
+    def on_training_step_end(self, model, data, output, loss, iteration=0):
+        Count.steps += 1
+
+    def on_save_checkpoint_start(self, model, iteration=0):
+        Count.saves += 1
+
+
+@pytest.fixture
+def single_rank(tmp_path, monkeypatch):
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    for k, v in dict(RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                     IMAGINAIRE_OUTPUT_ROOT=str(tmp_path)).items():
+        monkeypatch.setenv(k, v)
+    yield tmp_path
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    parallel_state.destroy_model_parallel()
+
+
+def _config(max_iter):
+    c = Config(model=L(Regressor)(), optimizer=L(torch.optim.SGD)(params=None, lr=0.05),
+               scheduler=L(torch.optim.lr_scheduler.StepLR)(optimizer=None, step_size=2, gamma=0.5), dataloader_train=None, dataloader_val=None)
+    c["job"] = JobConfig(project="p", group="g", name="toy")
+    c["trainer"].update(max_iter=max_iter, logging_iter=1, callbacks=dict(count=L(Count)()))
+    c["checkpoint"].update(save_iter=2)
+    return c
+
+
+def test_whole_config_trainer_runs_a_user_model_and_resumes(single_rank):
+    torch.manual_seed(0)
+    data = [{"x": torch.randn(8, 10), "y": torch.randn(8, 5)} for _ in range(3)]
+    Count.steps = Count.saves = 0
+    config = _config(4)
+    trainer = ImaginaireTrainer(config)
+    assert trainer.output_dir == os.path.join(str(single_rank), "p", "g", "toy") and dist.is_initialized()
+    model = Regressor()
+    w0 = model.fc.weight.detach().clone()
+    trainer.train(model, data)
+    assert Count.steps == 4 and Count.saves == 2 and not torch.equal(model.fc.weight, w0)
+    ckpt_dir = os.path.join(trainer.output_dir, "checkpoints")
+    assert open(os.path.join(ckpt_dir, "latest_checkpoint.txt")).read().strip() == "iter_000000004"
+    assert isinstance(trainer.inner.optimizer, torch.optim.SGD) and trainer.inner.scheduler.get_last_lr() == [0.05 * 0.25]
+    # a second run of the same job resumes at iteration 4 with the saved weights and goes on to 6
+    trainer2 = ImaginaireTrainer(_config(6))
+    model2 = Regressor()
+    trainer2.train(model2, data)
+    assert trainer2.inner.iteration == 6 and Count.steps == 6
+    assert trainer2.inner.scheduler.get_last_lr() == [0.05 * 0.125]
+
+
+def test_checkpointer_calling_convention_and_parallel_state(single_rank):
+    trainer = ImaginaireTrainer(_config(1))
+    parallel_state.initialize_model_parallel(context_parallel_size=1)
+    assert parallel_state.is_initialized() and parallel_state.get_context_parallel_world_size() == 1
+    assert parallel_state.get_data_parallel_rank(with_context_parallel=True) == 0 and parallel_state.get_model_parallel_group().size() == 1
+    assert parallel_state.get_pipeline_model_parallel_world_size() == parallel_state.get_expert_model_parallel_world_size() == 1
+    with pytest.raises(NotImplementedError):
+        parallel_state.destroy_model_parallel()
+        parallel_state.initialize_model_parallel(tensor_model_parallel_size=2)
+    store = ObjectStoreConfig(enabled=False, bucket="b", credentials="c")
+    cc = CheckpointConfig(save_to_object_store=store, load_from_object_store=store, strict_resume=True, load_path=None,
+                          load_training_state=True, only_load_scheduler_state=False)
+    job = JobConfig(project="p", group="g", name="convention")
+    ck = Checkpointer(cc, job, trainer.callbacks)
+    assert ck.checkpoint_dir_local == os.path.join(str(single_rank), "p", "g", "convention", "checkpoints")
+    model = Regressor()
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2)
+    sch = torch.optim.lr_scheduler.StepLR(opt, step_size=1, gamma=0.1)
+    scaler = torch.amp.GradScaler("cpu", enabled=False)
+    model(torch.randn(4, 10)).sum().backward()
+    opt.step(), sch.step()
+    ck.save(model, opt, sch, scaler, iteration=7)
+    ck.finalize()
+    model2 = Regressor()
+    opt2 = torch.optim.Adam(model2.parameters(), lr=1e-2)
+    sch2 = torch.optim.lr_scheduler.StepLR(opt2, step_size=1, gamma=0.1)
+    assert Checkpointer(cc, job, trainer.callbacks).load(model2, opt2, sch2, scaler) == 7
+    assert torch.equal(model2.fc.weight, model.fc.weight) and sch2.get_last_lr() == sch.get_last_lr()
+    s1, s2 = opt.state_dict()["state"], opt2.state_dict()["state"]
+    assert all(torch.equal(s1[k]["exp_avg"], s2[k]["exp_avg"]) for k in s1)

@@ -21,7 +21,19 @@ def _offline_checkpoint_cache(tmp_path):
     return {"COSMOS_CHECKPOINT_DIR": str(root)}
 
 
-PREPARE = {"checkpoint_db_test.py": _offline_checkpoint_cache}
+def _single_rank_on_the_host(tmp_path):
+    """The data-parallel checkpointer test as one gloo rank writing under the temporary directory."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    return {"COSMOS_ALIAS_NO_CUDA": "1", "IMAGINAIRE_OUTPUT_ROOT": str(tmp_path / "out"), "RANK": "0", "WORLD_SIZE": "1", "LOCAL_RANK": "0",
+            "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)}
+
+
+PREPARE = {"checkpoint_db_test.py": _offline_checkpoint_cache, "ddp_test.py": _single_rank_on_the_host}
+# tests the reference marks "run manually" that do run here: the mark is dropped from the copy
+UNSKIP = {"ddp_test.py": ["test_checkpointer_local"]}
 SUITES = [
     ("cosmos_predict2/_src/imaginaire/modules/camera_test.py", {"cosmos_predict2._src.imaginaire.modules.camera": f"{P}.modules.camera"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/validator_test.py",
@@ -43,6 +55,12 @@ SUITES = [
      {"cosmos_predict2._src.imaginaire.config": f"{P}.utils.config", "cosmos_predict2._src.imaginaire.utils": f"{P}.utils",
       "cosmos_predict2._src.imaginaire.datasets.webdataset.config.schema": f"{P}.data.webdataset",
       "cosmos_predict2._src.imaginaire.datasets.webdataset.distributors.multi_aspect_ratio_v2": f"{P}.data.webdataset"}, ""),
+    ("cosmos_predict2/_src/imaginaire/checkpointer/ddp_test.py",
+     {"cosmos_predict2._src.imaginaire.checkpointer.ddp": f"{P}.checkpoint.ddp", "cosmos_predict2._src.imaginaire.config": f"{P}.utils.config",
+      "cosmos_predict2._src.imaginaire.lazy_config": f"{P}.utils.lazy_config", "cosmos_predict2._src.imaginaire.model": f"{P}.trainer.model",
+      "cosmos_predict2._src.imaginaire.trainer": f"{P}.trainer.trainer", "cosmos_predict2._src.imaginaire.utils.distributed": f"{P}.utils.distributed",
+      "cosmos_predict2._src.imaginaire.utils.log": f"{P}.utils.log", "megatron.core.parallel_state": f"{P}.parallel.parallel_state"},
+     "test_checkpointer_local"),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",
@@ -58,7 +76,13 @@ def test_reference_test_file_passes_against_this_package(path, aliases, select, 
     src = os.path.join(root, path)
     # a copy outside the reference tree: its pyproject / conftest must not configure the run, its packages must not be importable
     dst = tmp_path / os.path.basename(path)
-    dst.write_text(open(src).read())
+    text = open(src).read()
+    for name in UNSKIP.get(os.path.basename(path), []):
+        head, sep, tail = text.partition(f"def {name}(")
+        lines = head.rstrip("\n").split("\n")
+        assert sep and lines[-1].startswith("@pytest.mark.skip"), name
+        text = "\n".join(lines[:-1]) + "\n" + sep + tail
+    dst.write_text(text)
     (tmp_path / "pytest.ini").write_text("[pytest]\n")
     extra = PREPARE.get(os.path.basename(path), lambda _: {})(tmp_path)
     env = dict(os.environ, **extra, COSMOS_ALIAS_JSON=json.dumps(aliases), PYTHONPATH=os.pathsep.join([_HERE, os.path.dirname(_HERE)]))
