@@ -97,12 +97,24 @@ def ema_exp_coefficient(rate: float) -> float:
     return float(np.roots([1, 7, 16 - s ** -2, 12 - s ** -2]).real.max())
 
 
+def materialise_config(config):
+    """Build the fields of a model config that were given as lazy calls (network, tokenizer, conditioner, EMA, text encoder): the
+    reference's way of writing ``Config(net=mini_net, tokenizer=DummyJointImageVideoConfig, ...)`` with registry constants."""
+    from ..utils.lazy_config import instantiate, is_lazy
+    for name in ("net", "tokenizer", "conditioner", "ema", "text_encoder"):
+        v = getattr(config, name, None)
+        if is_lazy(v):
+            setattr(config, name, instantiate(v))
+    return config
+
+
 class Text2WorldModelRectifiedFlow(nn.Module):
     condition_is_video2world = False
 
     def __init__(self, config: Text2WorldRFConfig, device: Optional[torch.device] = None, fsdp_group=None, cp_group=None,
                  replicate_group=None):
         super().__init__()
+        config = materialise_config(config)
         self.config = config
         self.replicate_group = replicate_group
         self.precision = _PRECISION[config.precision]

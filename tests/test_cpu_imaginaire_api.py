@@ -115,3 +115,24 @@ def test_checkpointer_calling_convention_and_parallel_state(single_rank):
     assert torch.equal(model2.fc.weight, model.fc.weight) and sch2.get_last_lr() == sch.get_last_lr()
     s1, s2 = opt.state_dict()["state"], opt2.state_dict()["state"]
     assert all(torch.equal(s1[k]["exp_avg"], s2[k]["exp_avg"]) for k in s1)
+
+
+def test_model_config_from_named_default_objects():
+    """The reference's spelling: a model config assembled from module-level default objects (lazy calls), for the rectified-flow
+    and the noise-level Video2World models; the tiny network keeps this a CPU test."""
+    from cosmos_predict25_b200.configs.defaults import (DummyJointImageVideoConfig, PowerEMAConfig, VideoPredictionConditioner, mini_net,
+                                                        tiny_net)
+    from cosmos_predict25_b200.models import edm
+    from cosmos_predict25_b200.models.rectified_flow import Video2WorldModelRectifiedFlow, Video2WorldRFConfig
+    assert mini_net["model_channels"] == 1024 and mini_net["num_blocks"] == 2 and mini_net["num_heads"] == 8
+    batch = {"video": torch.randint(0, 255, (1, 3, 5, 32, 32), dtype=torch.uint8), "t5_text_embeddings": torch.randn(1, 16, 256),
+             "fps": torch.full((1,), 16.0), "padding_mask": torch.zeros(1, 1, 32, 32)}
+    for cls, cfg_cls in ((Video2WorldModelRectifiedFlow, Video2WorldRFConfig), (edm.Video2WorldModel, edm.EDMConfig)):
+        cfg = cfg_cls(tokenizer=DummyJointImageVideoConfig, conditioner=VideoPredictionConditioner, net=tiny_net, ema=PowerEMAConfig,
+                      precision="float32", state_t=2)
+        model = cls(cfg, device=torch.device("cpu"))
+        model.on_train_start()
+        assert type(model.tokenizer).__name__ == "DummyTokenizer" and model.config.ema.enabled and model.config.ema.rate == 0.1
+        _, loss = model.training_step(dict(batch), 1)
+        loss.backward()
+        assert torch.isfinite(loss)
