@@ -31,7 +31,23 @@ def _single_rank_on_the_host(tmp_path):
             "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)}
 
 
-PREPARE = {"checkpoint_db_test.py": _offline_checkpoint_cache, "ddp_test.py": _single_rank_on_the_host}
+def _tiny_t5_checkpoint(tmp_path):
+    """No network here: a one-layer random T5 encoder of the real width (1024) with a sentencepiece model trained on a few
+    sentences stands in for the 11B checkpoint; shapes, padding, truncation and caching are what those tests check."""
+    import sentencepiece as spm
+    from transformers import T5Config, T5EncoderModel, T5TokenizerFast
+    d = tmp_path / "t5"
+    d.mkdir()
+    (d / "corpus.txt").write_text("\n".join(["this is a test prompt", "first second third prompt", "testing global encoder",
+                                             "this is a very long prompt", "short prompt"] * 20))
+    spm.SentencePieceTrainer.train(input=str(d / "corpus.txt"), model_prefix=str(d / "spiece"), vocab_size=60, model_type="unigram",
+                                   pad_id=0, eos_id=1, unk_id=2, bos_id=-1, hard_vocab_limit=False, minloglevel=2)
+    T5TokenizerFast(vocab_file=str(d / "spiece.model"), extra_ids=0).save_pretrained(str(d))
+    T5EncoderModel(T5Config(vocab_size=64, d_model=1024, d_kv=16, num_heads=2, d_ff=64, num_layers=1, feed_forward_proj="relu")).save_pretrained(str(d))
+    return {"COSMOS_T5_MODEL_DIR": str(d)}
+
+
+PREPARE = {"checkpoint_db_test.py": _offline_checkpoint_cache, "ddp_test.py": _single_rank_on_the_host, "get_t5_emb_test.py": _tiny_t5_checkpoint}
 # tests the reference marks "run manually" that do run here: the mark is dropped from the copy
 UNSKIP = {"ddp_test.py": ["test_checkpointer_local"]}
 SUITES = [
@@ -61,6 +77,8 @@ SUITES = [
       "cosmos_predict2._src.imaginaire.trainer": f"{P}.trainer.trainer", "cosmos_predict2._src.imaginaire.utils.distributed": f"{P}.utils.distributed",
       "cosmos_predict2._src.imaginaire.utils.log": f"{P}.utils.log", "megatron.core.parallel_state": f"{P}.parallel.parallel_state"},
      "test_checkpointer_local"),
+    ("cosmos_predict2/_src/predict2/inference/get_t5_emb_test.py",
+     {"cosmos_predict2._src.predict2.inference.get_t5_emb": f"{P}.pipeline.get_t5_emb"}, ""),
     ("cosmos_predict2/config_test.py", {"cosmos_predict2.config": f"{P}.config"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/misc_test.py", {"cosmos_predict2._src.imaginaire.utils.misc": f"{P}.utils.misc"}, ""),
     ("cosmos_predict2/_src/imaginaire/utils/checkpoint_db_test.py",

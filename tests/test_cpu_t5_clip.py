@@ -88,3 +88,35 @@ def test_openai_clip_matches_transformers():
     assert torch.allclose(got_i, want_i, atol=1e-4), (got_i - want_i).abs().max()
     assert torch.allclose(got_t, want_t, atol=1e-4), (got_t - want_t).abs().max()
     assert li.shape == (2, 2) and torch.allclose(li, lt.t())
+
+
+def test_t5_embedding_helper_matches_transformers(tmp_path):
+    """``CosmosT5TextEncoder`` on a checkpoint directory written by transformers: embeddings equal the transformers encoder's,
+    padded positions are zero, the mask comes back on request, an empty list is refused."""
+    import pytest
+    import sentencepiece as spm
+    from transformers import T5Config as HFConfig, T5EncoderModel, T5TokenizerFast
+    from cosmos_predict25_b200.pipeline.get_t5_emb import CosmosT5TextEncoder, get_text_embedding
+    d = tmp_path / "t5"
+    d.mkdir()
+    (d / "c.txt").write_text("\n".join(["a red car drives", "the robot arm moves left", "people walk in the rain"] * 30))
+    spm.SentencePieceTrainer.train(input=str(d / "c.txt"), model_prefix=str(d / "spiece"), vocab_size=48, model_type="unigram", pad_id=0,
+                                   eos_id=1, unk_id=2, bos_id=-1, hard_vocab_limit=False, minloglevel=2)
+    tok = T5TokenizerFast(vocab_file=str(d / "spiece.model"), extra_ids=0)
+    tok.save_pretrained(str(d))
+    torch.manual_seed(0)
+    hf = T5EncoderModel(HFConfig(vocab_size=64, d_model=64, d_kv=8, num_heads=4, d_ff=128, num_layers=2, feed_forward_proj="gated-gelu")).eval()
+    hf.save_pretrained(str(d))
+    enc = CosmosT5TextEncoder(model_name=str(d), device="cpu")
+    prompts = ["a red car drives in the rain", "people walk"]
+    out, mask = enc.encode_prompts(prompts, max_length=24, return_mask=True)
+    ids = tok(prompts, return_tensors="pt", padding="max_length", max_length=24, truncation=True)
+    with torch.no_grad():
+        want = hf(**ids).last_hidden_state * ids["attention_mask"].unsqueeze(-1)
+    assert out.shape == (2, 24, 64) and mask.dtype == torch.bool and torch.equal(mask, ids["attention_mask"].bool())
+    assert torch.allclose(out, want, atol=1e-5) and out[1, int(mask[1].sum()):].abs().max() == 0
+    assert torch.equal(get_text_embedding("people walk", encoder=enc, device="cpu", max_length=24), out[1:2])
+    with pytest.raises(ValueError, match="empty"):
+        enc.encode_prompts([])
+    with pytest.raises(FileNotFoundError):
+        CosmosT5TextEncoder(model_name="no/such-model", device="cpu", local_files_only=True)
