@@ -136,3 +136,18 @@ def test_model_config_from_named_default_objects():
         _, loss = model.training_step(dict(batch), 1)
         loss.backward()
         assert torch.isfinite(loss)
+
+
+def test_runif_and_run_command():
+    from cosmos_predict25_b200.utils.helper_test import RunIf, get_gpu_architecture, run_command
+    ok = RunIf(min_torch="1.8", min_python="3.8", requires_package="torch")
+    assert ok.name == "skipif" and ok.kwargs["condition"] is False
+    no = RunIf(min_gpus=64, max_torch="1.0", requires_file="/no/such/file", requires_package=["no_such_package_xyz"], supported_arch="Z999")
+    assert no.kwargs["condition"] is True
+    for part in ("GPUs>=64", "torch<1.0", "requires file=/no/such/file", "no_such_package_xyz", "arch=Z999"):
+        assert part in no.kwargs["reason"]
+    assert get_gpu_architecture() in ("B200", "H100", "A100", "L40S", "Other")
+    assert run_command("echo hello").stdout.strip() == "hello"
+    assert run_command("exit 3", max_retry_counter=0, is_raise=False).returncode == 3
+    with pytest.raises(RuntimeError, match="exit 3"):
+        run_command("exit 3", max_retry_counter=0)
